@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Headline benchmark: greedy decode tokens/s of a Llama2-7B-shaped fp16 model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decoded token (one pass over all weights). N = 1 runs the 7B shape on one B200
+(128-token seeded prompt, then decode); N > 1 (under torchrun, one rank per GPU) runs the same
+model tensor-parallel with a 512-token context. Weights are random N(0, 0.02) generated on the
+device, norms = 1, token ids seeded: synthetic data of the benchmark's shape.
+
+The JSON line:
+  value      tokens/s with everything resident on the device: one CUDA-graph replay per token,
+             the sampled id fed back in device memory; timed with CUDA events on the launching
+             stream, barrier + synchronize on both sides, max over ranks.
+  e2e        the same metric through the reference-facing call tl_llama2_generate: every step
+             moves the token id host->device and the sampled id device->host, like
+             Llama2::generate does; wall clock like the reference measures it.
+  roofline   the dominant kernel (RMSNorm + w1|w3 GEMV + SiLU*up, 43 % of the weight bytes of a
+             token), launched over all layers' weights (5.8 GB >> L2) and timed with CUDA events.
+  cpu_baseline / --impl reference
+             the reference's own OpenMP CPU code (oracle/_ref) on the host cores, on a bounded
+             sample: a ONE-layer 7B-shaped model with 1/32 of the classifier rows, one decode
+             step per sample; a full token is 32 such samples.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from tensorlib_b200 import synth  # noqa: E402
+
+SEED = 20240229
+CFG = synth.LLAMA2_7B
+METRIC = "decode tokens/s Llama2-7B fp16"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own code on the host cores
+# -------------------------------------------------------------------------------------------------
+def cpu_reference_decode(steps: int, warmup: int, budget_s: float):
+    """Decode steps of a one-layer 7B-shaped model (vocab/32 classifier rows) on the reference's
+    CPU backend. Returns (tokens_per_s_extrapolated, ms_per_step, cores, kind, steps_done)."""
+    from oracle import ref_lib
+    if ref_lib.have_ref():
+        lib, kind = ref_lib.RefLib(), "reference"
+    else:
+        lib, kind = ref_lib.OracleLib(), "port"
+    layers_full = CFG.n_layers
+    cfg = synth.LlamaConfig(dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=1, n_heads=CFG.n_heads,
+                            vocab_size=CFG.vocab_size // layers_full, seq_len=CFG.seq_len, shared_classifier=True)
+    # values do not matter for timing: one seeded block tiled over the payload
+    block = synth.normal_f16(SEED, 1, 1 << 22, 0.02)
+    payload = np.resize(block, cfg.payload_elems())
+    d, L, V = cfg.dim, cfg.n_layers, cfg.vocab_size
+    payload[V * d: V * d + L * d] = 1.0                                   # attention_norm
+    off = V * d + L * d + 4 * L * d * d
+    payload[off: off + L * d] = 1.0                                       # ffn_norm
+    payload[-d:] = 1.0                                                    # final norm
+    model = lib.llama2(cfg, payload)
+    tok = np.array([1], dtype=np.int32)
+    pos = 0
+    for _ in range(warmup):
+        model.forward(tok, pos, 1); pos += 1
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        model.forward(tok, pos, 1); pos += 1; done += 1
+        if time.perf_counter() - t0 > budget_s and done >= 3:
+            break
+    dt = (time.perf_counter() - t0) / done
+    return 1.0 / (dt * layers_full), dt * 1e3, lib.max_threads(), kind, done
+
+
+def run_reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    tps, ms, cores, kind, done = cpu_reference_decode(args.steps, max(args.warmup, 1), budget_s=150.0)
+    sample = ("one decode step of a 1-layer 7B-shaped model with vocab/32 classifier rows "
+              "(= 1/32 of a token) per step; tokens/s = 1 / (32 x step time)")
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": done, "warmup": max(args.warmup, 1), "ms_per_step": ms * CFG.n_layers,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(args.gpus), "timing": "host wall clock, OpenMP on all host cores"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(n_gpus: int) -> str:
+    if n_gpus == 1:
+        return ("Llama2-7B shape (dim 4096, hidden 11008, 32 layers, 32 heads, vocab 32000), batch 1, "
+                "128-token prompt then greedy decode")
+    return (f"Llama2-7B shape tensor-parallel over {n_gpus} GPUs (wq/wk/wv/w1/w3 row-split, wo/w2 column-split, "
+            "allreduce after each K-split matmul), batch 1, 512-token context then greedy decode")
+
+
+# -------------------------------------------------------------------------------------------------
+# GPU arm
+# -------------------------------------------------------------------------------------------------
+def roofline_gateup(tl, model, stream, torch, n_layers):
+    """Time the dominant kernel over all layers' w1|w3 (distinct weights every launch)."""
+    lib = tl.load()
+    dim, hid, L = CFG.dim, model.c.hidden_dim // model.c.tp_world, n_layers
+    stream_ptr = stream.cuda_stream
+
+    def tensor(name, layer):
+        p, r, c = C.c_void_p(), C.c_int(), C.c_int()
+        tl.check(lib.tl_llama2_tensor(model.h, name.encode(), layer, C.byref(p), C.byref(r), C.byref(c)), name)
+        return p.value
+
+    x = torch.randn(dim, device="cuda").half()
+    out = torch.empty(hid, device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    ptrs = [(tensor("ffn_norm", l), tensor("w1", l), tensor("w3", l)) for l in range(L)]
+
+    def sweep():
+        for nw, w1, w3 in ptrs:
+            tl.check(lib.tl_rmsnorm_gateup_swiglu_f16(x.data_ptr(), nw, 1e-5, w1, w3, out.data_ptr(), hid, dim,
+                                                      stream_ptr), "gateup")
+    for _ in range(3):
+        sweep()
+    reps = 5
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)          # events on the stream the kernels are launched on
+    for _ in range(reps):
+        sweep()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) * 1e-3 / (reps * L)
+    bytes_per_launch = 2 * hid * dim * 2 + 2 * dim * 2 + hid * 2   # w1+w3, x + norm weight, out
+    peak, peak_src = measured_peaks()
+    achieved = bytes_per_launch / sec / 1e9
+    return {"bound": "hbm", "kernel": "k_gemv_fused<SWIGLU,NORM> (RMSNorm + w1|w3 GEMV + SiLU*up)",
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+            "bytes_per_launch": bytes_per_launch, "us_per_launch": sec * 1e6, "traffic": NCU_TRAFFIC_GATEUP}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel from the ncu
+# capture summarised under profiles/ (None until a capture exists)
+NCU_TRAFFIC_GATEUP = None
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    import tensorlib_b200 as tl
+
+    torch.cuda.set_device(local_rank)
+    tl.init(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl" if args.dist_backend == "nccl" else "gloo", rank=rank, world_size=world)
+    cfg = CFG if args.layers == CFG.n_layers else synth.LlamaConfig(
+        dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=args.layers, n_heads=CFG.n_heads,
+        vocab_size=CFG.vocab_size, seq_len=CFG.seq_len, shared_classifier=False)
+    model = tl.Llama2(cfg, numerics=tl.FAST, tp_rank=rank, tp_world=world)
+    if world > 1:
+        from tensorlib_b200 import tp
+        tp.attach(model, rank, world, dist)
+    model.init_random(SEED, 0.02)
+
+    n_ctx = 128 if world == 1 else 512
+    K, W = args.steps, args.warmup
+    assert n_ctx + W + 2 * K + 2 <= CFG.seq_len, "steps + warmup exceed the 2048-token context"
+    prompt = synth.prompt_tokens(CFG, SEED, n_ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # prefill (untimed): leaves the first sampled id in the device slot
+    if args.skip_prefill:
+        model.set_next_token(int(prompt[-1]))      # profiling runs: decode over a zero KV cache
+    else:
+        model.forward(prompt, 0, all_logits=False)
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    pos = n_ctx
+    with torch.cuda.stream(stream):
+        model.decode_device(pos, W, fetch=False, stream=sp)           # warm-up (captures the graph)
+        pos += W
+        barrier()
+        launches0 = model.kernel_launches()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        model.decode_device(pos, K, fetch=False, stream=sp)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+        launches = model.kernel_launches() - launches0
+        pos += K
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = K / (ms * 1e-3)
+
+    # end to end through the reference-facing generate(): id host->device->host every step
+    barrier()
+    if args.skip_prefill:
+        print(json.dumps({"profiling_only": True, "layers": cfg.n_layers, "ms_per_step": ms / K,
+                          "launches_per_step": launches / K}), flush=True)
+        model.close()
+        return
+    ids, t_prefill, t_decode = model.generate(prompt, K + 1)
+    e2e_ms = t_decode * 1e3
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = (len(ids) - 1) / (e2e_ms * 1e-3)
+
+    roof = roofline_gateup(tl, model, stream, torch, cfg.n_layers) if rank == 0 else None
+    weight_bytes = model.weight_bytes()
+    if rank == 0:
+        peak, _ = measured_peaks()
+        emb_bytes = cfg.vocab_size * cfg.dim * 2            # the embedding table is gathered, not streamed
+        step_bytes = weight_bytes - emb_bytes
+        line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic",
+                "config": {"workload": workload_name(world) + ("" if cfg.n_layers == CFG.n_layers else f" [PROFILING ONLY: {cfg.n_layers} layers]"),
+                           "context_at_start": n_ctx + W,
+                           "parallelism": f"tp{world}", "numerics": "fp16 storage, fp32 accumulate",
+                           "l2": "inputs larger than L2 (weights streamed per token >> 126 MB)",
+                           "weight_bytes_per_token_per_gpu": step_bytes},
+                "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4,
+                        "prefill_s": t_prefill},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+                "step_hbm_frac": (step_bytes / (ms / K * 1e-3) / 1e9) / peak}
+        if world == 1 and not args.no_cpu:
+            tps, ms_cpu, cores, kind, done = cpu_reference_decode(64, 2, budget_s=20.0)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
+                                    "sample": f"{done} decode steps of a 1-layer 7B-shaped model with vocab/32 "
+                                              "classifier rows (1/32 of a token each), extrapolated x32"}
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--dist-backend", default="nccl")
+    ap.add_argument("--layers", type=int, default=CFG.n_layers, help="profiling only: fewer layers of the 7B shape")
+    ap.add_argument("--skip-prefill", action="store_true", help="profiling only: decode without a prompt pass")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

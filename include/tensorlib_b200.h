@@ -1,0 +1,211 @@
+/*
+ * tensorlib_b200 — C ABI of the B200 (sm_100a) matmul backend for tensorLib's
+ * Tensor::matmul -> Llama2 forward path.
+ *
+ * Conventions
+ *   - fp16 values are IEEE binary16 bit patterns (tl_half). Unless a parameter is named
+ *     *_host, every pointer is a DEVICE pointer on the device chosen by tl_init().
+ *   - Every function returns a tl_status (0 = TL_OK); nothing prints or exits. The message of
+ *     the last failure on the calling thread is returned by tl_last_error().
+ *   - Functions taking a tl_stream only enqueue work on that cudaStream_t (NULL = the legacy
+ *     default stream, which is what the reference uses everywhere) and return without
+ *     synchronising, unless stated.
+ *   - There is no CPU fallback: without a usable sm_100 device tl_init() fails and every
+ *     compute entry point returns TL_ERR_NOT_INITIALIZED.
+ *   - `numerics` selects the summation order, never the storage type (always fp16 in, fp32
+ *     accumulate, fp16 out):
+ *       TL_NUMERICS_REFERENCE_ORDER  the rounding points and the sequential accumulation order
+ *                                    of the reference's CPU backend; results are bit-identical
+ *                                    to it. Slow (dependent chains), meant for parity runs.
+ *       TL_NUMERICS_FAST             parallel fp32 reductions / tensor cores.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside DavidZyy/tensorLib).
+ */
+#ifndef TENSORLIB_B200_H
+#define TENSORLIB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TL_API __attribute__((visibility("default")))
+#else
+#define TL_API
+#endif
+
+typedef uint16_t tl_half;
+typedef void* tl_stream; /* cudaStream_t */
+
+typedef enum tl_status {
+    TL_OK = 0,
+    TL_ERR_INVALID_ARGUMENT = 1, /* the reference throws std::invalid_argument here */
+    TL_ERR_NOT_INITIALIZED = 2,
+    TL_ERR_CUDA = 3,             /* the reference prints and exit(1)s here (CUDA.cuh:131-151) */
+    TL_ERR_UNSUPPORTED = 4,
+    TL_ERR_OUT_OF_MEMORY = 5,
+    TL_ERR_TIMEOUT = 6,          /* a bounded device-side wait gave up */
+    TL_ERR_COMM = 7,
+    TL_ERR_IO = 8
+} tl_status;
+
+enum { TL_NUMERICS_REFERENCE_ORDER = 0, TL_NUMERICS_FAST = 1 };
+
+/* ---- library ---------------------------------------------------------------------------- */
+TL_API const char* tl_strerror(int status);
+TL_API const char* tl_last_error(void);
+TL_API int tl_version(void);
+/* Select `device`, verify it is sm_100, make it current for the calling thread. */
+TL_API int tl_init(int device);
+TL_API int tl_device_count(int* count);
+/* Synchronise the device and fetch (then clear) the device status word: 0, or TL_ERR_TIMEOUT if a
+ * kernel gave up on one of its bounded waits (mbarrier polls). The reference has no counterpart:
+ * its kernels never wait on anything. */
+TL_API int tl_device_status(int* status);
+
+/* Host-only introspection of the lookup tables the kernels use for exp / SiLU / RoPE. They are
+ * evaluated on the host with the formulas of the reference's CPU backend (cpu/softmax.cpp:22,
+ * CPU.cpp:216-222, CPU.cpp:444-447); each *_tab has 65536 entries indexed by the fp16 bit
+ * pattern; the rope tables are [rows, head_dim/2]. No device needed. */
+TL_API int tl_host_lookup_tables(tl_half* exp_tab, tl_half* silu_float_tab, tl_half* silu_half_tab);
+TL_API int tl_host_rope_table(int head_dim, int rows, tl_half* cos_out, tl_half* sin_out);
+
+/* ---- device memory: what CUDA<dtype>'s ctor/dtor and getData/setData do
+ *      (tensorLib/src/device/cuda/CUDA.cu:17-32, :72-81) -------------------------------------- */
+TL_API int tl_malloc(void** dptr, size_t bytes);
+TL_API int tl_free(void* dptr);
+TL_API int tl_memcpy_h2d(void* dst, const void* src_host, size_t bytes, tl_stream stream);
+TL_API int tl_memcpy_d2h(void* dst_host, const void* src, size_t bytes, tl_stream stream);
+TL_API int tl_memcpy_d2d(void* dst, const void* src, size_t bytes, tl_stream stream);
+TL_API int tl_memset(void* dst, int value, size_t bytes, tl_stream stream);
+TL_API int tl_stream_synchronize(tl_stream stream);
+TL_API int tl_malloc_host(void** hptr, size_t bytes); /* pinned */
+TL_API int tl_free_host(void* hptr);
+
+/* ---- matmul: the drop-in boundary --------------------------------------------------------- */
+/* Device<half>::matmul2d (tensorLib/include/device/Device.hpp:22; CUDA implementation
+ * tensorLib/src/device/cuda/gemm.cu:153-172): C[M,N] = A[M,K] * B[N,K]^T, all row-major
+ * contiguous. Dispatches on M: GEMV (M<=8), skinny, tcgen05 HGEMM. */
+TL_API int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t M, size_t N, size_t K,
+                    int numerics, tl_stream stream);
+/* The per-batch loop of ops::matmul::call2 (tensorLib/src/ops/matmul.cpp:297-321) as one call:
+ * for b in [0,batch): C_b[M,N] = A_b[M,K] * B_b[N,K]^T with row pitches lda/ldb/ldc and batch
+ * strides (all in elements; a batch stride of 0 broadcasts, as call2's stride-0 views do). */
+TL_API int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t batch, size_t M,
+                          size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, size_t strideA,
+                          size_t strideB, size_t strideC, int numerics, tl_stream stream);
+/* Same contract as tl_matmul2d_f16 with HOST buffers: copies A and B in, C out, synchronises. */
+TL_API int tl_matmul2d_f16_host(const tl_half* A_host, const tl_half* B_host, tl_half* C_host, size_t M,
+                         size_t N, size_t K, int numerics);
+
+/* ---- the operators next to a matmul in the Llama2 forward --------------------------------- */
+/* CUDA<half>::rms_norm (tensorLib/include/device/cuda/CUDA.cuh:108, rms_norm.cu:181-184; CPU
+ * semantics nn::RMSNorm::forward_plain, tensorLib/src/nn/rmsNorm.cpp:15-56). */
+TL_API int tl_rms_norm_f16(tl_half* out, const tl_half* in, const tl_half* weight, float eps, int hidden,
+                    int tokens, int numerics, tl_stream stream);
+/* Device::apply_rotary_emb (Device.hpp:91-98, CPU.cpp:427-461): interleaved-pair rotation of a
+ * contiguous (B,T,n_heads,head_dim) tensor; in == out allowed. cos/sin come from a table
+ * computed on the host with the reference's float formula, so both numerics agree bit for bit.
+ * The table grows (allocates, synchronises) when start_pos+T exceeds what earlier calls needed. */
+TL_API int tl_apply_rotary_emb_f16(const tl_half* in, tl_half* out, int start_pos, int B, int T,
+                            int n_heads, int head_dim, tl_stream stream);
+/* Device::softmax over the last dimension (Device.hpp:77, cpu/softmax.cpp:10-31). */
+TL_API int tl_softmax_f16(tl_half* out, const tl_half* in, size_t rows, size_t cols, int numerics,
+                   tl_stream stream);
+/* Device::silu (Device.hpp:57). via_float = 1: x*sigmoid(x) in fp32, one rounding (the
+ * reference's CUDA kernel, CUDA.cu:334-342, and its CPU float route). via_float = 0: the CPU
+ * fp16 route as shipped, including its 1/(1+exp(x)) sign defect (CPU.cpp:216-219). */
+TL_API int tl_silu_f16(tl_half* out, const tl_half* in, size_t n, int via_float, tl_stream stream);
+/* Device::add / mul / div-by-scalar (Device.hpp:62-70). */
+TL_API int tl_add_f16(tl_half* out, const tl_half* a, const tl_half* b, size_t n, tl_stream stream);
+TL_API int tl_mul_f16(tl_half* out, const tl_half* a, const tl_half* b, size_t n, tl_stream stream);
+TL_API int tl_div_scalar_f16(tl_half* out, const tl_half* a, double scalar, size_t n, tl_stream stream);
+/* Device::argmax over the last dimension (Device.hpp:75, CPU.cpp:358-372): the LOWEST index
+ * wins ties. out_idx: int32[rows]. */
+TL_API int tl_argmax_f16(int* out_idx, const tl_half* in, size_t rows, size_t cols, tl_stream stream);
+/* nn::Embedding::forward (tensorLib/src/nn/embedding.cpp:48-81): out[t,:] = table[tokens[t],:],
+ * token ids read from device memory. */
+TL_API int tl_embedding_f16(tl_half* out, const tl_half* table, const int* tokens, int n_tokens, int dim,
+                     int vocab, tl_stream stream);
+
+/* ---- fused decode stages (one token, fast numerics) ----------------------------------------
+ * Each replaces a run of launches of the reference's decode step; the reference lines are the
+ * ones the stage covers. All require 16-byte aligned pointers and K % 8 == 0. */
+/* attention_norm + wq|wk|wv GEMVs + rotary embedding + KV-cache write
+ * (Transformer.cpp:165, :35-53): x[dim] -> q_out[n_q]; k, v rows written at position `pos` of
+ * caches laid out (max_seq, n_q) with n_q = local_heads*head_dim. */
+TL_API int tl_rmsnorm_qkv_rope_f16(const tl_half* x, const tl_half* norm_w, float eps, const tl_half* wq,
+                            const tl_half* wk, const tl_half* wv, tl_half* q_out, tl_half* k_cache,
+                            tl_half* v_cache, int dim, int n_q, int head_dim, int pos,
+                            tl_stream stream);
+/* per-head attention of one query over positions [0, seq_len) of the caches, read in place
+ * (Transformer.cpp:56-109). scratch: float[n_heads*splits*(head_dim+2)], counters:
+ * uint32[n_heads] zeroed once by the caller. */
+TL_API int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
+                       float* scratch, unsigned int* counters, int n_heads, int head_dim, int seq_len,
+                       int splits, tl_stream stream);
+/* y[n] = residual[n] + sum_k x[k] W[n,k]  (wo / w2 GEMV + EwiseAdd, Transformer.cpp:111+:169,
+ * :143+:175). y may alias residual. */
+TL_API int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,
+                         int N, int K, tl_stream stream);
+/* ffn_norm + w1|w3 GEMVs + SiLU(gate)*up (Transformer.cpp:171, :136-141): x[dim] -> out[hidden]. */
+TL_API int tl_rmsnorm_gateup_swiglu_f16(const tl_half* x, const tl_half* norm_w, float eps, const tl_half* w1,
+                                 const tl_half* w3, tl_half* out, int hidden, int dim,
+                                 tl_stream stream);
+
+/* ---- Llama2 model (model/llama2_7b) -------------------------------------------------------- */
+typedef struct tl_llama2_config {
+    int dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, max_seq_len; /* main.cpp:26-34 */
+    int numerics;           /* TL_NUMERICS_* */
+    int silu_via_float;     /* 1: SiLU as on the reference's CUDA path; 0: its CPU fp16 route */
+    int tp_rank, tp_world;  /* tensor-parallel shard of this process; 0,1 = single GPU */
+} tl_llama2_config;
+
+typedef struct tl_llama2 tl_llama2;
+
+/* Transformer<half>::Transformer (model/llama2_7b/src/Transformer.cpp:186-202): allocates
+ * weights, KV caches (1,max_seq,n_heads,head_dim) per layer and activation buffers. */
+TL_API int tl_llama2_create(const tl_llama2_config* cfg, tl_llama2** out);
+TL_API int tl_llama2_destroy(tl_llama2* m);
+/* read_weights (model/llama2_7b/src/main.cpp:36-190) from a host copy of the checkpoint payload
+ * (everything after the 28-byte header), or from a file including the header. With tp_world>1
+ * each rank keeps its slice: wq/wk/wv/w1/w3 by output rows, wo/w2 by input columns. */
+TL_API int tl_llama2_load_payload_host(tl_llama2* m, const tl_half* payload_host, int shared_classifier);
+TL_API int tl_llama2_load_file(tl_llama2* m, const char* path);
+/* Fill every weight with a seeded N(0, std^2) pattern generated on the device (norm weights = 1);
+ * for throughput runs at sizes where a host checkpoint is impractical. */
+TL_API int tl_llama2_init_random(tl_llama2* m, uint64_t seed, float std);
+/* Transformer<half>::forward (Transformer.cpp:264-299): tokens_host[T] at start_pos.
+ * logits_host (optional) receives (T, vocab) fp16 for all positions like the reference returns;
+ * last_logits_host (optional) only the final position. Synchronises. */
+TL_API int tl_llama2_forward(tl_llama2* m, const int* tokens_host, int T, int start_pos,
+                      tl_half* logits_host, tl_half* last_logits_host);
+/* Llama2<half>::generate (model/llama2_7b/src/llama2.cpp:15-101): prefill the prompt, then greedy
+ * decode. Every step moves the sampled id device->host and back like the reference does. Stops
+ * early on id 1 or 2 only if stop_on_eos != 0. Returns the number of ids written to out_tokens,
+ * and wall-clock seconds of the two phases as the reference prints them. */
+TL_API int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int max_new,
+                       int stop_on_eos, int* out_tokens_host, int* n_out, double* prefill_seconds,
+                       double* decode_seconds);
+/* Device-resident greedy decode: `steps` tokens starting from the id in the model's device-side
+ * token slot (left there by a previous forward/generate/decode call), one CUDA-graph replay per
+ * token, no host round trip. out_tokens_host (optional) is filled after the last step. Runs on
+ * `stream` and synchronises it only when out_tokens_host != NULL. */
+TL_API int tl_llama2_decode_device(tl_llama2* m, int start_pos, int steps, int* out_tokens_host,
+                            tl_stream stream);
+/* position bookkeeping and introspection */
+TL_API int tl_llama2_set_next_token(tl_llama2* m, int token);
+TL_API int tl_llama2_kernel_launches(tl_llama2* m, long long* launches); /* kernels enqueued so far */
+TL_API int tl_llama2_weight_bytes(tl_llama2* m, long long* bytes);       /* on this rank */
+/* Device pointer and local shape of a weight tensor: name in {"tok_embeddings", "attention_norm",
+ * "wq", "wk", "wv", "wo", "ffn_norm", "w1", "w2", "w3", "norm", "output"} (the member names of
+ * Transformer / TransformerBlock, Transformer.hpp:36-92); layer ignored for the model-level ones. */
+TL_API int tl_llama2_tensor(tl_llama2* m, const char* name, int layer, void** dptr, int* rows, int* cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENSORLIB_B200_H */

@@ -1,0 +1,410 @@
+// extern "C" entry points declared in include/tensorlib_b200.h: argument checks with the
+// reference's error behaviour (invalid shapes -> TL_ERR_INVALID_ARGUMENT where the reference
+// throws std::invalid_argument), dispatch on numerics and shape, launch.
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "engine.cuh"
+
+using namespace tlb;
+
+struct tl_llama2 {
+    Llama2Engine* eng;
+    int* pinned;  // [max_seq + 8] staging for token ids
+};
+
+namespace {
+inline const __half* H(const tl_half* p) { return reinterpret_cast<const __half*>(p); }
+inline __half* H(tl_half* p) { return reinterpret_cast<__half*>(p); }
+bool valid_numerics(int n) { return n == TL_NUMERICS_REFERENCE_ORDER || n == TL_NUMERICS_FAST; }
+}  // namespace
+
+extern "C" {
+
+int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t batch, size_t M,
+                          size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, size_t strideA,
+                          size_t strideB, size_t strideC, int numerics, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(valid_numerics(numerics), "unknown numerics %d", numerics);
+    if (batch == 0 || M == 0 || N == 0) return TL_OK;
+    TL_REQUIRE(A && B && C, "null matrix pointer");
+    TL_REQUIRE(lda >= K && ldb >= K && ldc >= N, "row pitch smaller than the row");
+    TL_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31) && batch < (1u << 31), "dimension too large");
+    cudaStream_t st = as_stream(stream);
+    if (numerics == TL_NUMERICS_FAST && K > 0) {
+        if (M > 8 && hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc))
+            return launch_hgemm(H(A), H(B), H(C), (int)batch, (int)M, (int)N, (int)K, lda, ldb, ldc,
+                                strideA, strideB, strideC, st);
+        if (gemv_supported(A, B, M < 8 ? M : 8, N, K, ldb) && lda % 8 == 0 && strideA % 8 == 0 && strideB % 8 == 0) {
+            for (size_t b = 0; b < batch; b++)
+                for (size_t m0 = 0; m0 < M; m0 += 8) {
+                    int m = (int)(M - m0 < 8 ? M - m0 : 8);
+                    TL_PROPAGATE(launch_gemv(H(A) + b * strideA + m0 * lda, H(B) + b * strideB,
+                                             H(C) + b * strideC + m0 * ldc, m, (int)N, (int)K, ldb, lda, ldc, st));
+                }
+            return TL_OK;
+        }
+    }
+    // reference-order kernel: any shape, any alignment (also the fast path's fallback for those)
+    SeqMatmul p{H(A), H(B), H(C), (int)batch, (int)M, (int)N, (int)K, (long long)lda, 1,
+                (long long)ldb, 1, (long long)ldc, (long long)strideA, (long long)strideB, (long long)strideC};
+    for (size_t m0 = 0; m0 < M; m0 += 65535) {  // grid.y limit
+        SeqMatmul q = p;
+        q.A = p.A + m0 * lda;
+        q.C = p.C + m0 * ldc;
+        q.M = (int)(M - m0 < 65535 ? M - m0 : 65535);
+        TL_PROPAGATE(launch_matmul_seq(q, st));
+    }
+    return TL_OK;
+}
+
+int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t M, size_t N, size_t K,
+                    int numerics, tl_stream stream) {
+    return tl_matmul_batched_f16(A, B, C, 1, M, N, K, K, K, N, 0, 0, 0, numerics, stream);
+}
+
+int tl_matmul2d_f16_host(const tl_half* A_host, const tl_half* B_host, tl_half* C_host, size_t M,
+                         size_t N, size_t K, int numerics) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(A_host && B_host && C_host, "null host pointer");
+    __half *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    const size_t ba = M * K * 2, bb = N * K * 2, bc = M * N * 2;
+    int rc = TL_OK;
+    cudaError_t e;
+    if ((e = cudaMalloc(&dA, ba ? ba : 2)) != cudaSuccess || (e = cudaMalloc(&dB, bb ? bb : 2)) != cudaSuccess ||
+        (e = cudaMalloc(&dC, bc ? bc : 2)) != cudaSuccess) {
+        rc = set_error(TL_ERR_OUT_OF_MEMORY, "cudaMalloc: %s", cudaGetErrorString(e));
+    } else {
+        cudaMemcpyAsync(dA, A_host, ba, cudaMemcpyHostToDevice, nullptr);
+        cudaMemcpyAsync(dB, B_host, bb, cudaMemcpyHostToDevice, nullptr);
+        rc = tl_matmul2d_f16(reinterpret_cast<tl_half*>(dA), reinterpret_cast<tl_half*>(dB),
+                             reinterpret_cast<tl_half*>(dC), M, N, K, numerics, nullptr);
+        if (rc == TL_OK) {
+            e = cudaMemcpy(C_host, dC, bc, cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) rc = set_error(TL_ERR_CUDA, "copy back failed: %s", cudaGetErrorString(e));
+        }
+    }
+    cudaFree(dA); cudaFree(dB); cudaFree(dC);
+    return rc;
+}
+
+int tl_rms_norm_f16(tl_half* out, const tl_half* in, const tl_half* weight, float eps, int hidden,
+                    int tokens, int numerics, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(valid_numerics(numerics), "unknown numerics %d", numerics);
+    TL_REQUIRE(hidden > 0 && tokens >= 0 && out && in && weight, "rms_norm: bad arguments");
+    if (numerics == TL_NUMERICS_REFERENCE_ORDER)
+        return launch_rmsnorm_seq(H(out), H(in), H(weight), eps, hidden, tokens, as_stream(stream));
+    return launch_rmsnorm_fast(H(out), H(in), H(weight), eps, hidden, tokens, as_stream(stream));
+}
+
+int tl_apply_rotary_emb_f16(const tl_half* in, tl_half* out, int start_pos, int B, int T,
+                            int n_heads, int head_dim, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(in && out && start_pos >= 0 && B >= 0 && T >= 0 && n_heads > 0 && head_dim > 0 && head_dim % 2 == 0,
+               "apply_rotary_emb: bad arguments");
+    if (B == 0 || T == 0) return TL_OK;
+    const __half *c, *s;
+    TL_PROPAGATE(rope_table(head_dim, start_pos + T, &c, &s));
+    return launch_rope(H(in), H(out), start_pos, B * T, T, n_heads, head_dim, c, s, as_stream(stream));
+}
+
+int tl_softmax_f16(tl_half* out, const tl_half* in, size_t rows, size_t cols, int numerics,
+                   tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(valid_numerics(numerics), "unknown numerics %d", numerics);
+    TL_REQUIRE(out && in, "softmax: null pointer");
+    if (numerics == TL_NUMERICS_REFERENCE_ORDER) return launch_softmax_seq(H(out), H(in), rows, cols, as_stream(stream));
+    return launch_softmax_fast(H(out), H(in), rows, cols, as_stream(stream));
+}
+
+int tl_silu_f16(tl_half* out, const tl_half* in, size_t n, int via_float, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(out && in, "silu: null pointer");
+    return launch_silu(H(out), H(in), n, via_float, as_stream(stream));
+}
+int tl_add_f16(tl_half* out, const tl_half* a, const tl_half* b, size_t n, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(out && a && b, "add: null pointer");
+    return launch_binary(H(out), H(a), H(b), n, 0, as_stream(stream));
+}
+int tl_mul_f16(tl_half* out, const tl_half* a, const tl_half* b, size_t n, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(out && a && b, "mul: null pointer");
+    return launch_binary(H(out), H(a), H(b), n, 1, as_stream(stream));
+}
+int tl_div_scalar_f16(tl_half* out, const tl_half* a, double scalar, size_t n, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(out && a, "div: null pointer");
+    __half hs(scalar);  // double -> fp16 like the reference's dtype scalar parameter
+    TL_REQUIRE(__half2float(hs) != 0.0f, "Division by zero.");  // divFunc, CPU.cpp:280-293
+    return launch_div_scalar(H(out), H(a), hs, n, as_stream(stream));
+}
+int tl_argmax_f16(int* out_idx, const tl_half* in, size_t rows, size_t cols, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(out_idx && in, "argmax: null pointer");
+    return launch_argmax(out_idx, H(in), rows, cols, as_stream(stream));
+}
+int tl_embedding_f16(tl_half* out, const tl_half* table, const int* tokens, int n_tokens, int dim,
+                     int vocab, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(out && table && tokens && dim > 0 && vocab > 0 && n_tokens >= 0, "embedding: bad arguments");
+    return launch_embedding(H(out), H(table), tokens, n_tokens, dim, vocab, as_stream(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Llama2
+// ---------------------------------------------------------------------------------------------
+int tl_llama2_create(const tl_llama2_config* cfg, tl_llama2** out) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(cfg && out, "null argument");
+    tl_llama2_config c = *cfg;
+    if (c.tp_world <= 0) { c.tp_world = 1; c.tp_rank = 0; }
+    if (c.n_kv_heads <= 0) c.n_kv_heads = c.n_heads;
+    TL_REQUIRE(c.dim > 0 && c.hidden_dim > 0 && c.n_layers > 0 && c.n_heads > 0 && c.vocab_size > 0 && c.max_seq_len > 0,
+               "model dimensions must be positive");
+    TL_REQUIRE(c.dim % c.n_heads == 0 && (c.dim / c.n_heads) % 2 == 0, "dim must split into even-sized heads");
+    TL_REQUIRE(c.n_kv_heads == c.n_heads, "n_kv_heads != n_heads is not supported (nor by the reference, Transformer.hpp:21)");
+    TL_REQUIRE(valid_numerics(c.numerics), "unknown numerics %d", c.numerics);
+    TL_REQUIRE(c.tp_rank >= 0 && c.tp_rank < c.tp_world, "tp_rank out of range");
+    TL_REQUIRE(c.n_heads % c.tp_world == 0 && c.hidden_dim % c.tp_world == 0 && c.vocab_size % c.tp_world == 0,
+               "heads, hidden_dim and vocab_size must divide by tp_world");
+    TL_REQUIRE(c.tp_world == 1 || c.numerics == TL_NUMERICS_FAST, "tensor parallelism needs fast numerics");
+    if (c.numerics == TL_NUMERICS_FAST) {
+        TL_REQUIRE(c.dim % 8 == 0 && (c.hidden_dim / c.tp_world) % 8 == 0 && ((c.dim / c.n_heads) * (c.n_heads / c.tp_world)) % 8 == 0,
+                   "fast numerics needs dim, local hidden_dim and local attention width to be multiples of 8");
+        TL_REQUIRE(c.dim <= 16384 && c.hidden_dim / c.tp_world <= 16384, "fast numerics: reduction length above 16384");
+        TL_REQUIRE(c.dim / c.n_heads <= 256, "fast numerics: head_dim above 256");
+    }
+    tl_llama2* m = new (std::nothrow) tl_llama2{nullptr, nullptr};
+    if (!m) return set_error(TL_ERR_OUT_OF_MEMORY, "host allocation failed");
+    m->eng = new (std::nothrow) Llama2Engine(c);
+    if (!m->eng) { delete m; return set_error(TL_ERR_OUT_OF_MEMORY, "host allocation failed"); }
+    int rc = m->eng->allocate();
+    if (rc == TL_OK && cudaMallocHost(&m->pinned, (size_t)(c.max_seq_len + 8) * sizeof(int)) != cudaSuccess)
+        rc = set_error(TL_ERR_OUT_OF_MEMORY, "pinned allocation failed");
+    if (rc != TL_OK) { delete m->eng; delete m; return rc; }
+    *out = m;
+    return TL_OK;
+}
+
+int tl_llama2_destroy(tl_llama2* m) {
+    if (!m) return TL_OK;
+    cudaDeviceSynchronize();
+    delete m->eng;
+    if (m->pinned) cudaFreeHost(m->pinned);
+    delete m;
+    return TL_OK;
+}
+
+int tl_llama2_load_payload_host(tl_llama2* m, const tl_half* payload_host, int shared_classifier) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && payload_host, "null argument");
+    return m->eng->load_payload_host(H(payload_host), shared_classifier != 0);
+}
+
+// read_checkpoint + read_weights (model/llama2_7b/src/main.cpp:195-228, :36-190)
+int tl_llama2_load_file(tl_llama2* m, const char* path) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && path, "null argument");
+    FILE* f = fopen(path, "rb");
+    if (!f) return set_error(TL_ERR_IO, "Couldn't open file %s", path);
+    int hdr[7];
+    if (fread(hdr, sizeof(int), 7, f) != 7) { fclose(f); return set_error(TL_ERR_IO, "short header in %s", path); }
+    const tl_llama2_config& c = m->eng->cfg();
+    const bool shared = hdr[5] > 0;
+    const int vocab = hdr[5] > 0 ? hdr[5] : -hdr[5];
+    if (hdr[0] != c.dim || hdr[1] != c.hidden_dim || hdr[2] != c.n_layers || hdr[3] != c.n_heads ||
+        vocab != c.vocab_size || hdr[6] != c.max_seq_len) {
+        fclose(f);
+        return set_error(TL_ERR_INVALID_ARGUMENT, "checkpoint header (%d,%d,%d,%d,%d,%d) does not match the model",
+                         hdr[0], hdr[1], hdr[2], hdr[3], vocab, hdr[6]);
+    }
+    const size_t d = c.dim, h = c.hidden_dim, L = c.n_layers, V = c.vocab_size;
+    size_t n = V * d + L * (2 * d + 4 * d * d + 3 * d * h) + d;
+    if (!shared) n += (size_t)c.max_seq_len * (d / c.n_heads) + V * d;
+    std::vector<tl_half> buf;
+    try { buf.resize(n); } catch (...) { fclose(f); return set_error(TL_ERR_OUT_OF_MEMORY, "host buffer of %zu halfs", n); }
+    size_t got = fread(buf.data(), sizeof(tl_half), n, f);
+    fclose(f);
+    if (got != n) return set_error(TL_ERR_IO, "checkpoint %s is truncated: %zu of %zu values", path, got, n);
+    return m->eng->load_payload_host(H(buf.data()), shared);
+}
+
+int tl_llama2_init_random(tl_llama2* m, uint64_t seed, float std) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m, "null model");
+    return m->eng->init_random(seed, std);
+}
+
+int tl_llama2_forward(tl_llama2* m, const int* tokens_host, int T, int start_pos,
+                      tl_half* logits_host, tl_half* last_logits_host) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && tokens_host, "null argument");
+    Llama2Engine& e = *m->eng;
+    const int V = e.cfg().vocab_size;
+    TL_REQUIRE(T > 0 && T <= e.cfg().max_seq_len, "T=%d out of range", T);
+    for (int i = 0; i < T; i++)
+        TL_REQUIRE(tokens_host[i] >= 0 && tokens_host[i] < V, "token id %d out of range", tokens_host[i]);
+    memcpy(m->pinned, tokens_host, (size_t)T * sizeof(int));
+    TL_PROPAGATE(e.set_tokens(m->pinned, T, nullptr));
+    TL_PROPAGATE(e.forward(T, start_pos, logits_host != nullptr, nullptr));
+    TL_PROPAGATE(e.sample_last(T, nullptr));
+    if (logits_host)
+        TL_CUDA(cudaMemcpyAsync(logits_host, e.logits(), (size_t)T * V * 2, cudaMemcpyDeviceToHost, nullptr));
+    if (last_logits_host)
+        TL_CUDA(cudaMemcpyAsync(last_logits_host, e.logits() + (size_t)(T - 1) * V, (size_t)V * 2, cudaMemcpyDeviceToHost, nullptr));
+    TL_CUDA(cudaStreamSynchronize(nullptr));
+    return TL_OK;
+}
+
+int tl_llama2_set_next_token(tl_llama2* m, int token) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && token >= 0 && token < m->eng->cfg().vocab_size, "bad token");
+    m->pinned[0] = token;
+    TL_CUDA(cudaMemcpy(m->eng->d_next(), m->pinned, sizeof(int), cudaMemcpyHostToDevice));
+    return TL_OK;
+}
+
+int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int max_new,
+                       int stop_on_eos, int* out_tokens_host, int* n_out, double* prefill_seconds,
+                       double* decode_seconds) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && prompt_host && out_tokens_host && n_out, "null argument");
+    Llama2Engine& e = *m->eng;
+    const int V = e.cfg().vocab_size;
+    TL_REQUIRE(n_prompt > 0 && max_new > 0 && n_prompt + max_new - 1 <= e.cfg().max_seq_len,
+               "prompt (%d) + generation (%d) exceeds max_seq_len", n_prompt, max_new);
+    for (int i = 0; i < n_prompt; i++) TL_REQUIRE(prompt_host[i] >= 0 && prompt_host[i] < V, "token id out of range");
+    using clk = std::chrono::high_resolution_clock;
+    cudaStream_t st = nullptr;
+    int* tok = m->pinned;
+    *n_out = 0;
+    // prefill + first argmax, timed together like llama2.cpp:35-61
+    auto t0 = clk::now();
+    memcpy(tok, prompt_host, (size_t)n_prompt * sizeof(int));
+    TL_PROPAGATE(e.set_tokens(tok, n_prompt, st));
+    TL_PROPAGATE(e.forward(n_prompt, 0, false, st));
+    TL_PROPAGATE(e.sample_last(n_prompt, st));
+    TL_CUDA(cudaMemcpyAsync(tok, e.d_next(), sizeof(int), cudaMemcpyDeviceToHost, st));
+    TL_CUDA(cudaStreamSynchronize(st));
+    int next = tok[0];
+    if (prefill_seconds) *prefill_seconds = std::chrono::duration<double>(clk::now() - t0).count();
+    out_tokens_host[(*n_out)++] = next;
+    // decode loop (llama2.cpp:67-99): every step the id goes host -> device -> host
+    const bool fast = e.cfg().numerics == TL_NUMERICS_FAST;
+    if (fast && max_new > 1) TL_PROPAGATE(e.ensure_decode_graph(st));
+    auto t1 = clk::now();
+    int pos = n_prompt;
+    while (*n_out < max_new) {
+        if (stop_on_eos && (next == 1 || next == 2)) break;
+        tok[0] = next;
+        if (fast) {
+            TL_CUDA(cudaMemcpyAsync(e.d_next(), tok, sizeof(int), cudaMemcpyHostToDevice, st));
+            TL_PROPAGATE(e.decode_steps(pos, 1, st));
+        } else {
+            TL_PROPAGATE(e.set_tokens(tok, 1, st));
+            TL_PROPAGATE(e.forward(1, pos, false, st));
+            TL_PROPAGATE(e.sample_last(1, st));
+        }
+        TL_CUDA(cudaMemcpyAsync(tok, e.d_next(), sizeof(int), cudaMemcpyDeviceToHost, st));
+        TL_CUDA(cudaStreamSynchronize(st));
+        next = tok[0];
+        out_tokens_host[(*n_out)++] = next;
+        pos++;
+    }
+    if (decode_seconds) *decode_seconds = std::chrono::duration<double>(clk::now() - t1).count();
+    return TL_OK;
+}
+
+int tl_llama2_decode_device(tl_llama2* m, int start_pos, int steps, int* out_tokens_host, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && steps >= 0, "bad argument");
+    Llama2Engine& e = *m->eng;
+    cudaStream_t st = as_stream(stream);
+    TL_PROPAGATE(e.decode_steps(start_pos, steps, st));
+    if (out_tokens_host && steps > 0) {
+        TL_CUDA(cudaMemcpyAsync(out_tokens_host, e.d_generated() + start_pos, (size_t)steps * sizeof(int),
+                                cudaMemcpyDeviceToHost, st));
+        TL_CUDA(cudaStreamSynchronize(st));
+    }
+    return TL_OK;
+}
+
+int tl_llama2_kernel_launches(tl_llama2* m, long long* launches) {
+    TL_REQUIRE(m && launches, "null argument");
+    *launches = m->eng->launches();
+    return TL_OK;
+}
+int tl_llama2_weight_bytes(tl_llama2* m, long long* bytes) {
+    TL_REQUIRE(m && bytes, "null argument");
+    *bytes = m->eng->weight_bytes();
+    return TL_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Fused decode stages as stand-alone entry points
+// ---------------------------------------------------------------------------------------------
+extern "C" {
+
+int tl_rmsnorm_qkv_rope_f16(const tl_half* x, const tl_half* norm_w, float eps, const tl_half* wq,
+                            const tl_half* wk, const tl_half* wv, tl_half* q_out, tl_half* k_cache,
+                            tl_half* v_cache, int dim, int n_q, int head_dim, int pos, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(x && norm_w && wq && wk && wv && q_out && k_cache && v_cache, "null pointer");
+    TL_REQUIRE(dim > 0 && n_q > 0 && head_dim > 0 && pos >= 0, "bad shape");
+    const __half *c, *s;
+    TL_PROPAGATE(rope_table(head_dim, pos + 1, &c, &s));
+    FusedGemv a{};
+    a.x = H(x); a.norm_w = H(norm_w); a.eps = eps;
+    a.W[0] = H(wq); a.W[1] = H(wk); a.W[2] = H(wv); a.n_mats = 3; a.N_each = n_q; a.K = dim;
+    a.epilogue = EPI_QKV_ROPE; a.y = H(q_out);
+    a.k_out = H(k_cache) + (size_t)pos * n_q; a.v_out = H(v_cache) + (size_t)pos * n_q;
+    a.cos_row = c + (size_t)pos * (head_dim / 2); a.sin_row = s + (size_t)pos * (head_dim / 2);
+    a.head_dim = head_dim; a.pos_ptr = nullptr; a.kv_pitch = n_q; a.pdl = false;
+    return launch_fused_gemv(a, as_stream(stream));
+}
+
+int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
+                       float* scratch, unsigned int* counters, int n_heads, int head_dim, int seq_len,
+                       int splits, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(q && k_cache && v_cache && out && scratch && counters, "null pointer");
+    TL_REQUIRE(n_heads > 0 && seq_len > 0 && splits > 0, "bad shape");
+    DecodeAttn a{H(q), H(k_cache), H(v_cache), H(out), scratch, counters, n_heads, head_dim, seq_len,
+                 splits, nullptr, (long long)n_heads * head_dim, false};
+    return launch_decode_attn(a, as_stream(stream));
+}
+
+int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,
+                         int N, int K, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(x && W && residual && y && N > 0 && K > 0, "bad argument");
+    FusedGemv a{};
+    a.x = H(x); a.W[0] = H(W); a.n_mats = 1; a.N_each = N; a.K = K;
+    a.epilogue = EPI_RESIDUAL; a.y = H(y); a.residual = H(residual); a.pdl = false;
+    return launch_fused_gemv(a, as_stream(stream));
+}
+
+int tl_rmsnorm_gateup_swiglu_f16(const tl_half* x, const tl_half* norm_w, float eps, const tl_half* w1,
+                                 const tl_half* w3, tl_half* out, int hidden, int dim, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(x && norm_w && w1 && w3 && out && hidden > 0 && dim > 0, "bad argument");
+    FusedGemv a{};
+    a.x = H(x); a.norm_w = H(norm_w); a.eps = eps;
+    a.W[0] = H(w1); a.W[1] = H(w3); a.n_mats = 2; a.N_each = hidden; a.K = dim;
+    a.epilogue = EPI_SWIGLU; a.y = H(out); a.pdl = false;
+    return launch_fused_gemv(a, as_stream(stream));
+}
+
+int tl_llama2_tensor(tl_llama2* m, const char* name, int layer, void** dptr, int* rows, int* cols) {
+    TL_REQUIRE(m && name && dptr && rows && cols, "null argument");
+    return m->eng->tensor(name, layer, dptr, rows, cols);
+}
+
+}  // extern "C"

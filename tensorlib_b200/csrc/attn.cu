@@ -1,0 +1,285 @@
+// Fast-numerics attention and the small row-wise operators of the prefill path.
+//
+// Decode attention replaces, for one new token, the reference's chain
+//   contiguous copies of the whole K/V prefix -> n_heads GEMVs q.K^T -> ScalarDiv -> softmax ->
+//   n_heads GEMVs P.V -> transpose copy        (model/llama2_7b/src/Transformer.cpp:56-109)
+// with one kernel that reads the (S, H, hd) caches in place: grid (H, splits); each CTA keeps an
+// online-softmax state (max, sum, acc[hd]) in fp32 for its slice of the sequence, writes it to a
+// scratch slot, and the last CTA to finish a head merges the slots. HBM-bound on the KV bytes:
+// 2 * S * H * hd * 2 bytes per call.
+#include "kernels.cuh"
+
+namespace tlb {
+
+namespace {
+
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int MAX_HD = 256;   // head_dim <= 256, even
+constexpr int HD_ITERS = MAX_HD / 64;
+
+struct AttnArgs {
+    const __half* q; const __half* kc; const __half* vc; __half* out;
+    float* scratch; unsigned int* counters;
+    int H, hd, seq_len, splits;
+    const int* pos_ptr; long long pitch; float scale;
+};
+
+// Each lane owns the half2 slices d = 2*lane + 64*i of the head dimension.
+__global__ void __launch_bounds__(ATT_THREADS) k_decode_attn(AttnArgs p) {
+    __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
+    __shared__ float sm_acc[ATT_WARPS][MAX_HD];
+    __shared__ bool is_last;
+    const int h = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hd = p.hd;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int S = p.pos_ptr ? (*p.pos_ptr + 1) : p.seq_len;
+    const int per = (S + p.splits - 1) / p.splits;
+    const int s_begin = split * per, s_end = min(S, s_begin + per);
+
+    float2 qf[HD_ITERS];
+#pragma unroll
+    for (int i = 0; i < HD_ITERS; i++) {
+        int d = 2 * lane + 64 * i;
+        qf[i] = d < hd ? __half22float2(*reinterpret_cast<const __half2*>(p.q + (size_t)h * hd + d))
+                       : make_float2(0.f, 0.f);
+    }
+    float m = -INFINITY, l = 0.f;
+    float2 acc[HD_ITERS];
+#pragma unroll
+    for (int i = 0; i < HD_ITERS; i++) acc[i] = make_float2(0.f, 0.f);
+
+    constexpr int U = 4;  // positions per warp iteration, loads issued together
+    for (int s0 = s_begin + warp * U; s0 < s_end; s0 += ATT_WARPS * U) {
+        __half2 kv[U][HD_ITERS], vv[U][HD_ITERS];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int s = s0 + u;
+            const size_t base = (size_t)s * p.pitch + (size_t)h * hd;
+#pragma unroll
+            for (int i = 0; i < HD_ITERS; i++) {
+                int d = 2 * lane + 64 * i;
+                bool ok = s < s_end && d < hd;
+                kv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.kc + base + d) : __half2half2(__float2half(0.f));
+                vv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.vc + base + d) : __half2half2(__float2half(0.f));
+            }
+        }
+        float sc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD_ITERS; i++) {
+                float2 kf = __half22float2(kv[u][i]);
+                d = fmaf(qf[i].x, kf.x, d);
+                d = fmaf(qf[i].y, kf.y, d);
+            }
+            sc[u] = d;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (s0 + u < s_end) {
+                const float x = sc[u] * p.scale;
+                const float mn = fmaxf(m, x);
+                const float corr = __expf(m - mn), pe = __expf(x - mn);
+                l = l * corr + pe;
+#pragma unroll
+                for (int i = 0; i < HD_ITERS; i++) {
+                    float2 vf = __half22float2(vv[u][i]);
+                    acc[i].x = fmaf(pe, vf.x, acc[i].x * corr);
+                    acc[i].y = fmaf(pe, vf.y, acc[i].y * corr);
+                }
+                m = mn;
+            }
+        }
+    }
+    // merge the warps of this CTA
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < HD_ITERS; i++) {
+        int d = 2 * lane + 64 * i;
+        if (d < hd) { sm_acc[warp][d] = acc[i].x; sm_acc[warp][d + 1] = acc[i].y; }
+    }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sm_m[w]);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) L += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * __expf(sm_m[w] - M);
+    float* slot = p.scratch + ((size_t)h * p.splits + split) * (hd + 2);
+    for (int d = threadIdx.x; d < hd; d += ATT_THREADS) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++)
+            a += sm_m[w] == -INFINITY ? 0.f : sm_acc[w][d] * __expf(sm_m[w] - M);
+        slot[2 + d] = a;
+    }
+    if (threadIdx.x == 0) { slot[0] = M; slot[1] = L; }
+    // last CTA of this head merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int prev = atomicAdd(&p.counters[h], 1u);
+        is_last = prev == (unsigned)p.splits - 1;
+        if (is_last) p.counters[h] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* base = p.scratch + (size_t)h * p.splits * (hd + 2);
+    float GM = -INFINITY;
+    for (int sp = 0; sp < p.splits; sp++) GM = fmaxf(GM, __ldcg(base + (size_t)sp * (hd + 2)));
+    float GL = 0.f;
+    for (int sp = 0; sp < p.splits; sp++) {
+        float ms = __ldcg(base + (size_t)sp * (hd + 2));
+        if (ms != -INFINITY) GL += __ldcg(base + (size_t)sp * (hd + 2) + 1) * __expf(ms - GM);
+    }
+    for (int d = threadIdx.x; d < hd; d += ATT_THREADS) {
+        float a = 0.f;
+        for (int sp = 0; sp < p.splits; sp++) {
+            float ms = __ldcg(base + (size_t)sp * (hd + 2));
+            if (ms != -INFINITY) a += __ldcg(base + (size_t)sp * (hd + 2) + 2 + d) * __expf(ms - GM);
+        }
+        p.out[(size_t)h * hd + d] = __float2half_rn(a / GL);
+    }
+}
+
+// RMSNorm, fp32 sum, one rounding: out = half(x * rsqrt(mean(x^2) + eps) * w). One warp per token
+// like the reference's rms_norm_kernel_v1 (tensorLib/src/device/cuda/rms_norm.cu:140-167).
+__global__ void k_rmsnorm_fast(__half* out, const __half* in, const __half* w, float eps, int hidden, int tokens) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const __half* x = in + (size_t)t * hidden;
+    float ss = 0.f;
+    for (int j = lane; j < hidden; j += 32) { float v = __half2float(x[j]); ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float rinv = rsqrtf(ss / (float)hidden + eps);
+    for (int j = lane; j < hidden; j += 32)
+        out[(size_t)t * hidden + j] = __float2half_rn(__half2float(x[j]) * rinv * __half2float(w[j]));
+}
+
+// softmax over the last dim with fp32 internals; optional scale and causal mask (col > pos + t)
+__global__ void k_softmax_fast(__half* out, const __half* in, size_t cols, int T, int pos, float scale, bool causal) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const __half* x = in + row * cols;
+    __half* y = out + row * cols;
+    const int t = causal ? (int)(row % T) : 0;
+    const size_t lim = causal ? min(cols, (size_t)(pos + t + 1)) : cols;
+    float mx = -INFINITY;
+    for (size_t j = threadIdx.x; j < lim; j += blockDim.x) mx = fmaxf(mx, __half2float(x[j]) * scale);
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : -INFINITY;
+        v = warp_max(v);
+        if (threadIdx.x == 0) red[0] = v;
+    }
+    __syncthreads();
+    mx = red[0];
+    __syncthreads();
+    float sum = 0.f;
+    for (size_t j = threadIdx.x; j < lim; j += blockDim.x) sum += __expf(__half2float(x[j]) * scale - mx);
+    sum = warp_sum(sum);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) red[0] = v;
+    }
+    __syncthreads();
+    const float inv = 1.f / red[0];
+    for (size_t j = threadIdx.x; j < cols; j += blockDim.x)
+        y[j] = j < lim ? __float2half_rn(__expf(__half2float(x[j]) * scale - mx) * inv) : __float2half_rn(0.f);
+}
+
+__global__ void k_swiglu_fast(__half* out, const __half* gate, const __half* up, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float g = __half2float(gate[i]);
+    __half s = __float2half_rn(g / (1.f + __expf(-g)));
+    out[i] = __hmul(s, up[i]);
+}
+
+// vt[h][d][s] = v[s][h][d]
+__global__ void k_transpose_v(__half* vt, const __half* v, int S, int H, int hd, long long v_pitch, long long vt_pitch_s) {
+    __shared__ __half tile[32][34];
+    const int h = blockIdx.z;
+    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        int s = s0 + i, d = d0 + threadIdx.x;
+        if (s < S && d < hd) tile[i][threadIdx.x] = v[(long long)s * v_pitch + (long long)h * hd + d];
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        int d = d0 + i, s = s0 + threadIdx.x;
+        if (s < S && d < hd) vt[((long long)h * hd + d) * vt_pitch_s + s] = tile[threadIdx.x][i];
+    }
+}
+
+}  // namespace
+
+int launch_decode_attn(const DecodeAttn& q, cudaStream_t st) {
+    TL_REQUIRE(q.head_dim > 0 && q.head_dim <= MAX_HD && q.head_dim % 2 == 0, "decode attention: head_dim %d unsupported", q.head_dim);
+    TL_REQUIRE(q.H > 0 && q.splits > 0 && q.splits <= 65535, "decode attention: bad grid");
+    AttnArgs a{q.q, q.k_cache, q.v_cache, q.out, q.scratch, q.counters, q.H, q.head_dim, q.seq_len,
+               q.splits, q.pos_ptr, q.kv_pitch, 1.0f / sqrtf((float)q.head_dim)};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(q.H, q.splits);
+    cfg.blockDim = dim3(ATT_THREADS);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = q.pdl ? 1 : 0;
+    TL_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn, a));
+    return TL_OK;
+}
+
+int launch_rmsnorm_fast(__half* out, const __half* in, const __half* w, float eps, int hidden,
+                        int tokens, cudaStream_t st) {
+    if (tokens <= 0) return TL_OK;
+    k_rmsnorm_fast<<<(unsigned)ceil_div(tokens, 8), 256, 0, st>>>(out, in, w, eps, hidden, tokens);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+int launch_softmax_fast(__half* out, const __half* in, size_t rows, size_t cols, cudaStream_t st) {
+    if (rows == 0 || cols == 0) return TL_OK;
+    k_softmax_fast<<<(unsigned)rows, 256, 0, st>>>(out, in, cols, 1, 0, 1.0f, false);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+int launch_softmax_causal_fast(__half* scores, int H, int T, int S, int pos, float scale, cudaStream_t st) {
+    if ((size_t)H * T == 0 || S == 0) return TL_OK;
+    k_softmax_fast<<<(unsigned)((size_t)H * T), 256, 0, st>>>(scores, scores, (size_t)S, T, pos, scale, true);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+int launch_swiglu_fast(__half* out, const __half* gate, const __half* up, size_t n, cudaStream_t st) {
+    if (n == 0) return TL_OK;
+    k_swiglu_fast<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(out, gate, up, n);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+int launch_transpose_v(__half* vt, const __half* v, int S, int H, int hd, long long v_pitch,
+                       long long vt_pitch_s, cudaStream_t st) {
+    if (S <= 0) return TL_OK;
+    dim3 grid((unsigned)ceil_div(S, 32), (unsigned)ceil_div(hd, 32), H), block(32, 8);
+    k_transpose_v<<<grid, block, 0, st>>>(vt, v, S, H, hd, v_pitch, vt_pitch_s);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
+}  // namespace tlb

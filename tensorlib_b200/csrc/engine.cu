@@ -1,0 +1,532 @@
+// Llama2 forward plumbing. See engine.cuh.
+#include "engine.cuh"
+
+#include <cmath>
+#include <cstring>
+#include <string>
+
+namespace tlb {
+
+namespace {
+
+// seeded N(0, std^2) fill on the device (splitmix64 counter hash + Box-Muller)
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+__global__ void k_fill_normal(__half* out, size_t n, unsigned long long key, float std) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    unsigned long long b = mix64(i * 0xD1342543DE82EF95ull + key);
+    float u1 = ((float)(b >> 40) + 1.0f) * (1.0f / 16777216.0f);
+    float u2 = (float)((b >> 8) & 0xFFFFFF) * (1.0f / 16777216.0f);
+    out[i] = __float2half_rn(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2) * std);
+}
+__global__ void k_fill_const(__half* out, size_t n, float v) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2half_rn(v);
+}
+// bookkeeping at the end of a decode step: record the sampled id, advance the position
+__global__ void k_advance(int* pos, const int* next, int* generated, int max_seq) {
+    int p = *pos;
+    if (p >= 0 && p < max_seq) generated[p] = *next;
+    *pos = p + 1;
+}
+
+}  // namespace
+
+Llama2Engine::Llama2Engine(const tl_llama2_config& cfg) : cfg_(cfg) {
+    hd_ = cfg.dim / cfg.n_heads;
+    H_local_ = cfg.n_heads / cfg.tp_world;
+    dim_local_ = H_local_ * hd_;
+    hidden_local_ = cfg.hidden_dim / cfg.tp_world;
+    vocab_local_ = cfg.vocab_size / cfg.tp_world;
+}
+
+Llama2Engine::~Llama2Engine() { free_all(); }
+
+int Llama2Engine::free_all() {
+    if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
+    for (void* p : allocs_) cudaFree(p);
+    for (void* p : act_allocs_) cudaFree(p);
+    allocs_.clear();
+    act_allocs_.clear();
+    return TL_OK;
+}
+
+int Llama2Engine::allocate() {
+    const size_t dim = cfg_.dim, L = cfg_.n_layers, V = cfg_.vocab_size, S = cfg_.max_seq_len;
+    auto alloc = [&](__half** p, size_t elems, bool weight) -> int {
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, elems * sizeof(__half)));
+        allocs_.push_back(d);
+        *p = static_cast<__half*>(d);
+        if (weight) weight_bytes_ += (long long)(elems * sizeof(__half));
+        return TL_OK;
+    };
+    // one allocation per tensor kind, layers consecutive, like the checkpoint groups them
+    __half *an, *wq, *wk, *wv, *wo, *fn, *w1, *w2, *w3, *ck, *cv;
+    TL_PROPAGATE(alloc(&emb_, V * dim, true));
+    TL_PROPAGATE(alloc(&an, L * dim, true));
+    TL_PROPAGATE(alloc(&wq, L * dim_local_ * dim, true));
+    TL_PROPAGATE(alloc(&wk, L * dim_local_ * dim, true));
+    TL_PROPAGATE(alloc(&wv, L * dim_local_ * dim, true));
+    TL_PROPAGATE(alloc(&wo, L * dim * dim_local_, true));
+    TL_PROPAGATE(alloc(&fn, L * dim, true));
+    TL_PROPAGATE(alloc(&w1, L * hidden_local_ * dim, true));
+    TL_PROPAGATE(alloc(&w2, L * dim * hidden_local_, true));
+    TL_PROPAGATE(alloc(&w3, L * hidden_local_ * dim, true));
+    TL_PROPAGATE(alloc(&final_norm_, dim, true));
+    TL_PROPAGATE(alloc(&wcls_, (size_t)vocab_local_ * dim, true));  // unused (aliased) when shared on 1 GPU
+    TL_PROPAGATE(alloc(&ck, L * S * dim_local_, false));
+    TL_PROPAGATE(alloc(&cv, L * S * dim_local_, false));
+    TL_CUDA(cudaMemset(ck, 0, L * S * dim_local_ * sizeof(__half)));
+    TL_CUDA(cudaMemset(cv, 0, L * S * dim_local_ * sizeof(__half)));
+    layers_.resize(L);
+    for (size_t l = 0; l < L; l++) {
+        LayerWeights& w = layers_[l];
+        w.attn_norm = an + l * dim;
+        w.wq = wq + l * dim_local_ * dim;
+        w.wk = wk + l * dim_local_ * dim;
+        w.wv = wv + l * dim_local_ * dim;
+        w.wo = wo + l * dim * dim_local_;
+        w.ffn_norm = fn + l * dim;
+        w.w1 = w1 + l * hidden_local_ * dim;
+        w.w2 = w2 + l * dim * hidden_local_;
+        w.w3 = w3 + l * hidden_local_ * dim;
+        w.cache_k = ck + l * S * dim_local_;
+        w.cache_v = cv + l * S * dim_local_;
+    }
+    void* d = nullptr;
+    TL_CUDA(cudaMalloc(&d, (2 * S + 8) * sizeof(int)));
+    allocs_.push_back(d);
+    d_tokens_ = static_cast<int*>(d);
+    d_generated_ = d_tokens_ + S;
+    d_next_ = d_generated_ + S;
+    d_pos_ = d_next_ + 1;
+    TL_CUDA(cudaMemset(d, 0, (2 * S + 8) * sizeof(int)));
+    TL_PROPAGATE(rope_table(hd_, (int)S, &cos_t_, &sin_t_));
+    // decode attention: enough CTAs to cover the SMs
+    attn_splits_ = 1;
+    while (H_local_ * attn_splits_ < sm_count() && attn_splits_ < 16) attn_splits_ *= 2;
+    TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * attn_splits_ * (hd_ + 2) * sizeof(float)));
+    allocs_.push_back(d);
+    attn_scratch_ = static_cast<float*>(d);
+    TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * sizeof(unsigned int)));
+    allocs_.push_back(d);
+    attn_counters_ = static_cast<unsigned int*>(d);
+    TL_CUDA(cudaMemset(d, 0, (size_t)H_local_ * sizeof(unsigned int)));
+    return ensure_activations(1, 0);
+}
+
+// ActivationBuffer (model/llama2_7b/include/ActivationBuffer.hpp:8-57): buffers for T tokens;
+// the (H,T,S) score buffers only exist for multi-token passes.
+int Llama2Engine::ensure_activations(int T, int S) {
+    // score buffers are sized for the whole context once they are needed at all
+    const bool need_scores = S > 0 && (scores_ == nullptr || T > act_T_);
+    if (T <= act_T_ && !need_scores) return TL_OK;
+    if (S > 0 || act_S_ > 0) S = cfg_.max_seq_len;
+    TL_CUDA(cudaDeviceSynchronize());
+    if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
+    for (void* p : act_allocs_) cudaFree(p);
+    act_allocs_.clear();
+    const int Tn = std::max(T, act_T_), Sn = std::max(S, act_S_);
+    auto alloc = [&](__half** p, size_t elems) -> int {
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, std::max<size_t>(elems, 8) * sizeof(__half)));
+        act_allocs_.push_back(d);
+        *p = static_cast<__half*>(d);
+        return TL_OK;
+    };
+    const size_t dim = cfg_.dim;
+    TL_PROPAGATE(alloc(&x_, Tn * dim));
+    TL_PROPAGATE(alloc(&xn_, Tn * dim));
+    TL_PROPAGATE(alloc(&h_, Tn * dim));
+    TL_PROPAGATE(alloc(&q_, (size_t)Tn * dim_local_));
+    TL_PROPAGATE(alloc(&k_, (size_t)Tn * dim_local_));
+    TL_PROPAGATE(alloc(&v_, (size_t)Tn * dim_local_));
+    TL_PROPAGATE(alloc(&att_, (size_t)Tn * dim_local_));
+    TL_PROPAGATE(alloc(&ao_, Tn * dim));
+    TL_PROPAGATE(alloc(&g_, (size_t)Tn * hidden_local_));
+    TL_PROPAGATE(alloc(&u_, (size_t)Tn * hidden_local_));
+    TL_PROPAGATE(alloc(&logits_, (size_t)Tn * cfg_.vocab_size));
+    scores_ = probs_ = vt_ = nullptr;
+    if (Sn > 0) {
+        TL_PROPAGATE(alloc(&scores_, (size_t)H_local_ * Tn * Sn));
+        TL_PROPAGATE(alloc(&probs_, (size_t)H_local_ * Tn * Sn));
+        TL_PROPAGATE(alloc(&vt_, (size_t)dim_local_ * Sn));
+    }
+    act_T_ = Tn;
+    act_S_ = Sn;
+    return TL_OK;
+}
+
+// read_weights (model/llama2_7b/src/main.cpp:36-190): same tensor order; each rank keeps its
+// tensor-parallel slice (row blocks of wq/wk/wv/w1/w3 and of the classifier, column blocks of
+// wo/w2).
+int Llama2Engine::load_payload_host(const __half* payload, bool shared_classifier) {
+    const size_t dim = cfg_.dim, hid = cfg_.hidden_dim, L = cfg_.n_layers, V = cfg_.vocab_size;
+    const int r = cfg_.tp_rank;
+    shared_classifier_ = shared_classifier;
+    const __half* cur = payload;
+    auto rows = [&](__half* dst, const __half* src, size_t row0, size_t nrows, size_t cols) -> int {
+        TL_CUDA(cudaMemcpy(dst, src + row0 * cols, nrows * cols * sizeof(__half), cudaMemcpyHostToDevice));
+        return TL_OK;
+    };
+    auto cols = [&](__half* dst, const __half* src, size_t nrows, size_t ncols_full, size_t col0, size_t ncols) -> int {
+        TL_CUDA(cudaMemcpy2D(dst, ncols * sizeof(__half), src + col0, ncols_full * sizeof(__half),
+                             ncols * sizeof(__half), nrows, cudaMemcpyHostToDevice));
+        return TL_OK;
+    };
+    const __half* emb_host = cur;
+    TL_PROPAGATE(rows(emb_, cur, 0, V, dim)); cur += V * dim;
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].attn_norm, cur, 0, 1, dim)); cur += dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].wq, cur, (size_t)r * dim_local_, dim_local_, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].wk, cur, (size_t)r * dim_local_, dim_local_, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].wv, cur, (size_t)r * dim_local_, dim_local_, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(cols(layers_[l].wo, cur, dim, dim, (size_t)r * dim_local_, dim_local_)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].ffn_norm, cur, 0, 1, dim)); cur += dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].w1, cur, (size_t)r * hidden_local_, hidden_local_, dim)); cur += hid * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(cols(layers_[l].w2, cur, dim, hid, (size_t)r * hidden_local_, hidden_local_)); cur += hid * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].w3, cur, (size_t)r * hidden_local_, hidden_local_, dim)); cur += hid * dim; }
+    TL_PROPAGATE(rows(final_norm_, cur, 0, 1, dim)); cur += dim;
+    if (shared_classifier) {
+        TL_PROPAGATE(rows(wcls_, emb_host, (size_t)r * vocab_local_, vocab_local_, dim));
+    } else {
+        cur += (size_t)cfg_.max_seq_len * hd_;  // RoPE values the reference skips (main.cpp:175-177)
+        TL_PROPAGATE(rows(wcls_, cur, (size_t)r * vocab_local_, vocab_local_, dim));
+    }
+    return TL_OK;
+}
+
+int Llama2Engine::init_random(uint64_t seed, float std) {
+    const size_t dim = cfg_.dim, L = cfg_.n_layers;
+    unsigned long long id = 0;
+    auto fill = [&](__half* p, size_t n) -> int {
+        unsigned long long key = seed * 0x9E3779B97F4A7C15ull + (++id) * 0xD6E8FEB86659FD93ull +
+                                 (unsigned long long)cfg_.tp_rank * 0xA0761D6478BD642Full;
+        k_fill_normal<<<(unsigned)ceil_div(n, 256), 256>>>(p, n, key, std);
+        TL_LAUNCH_CHECK();
+        return TL_OK;
+    };
+    auto ones = [&](__half* p, size_t n) -> int {
+        k_fill_const<<<(unsigned)ceil_div(n, 256), 256>>>(p, n, 1.0f);
+        TL_LAUNCH_CHECK();
+        return TL_OK;
+    };
+    shared_classifier_ = false;
+    TL_PROPAGATE(fill(emb_, (size_t)cfg_.vocab_size * dim));
+    TL_PROPAGATE(fill(wcls_, (size_t)vocab_local_ * dim));
+    TL_PROPAGATE(ones(final_norm_, dim));
+    for (size_t l = 0; l < L; l++) {
+        LayerWeights& w = layers_[l];
+        TL_PROPAGATE(ones(w.attn_norm, dim));
+        TL_PROPAGATE(ones(w.ffn_norm, dim));
+        TL_PROPAGATE(fill(w.wq, (size_t)dim_local_ * dim));
+        TL_PROPAGATE(fill(w.wk, (size_t)dim_local_ * dim));
+        TL_PROPAGATE(fill(w.wv, (size_t)dim_local_ * dim));
+        TL_PROPAGATE(fill(w.wo, dim * dim_local_));
+        TL_PROPAGATE(fill(w.w1, (size_t)hidden_local_ * dim));
+        TL_PROPAGATE(fill(w.w2, dim * hidden_local_));
+        TL_PROPAGATE(fill(w.w3, (size_t)hidden_local_ * dim));
+    }
+    TL_CUDA(cudaDeviceSynchronize());
+    return TL_OK;
+}
+
+int Llama2Engine::tensor(const char* name, int layer, void** dptr, int* rows, int* cols) const {
+    const std::string n(name);
+    auto set = [&](const __half* p, int r, int c) { *dptr = const_cast<__half*>(p); *rows = r; *cols = c; return TL_OK; };
+    if (n == "tok_embeddings") return set(emb_, cfg_.vocab_size, cfg_.dim);
+    if (n == "norm") return set(final_norm_, 1, cfg_.dim);
+    if (n == "output") return set((shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_, vocab_local_, cfg_.dim);
+    TL_REQUIRE(layer >= 0 && layer < cfg_.n_layers, "layer %d out of range", layer);
+    const LayerWeights& w = layers_[layer];
+    if (n == "attention_norm") return set(w.attn_norm, 1, cfg_.dim);
+    if (n == "ffn_norm") return set(w.ffn_norm, 1, cfg_.dim);
+    if (n == "wq") return set(w.wq, dim_local_, cfg_.dim);
+    if (n == "wk") return set(w.wk, dim_local_, cfg_.dim);
+    if (n == "wv") return set(w.wv, dim_local_, cfg_.dim);
+    if (n == "wo") return set(w.wo, cfg_.dim, dim_local_);
+    if (n == "w1") return set(w.w1, hidden_local_, cfg_.dim);
+    if (n == "w3") return set(w.w3, hidden_local_, cfg_.dim);
+    if (n == "w2") return set(w.w2, cfg_.dim, hidden_local_);
+    return set_error(TL_ERR_INVALID_ARGUMENT, "unknown tensor name '%s'", name);
+}
+
+int Llama2Engine::set_tokens(const int* tokens_host, int T, cudaStream_t st) {
+    TL_REQUIRE(T > 0 && T <= cfg_.max_seq_len, "token count %d out of range", T);
+    TL_CUDA(cudaMemcpyAsync(d_tokens_, tokens_host, (size_t)T * sizeof(int), cudaMemcpyHostToDevice, st));
+    return TL_OK;
+}
+
+// nn::Linear::forward -> Tensor::matmul -> Device::matmul2d (linear.cpp:43-49, matmul.cpp:313-320)
+int Llama2Engine::linear(const __half* x, const __half* W, __half* y, int T, int N, int K, cudaStream_t st) {
+    if (cfg_.numerics == TL_NUMERICS_REFERENCE_ORDER) {
+        SeqMatmul p{x, W, y, 1, T, N, K, K, 1, K, 1, N, 0, 0, 0};
+        launches_++;
+        return launch_matmul_seq(p, st);
+    }
+    if (T > 8 && hgemm_supported(x, W, y, T, N, K, K, K, N)) {
+        launches_++;
+        return launch_hgemm(x, W, y, 1, T, N, K, K, K, N, 0, 0, 0, st);
+    }
+    if (gemv_supported(x, W, T <= 8 ? T : 8, N, K, K)) {
+        for (int t0 = 0; t0 < T; t0 += 8) {  // skinny batches: stream the weights once per 8 rows
+            int m = std::min(8, T - t0);
+            launches_++;
+            TL_PROPAGATE(launch_gemv(x + (size_t)t0 * K, W, y + (size_t)t0 * N, m, N, K, K, K, N, st));
+        }
+        return TL_OK;
+    }
+    SeqMatmul p{x, W, y, 1, T, N, K, K, 1, K, 1, N, 0, 0, 0};
+    launches_++;
+    return launch_matmul_seq(p, st);
+}
+
+int Llama2Engine::forward(int T, int start_pos, bool all_logits, cudaStream_t st) {
+    TL_REQUIRE(T > 0 && start_pos >= 0 && start_pos + T <= cfg_.max_seq_len,
+               "forward: T=%d start_pos=%d exceeds max_seq_len=%d", T, start_pos, cfg_.max_seq_len);
+    const bool exact = cfg_.numerics == TL_NUMERICS_REFERENCE_ORDER;
+    TL_PROPAGATE(ensure_activations(T, (exact || T > 1) ? start_pos + T : 0));
+    if (exact) return forward_reference_order(T, start_pos, all_logits, st);
+    if (T == 1) {
+        // same launch sequence as the graph, position passed through *d_pos_
+        TL_CUDA(cudaMemcpyAsync(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice, st));
+        TL_CUDA(cudaMemcpyAsync(d_next_, d_tokens_, sizeof(int), cudaMemcpyDeviceToDevice, st));
+        return decode_step_fast(st, false);
+    }
+    return forward_fast_prefill(T, start_pos, all_logits, st);
+}
+
+// The reference's op sequence, one kernel per op, reference-order numerics throughout:
+// Transformer::forward (Transformer.cpp:264-299), TransformerBlock::forward (:162-178),
+// Attention::forward (:28-112), FeedForward::forward (:133-145).
+int Llama2Engine::forward_reference_order(int T, int pos, bool all_logits, cudaStream_t st) {
+    const int dim = cfg_.dim, S = pos + T, H = H_local_;
+    TL_REQUIRE(cfg_.tp_world == 1, "reference-order numerics is single-GPU");
+    launches_++;
+    TL_PROPAGATE(launch_embedding(x_, emb_, d_tokens_, T, dim, cfg_.vocab_size, st));
+    for (int l = 0; l < cfg_.n_layers; l++) {
+        const LayerWeights& w = layers_[l];
+        launches_ += 16;
+        TL_PROPAGATE(launch_rmsnorm_seq(xn_, x_, w.attn_norm, 1e-5f, dim, T, st));
+        TL_PROPAGATE(linear(xn_, w.wq, q_, T, dim, dim, st));
+        TL_PROPAGATE(linear(xn_, w.wk, k_, T, dim, dim, st));
+        TL_PROPAGATE(linear(xn_, w.wv, v_, T, dim, dim, st));
+        TL_PROPAGATE(launch_rope(q_, q_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
+        TL_PROPAGATE(launch_rope(k_, k_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
+        TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dim, k_, T, dim, dim, st));
+        TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dim, v_, T, dim, dim, st));
+        // scores[h] (T x S) = q[:, h, :] . K[:, h, :]^T
+        SeqMatmul qk{q_, w.cache_k, scores_, H, T, S, hd_, dim, 1, dim, 1, S, hd_, hd_, (long long)T * S};
+        TL_PROPAGATE(launch_matmul_seq(qk, st));
+        TL_PROPAGATE(launch_scale_mask(scores_, H, T, S, pos, hd_, st));
+        TL_PROPAGATE(launch_softmax_seq(probs_, scores_, (size_t)H * T, S, st));
+        // att[:, h, :] (T x hd) = P[h] (T x S) . V[:, h, :]
+        SeqMatmul pv{probs_, w.cache_v, att_, H, T, hd_, S, S, 1, 1, dim, dim, (long long)T * S, hd_, hd_};
+        TL_PROPAGATE(launch_matmul_seq(pv, st));
+        TL_PROPAGATE(linear(att_, w.wo, ao_, T, dim, dim, st));
+        TL_PROPAGATE(launch_binary(h_, x_, ao_, (size_t)T * dim, 0, st));
+        TL_PROPAGATE(launch_rmsnorm_seq(xn_, h_, w.ffn_norm, 1e-5f, dim, T, st));
+        TL_PROPAGATE(linear(xn_, w.w1, g_, T, cfg_.hidden_dim, dim, st));
+        TL_PROPAGATE(launch_silu(g_, g_, (size_t)T * cfg_.hidden_dim, cfg_.silu_via_float, st));
+        TL_PROPAGATE(linear(xn_, w.w3, u_, T, cfg_.hidden_dim, dim, st));
+        TL_PROPAGATE(launch_binary(g_, g_, u_, (size_t)T * cfg_.hidden_dim, 1, st));
+        TL_PROPAGATE(linear(g_, w.w2, ao_, T, dim, cfg_.hidden_dim, st));
+        TL_PROPAGATE(launch_binary(x_, h_, ao_, (size_t)T * dim, 0, st));
+    }
+    launches_ += 1;
+    const int t0 = all_logits ? 0 : T - 1, tn = all_logits ? T : 1;
+    TL_PROPAGATE(launch_rmsnorm_seq(xn_ + (size_t)t0 * dim, x_ + (size_t)t0 * dim, final_norm_, 1e-5f, dim, tn, st));
+    const __half* cls = shared_classifier_ ? emb_ : wcls_;
+    return linear(xn_ + (size_t)t0 * dim, cls, logits_ + (size_t)t0 * cfg_.vocab_size, tn, cfg_.vocab_size, dim, st);
+}
+
+// Multi-token pass, fast numerics: unfused operators around the matmuls.
+int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStream_t st) {
+    const int dim = cfg_.dim, S = pos + T, H = H_local_, dl = dim_local_, hl = hidden_local_;
+    const float scale = 1.0f / sqrtf((float)hd_);
+    launches_++;
+    TL_PROPAGATE(launch_embedding(x_, emb_, d_tokens_, T, dim, cfg_.vocab_size, st));
+    for (int l = 0; l < cfg_.n_layers; l++) {
+        const LayerWeights& w = layers_[l];
+        launches_ += 12;
+        TL_PROPAGATE(launch_rmsnorm_fast(xn_, x_, w.attn_norm, 1e-5f, dim, T, st));
+        TL_PROPAGATE(linear(xn_, w.wq, q_, T, dl, dim, st));
+        TL_PROPAGATE(linear(xn_, w.wk, k_, T, dl, dim, st));
+        TL_PROPAGATE(linear(xn_, w.wv, v_, T, dl, dim, st));
+        TL_PROPAGATE(launch_rope(q_, q_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
+        TL_PROPAGATE(launch_rope(k_, k_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
+        TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dl, k_, T, dl, dl, st));
+        TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dl, v_, T, dl, dl, st));
+        // scores[h] = q_h . K_h^T ; softmax (scale + causal mask inside) ; att_h = P_h . V_h
+        if (hgemm_supported(q_, w.cache_k, scores_, T, S, hd_, dl, dl, S) &&
+            hgemm_supported(scores_, vt_, att_, T, hd_, S, S, S, dl)) {
+            TL_PROPAGATE(launch_hgemm(q_, w.cache_k, scores_, H, T, S, hd_, dl, dl, S, hd_, hd_, (long long)T * S, st));
+            TL_PROPAGATE(launch_softmax_causal_fast(scores_, H, T, S, pos, scale, st));
+            TL_PROPAGATE(launch_transpose_v(vt_, w.cache_v, S, H, hd_, dl, S, st));
+            TL_PROPAGATE(launch_hgemm(scores_, vt_, att_, H, T, hd_, S, S, S, dl, (long long)T * S, (long long)hd_ * S, hd_, st));
+        } else {
+            SeqMatmul qk{q_, w.cache_k, scores_, H, T, S, hd_, dl, 1, dl, 1, S, hd_, hd_, (long long)T * S};
+            TL_PROPAGATE(launch_matmul_seq(qk, st));
+            TL_PROPAGATE(launch_softmax_causal_fast(scores_, H, T, S, pos, scale, st));
+            SeqMatmul pv{scores_, w.cache_v, att_, H, T, hd_, S, S, 1, 1, dl, dl, (long long)T * S, hd_, hd_};
+            TL_PROPAGATE(launch_matmul_seq(pv, st));
+        }
+        TL_PROPAGATE(linear(att_, w.wo, ao_, T, dim, dl, st));
+        if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
+        TL_PROPAGATE(launch_binary(h_, x_, ao_, (size_t)T * dim, 0, st));
+        TL_PROPAGATE(launch_rmsnorm_fast(xn_, h_, w.ffn_norm, 1e-5f, dim, T, st));
+        TL_PROPAGATE(linear(xn_, w.w1, g_, T, hl, dim, st));
+        TL_PROPAGATE(linear(xn_, w.w3, u_, T, hl, dim, st));
+        TL_PROPAGATE(launch_swiglu_fast(g_, g_, u_, (size_t)T * hl, st));
+        TL_PROPAGATE(linear(g_, w.w2, ao_, T, dim, hl, st));
+        if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
+        TL_PROPAGATE(launch_binary(x_, h_, ao_, (size_t)T * dim, 0, st));
+    }
+    launches_ += 1;
+    const int t0 = all_logits ? 0 : T - 1, tn = all_logits ? T : 1;
+    TL_PROPAGATE(launch_rmsnorm_fast(xn_ + (size_t)t0 * dim, x_ + (size_t)t0 * dim, final_norm_, 1e-5f, dim, tn, st));
+    const __half* cls = (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_;
+    if (cfg_.tp_world == 1)
+        return linear(xn_ + (size_t)t0 * dim, cls, logits_ + (size_t)t0 * cfg_.vocab_size, tn, cfg_.vocab_size, dim, st);
+    // vocabulary-split classifier: local slice, then gather the slices of every rank
+    for (int t = t0; t < t0 + tn; t++) {
+        TL_PROPAGATE(linear(xn_ + (size_t)t * dim, cls, u_, 1, vocab_local_, dim, st));
+        TL_PROPAGATE(coll_->allgather_f16(u_, logits_ + (size_t)t * cfg_.vocab_size, vocab_local_, st));
+    }
+    return TL_OK;
+}
+
+// One decode step, fast numerics, 5 kernels per layer:
+//   [RMSNorm + wq|wk|wv GEMV + RoPE + KV-cache write] -> [attention over the cache in place] ->
+//   [wo GEMV + residual] -> [RMSNorm + w1|w3 GEMV + SiLU*up] -> [w2 GEMV + residual]
+// then [RMSNorm + classifier GEMV] -> argmax -> advance. Token and position are read from device
+// memory so the same launches can be replayed from a CUDA graph.
+int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
+    const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_;
+    long long n = 0;
+    TL_PROPAGATE(launch_embedding(x_, emb_, d_next_, 1, dim, cfg_.vocab_size, st)); n++;
+    for (int l = 0; l < cfg_.n_layers; l++) {
+        const LayerWeights& w = layers_[l];
+        FusedGemv a{};
+        a.x = x_; a.norm_w = w.attn_norm; a.eps = 1e-5f;
+        a.W[0] = w.wq; a.W[1] = w.wk; a.W[2] = w.wv; a.n_mats = 3; a.N_each = dl; a.K = dim;
+        a.epilogue = EPI_QKV_ROPE; a.y = q_; a.k_out = w.cache_k; a.v_out = w.cache_v;
+        a.cos_row = cos_t_; a.sin_row = sin_t_; a.head_dim = hd_; a.pos_ptr = d_pos_; a.kv_pitch = dl;
+        a.pdl = pdl;
+        TL_PROPAGATE(launch_fused_gemv(a, st)); n++;
+
+        DecodeAttn at{q_, w.cache_k, w.cache_v, att_, attn_scratch_, attn_counters_, H_local_, hd_, 0,
+                      attn_splits_, d_pos_, dl, pdl};
+        TL_PROPAGATE(launch_decode_attn(at, st)); n++;
+
+        FusedGemv o{};
+        o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
+        if (coll_) {
+            o.epilogue = EPI_STORE; o.y = ao_;
+            TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
+            TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, dim, st)); n++;
+            TL_PROPAGATE(launch_binary(h_, x_, ao_, dim, 0, st)); n++;
+        } else {
+            o.epilogue = EPI_RESIDUAL; o.y = h_; o.residual = x_;
+            TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
+        }
+
+        FusedGemv f{};
+        f.x = h_; f.norm_w = w.ffn_norm; f.eps = 1e-5f;
+        f.W[0] = w.w1; f.W[1] = w.w3; f.n_mats = 2; f.N_each = hl; f.K = dim;
+        f.epilogue = EPI_SWIGLU; f.y = g_; f.pdl = pdl;
+        TL_PROPAGATE(launch_fused_gemv(f, st)); n++;
+
+        FusedGemv d{};
+        d.x = g_; d.W[0] = w.w2; d.n_mats = 1; d.N_each = dim; d.K = hl; d.pdl = pdl;
+        if (coll_) {
+            d.epilogue = EPI_STORE; d.y = ao_;
+            TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
+            TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, dim, st)); n++;
+            TL_PROPAGATE(launch_binary(x_, h_, ao_, dim, 0, st)); n++;
+        } else {
+            d.epilogue = EPI_RESIDUAL; d.y = x_; d.residual = h_;
+            TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
+        }
+    }
+    FusedGemv c{};
+    c.x = x_; c.norm_w = final_norm_; c.eps = 1e-5f;
+    c.W[0] = (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_;
+    c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_STORE; c.pdl = pdl;
+    if (coll_) {
+        c.y = u_;
+        TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
+        TL_PROPAGATE(coll_->allgather_f16(u_, logits_, vocab_local_, st)); n++;
+    } else {
+        c.y = logits_;
+        TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
+    }
+    TL_PROPAGATE(launch_argmax(d_next_, logits_, 1, cfg_.vocab_size, st)); n++;
+    k_advance<<<1, 1, 0, st>>>(d_pos_, d_next_, d_generated_, cfg_.max_seq_len); n++;
+    TL_LAUNCH_CHECK();
+    decode_step_launches_ = n;
+    launches_ += n;
+    return TL_OK;
+}
+
+int Llama2Engine::sample_last(int T, cudaStream_t st) {
+    launches_++;
+    return launch_argmax(d_next_, logits_ + (size_t)(T - 1) * cfg_.vocab_size, 1, cfg_.vocab_size, st);
+}
+
+int Llama2Engine::ensure_decode_graph(cudaStream_t st) {
+    if (decode_graph_) return TL_OK;
+    TL_REQUIRE(cfg_.numerics == TL_NUMERICS_FAST, "the decode graph exists for fast numerics only");
+    TL_REQUIRE(!coll_ || coll_->graph_capturable(), "collective is not capturable");
+    TL_PROPAGATE(ensure_activations(1, 0));
+    cudaStream_t cap = st;
+    bool own = false;
+    if (cap == nullptr) {  // the legacy default stream cannot be captured
+        TL_CUDA(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking));
+        own = true;
+    }
+    cudaGraph_t graph = nullptr;
+    const long long before = launches_;
+    TL_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal));
+    int rc = decode_step_fast(cap, true);
+    cudaError_t e = cudaStreamEndCapture(cap, &graph);
+    launches_ = before;  // capture enqueues nothing
+    if (own) cudaStreamDestroy(cap);
+    if (rc != TL_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) return set_error(TL_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&decode_graph_, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { decode_graph_ = nullptr; return set_error(TL_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e)); }
+    return TL_OK;
+}
+
+int Llama2Engine::decode_steps(int start_pos, int steps, cudaStream_t st) {
+    TL_REQUIRE(steps >= 0 && start_pos >= 0 && start_pos + steps <= cfg_.max_seq_len,
+               "decode: positions [%d,%d) exceed max_seq_len=%d", start_pos, start_pos + steps, cfg_.max_seq_len);
+    TL_CUDA(cudaMemcpyAsync(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice, st));
+    if (cfg_.numerics == TL_NUMERICS_FAST) {
+        TL_PROPAGATE(ensure_decode_graph(st));
+        for (int i = 0; i < steps; i++) {
+            TL_CUDA(cudaGraphLaunch(decode_graph_, st));
+            launches_ += decode_step_launches_;
+        }
+        return TL_OK;
+    }
+    // reference-order numerics: plain launches, token fed back on the device
+    for (int i = 0; i < steps; i++) {
+        TL_CUDA(cudaMemcpyAsync(d_tokens_, d_next_, sizeof(int), cudaMemcpyDeviceToDevice, st));
+        TL_PROPAGATE(forward(1, start_pos + i, false, st));
+        TL_PROPAGATE(sample_last(1, st));
+        k_advance<<<1, 1, 0, st>>>(d_pos_, d_next_, d_generated_, cfg_.max_seq_len);
+        TL_LAUNCH_CHECK();
+        launches_++;
+    }
+    return TL_OK;
+}
+
+}  // namespace tlb

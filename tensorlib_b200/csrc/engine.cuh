@@ -1,0 +1,90 @@
+// Host-side plumbing of the Llama2 forward: weights, KV caches, activation buffers, the per-layer
+// launch sequence and the CUDA graph of one decode step. Mirrors Transformer<half> / Attention /
+// FeedForward / TransformerBlock (model/llama2_7b/src/Transformer.cpp) and ActivationBuffer
+// (model/llama2_7b/include/ActivationBuffer.hpp) of the reference.
+#pragma once
+
+#include <vector>
+
+#include "kernels.cuh"
+
+namespace tlb {
+
+struct LayerWeights {
+    __half *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *w1, *w2, *w3;
+    __half *cache_k, *cache_v;  // (max_seq, H_local, hd)
+};
+
+// Hook the tensor-parallel build installs: sum `n` halfs in place across ranks, enqueued on `st`.
+struct Collective {
+    virtual ~Collective() = default;
+    virtual int allreduce_sum_f16(__half* buf, size_t n, cudaStream_t st) = 0;
+    virtual int allgather_f16(const __half* send, __half* recv, size_t n_per_rank, cudaStream_t st) = 0;
+    virtual bool graph_capturable() const = 0;
+};
+
+class Llama2Engine {
+public:
+    explicit Llama2Engine(const tl_llama2_config& cfg);
+    ~Llama2Engine();
+    int allocate();
+    int load_payload_host(const __half* payload, bool shared_classifier);
+    int init_random(uint64_t seed, float std);
+
+    // Transformer::forward. Token ids must already be in d_tokens_[0..T) (see set_tokens).
+    // all_logits: compute logits for every position (what the reference returns) or only the last.
+    int forward(int T, int start_pos, bool all_logits, cudaStream_t st);
+    int set_tokens(const int* tokens_host, int T, cudaStream_t st);
+    int sample_last(int T, cudaStream_t st);  // greedy argmax of the last position -> d_next_
+
+    // One decode step replayed from a CUDA graph: token = *d_next_, position = *d_pos_; writes the
+    // sampled id to d_next_ and d_generated_[pos], then increments *d_pos_.
+    int decode_steps(int start_pos, int steps, cudaStream_t st);
+    int ensure_decode_graph(cudaStream_t st);
+
+    const tl_llama2_config& cfg() const { return cfg_; }
+    __half* logits() const { return logits_; }
+    int* d_next() const { return d_next_; }
+    int* d_pos() const { return d_pos_; }
+    int* d_generated() const { return d_generated_; }
+    long long launches() const { return launches_; }
+    long long weight_bytes() const { return weight_bytes_; }
+    int vocab_local() const { return vocab_local_; }
+    void set_collective(Collective* c) { coll_ = c; }
+    int tensor(const char* name, int layer, void** dptr, int* rows, int* cols) const;
+
+private:
+    int ensure_activations(int T, int S);
+    int linear(const __half* x, const __half* W, __half* y, int T, int N, int K, cudaStream_t st);
+    int forward_reference_order(int T, int pos, bool all_logits, cudaStream_t st);
+    int forward_fast_prefill(int T, int pos, bool all_logits, cudaStream_t st);
+    int decode_step_fast(cudaStream_t st, bool pdl);  // position-indirect (reads *d_pos_)
+    int free_all();
+
+    tl_llama2_config cfg_;
+    int hd_, H_local_, dim_local_, hidden_local_, vocab_local_;
+    bool shared_classifier_ = true;
+    __half *emb_ = nullptr, *final_norm_ = nullptr, *wcls_ = nullptr;
+    std::vector<LayerWeights> layers_;
+    std::vector<void*> allocs_;
+    long long weight_bytes_ = 0;
+
+    // activations
+    int act_T_ = 0, act_S_ = 0;
+    __half *x_ = nullptr, *xn_ = nullptr, *h_ = nullptr, *q_ = nullptr, *k_ = nullptr, *v_ = nullptr,
+           *att_ = nullptr, *ao_ = nullptr, *g_ = nullptr, *u_ = nullptr, *logits_ = nullptr,
+           *scores_ = nullptr, *probs_ = nullptr, *vt_ = nullptr;
+    std::vector<void*> act_allocs_;
+    float* attn_scratch_ = nullptr;
+    unsigned int* attn_counters_ = nullptr;
+    int attn_splits_ = 1;
+    int *d_tokens_ = nullptr, *d_next_ = nullptr, *d_pos_ = nullptr, *d_generated_ = nullptr;
+    const __half *cos_t_ = nullptr, *sin_t_ = nullptr;
+
+    cudaGraphExec_t decode_graph_ = nullptr;
+    long long launches_ = 0;
+    long long decode_step_launches_ = 0;
+    Collective* coll_ = nullptr;
+};
+
+}  // namespace tlb

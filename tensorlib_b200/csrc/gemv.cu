@@ -1,0 +1,471 @@
+// Decode-path GEMV, M = 1..8, fast numerics: y[m,n] = sum_k x[m,k] * W[n,k] with W in the
+// llama2.c [out,in] fp16 layout the reference keeps (nn::Linear, tensorLib/src/nn/linear.cpp:10-14).
+// Replaces gemv_v6 / gemv_v4 (tensorLib/src/device/cuda/gemv.cu:379-450, :260-306).
+//
+// Two kernels:
+//
+//  k_gemv_ring (M = 1, the decode step). One persistent CTA per SM. A producer warp streams the
+//  CTA's weight rows through a 6-stage shared-memory ring with TMA bulk copies
+//  (cp.async.bulk global -> shared, completion on an mbarrier): a stage holds 16 row-chunks of
+//  1024 halfs (32 KB), so ~190 KB per SM are in flight independent of what the consumers do.
+//  Eight consumer warps each own one "unit" of a stage (two weight rows), read it back with
+//  128-bit shared loads against the activation vector staged once in shared memory, accumulate
+//  in fp32, reduce with xor shuffles and apply the epilogue. HBM-bound; algorithmic bytes =
+//  2*(rows*K) + small vectors.
+//  The neighbouring operators of the Llama2 block ride along: RMSNorm in the prologue (computed
+//  by the consumers while the producer is already streaming: weights never depend on the
+//  previous kernel, so the producer does not wait for it), RoPE + KV-cache write / residual add /
+//  SiLU*up in the epilogue.
+//
+//  k_gemv (M = 1..8, tl_matmul2d_f16): activations staged in shared memory, each warp owns two
+//  rows and streams them with 128-bit non-allocating loads, 16 of them in flight per lane.
+#include "kernels.cuh"
+
+namespace tlb {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// shared helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+    const __half2* wh = reinterpret_cast<const __half2*>(&w);
+    const __half2* xh = reinterpret_cast<const __half2*>(&x);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 wf = __half22float2(wh[i]);
+        float2 xf = __half22float2(xh[i]);
+        acc = fmaf(wf.x, xf.x, acc);
+        acc = fmaf(wf.y, xf.y, acc);
+    }
+    return acc;
+}
+
+__device__ __forceinline__ float sumsq8(const uint4& v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 f = __half22float2(h[i]);
+        s = fmaf(f.x, f.x, s);
+        s = fmaf(f.y, f.y, s);
+    }
+    return s;
+}
+
+// ---- mbarrier / TMA bulk copy (sm_90+ PTX) -------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after WAIT_LIMIT polls (each poll may itself block for a hardware time
+// slice), so a logic error shows up as a status word instead of a hung GPU.
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar,
+                                            uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void consumer_bar_sync() {  // the 8 consumer warps only
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// k_gemv_ring
+// ---------------------------------------------------------------------------------------------
+constexpr int CONSUMERS = 8;                       // consumer warps == units per stage
+constexpr int RING_THREADS = (CONSUMERS + 1) * 32; // + one producer warp
+constexpr int KC = 1024;                           // halfs per row-chunk
+constexpr int CHUNK_BYTES = KC * 2;                // 2 KB
+constexpr int STAGE_BYTES = CONSUMERS * 2 * CHUNK_BYTES;  // 32 KB
+constexpr int NSTAGES = 6;
+
+struct RingArgs {
+    const __half* x; const __half* norm_w; float eps;
+    const __half* W0; const __half* W1; const __half* W2;
+    int N_each, K, total_units;   // a unit = the two weight rows one consumer warp owns
+    __half* y; const __half* residual;
+    __half* k_out; __half* v_out; const __half* cos_t; const __half* sin_t; int head_dim;
+    const int* pos_ptr; long long kv_pitch;
+    const __half* silu_tab;
+    int* status;                  // device status word: set on a timed-out wait
+};
+
+template <int EPI>
+__device__ __forceinline__ void unit_rows(const RingArgs& p, int unit, const __half*& ra, const __half*& rb,
+                                          int& mat, int& r) {
+    if (EPI == EPI_SWIGLU) {  // row `unit` of w1 (gate) and of w3 (up)
+        mat = 0; r = unit;
+        ra = p.W0 + (long long)unit * p.K;
+        rb = p.W1 + (long long)unit * p.K;
+    } else {                  // rows 2u, 2u+1 of one of up to three matrices
+        int row = unit * 2;
+        mat = row / p.N_each;
+        r = row - mat * p.N_each;
+        const __half* Wm = mat == 0 ? p.W0 : (mat == 1 ? p.W1 : p.W2);
+        ra = Wm + (long long)r * p.K;
+        rb = ra + p.K;
+    }
+}
+
+template <int EPI, bool NORM>
+__global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    // layout: [NSTAGES stages][x: K halfs][full barriers][empty barriers][reduction scratch]
+    unsigned char* stages = smem;
+    uint4* xs = reinterpret_cast<uint4*>(smem + NSTAGES * STAGE_BYTES);
+    const int K8 = p.K >> 3;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGES * STAGE_BYTES + (((size_t)p.K * 2 + 127) & ~(size_t)127));
+    float* red = reinterpret_cast<float*>(bars + 2 * NSTAGES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NSTAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // this CTA's contiguous share of the units, balanced to +-1
+    const int u_begin = (int)((long long)p.total_units * blockIdx.x / gridDim.x);
+    const int u_end = (int)((long long)p.total_units * (blockIdx.x + 1) / gridDim.x);
+    const int n_units = u_end - u_begin;
+    const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
+    const int nk = (p.K + KC - 1) / KC;
+    const int n_iters = n_tiles * nk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, CONSUMERS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == CONSUMERS) {
+        // ---------------- producer: weights only, independent of the previous kernel ----------
+        const uint64_t pol = policy_evict_first();
+        const __half* row_ptr = nullptr;
+        int cur_tile = -1, rows_in_tile = 0;
+        bool ok = true;
+        for (int it = 0; it < n_iters && ok; it++) {
+            const int s = it % NSTAGES, use = it / NSTAGES;
+            const int tile = it / nk, chunk = it - tile * nk;
+            if (tile != cur_tile) {
+                cur_tile = tile;
+                const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
+                rows_in_tile = units_here * 2;
+                if (lane < rows_in_tile) {
+                    const __half *ra, *rb; int mat, r;
+                    unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
+                    row_ptr = (lane & 1) ? rb : ra;
+                }
+            }
+            if (use > 0) ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const int kc = min(KC, p.K - chunk * KC);
+            if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
+            __syncwarp();
+            if (lane < rows_in_tile)
+                tma_load_1d(smem_u32(stages + (size_t)s * STAGE_BYTES + (size_t)lane * CHUNK_BYTES),
+                            row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), full0 + 8 * s, pol);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+        return;
+    }
+
+    // ---------------- consumers -------------------------------------------------------------------
+    pdl_wait();  // activations written by the previous kernel are visible from here on
+    const int ctid = threadIdx.x;  // 0..255
+    const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
+    if (NORM) {  // RMSNorm: fp32 sum of squares, xs = half(x * rinv * w)
+        float ss = 0.f;
+        for (int c = ctid; c < K8; c += CONSUMERS * 32) {
+            uint4 v = x4[c];
+            xs[c] = v;
+            ss += sumsq8(v);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        consumer_bar_sync();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; w++) tot += red[w];
+        const float rinv = rsqrtf(tot / (float)p.K + p.eps);
+        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
+        for (int c = ctid; c < K8; c += CONSUMERS * 32) {
+            uint4 v = xs[c], g = nw4[c];
+            __half2* vh = reinterpret_cast<__half2*>(&v);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 vf = __half22float2(vh[i]), gf = __half22float2(gh[i]);
+                vh[i] = __floats2half2_rn(vf.x * rinv * gf.x, vf.y * rinv * gf.y);
+            }
+            xs[c] = v;
+        }
+    } else {
+        for (int c = ctid; c < K8; c += CONSUMERS * 32) xs[c] = x4[c];
+    }
+    consumer_bar_sync();
+
+    bool ok = true;
+    int it = 0;
+    for (int tile = 0; tile < n_tiles && ok; tile++) {
+        const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
+        const bool mine = warp < units_here;
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+        for (int chunk = 0; chunk < nk; chunk++, it++) {
+            const int s = it % NSTAGES, use = it / NSTAGES;
+            ok = mbar_wait(full0 + 8 * s, use & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (mine) {
+                const int kc8 = min(KC, p.K - chunk * KC) >> 3;
+                const uint4* wa = reinterpret_cast<const uint4*>(stages + (size_t)s * STAGE_BYTES + (size_t)(2 * warp) * CHUNK_BYTES);
+                const uint4* wb = wa + CHUNK_BYTES / 16;
+                const uint4* xc = xs + chunk * (KC / 8);
+#pragma unroll
+                for (int j = 0; j < KC / 8 / 32; j++) {
+                    const int idx = lane + 32 * j;
+                    if (idx < kc8) {
+                        const uint4 xv = xc[idx], va = wa[idx], vb = wb[idx];
+                        if (j & 1) { a1 = dot8(va, xv, a1); b1 = dot8(vb, xv, b1); }
+                        else       { a0 = dot8(va, xv, a0); b0 = dot8(vb, xv, b0); }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+        if (!ok || !mine) continue;
+        const float sa = warp_sum(a0 + a1), sb = warp_sum(b0 + b1);
+        if (lane != 0) continue;
+        const __half ha = __float2half_rn(sa), hb = __float2half_rn(sb);
+        const __half *ra, *rb; int mat, r;
+        unit_rows<EPI>(p, u_begin + tile * CONSUMERS + warp, ra, rb, mat, r);
+        if (EPI == EPI_STORE) {
+            p.y[(long long)mat * p.N_each + r] = ha;
+            p.y[(long long)mat * p.N_each + r + 1] = hb;
+        } else if (EPI == EPI_RESIDUAL) {  // h = x + linear(...), fp16 add like Tensor::EwiseAdd
+            p.y[r] = hadd_ref(p.residual[r], ha);
+            p.y[r + 1] = hadd_ref(p.residual[r + 1], hb);
+        } else if (EPI == EPI_QKV_ROPE) {
+            const int pos = p.pos_ptr ? *p.pos_ptr : 0;
+            if (mat == 2) {                // v: straight into the cache row of this position
+                __half* vo = p.v_out + (long long)pos * p.kv_pitch;
+                vo[r] = ha; vo[r + 1] = hb;
+            } else {                       // q, k: interleaved-pair rotation, fp16 rounding per op
+                const int half_dim = p.head_dim >> 1;
+                const int d2 = (r % p.head_dim) >> 1;
+                const __half c = p.cos_t[(long long)pos * half_dim + d2];
+                const __half s = p.sin_t[(long long)pos * half_dim + d2];
+                const __half o0 = hsub_ref(hmul_ref(ha, c), hmul_ref(hb, s));
+                const __half o1 = hadd_ref(hmul_ref(ha, s), hmul_ref(hb, c));
+                __half* dst = mat == 0 ? p.y : p.k_out + (long long)pos * p.kv_pitch;
+                dst[r] = o0; dst[r + 1] = o1;
+            }
+        } else {                           // EPI_SWIGLU: silu(gate) * up, each rounded to fp16
+            const __half g = p.silu_tab[__half_as_ushort(ha)];
+            p.y[r] = hmul_ref(g, hb);
+        }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Plain GEMV for M rows of x (tl_matmul2d_f16 with M <= 8).
+// x is staged in K-tiles of KT halfs so that M*KT*2 bytes fit a 32 KB shared buffer.
+// ---------------------------------------------------------------------------------------------
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int UNROLL = 8;  // 16-byte chunks per row kept in flight per lane
+
+template <int M>
+__global__ void __launch_bounds__(THREADS) k_gemv(const __half* __restrict__ x, const __half* __restrict__ W,
+                                                  __half* __restrict__ y, int N, int K, long long ldw,
+                                                  long long ldx, long long ldy, int KT) {
+    extern __shared__ uint4 xsm[];  // [M][KT/8]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = (blockIdx.x * WARPS + warp) * 2;
+    const bool has0 = row0 < N, has1 = row0 + 1 < N;
+    const uint4* w0 = reinterpret_cast<const uint4*>(W + (long long)(has0 ? row0 : 0) * ldw);
+    const uint4* w1 = reinterpret_cast<const uint4*>(W + (long long)(has1 ? row0 + 1 : 0) * ldw);
+    float acc0[M], acc1[M];
+#pragma unroll
+    for (int m = 0; m < M; m++) acc0[m] = acc1[m] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += KT) {
+        const int kt8 = (min(KT, K - k0)) >> 3;  // 16-byte chunks in this tile
+        if (k0) __syncthreads();
+        for (int i = threadIdx.x; i < M * kt8; i += THREADS) {
+            int m = i / kt8, c = i - m * kt8;
+            xsm[m * (KT >> 3) + c] = reinterpret_cast<const uint4*>(x + (long long)m * ldx + k0)[c];
+        }
+        __syncthreads();
+        if (has0) {
+            const uint4* a0 = w0 + (k0 >> 3);
+            const uint4* a1 = w1 + (k0 >> 3);
+            for (int c0 = lane; c0 < kt8; c0 += 32 * UNROLL) {
+                uint4 v0[UNROLL], v1[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    int c = c0 + u * 32;
+                    if (c < kt8) { v0[u] = ldg_stream(a0 + c); v1[u] = ldg_stream(a1 + c); }
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    int c = c0 + u * 32;
+                    if (c < kt8) {
+#pragma unroll
+                        for (int m = 0; m < M; m++) {
+                            uint4 xv = xsm[m * (KT >> 3) + c];
+                            acc0[m] = dot8(v0[u], xv, acc0[m]);
+                            acc1[m] = dot8(v1[u], xv, acc1[m]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!has0) return;
+#pragma unroll
+    for (int m = 0; m < M; m++) {
+        float s0 = warp_sum(acc0[m]), s1 = warp_sum(acc1[m]);
+        if (lane == 0) {
+            y[(long long)m * ldy + row0] = __float2half_rn(s0);
+            if (has1) y[(long long)m * ldy + row0 + 1] = __float2half_rn(s1);
+        }
+    }
+}
+
+template <typename Kern, typename... Args>
+int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    TL_CUDA(cudaLaunchKernelEx(&cfg, kern, args...));
+    return TL_OK;
+}
+
+template <int EPI, bool NORM>
+int launch_ring(const RingArgs& a, size_t smem, int grid, cudaStream_t st, bool pdl) {
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        TL_CUDA(cudaFuncSetAttribute(k_gemv_ring<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    return launch_pdl(k_gemv_ring<EPI, NORM>, dim3(grid), dim3(RING_THREADS), smem, st, pdl, a);
+}
+
+}  // namespace
+
+bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw) {
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    return M >= 1 && M <= 8 && N >= 1 && K >= 8 && K % 8 == 0 && ldw % 8 == 0 && al16(x) && al16(W);
+}
+
+int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
+                long long ldx, long long ldy, cudaStream_t st) {
+    TL_REQUIRE(gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0, "gemv: unsupported shape or alignment");
+    if (M == 1 && ldw == K && N % 2 == 0 && K <= 16384) {  // the decode kernel, plain store epilogue
+        FusedGemv f{};
+        f.x = x; f.W[0] = W; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = y; f.pdl = false;
+        return launch_fused_gemv(f, st);
+    }
+    int KT = 16384 / M;                 // halfs per tile so that M*KT*2 <= 32 KB
+    KT &= ~255;
+    if (KT > K) KT = (K + 7) & ~7;
+    size_t smem = (size_t)M * KT * sizeof(__half);
+    dim3 grid((unsigned)ceil_div(ceil_div(N, 2), WARPS)), block(THREADS);
+#define TL_GEMV_CASE(MM) \
+    case MM: k_gemv<MM><<<grid, block, smem, st>>>(x, W, y, N, K, ldw, ldx, ldy, KT); break;
+    switch (M) {
+        TL_GEMV_CASE(1) TL_GEMV_CASE(2) TL_GEMV_CASE(3) TL_GEMV_CASE(4)
+        TL_GEMV_CASE(5) TL_GEMV_CASE(6) TL_GEMV_CASE(7) TL_GEMV_CASE(8)
+    }
+#undef TL_GEMV_CASE
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
+int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
+    auto al16 = [](const void* v) { return (reinterpret_cast<uintptr_t>(v) & 15) == 0; };
+    TL_REQUIRE(q.K >= 8 && q.K % 8 == 0 && q.K <= 16384, "fused gemv: K=%d must be a multiple of 8, <= 16384", q.K);
+    TL_REQUIRE(q.N_each > 0 && q.N_each % 2 == 0, "fused gemv: N must be even");
+    TL_REQUIRE(al16(q.x) && al16(q.W[0]) && (!q.norm_w || al16(q.norm_w)), "fused gemv: 16-byte alignment required");
+    for (int i = 1; i < q.n_mats; i++) TL_REQUIRE(al16(q.W[i]), "fused gemv: 16-byte alignment required");
+    RingArgs a{};
+    a.x = q.x; a.norm_w = q.norm_w; a.eps = q.eps;
+    a.W0 = q.W[0]; a.W1 = q.n_mats > 1 ? q.W[1] : nullptr; a.W2 = q.n_mats > 2 ? q.W[2] : nullptr;
+    a.N_each = q.N_each; a.K = q.K;
+    a.y = q.y; a.residual = q.residual;
+    a.k_out = q.k_out; a.v_out = q.v_out; a.cos_t = q.cos_row; a.sin_t = q.sin_row; a.head_dim = q.head_dim;
+    a.pos_ptr = q.pos_ptr; a.kv_pitch = q.kv_pitch;
+    a.silu_tab = tables().silu_float_tab;
+    a.status = device_status_word();
+    if (q.epilogue == EPI_SWIGLU) {
+        TL_REQUIRE(q.n_mats == 2, "swiglu epilogue needs w1 and w3");
+        a.total_units = q.N_each;
+    } else {
+        if (q.epilogue == EPI_QKV_ROPE)
+            TL_REQUIRE(q.n_mats == 3 && q.head_dim % 2 == 0 && q.N_each % q.head_dim == 0, "qkv epilogue: bad shape");
+        if (q.epilogue == EPI_RESIDUAL) TL_REQUIRE(q.n_mats == 1 && q.residual, "residual epilogue: one matrix and a residual");
+        a.total_units = q.n_mats * q.N_each / 2;
+    }
+    // one persistent CTA per SM; small problems get one CTA per stage-full of units
+    const int grid = std::max(1, std::min(sm_count(), (a.total_units + CONSUMERS - 1) / CONSUMERS));
+    const size_t smem = (size_t)NSTAGES * STAGE_BYTES + (((size_t)q.K * 2 + 127) & ~(size_t)127) +
+                        2 * NSTAGES * sizeof(uint64_t) + CONSUMERS * sizeof(float) + 64;
+    const bool norm = q.norm_w != nullptr;
+#define TL_FUSED(E) (norm ? launch_ring<E, true>(a, smem, grid, st, q.pdl) : launch_ring<E, false>(a, smem, grid, st, q.pdl))
+    switch (q.epilogue) {
+        case EPI_STORE: return TL_FUSED(EPI_STORE);
+        case EPI_RESIDUAL: return TL_FUSED(EPI_RESIDUAL);
+        case EPI_QKV_ROPE: return TL_FUSED(EPI_QKV_ROPE);
+        case EPI_SWIGLU: return TL_FUSED(EPI_SWIGLU);
+        default: return set_error(TL_ERR_INVALID_ARGUMENT, "fused gemv: unknown epilogue %d", q.epilogue);
+    }
+#undef TL_FUSED
+}
+
+}  // namespace tlb

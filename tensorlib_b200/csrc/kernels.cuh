@@ -1,0 +1,109 @@
+// Internal launcher interface between the C ABI (api.cu), the Llama2 host plumbing (engine.cu)
+// and the kernel files. Every launcher only enqueues on `st` and returns a tl_status.
+#pragma once
+
+#include "common.cuh"
+
+namespace tlb {
+
+// ---- runtime.cu: lookup tables computed on the host with the reference's own formulas ---------
+struct Tables {
+    const __half* exp_tab;         // [65536] half(exp((double)float(h)))        softmax.cpp:22
+    const __half* silu_float_tab;  // [65536] SiLU through float                 CPU.cpp:220-222
+    const __half* silu_half_tab;   // [65536] SiLU fp16 route as shipped         CPU.cpp:216-219
+};
+const Tables& tables();
+// int32 in device memory, 0 unless a kernel gave up on a bounded wait (then a tl_status code)
+int* device_status_word();
+// cos/sin tables [rows, head_dim/2] for positions [0, rows); grows on demand (sync + alloc).
+int rope_table(int head_dim, int min_rows, const __half** cos_t, const __half** sin_t);
+
+// ---- ops_refmode.cu: reference-order kernels (bit-identical to the reference CPU backend) ----
+// C_b(m,n) = sum_k A_b(m,k) * B_b(n,k), k ascending, fp32 accumulate, one rounding; arbitrary
+// element strides (a_m,a_k / b_n,b_k / c_m; C is contiguous along n) and batch strides.
+struct SeqMatmul {
+    const __half* A; const __half* B; __half* C;
+    int batch, M, N, K;
+    long long a_m, a_k, b_n, b_k, c_m, sA, sB, sC;
+};
+int launch_matmul_seq(const SeqMatmul& p, cudaStream_t st);
+int launch_rmsnorm_seq(__half* out, const __half* in, const __half* w, float eps, int hidden,
+                       int tokens, cudaStream_t st);
+int launch_softmax_seq(__half* out, const __half* in, size_t rows, size_t cols, cudaStream_t st);
+// scores (H,T,S): e = e / half(sqrt(head_dim)); if T > 1: e += (s > pos + t ? -inf : 0)
+int launch_scale_mask(__half* scores, int H, int T, int S, int pos, int head_dim, cudaStream_t st);
+
+// ---- elementwise / gather / argmax (same in both numerics) ------------------------------------
+int launch_rope(const __half* in, __half* out, int start_pos, int rows_bt, int T, int n_heads,
+                int head_dim, const __half* cos_t, const __half* sin_t, cudaStream_t st);
+int launch_silu(__half* out, const __half* in, size_t n, int via_float, cudaStream_t st);
+int launch_binary(__half* out, const __half* a, const __half* b, size_t n, int op, cudaStream_t st);
+int launch_div_scalar(__half* out, const __half* a, __half scalar, size_t n, cudaStream_t st);
+int launch_argmax(int* out_idx, const __half* in, size_t rows, size_t cols, cudaStream_t st);
+int launch_embedding(__half* out, const __half* table, const int* tokens, int n_tokens, int dim,
+                     int vocab, cudaStream_t st);
+// rows of `dim` halfs: dst[(dst_row0 + r) * dst_pitch ...] = src[r * dim ...]
+int launch_copy_rows(__half* dst, const __half* src, int rows, int dim, long long dst_pitch,
+                     cudaStream_t st);
+
+// ---- gemv.cu: the decode path (M = 1..8), fast numerics ---------------------------------------
+// y[m, n] = sum_k x[m, k] W[n, k]; requires K % 8 == 0 and 16-byte aligned rows.
+bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw);
+int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
+                long long ldx, long long ldy, cudaStream_t st);
+
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
+struct FusedGemv {
+    // input vector (M = 1) and optional RMSNorm prologue
+    const __half* x;            // [K]
+    const __half* norm_w;       // [K] or nullptr: no norm
+    float eps;
+    // up to three weight matrices [N_each, K] sharing x (wq|wk|wv, w1|w3, or a single one)
+    const __half* W[3];
+    int n_mats, N_each, K;
+    int epilogue;
+    // EPI_STORE / EPI_RESIDUAL: y[n] (+ residual[n])
+    __half* y; const __half* residual;
+    // EPI_QKV_ROPE: q -> y, k -> k_out, v -> v_out (rows of the caches at the current position)
+    __half* k_out; __half* v_out; const __half* cos_row; const __half* sin_row; int head_dim;
+    // position-dependent pointers when replayed from a CUDA graph: if pos_ptr != nullptr the
+    // kernel adds (*pos_ptr) * kv_pitch to k_out / v_out and (*pos_ptr) * head_dim/2 to cos/sin
+    const int* pos_ptr; long long kv_pitch;
+    bool pdl;                   // launch with programmatic stream serialization
+};
+int launch_fused_gemv(const FusedGemv& p, cudaStream_t st);
+
+// ---- attn.cu: attention, fast numerics -----------------------------------------------------------
+struct DecodeAttn {
+    const __half* q;        // [H, hd]
+    const __half* k_cache;  // [S_max, H, hd]
+    const __half* v_cache;
+    __half* out;            // [H, hd]
+    float* scratch;         // [H, splits, hd + 2] fp32 partials
+    unsigned int* counters; // [H] zero before the first launch; the kernel re-zeroes them
+    int H, head_dim, seq_len /* positions 0..seq_len-1 are attended */, splits;
+    const int* pos_ptr;     // if set: seq_len = *pos_ptr + 1
+    long long kv_pitch;     // elements between consecutive positions (H*hd of this rank)
+    bool pdl;
+};
+int launch_decode_attn(const DecodeAttn& p, cudaStream_t st);
+// causal softmax over materialised scores (H,T,S) with scale, fp32 internals, in place
+int launch_softmax_causal_fast(__half* scores, int H, int T, int S, int pos, float scale,
+                               cudaStream_t st);
+int launch_rmsnorm_fast(__half* out, const __half* in, const __half* w, float eps, int hidden,
+                        int tokens, cudaStream_t st);
+int launch_softmax_fast(__half* out, const __half* in, size_t rows, size_t cols, cudaStream_t st);
+// out[i] = silu(gate[i]) * up[i] (fp32 internals); residual add
+int launch_swiglu_fast(__half* out, const __half* gate, const __half* up, size_t n, cudaStream_t st);
+// vt[h, d, s] = v[s, h, d] for s in [0,S)
+int launch_transpose_v(__half* vt, const __half* v, int S, int H, int hd, long long v_pitch,
+                       long long vt_pitch_s, cudaStream_t st);
+
+// ---- hgemm_sm100.cu: prefill HGEMM on tcgen05 / TMEM / TMA -----------------------------------------
+bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K,
+                     size_t lda, size_t ldb, size_t ldc);
+int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, int N, int K,
+                 long long lda, long long ldb, long long ldc, long long sA, long long sB,
+                 long long sC, cudaStream_t st);
+
+}  // namespace tlb
