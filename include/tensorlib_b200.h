@@ -147,6 +147,21 @@ TL_API int tl_rmsnorm_qkv_rope_f16(const tl_half* x, const tl_half* norm_w, floa
 TL_API int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
                        float* scratch, unsigned int* counters, int n_heads, int head_dim, int seq_len,
                        int splits, tl_stream stream);
+/* tl_attn_decode_f16 for callers that cannot allocate device memory (inside a stream capture,
+ * under a fixed memory budget set by an embedding application, or in a serving loop that bans
+ * allocator calls after start-up). No counterpart in the reference, which allocates freely.
+ * The scratch and the counters live in a fixed array inside the library image (about 0.5 MB of
+ * device memory per GPU that loads the library, held until exit), so the call performs no
+ * cudaMalloc / cudaFree and needs no buffers beyond its inputs and output.
+ * Limits: n_heads <= 128 and n_heads*splits*(head_dim+2) <= 131072; larger requests are rejected
+ * with TL_ERR_INVALID_ARGUMENT (use tl_attn_decode_f16 with caller-owned scratch instead).
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress); make
+ * that first call before starting any stream capture. All calls share the one array: the entry
+ * point clears the counters it needs on `stream` before launching, but two calls that overlap
+ * on the GPU (different streams, no ordering between them) race on it. */
+TL_API int tl_attn_decode_f16_noalloc(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache,
+                                      tl_half* out, int n_heads, int head_dim, int seq_len, int splits,
+                                      tl_stream stream);
 /* y[n] = residual[n] + sum_k x[k] W[n,k]  (wo / w2 GEMV + EwiseAdd, Transformer.cpp:111+:169,
  * :143+:175). y may alias residual. */
 TL_API int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,

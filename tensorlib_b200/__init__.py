@@ -77,6 +77,7 @@ _SIGS = {
     "tl_llama2_tensor": [_vp, C.c_char_p, _int, C.POINTER(_vp), C.POINTER(_int), C.POINTER(_int)],
     "tl_rmsnorm_qkv_rope_f16": [_vp, _vp, C.c_float] + [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16": [_vp] * 6 + [_int, _int, _int, _int, _vp],
+    "tl_attn_decode_f16_noalloc": [_vp] * 4 + [_int, _int, _int, _int, _vp],
     "tl_gemv_residual_f16": [_vp, _vp, _vp, _vp, _int, _int, _vp],
     "tl_rmsnorm_gateup_swiglu_f16": [_vp, _vp, C.c_float, _vp, _vp, _vp, _int, _int, _vp],
 }

@@ -7,6 +7,8 @@
 // online-softmax state (max, sum, acc[hd]) in fp32 for its slice of the sequence, writes it to a
 // scratch slot, and the last CTA to finish a head merges the slots. HBM-bound on the KV bytes:
 // 2 * S * H * hd * 2 bytes per call.
+#include <mutex>
+
 #include "kernels.cuh"
 
 namespace tlb {
@@ -247,6 +249,76 @@ int launch_decode_attn(const DecodeAttn& q, cudaStream_t st) {
     TL_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn, a));
     return TL_OK;
 }
+
+}  // namespace tlb
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need attention: code
+// running inside a CUDA-graph capture, a plugin that was handed a fixed memory budget by its
+// embedding application, or a latency-critical serving loop that forbids allocator calls after
+// start-up. tl_attn_decode_f16 asks such a caller for a scratch buffer and a counter array it may
+// have no way to provide. This variant keeps both in a fixed array that is part of the loaded
+// library image instead: every GPU that loads the library holds NOALLOC_BYTES (about 0.5 MB) of
+// device memory for it until the process exits.
+//
+// The array's name is only a host-side handle in host code; the device address is looked up with
+// cudaGetSymbolAddress once per device (on the first call made while that device is current) and
+// handed to the kernel like any other pointer.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t NOALLOC_MAX_HEADS = 128;
+constexpr size_t NOALLOC_MAX_PARTIAL_FLOATS = 128 * 1024;  // n_heads * splits * (head_dim + 2) at most
+constexpr size_t NOALLOC_COUNTER_BYTES = NOALLOC_MAX_HEADS * sizeof(unsigned int);
+constexpr size_t NOALLOC_BYTES = NOALLOC_COUNTER_BYTES + NOALLOC_MAX_PARTIAL_FLOATS * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mu;
+}  // namespace
+
+extern "C" int tl_attn_decode_f16_noalloc(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache,
+                                          tl_half* out, int n_heads, int head_dim, int seq_len, int splits,
+                                          tl_stream stream) {
+    using namespace tlb;
+    TL_CHECK_INIT();
+    TL_REQUIRE(q && k_cache && v_cache && out, "null pointer");
+    TL_REQUIRE(n_heads > 0 && head_dim > 0 && seq_len > 0 && splits > 0, "bad shape");
+    TL_REQUIRE((size_t)n_heads <= NOALLOC_MAX_HEADS,
+               "tl_attn_decode_f16_noalloc: n_heads=%d exceeds the built-in scratch (max %zu heads); "
+               "use tl_attn_decode_f16 with your own scratch", n_heads, NOALLOC_MAX_HEADS);
+    TL_REQUIRE((size_t)n_heads * splits * (head_dim + 2) <= NOALLOC_MAX_PARTIAL_FLOATS,
+               "tl_attn_decode_f16_noalloc: n_heads*splits*(head_dim+2)=%zu floats exceeds the built-in scratch "
+               "(max %zu); use fewer splits or tl_attn_decode_f16 with your own scratch",
+               (size_t)n_heads * splits * (head_dim + 2), NOALLOC_MAX_PARTIAL_FLOATS);
+    int dev = -1;
+    TL_CUDA(cudaGetDevice(&dev));
+    TL_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "device index %d out of range", dev);
+    unsigned char* base;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {  // first call on this device: resolve the symbol (not capturable)
+            unsigned char* p = nullptr;
+            TL_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch));
+            g_noalloc_ptr[dev] = p;
+        }
+        base = g_noalloc_ptr[dev];
+    }
+    unsigned int* counters = reinterpret_cast<unsigned int*>(base);
+    float* partials = reinterpret_cast<float*>(base + NOALLOC_COUNTER_BYTES);
+    cudaStream_t st = as_stream(stream);
+    // The array keeps whatever the previous call left behind. The per-head arrival counters must
+    // start at zero; the partial-result slots are fully rewritten before they are read.
+    TL_CUDA(cudaMemsetAsync(counters, 0, (size_t)n_heads * sizeof(unsigned int), st));
+    DecodeAttn a{reinterpret_cast<const __half*>(q), reinterpret_cast<const __half*>(k_cache),
+                 reinterpret_cast<const __half*>(v_cache), reinterpret_cast<__half*>(out), partials, counters,
+                 n_heads, head_dim, seq_len, splits, nullptr, (long long)n_heads * head_dim, false};
+    return launch_decode_attn(a, st);
+}
+
+namespace tlb {
 
 int launch_rmsnorm_fast(__half* out, const __half* in, const __half* w, float eps, int hidden,
                         int tokens, cudaStream_t st) {
