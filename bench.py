@@ -220,7 +220,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(local_rank)
     tl.init(local_rank)
     if world > 1:
-        dist.init_process_group("nccl" if args.dist_backend == "nccl" else "gloo", rank=rank, world_size=world)
+        dist.init_process_group("gloo", rank=rank, world_size=world)  # rendezvous only; the data path is the library's own NCCL communicator
     cfg = CFG if args.layers == CFG.n_layers else synth.LlamaConfig(
         dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=args.layers, n_heads=CFG.n_heads,
         vocab_size=CFG.vocab_size, seq_len=CFG.seq_len, shared_classifier=False)
@@ -267,7 +267,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         launches = model.kernel_launches() - launches0
         pos += K
     if world > 1:
-        t = torch.tensor([ms], device="cuda")
+        t = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     value = K / (ms * 1e-3)
@@ -282,7 +282,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ids, t_prefill, t_decode = model.generate(prompt, K + 1)
     e2e_ms = t_decode * 1e3
     if world > 1:
-        t = torch.tensor([e2e_ms], device="cuda")
+        t = torch.tensor([e2e_ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = (len(ids) - 1) / (e2e_ms * 1e-3)
@@ -323,7 +323,6 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--dist-backend", default="nccl")
     ap.add_argument("--layers", type=int, default=CFG.n_layers, help="profiling only: fewer layers of the 7B shape")
     ap.add_argument("--skip-prefill", action="store_true", help="profiling only: decode without a prompt pass")
     args = ap.parse_args()

@@ -220,6 +220,22 @@ TL_API int tl_llama2_weight_bytes(tl_llama2* m, long long* bytes);       /* on t
  * Transformer / TransformerBlock, Transformer.hpp:36-92); layer ignored for the model-level ones. */
 TL_API int tl_llama2_tensor(tl_llama2* m, const char* name, int layer, void** dptr, int* rows, int* cols);
 
+/* ---- tensor parallelism (no counterpart in the reference, which is single-GPU) ---------------
+ * One process per GPU. Rank 0 creates an id, every rank passes the same 128 bytes to tl_tp_init
+ * (any out-of-band channel carries them), then attaches the group to its model shard, which was
+ * created with the same tp_rank / tp_world. wq/wk/wv/w1/w3 and the classifier are split by output
+ * rows, wo/w2 by input columns; the forward sums the partial results of wo and w2 over NVLink
+ * (NCCL allreduce; decode partials travel as fp32 and are rounded once after the sum). */
+TL_API int tl_tp_unique_id(void* out128, int nbytes);
+TL_API int tl_tp_init(const void* unique_id, int nbytes, int rank, int world);
+TL_API int tl_tp_attach(tl_llama2* m);
+TL_API int tl_tp_allreduce_f32(float* buf, size_t n, tl_stream stream);
+TL_API int tl_tp_destroy(void);
+/* Host-only: the block of a [rows, cols] checkpoint tensor that rank `rank` of `world` keeps.
+ * kind 0 = replicated, 1 = split by rows, 2 = split by columns. */
+TL_API int tl_tp_shard(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows,
+                       int* col0, int* ncols);
+
 #ifdef __cplusplus
 }
 #endif

@@ -80,18 +80,16 @@ _SIGS = {
     "tl_attn_decode_f16_noalloc": [_vp] * 4 + [_int, _int, _int, _int, _vp],
     "tl_gemv_residual_f16": [_vp, _vp, _vp, _vp, _int, _int, _vp],
     "tl_rmsnorm_gateup_swiglu_f16": [_vp, _vp, C.c_float, _vp, _vp, _vp, _int, _int, _vp],
-}
-_OTHER_RESTYPE = {"tl_strerror": (C.c_char_p, [_int]), "tl_last_error": (C.c_char_p, []),
-                  "tl_version": (_int, [])}
-# optional groups (present once the corresponding source file is part of the build)
-_OPTIONAL = {
     "tl_tp_unique_id": [_vp, _int],
     "tl_tp_init": [_vp, _int, _int, _int],
     "tl_tp_attach": [_vp],
-    "tl_tp_allreduce_f16": [_vp, _sz, _vp],
+    "tl_tp_allreduce_f32": [_vp, _sz, _vp],
     "tl_tp_destroy": [],
-    "tl_argmax_f16_noalloc": [_vp, _vp, _sz, _sz, _vp],
+    "tl_tp_shard": [_int] * 5 + [C.POINTER(_int)] * 4,
 }
+_OTHER_RESTYPE = {"tl_strerror": (C.c_char_p, [_int]), "tl_last_error": (C.c_char_p, []),
+                  "tl_version": (_int, [])}
+_OPTIONAL = {}
 
 _lib = None
 

@@ -11,11 +11,6 @@
 
 using namespace tlb;
 
-struct tl_llama2 {
-    Llama2Engine* eng;
-    int* pinned;  // [max_seq + 8] staging for token ids
-};
-
 namespace {
 inline const __half* H(const tl_half* p) { return reinterpret_cast<const __half*>(p); }
 inline __half* H(tl_half* p) { return reinterpret_cast<__half*>(p); }

@@ -118,6 +118,12 @@ int Llama2Engine::allocate() {
     allocs_.push_back(d);
     attn_counters_ = static_cast<unsigned int*>(d);
     TL_CUDA(cudaMemset(d, 0, (size_t)H_local_ * sizeof(unsigned int)));
+    TL_CUDA(cudaMalloc(&d, dim * sizeof(float)));
+    allocs_.push_back(d);
+    ao32_ = static_cast<float*>(d);
+    TL_CUDA(cudaMalloc(&d, (size_t)vocab_local_ * sizeof(__half)));
+    allocs_.push_back(d);
+    cls_local_ = static_cast<__half*>(d);
     return ensure_activations(1, 0);
 }
 
@@ -171,32 +177,31 @@ int Llama2Engine::load_payload_host(const __half* payload, bool shared_classifie
     const int r = cfg_.tp_rank;
     shared_classifier_ = shared_classifier;
     const __half* cur = payload;
-    auto rows = [&](__half* dst, const __half* src, size_t row0, size_t nrows, size_t cols) -> int {
-        TL_CUDA(cudaMemcpy(dst, src + row0 * cols, nrows * cols * sizeof(__half), cudaMemcpyHostToDevice));
-        return TL_OK;
-    };
-    auto cols = [&](__half* dst, const __half* src, size_t nrows, size_t ncols_full, size_t col0, size_t ncols) -> int {
-        TL_CUDA(cudaMemcpy2D(dst, ncols * sizeof(__half), src + col0, ncols_full * sizeof(__half),
-                             ncols * sizeof(__half), nrows, cudaMemcpyHostToDevice));
+    // copy this rank's block of a [nrows_full, ncols_full] checkpoint tensor (kind: see shard_block)
+    auto put = [&](__half* dst, const __half* src, int kind, size_t nrows_full, size_t ncols_full) -> int {
+        int r0, nr, c0, nc;
+        TL_PROPAGATE(shard_block(kind, (int)nrows_full, (int)ncols_full, r, cfg_.tp_world, &r0, &nr, &c0, &nc));
+        TL_CUDA(cudaMemcpy2D(dst, (size_t)nc * sizeof(__half), src + (size_t)r0 * ncols_full + c0,
+                             ncols_full * sizeof(__half), (size_t)nc * sizeof(__half), nr, cudaMemcpyHostToDevice));
         return TL_OK;
     };
     const __half* emb_host = cur;
-    TL_PROPAGATE(rows(emb_, cur, 0, V, dim)); cur += V * dim;
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].attn_norm, cur, 0, 1, dim)); cur += dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].wq, cur, (size_t)r * dim_local_, dim_local_, dim)); cur += dim * dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].wk, cur, (size_t)r * dim_local_, dim_local_, dim)); cur += dim * dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].wv, cur, (size_t)r * dim_local_, dim_local_, dim)); cur += dim * dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(cols(layers_[l].wo, cur, dim, dim, (size_t)r * dim_local_, dim_local_)); cur += dim * dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].ffn_norm, cur, 0, 1, dim)); cur += dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].w1, cur, (size_t)r * hidden_local_, hidden_local_, dim)); cur += hid * dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(cols(layers_[l].w2, cur, dim, hid, (size_t)r * hidden_local_, hidden_local_)); cur += hid * dim; }
-    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(rows(layers_[l].w3, cur, (size_t)r * hidden_local_, hidden_local_, dim)); cur += hid * dim; }
-    TL_PROPAGATE(rows(final_norm_, cur, 0, 1, dim)); cur += dim;
+    TL_PROPAGATE(put(emb_, cur, 0, V, dim)); cur += V * dim;
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].attn_norm, cur, 0, 1, dim)); cur += dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wq, cur, 1, dim, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wk, cur, 1, dim, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wv, cur, 1, dim, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wo, cur, 2, dim, dim)); cur += dim * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].ffn_norm, cur, 0, 1, dim)); cur += dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].w1, cur, 1, hid, dim)); cur += hid * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].w2, cur, 2, dim, hid)); cur += hid * dim; }
+    for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].w3, cur, 1, hid, dim)); cur += hid * dim; }
+    TL_PROPAGATE(put(final_norm_, cur, 0, 1, dim)); cur += dim;
     if (shared_classifier) {
-        TL_PROPAGATE(rows(wcls_, emb_host, (size_t)r * vocab_local_, vocab_local_, dim));
+        TL_PROPAGATE(put(wcls_, emb_host, 1, V, dim));
     } else {
         cur += (size_t)cfg_.max_seq_len * hd_;  // RoPE values the reference skips (main.cpp:175-177)
-        TL_PROPAGATE(rows(wcls_, cur, (size_t)r * vocab_local_, vocab_local_, dim));
+        TL_PROPAGATE(put(wcls_, cur, 1, V, dim));
     }
     return TL_OK;
 }
@@ -233,6 +238,21 @@ int Llama2Engine::init_random(uint64_t seed, float std) {
         TL_PROPAGATE(fill(w.w3, (size_t)hidden_local_ * dim));
     }
     TL_CUDA(cudaDeviceSynchronize());
+    return TL_OK;
+}
+
+int shard_block(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows, int* col0, int* ncols) {
+    TL_REQUIRE(row0 && nrows && col0 && ncols && world >= 1 && rank >= 0 && rank < world, "bad argument");
+    *row0 = 0; *nrows = rows; *col0 = 0; *ncols = cols;
+    if (kind == 1) {
+        TL_REQUIRE(rows % world == 0, "%d rows do not divide by %d ranks", rows, world);
+        *nrows = rows / world; *row0 = rank * *nrows;
+    } else if (kind == 2) {
+        TL_REQUIRE(cols % world == 0, "%d columns do not divide by %d ranks", cols, world);
+        *ncols = cols / world; *col0 = rank * *ncols;
+    } else {
+        TL_REQUIRE(kind == 0, "unknown shard kind %d", kind);
+    }
     return TL_OK;
 }
 
@@ -395,8 +415,8 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
         return linear(xn_ + (size_t)t0 * dim, cls, logits_ + (size_t)t0 * cfg_.vocab_size, tn, cfg_.vocab_size, dim, st);
     // vocabulary-split classifier: local slice, then gather the slices of every rank
     for (int t = t0; t < t0 + tn; t++) {
-        TL_PROPAGATE(linear(xn_ + (size_t)t * dim, cls, u_, 1, vocab_local_, dim, st));
-        TL_PROPAGATE(coll_->allgather_f16(u_, logits_ + (size_t)t * cfg_.vocab_size, vocab_local_, st));
+        TL_PROPAGATE(linear(xn_ + (size_t)t * dim, cls, cls_local_, 1, vocab_local_, dim, st));
+        TL_PROPAGATE(coll_->allgather_f16(cls_local_, logits_ + (size_t)t * cfg_.vocab_size, vocab_local_, st));
     }
     return TL_OK;
 }
@@ -427,10 +447,10 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
         FusedGemv o{};
         o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
         if (coll_) {
-            o.epilogue = EPI_STORE; o.y = ao_;
+            o.epilogue = EPI_STORE_F32; o.y32 = ao32_;
             TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
-            TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, dim, st)); n++;
-            TL_PROPAGATE(launch_binary(h_, x_, ao_, dim, 0, st)); n++;
+            TL_PROPAGATE(coll_->allreduce_sum_f32(ao32_, dim, st)); n++;
+            TL_PROPAGATE(launch_residual_add_f32(h_, x_, ao32_, dim, st)); n++;
         } else {
             o.epilogue = EPI_RESIDUAL; o.y = h_; o.residual = x_;
             TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
@@ -445,10 +465,10 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
         FusedGemv d{};
         d.x = g_; d.W[0] = w.w2; d.n_mats = 1; d.N_each = dim; d.K = hl; d.pdl = pdl;
         if (coll_) {
-            d.epilogue = EPI_STORE; d.y = ao_;
+            d.epilogue = EPI_STORE_F32; d.y32 = ao32_;
             TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
-            TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, dim, st)); n++;
-            TL_PROPAGATE(launch_binary(x_, h_, ao_, dim, 0, st)); n++;
+            TL_PROPAGATE(coll_->allreduce_sum_f32(ao32_, dim, st)); n++;
+            TL_PROPAGATE(launch_residual_add_f32(x_, h_, ao32_, dim, st)); n++;
         } else {
             d.epilogue = EPI_RESIDUAL; d.y = x_; d.residual = h_;
             TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
@@ -459,9 +479,9 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
     c.W[0] = (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_;
     c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_STORE; c.pdl = pdl;
     if (coll_) {
-        c.y = u_;
+        c.y = cls_local_;
         TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
-        TL_PROPAGATE(coll_->allgather_f16(u_, logits_, vocab_local_, st)); n++;
+        TL_PROPAGATE(coll_->allgather_f16(cls_local_, logits_, vocab_local_, st)); n++;
     } else {
         c.y = logits_;
         TL_PROPAGATE(launch_fused_gemv(c, st)); n++;

@@ -19,6 +19,7 @@ struct LayerWeights {
 struct Collective {
     virtual ~Collective() = default;
     virtual int allreduce_sum_f16(__half* buf, size_t n, cudaStream_t st) = 0;
+    virtual int allreduce_sum_f32(float* buf, size_t n, cudaStream_t st) = 0;
     virtual int allgather_f16(const __half* send, __half* recv, size_t n_per_rank, cudaStream_t st) = 0;
     virtual bool graph_capturable() const = 0;
 };
@@ -76,6 +77,8 @@ private:
            *scores_ = nullptr, *probs_ = nullptr, *vt_ = nullptr;
     std::vector<void*> act_allocs_;
     float* attn_scratch_ = nullptr;
+    float* ao32_ = nullptr;  // [dim] fp32 partial sums of the K-split matmuls (tensor parallel decode)
+    __half* cls_local_ = nullptr;  // [vocab/world] this rank's slice of the logits before the gather
     unsigned int* attn_counters_ = nullptr;
     int attn_splits_ = 1;
     int *d_tokens_ = nullptr, *d_next_ = nullptr, *d_pos_ = nullptr, *d_generated_ = nullptr;
@@ -87,4 +90,14 @@ private:
     Collective* coll_ = nullptr;
 };
 
+// Which block of a [rows, cols] checkpoint tensor rank `rank` of `world` keeps.
+// kind: 0 replicated, 1 split by rows (wq, wk, wv, w1, w3, classifier), 2 split by columns (wo, w2).
+int shard_block(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows, int* col0, int* ncols);
+
 }  // namespace tlb
+
+// the opaque handle of the C ABI
+struct tl_llama2 {
+    tlb::Llama2Engine* eng;
+    int* pinned;  // [max_seq + 8] staging for token ids
+};

@@ -119,7 +119,7 @@ struct RingArgs {
     const __half* x; const __half* norm_w; float eps;
     const __half* W0; const __half* W1; const __half* W2;
     int N_each, K, total_units;   // a unit = the two weight rows one consumer warp owns
-    __half* y; const __half* residual;
+    __half* y; const __half* residual; float* y32;
     __half* k_out; __half* v_out; const __half* cos_t; const __half* sin_t; int head_dim;
     const int* pos_ptr; long long kv_pitch;
     const __half* silu_tab;
@@ -279,6 +279,9 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         if (EPI == EPI_STORE) {
             p.y[(long long)mat * p.N_each + r] = ha;
             p.y[(long long)mat * p.N_each + r + 1] = hb;
+        } else if (EPI == EPI_STORE_F32) {
+            p.y32[(long long)mat * p.N_each + r] = sa;
+            p.y32[(long long)mat * p.N_each + r + 1] = sb;
         } else if (EPI == EPI_RESIDUAL) {  // h = x + linear(...), fp16 add like Tensor::EwiseAdd
             p.y[r] = hadd_ref(p.residual[r], ha);
             p.y[r + 1] = hadd_ref(p.residual[r + 1], hb);
@@ -438,7 +441,7 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     a.x = q.x; a.norm_w = q.norm_w; a.eps = q.eps;
     a.W0 = q.W[0]; a.W1 = q.n_mats > 1 ? q.W[1] : nullptr; a.W2 = q.n_mats > 2 ? q.W[2] : nullptr;
     a.N_each = q.N_each; a.K = q.K;
-    a.y = q.y; a.residual = q.residual;
+    a.y = q.y; a.residual = q.residual; a.y32 = q.y32;
     a.k_out = q.k_out; a.v_out = q.v_out; a.cos_t = q.cos_row; a.sin_t = q.sin_row; a.head_dim = q.head_dim;
     a.pos_ptr = q.pos_ptr; a.kv_pitch = q.kv_pitch;
     a.silu_tab = tables().silu_float_tab;
@@ -460,6 +463,7 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
 #define TL_FUSED(E) (norm ? launch_ring<E, true>(a, smem, grid, st, q.pdl) : launch_ring<E, false>(a, smem, grid, st, q.pdl))
     switch (q.epilogue) {
         case EPI_STORE: return TL_FUSED(EPI_STORE);
+        case EPI_STORE_F32: return TL_FUSED(EPI_STORE_F32);
         case EPI_RESIDUAL: return TL_FUSED(EPI_RESIDUAL);
         case EPI_QKV_ROPE: return TL_FUSED(EPI_QKV_ROPE);
         case EPI_SWIGLU: return TL_FUSED(EPI_SWIGLU);

@@ -43,6 +43,8 @@ int launch_argmax(int* out_idx, const __half* in, size_t rows, size_t cols, cuda
 int launch_embedding(__half* out, const __half* table, const int* tokens, int n_tokens, int dim,
                      int vocab, cudaStream_t st);
 // rows of `dim` halfs: dst[(dst_row0 + r) * dst_pitch ...] = src[r * dim ...]
+// out[i] = a[i] + half(sum32[i]) in fp16 (a K-split matmul's reduced sum, then the residual add)
+int launch_residual_add_f32(__half* out, const __half* a, const float* sum32, size_t n, cudaStream_t st);
 int launch_copy_rows(__half* dst, const __half* src, int rows, int dim, long long dst_pitch,
                      cudaStream_t st);
 
@@ -52,7 +54,7 @@ bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, 
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
                 long long ldx, long long ldy, cudaStream_t st);
 
-enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3 };
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3, EPI_STORE_F32 = 4 };
 struct FusedGemv {
     // input vector (M = 1) and optional RMSNorm prologue
     const __half* x;            // [K]
@@ -64,6 +66,7 @@ struct FusedGemv {
     int epilogue;
     // EPI_STORE / EPI_RESIDUAL: y[n] (+ residual[n])
     __half* y; const __half* residual;
+    float* y32;                 // EPI_STORE_F32: unrounded fp32 sums (partial sums of a K-split matmul)
     // EPI_QKV_ROPE: q -> y, k -> k_out, v -> v_out (rows of the caches at the current position)
     __half* k_out; __half* v_out; const __half* cos_row; const __half* sin_row; int head_dim;
     // position-dependent pointers when replayed from a CUDA graph: if pos_ptr != nullptr the

@@ -284,6 +284,17 @@ int launch_embedding(__half* out, const __half* table, const int* tokens, int n_
     return TL_OK;
 }
 
+__global__ void k_residual_add_f32(__half* out, const __half* a, const float* s, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = hadd_ref(a[i], __float2half_rn(s[i]));
+}
+int launch_residual_add_f32(__half* out, const __half* a, const float* sum32, size_t n, cudaStream_t st) {
+    if (n == 0) return TL_OK;
+    k_residual_add_f32<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(out, a, sum32, n);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
 __global__ void k_copy_rows(__half* dst, const __half* src, int dim, long long dst_pitch) {
     for (int j = threadIdx.x; j < dim; j += blockDim.x)
         dst[(long long)blockIdx.x * dst_pitch + j] = src[(size_t)blockIdx.x * dim + j];

@@ -1,0 +1,101 @@
+// Tensor parallelism for the Llama2 forward: one process per GPU, NCCL over NVLink.
+//
+// The reference has no multi-GPU code at all. The split follows the Megatron scheme its export
+// script undoes when it concatenates Meta's shards (script/export.py:444-460): wq/wk/wv/w1/w3 by
+// output rows (heads / hidden slice per rank, no communication after them), wo/w2 by input
+// columns (each rank produces a full-width partial sum -> allreduce), classifier by vocabulary
+// rows (allgather of the logit slices). Decode partial sums travel as fp32 and are rounded to
+// fp16 once after the sum, so a p-GPU run differs from the 1-GPU run only by fp32 summation order.
+#include <nccl.h>
+
+#include <cstring>
+
+#include "engine.cuh"
+
+namespace tlb {
+namespace {
+
+#define TL_NCCL(expr)                                                                         \
+    do {                                                                                      \
+        ncclResult_t _r = (expr);                                                             \
+        if (_r != ncclSuccess)                                                                \
+            return ::tlb::set_error(TL_ERR_COMM, "%s failed: %s (%s:%d)", #expr,              \
+                                    ncclGetErrorString(_r), __FILE__, __LINE__);              \
+    } while (0)
+
+class NcclCollective : public Collective {
+public:
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    int allreduce_sum_f16(__half* buf, size_t n, cudaStream_t st) override {
+        TL_NCCL(ncclAllReduce(buf, buf, n, ncclHalf, ncclSum, comm, st));
+        return TL_OK;
+    }
+    int allreduce_sum_f32(float* buf, size_t n, cudaStream_t st) override {
+        TL_NCCL(ncclAllReduce(buf, buf, n, ncclFloat, ncclSum, comm, st));
+        return TL_OK;
+    }
+    int allgather_f16(const __half* send, __half* recv, size_t n_per_rank, cudaStream_t st) override {
+        TL_NCCL(ncclAllGather(send, recv, n_per_rank, ncclHalf, comm, st));
+        return TL_OK;
+    }
+    bool graph_capturable() const override { return true; }
+};
+
+NcclCollective g_coll;
+
+}  // namespace
+}  // namespace tlb
+
+using namespace tlb;
+
+extern "C" {
+
+int tl_tp_unique_id(void* out, int nbytes) {
+    TL_REQUIRE(out && nbytes >= (int)sizeof(ncclUniqueId), "unique id buffer needs %zu bytes", sizeof(ncclUniqueId));
+    ncclUniqueId id;
+    TL_NCCL(ncclGetUniqueId(&id));
+    memcpy(out, &id, sizeof id);
+    return TL_OK;
+}
+
+int tl_tp_init(const void* unique_id, int nbytes, int rank, int world) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(unique_id && nbytes >= (int)sizeof(ncclUniqueId) && world >= 1 && rank >= 0 && rank < world, "bad argument");
+    TL_REQUIRE(g_coll.comm == nullptr, "tensor-parallel group already initialised");
+    ncclUniqueId id;
+    memcpy(&id, unique_id, sizeof id);
+    TL_NCCL(ncclCommInitRank(&g_coll.comm, world, id, rank));
+    g_coll.rank = rank;
+    g_coll.world = world;
+    return TL_OK;
+}
+
+int tl_tp_attach(tl_llama2* m) {
+    TL_REQUIRE(m && g_coll.comm, "no model or no tensor-parallel group");
+    TL_REQUIRE(m->eng->cfg().tp_world == g_coll.world && m->eng->cfg().tp_rank == g_coll.rank,
+               "model shard (%d of %d) does not match the group (%d of %d)", m->eng->cfg().tp_rank,
+               m->eng->cfg().tp_world, g_coll.rank, g_coll.world);
+    m->eng->set_collective(&g_coll);
+    return TL_OK;
+}
+
+int tl_tp_allreduce_f32(float* buf, size_t n, tl_stream stream) {
+    TL_REQUIRE(g_coll.comm, "no tensor-parallel group");
+    return g_coll.allreduce_sum_f32(buf, n, as_stream(stream));
+}
+
+int tl_tp_destroy(void) {
+    if (g_coll.comm) {
+        ncclCommDestroy(g_coll.comm);
+        g_coll.comm = nullptr;
+    }
+    return TL_OK;
+}
+
+// Host-only view of the sharding rule the loader applies (see shard_block in engine.cu).
+int tl_tp_shard(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows, int* col0, int* ncols) {
+    return shard_block(kind, rows, cols, rank, world, row0, nrows, col0, ncols);
+}
+
+}  // extern "C"
