@@ -310,10 +310,95 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
                                     "sample": f"{done} decode steps of a 1-layer 7B-shaped model with vocab/32 "
                                               "classifier rows (1/32 of a token each), extrapolated x32"}
-        print(json.dumps(line), flush=True)
+    # the compute-bound companion numbers: one 2048-token prefill (all ranks take part)
+    prefill = prefill_2048(model, cfg, world, torch, dist) if cfg.n_layers == CFG.n_layers else None
     model.close()
+    if rank == 0:
+        line["prefill_2048"] = prefill
+        if world == 1:
+            line["matmul_sweep"] = matmul_sweep(tl, torch)
+        print(json.dumps(line), flush=True)
     if world > 1:
+        from tensorlib_b200 import tp
+        tp.destroy()
         dist.destroy_process_group()
+    return
+
+
+def tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def prefill_2048(model, cfg, world, torch, dist, T: int = 2048):
+    """Config 3/4 of the benchmark spec: one 2048-token prompt, batch 1, through
+    tl_llama2_forward (token ids from the host, last-position logits back to the host)."""
+    prompt = synth.prompt_tokens(cfg, SEED + 1, T)
+    model.forward(prompt[:T], 0, all_logits=False)                       # warm-up (allocates score buffers)
+    times = []
+    for _ in range(3):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        model.forward(prompt, 0, all_logits=False)
+        times.append(time.perf_counter() - t0)
+    sec = min(times)
+    if world > 1:
+        t = torch.tensor([sec], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    per_layer = 4 * cfg.dim * cfg.dim + 3 * cfg.dim * cfg.hidden_dim
+    linear = 2.0 * T * cfg.n_layers * per_layer + 2.0 * cfg.vocab_size * cfg.dim      # classifier: last row only
+    attn = 4.0 * T * T * cfg.dim * cfg.n_layers                                       # full T x T, as computed
+    peak, src = tensor_peak()
+    tf = (linear + attn) / sec / 1e12
+    return {"tokens": T, "ms": sec * 1e3, "tokens_per_s": T / sec, "algorithmic_tflop": (linear + attn) / 1e12,
+            "tflops": tf, "tflops_per_gpu": tf / world, "frac_of_tensor_peak": tf / world / peak, "peak_source": src,
+            "note": "attention computed over the full T x T score matrix (no causal skipping is credited); "
+                    "wall clock through tl_llama2_forward including the host round trip"}
+
+
+def matmul_sweep(tl, torch, m_list=(1, 8, 32, 128, 512, 2048),
+                 kn_list=((4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000))):
+    """Config 1: y = x W^T, fp16 in / fp32 accumulate, device-resident, rotating over enough
+    weight copies (>= 512 MB) that no launch finds its weights in L2."""
+    lib = tl.load()
+    hbm, _ = measured_peaks()
+    tpk, _ = tensor_peak()
+    sp = torch.cuda.current_stream().cuda_stream
+    out = []
+    for (K, N) in kn_list:
+        copies = max(2, -(-512 * 2 ** 20 // (N * K * 2)))
+        Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(copies)]
+        for M in m_list:
+            x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+            y = torch.empty(M, N, device="cuda", dtype=torch.float16)
+
+            def run(i):
+                tl.check(lib.tl_matmul2d_f16(x.data_ptr(), Ws[i % copies].data_ptr(), y.data_ptr(), M, N, K,
+                                             tl.FAST, sp), "tl_matmul2d_f16")
+            for i in range(5):
+                run(i)
+            reps = 50
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(reps):
+                run(i)
+            e1.record()
+            torch.cuda.synchronize()
+            sec = e0.elapsed_time(e1) * 1e-3 / reps
+            flops, nbytes = 2.0 * M * N * K, 2.0 * (N * K + M * K + M * N)
+            t_roof = max(nbytes / (hbm * 1e9), flops / (tpk * 1e12))
+            out.append({"M": M, "K": K, "N": N, "us": sec * 1e6, "tflops": flops / sec / 1e12,
+                        "gbs": nbytes / sec / 1e9, "bound": "hbm" if nbytes / (hbm * 1e9) > flops / (tpk * 1e12) else "tensor",
+                        "frac_of_roofline": t_roof / sec})
+        del Ws
+    return out
 
 
 def main():
@@ -325,12 +410,22 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=CFG.n_layers, help="profiling only: fewer layers of the 7B shape")
     ap.add_argument("--skip-prefill", action="store_true", help="profiling only: decode without a prompt pass")
+    ap.add_argument("--sweep-only", default="", help="profiling only: time one matmul point 'M,K,N' and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.sweep_only:  # profiling only: one point of the matmul sweep, e.g. --sweep-only 2048,4096,4096
+        import torch
+
+        import tensorlib_b200 as tl
+        torch.cuda.set_device(0)
+        tl.init(0)
+        M, K, N = (int(v) for v in args.sweep_only.split(","))
+        print(json.dumps({"profiling_only": True, "matmul_sweep": matmul_sweep(tl, torch, (M,), ((K, N),))}), flush=True)
         return
     if args.warmup < 3:
         args.warmup = 3

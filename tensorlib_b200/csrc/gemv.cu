@@ -5,10 +5,10 @@
 // Two kernels:
 //
 //  k_gemv_ring (M = 1, the decode step). One persistent CTA per SM. A producer warp streams the
-//  CTA's weight rows through a 6-stage shared-memory ring with TMA bulk copies
-//  (cp.async.bulk global -> shared, completion on an mbarrier): a stage holds 16 row-chunks of
-//  1024 halfs (32 KB), so ~190 KB per SM are in flight independent of what the consumers do.
-//  Eight consumer warps each own one "unit" of a stage (two weight rows), read it back with
+//  CTA's weight rows through a 3-stage shared-memory ring with TMA bulk copies
+//  (cp.async.bulk global -> shared, completion on an mbarrier): a stage holds 32 row-chunks of
+//  1024 halfs (64 KB), so ~190 KB per SM are in flight independent of what the consumers do.
+//  Sixteen consumer warps each own one "unit" of a stage (two weight rows), read it back with
 //  128-bit shared loads against the activation vector staged once in shared memory, accumulate
 //  in fp32, reduce with xor shuffles and apply the epilogue. HBM-bound; algorithmic bytes =
 //  2*(rows*K) + small vectors.
@@ -101,19 +101,19 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
-__device__ __forceinline__ void consumer_bar_sync() {  // the 8 consumer warps only
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+__device__ __forceinline__ void consumer_bar_sync(int threads) {  // the consumer warps only
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
 // k_gemv_ring
 // ---------------------------------------------------------------------------------------------
-constexpr int CONSUMERS = 8;                       // consumer warps == units per stage
+constexpr int CONSUMERS = 16;                      // consumer warps == units per stage
 constexpr int RING_THREADS = (CONSUMERS + 1) * 32; // + one producer warp
 constexpr int KC = 1024;                           // halfs per row-chunk
 constexpr int CHUNK_BYTES = KC * 2;                // 2 KB
-constexpr int STAGE_BYTES = CONSUMERS * 2 * CHUNK_BYTES;  // 32 KB
-constexpr int NSTAGES = 6;
+constexpr int STAGE_BYTES = CONSUMERS * 2 * CHUNK_BYTES;  // 64 KB
+constexpr int NSTAGES = 3;
 
 struct RingArgs {
     const __half* x; const __half* norm_w; float eps;
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
-        consumer_bar_sync();
+        consumer_bar_sync(CONSUMERS * 32);
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < CONSUMERS; w++) tot += red[w];
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
     } else {
         for (int c = ctid; c < K8; c += CONSUMERS * 32) xs[c] = x4[c];
     }
-    consumer_bar_sync();
+    consumer_bar_sync(CONSUMERS * 32);
 
     bool ok = true;
     int it = 0;
