@@ -1,8 +1,10 @@
 // Llama2 forward plumbing. See engine.cuh.
 #include "engine.cuh"
+#include "decode_mega.cuh"
 
 #include <cmath>
 #include <cstring>
+#include <vector>
 #include <string>
 
 namespace tlb {
@@ -49,6 +51,7 @@ Llama2Engine::~Llama2Engine() { free_all(); }
 
 int Llama2Engine::free_all() {
     if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
+    mega_ready_ = false;
     for (void* p : allocs_) cudaFree(p);
     for (void* p : act_allocs_) cudaFree(p);
     allocs_.clear();
@@ -136,6 +139,7 @@ int Llama2Engine::ensure_activations(int T, int S) {
     if (S > 0 || act_S_ > 0) S = cfg_.max_seq_len;
     TL_CUDA(cudaDeviceSynchronize());
     if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
+    mega_ready_ = false;
     for (void* p : act_allocs_) cudaFree(p);
     act_allocs_.clear();
     const int Tn = std::max(T, act_T_), Sn = std::max(S, act_S_);
@@ -316,6 +320,10 @@ int Llama2Engine::forward(int T, int start_pos, bool all_logits, cudaStream_t st
         // same launch sequence as the graph, position passed through *d_pos_
         TL_CUDA(cudaMemcpyAsync(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice, st));
         TL_CUDA(cudaMemcpyAsync(d_next_, d_tokens_, sizeof(int), cudaMemcpyDeviceToDevice, st));
+        if (!coll_) {
+            TL_PROPAGATE(ensure_mega());
+            return decode_step_mega(st);
+        }
         return decode_step_fast(st, false);
     }
     return forward_fast_prefill(T, start_pos, all_logits, st);
@@ -502,6 +510,7 @@ int Llama2Engine::sample_last(int T, cudaStream_t st) {
 int Llama2Engine::ensure_decode_graph(cudaStream_t st) {
     if (decode_graph_) return TL_OK;
     TL_REQUIRE(cfg_.numerics == TL_NUMERICS_FAST, "the decode graph exists for fast numerics only");
+    if (!coll_) return ensure_mega();  // single GPU decodes with the one-kernel step, no graph
     TL_REQUIRE(!coll_ || coll_->graph_capturable(), "collective is not capturable");
     TL_PROPAGATE(ensure_activations(1, 0));
     cudaStream_t cap = st;
@@ -525,10 +534,92 @@ int Llama2Engine::ensure_decode_graph(cudaStream_t st) {
     return TL_OK;
 }
 
+// Phase list of the one-kernel decode step: the same stages as decode_step_fast, as data.
+int Llama2Engine::ensure_mega() {
+    if (mega_ready_) return TL_OK;
+    TL_PROPAGATE(ensure_activations(1, 0));
+    const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_;
+    std::vector<MegaPhase> ph;
+    auto gemv = [&](int epi, const __half* x, const __half* nw, const __half* W0, const __half* W1, const __half* W2,
+                    int n_mats, int N_each, int K) {
+        MegaPhase p{};
+        p.kind = 0; p.epilogue = epi; p.x = x; p.norm_w = nw; p.W0 = W0; p.W1 = W1; p.W2 = W2;
+        p.N_each = N_each; p.K = K;
+        p.total_units = epi == EPI_SWIGLU ? N_each : n_mats * N_each / 2;
+        return p;
+    };
+    for (int l = 0; l < cfg_.n_layers; l++) {
+        const LayerWeights& w = layers_[l];
+        const __half* xin = l == 0 ? nullptr : x_;   // layer 0 reads the embedding row of the token
+        MegaPhase qkv = gemv(EPI_QKV_ROPE, xin, w.attn_norm, w.wq, w.wk, w.wv, 3, dl, dim);
+        qkv.y = q_; qkv.k_cache = w.cache_k; qkv.v_cache = w.cache_v;
+        ph.push_back(qkv);
+        MegaPhase at{};
+        at.kind = 1; at.x = q_; at.k_cache = w.cache_k; at.v_cache = w.cache_v; at.y = att_;
+        ph.push_back(at);
+        MegaPhase wo = gemv(EPI_RESIDUAL, att_, nullptr, w.wo, nullptr, nullptr, 1, dim, dl);
+        wo.y = h_; wo.residual = xin;
+        ph.push_back(wo);
+        MegaPhase gu = gemv(EPI_SWIGLU, h_, w.ffn_norm, w.w1, w.w3, nullptr, 2, hl, dim);
+        gu.y = g_;
+        ph.push_back(gu);
+        MegaPhase dn = gemv(EPI_RESIDUAL, g_, nullptr, w.w2, nullptr, nullptr, 1, dim, hl);
+        dn.y = x_; dn.residual = h_;
+        ph.push_back(dn);
+    }
+    MegaPhase cls = gemv(EPI_STORE, x_, final_norm_, (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_,
+                         nullptr, nullptr, 1, vocab_local_, dim);
+    cls.y = logits_;
+    ph.push_back(cls);
+    mega_n_phases_ = (int)ph.size();
+    if (!mega_phases_) {
+        TL_CUDA(cudaMalloc(&mega_phases_, ph.size() * sizeof(MegaPhase)));
+        allocs_.push_back(mega_phases_);
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, 256));
+        allocs_.push_back(d);
+        grid_bar_ = static_cast<unsigned int*>(d);
+    }
+    TL_CUDA(cudaMemcpy(mega_phases_, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
+    const int max_k = std::max(std::max(dim, dl), hl);
+    mega_grid_ = sm_count();
+    mega_smem_ = mega_smem_bytes(max_k);
+    mega_x_bytes_ = mega_x_bytes(max_k);
+    TL_REQUIRE(mega_smem_ <= 227 * 1024, "decode step kernel needs %d bytes of shared memory", mega_smem_);
+    mega_splits_ = mega_attn_splits(H_local_, mega_grid_);
+    if (!mega_attn_scratch_) {
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * 16 * (hd_ + 2) * sizeof(float)));
+        allocs_.push_back(d);
+        mega_attn_scratch_ = static_cast<float*>(d);
+    }
+    mega_ready_ = true;
+    return TL_OK;
+}
+
+int Llama2Engine::decode_step_mega(cudaStream_t st) {
+    MegaArgs a{};
+    a.phases = static_cast<const MegaPhase*>(mega_phases_); a.n_phases = mega_n_phases_;
+    a.emb = emb_; a.dim = cfg_.dim; a.vocab = cfg_.vocab_size;
+    a.H = H_local_; a.hd = hd_; a.splits = mega_splits_; a.max_seq = cfg_.max_seq_len; a.kv_pitch = dim_local_;
+    a.attn_scratch = mega_attn_scratch_; a.attn_counters = attn_counters_;
+    a.cos_t = cos_t_; a.sin_t = sin_t_; a.silu_tab = tables().silu_float_tab;
+    a.logits = logits_; a.d_next = d_next_; a.d_pos = d_pos_; a.d_generated = d_generated_;
+    a.grid_bar = grid_bar_; a.status = device_status_word(); a.eps = 1e-5f; a.x_bytes = mega_x_bytes_;
+    launches_ += 1;
+    return launch_decode_mega(a, mega_grid_, mega_smem_, st);
+}
+
 int Llama2Engine::decode_steps(int start_pos, int steps, cudaStream_t st) {
     TL_REQUIRE(steps >= 0 && start_pos >= 0 && start_pos + steps <= cfg_.max_seq_len,
                "decode: positions [%d,%d) exceed max_seq_len=%d", start_pos, start_pos + steps, cfg_.max_seq_len);
     TL_CUDA(cudaMemcpyAsync(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice, st));
+    if (cfg_.numerics == TL_NUMERICS_FAST && !coll_) {
+        // single GPU: the whole step is one persistent kernel
+        TL_PROPAGATE(ensure_mega());
+        for (int i = 0; i < steps; i++) TL_PROPAGATE(decode_step_mega(st));
+        return TL_OK;
+    }
     if (cfg_.numerics == TL_NUMERICS_FAST) {
         TL_PROPAGATE(ensure_decode_graph(st));
         for (int i = 0; i < steps; i++) {

@@ -84,6 +84,15 @@ private:
     int *d_tokens_ = nullptr, *d_next_ = nullptr, *d_pos_ = nullptr, *d_generated_ = nullptr;
     const __half *cos_t_ = nullptr, *sin_t_ = nullptr;
 
+    // one-kernel decode step (single GPU, fast numerics): phase list in device memory
+    int ensure_mega();
+    int decode_step_mega(cudaStream_t st);
+    void* mega_phases_ = nullptr;
+    unsigned int* grid_bar_ = nullptr;
+    int mega_n_phases_ = 0, mega_grid_ = 0, mega_smem_ = 0, mega_splits_ = 1, mega_x_bytes_ = 0;
+    float* mega_attn_scratch_ = nullptr;
+    bool mega_ready_ = false;
+
     cudaGraphExec_t decode_graph_ = nullptr;
     long long launches_ = 0;
     long long decode_step_launches_ = 0;
