@@ -177,6 +177,9 @@ typedef struct tl_llama2_config {
     int numerics;           /* TL_NUMERICS_* */
     int silu_via_float;     /* 1: SiLU as on the reference's CUDA path; 0: its CPU fp16 route */
     int tp_rank, tp_world;  /* tensor-parallel shard of this process; 0,1 = single GPU */
+    int one_kernel_decode;  /* 0: decode step = CUDA graph of fused kernels chained by programmatic
+                               dependent launch (default). 1: single GPU only, the whole step as
+                               one persistent cooperative kernel with grid barriers. */
 } tl_llama2_config;
 
 typedef struct tl_llama2 tl_llama2;
@@ -215,6 +218,13 @@ TL_API int tl_llama2_decode_device(tl_llama2* m, int start_pos, int steps, int* 
 TL_API int tl_llama2_set_next_token(tl_llama2* m, int token);
 TL_API int tl_llama2_kernel_launches(tl_llama2* m, long long* launches); /* kernels enqueued so far */
 TL_API int tl_llama2_weight_bytes(tl_llama2* m, long long* bytes);       /* on this rank */
+/* Tracing aid (the reference only has wall-clock prints, llama2.cpp:35-99): run ONE decode step
+ * at start_pos (token = the id in the device slot) and return device timestamps (ns, %globaltimer)
+ * taken by CTA `cta` for every phase of the one-kernel step: stamps_host[phase][3] = {phase work
+ * starts (grid barrier passed), activation vector staged, phase work done}. Phases per layer:
+ * qkv, attention, wo, gate/up, w2; then the classifier. capacity = entries available. */
+TL_API int tl_llama2_decode_profile(tl_llama2* m, int start_pos, int cta, unsigned long long* stamps_host,
+                                    int capacity, int* n_phases);
 /* Device pointer and local shape of a weight tensor: name in {"tok_embeddings", "attention_norm",
  * "wq", "wk", "wv", "wo", "ffn_norm", "w1", "w2", "w3", "norm", "output"} (the member names of
  * Transformer / TransformerBlock, Transformer.hpp:36-92); layer ignored for the model-level ones. */

@@ -31,7 +31,7 @@ class TLError(RuntimeError):
 class tl_llama2_config(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads",
                                        "vocab_size", "max_seq_len", "numerics", "silu_via_float",
-                                       "tp_rank", "tp_world")]
+                                       "tp_rank", "tp_world", "one_kernel_decode")]
 
 
 # name -> argtypes; every function returns int status unless listed in _OTHER_RESTYPE
@@ -75,6 +75,7 @@ _SIGS = {
     "tl_llama2_kernel_launches": [_vp, C.POINTER(C.c_longlong)],
     "tl_llama2_weight_bytes": [_vp, C.POINTER(C.c_longlong)],
     "tl_llama2_tensor": [_vp, C.c_char_p, _int, C.POINTER(_vp), C.POINTER(_int), C.POINTER(_int)],
+    "tl_llama2_decode_profile": [_vp, _int, _int, _vp, _int, C.POINTER(_int)],
     "tl_rmsnorm_qkv_rope_f16": [_vp, _vp, C.c_float] + [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16": [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16_noalloc": [_vp] * 4 + [_int, _int, _int, _int, _vp],
@@ -308,11 +309,12 @@ def host_rope_table(head_dim: int, rows: int):
 class Llama2:
     """Handle on the native Llama2 model (Transformer<half> + Llama2<half>::generate)."""
 
-    def __init__(self, cfg, numerics: int = FAST, silu_via_float: bool = True, tp_rank: int = 0,
+    def __init__(self, cfg, numerics: int = FAST, silu_via_float: bool = True, one_kernel_decode: bool = False, tp_rank: int = 0,
                  tp_world: int = 1):
         self.cfg = cfg
         self.c = tl_llama2_config(cfg.dim, cfg.hidden_dim, cfg.n_layers, cfg.n_heads, cfg.n_heads,
-                                  cfg.vocab_size, cfg.seq_len, numerics, int(silu_via_float), tp_rank, tp_world)
+                                  cfg.vocab_size, cfg.seq_len, numerics, int(silu_via_float), tp_rank, tp_world,
+                                  int(one_kernel_decode))
         h = _vp()
         check(load().tl_llama2_create(C.byref(self.c), C.byref(h)), "tl_llama2_create")
         self.h = h

@@ -168,10 +168,12 @@ int tl_llama2_create(const tl_llama2_config* cfg, tl_llama2** out) {
     TL_REQUIRE(c.n_heads % c.tp_world == 0 && c.hidden_dim % c.tp_world == 0 && c.vocab_size % c.tp_world == 0,
                "heads, hidden_dim and vocab_size must divide by tp_world");
     TL_REQUIRE(c.tp_world == 1 || c.numerics == TL_NUMERICS_FAST, "tensor parallelism needs fast numerics");
+    TL_REQUIRE(!c.one_kernel_decode || (c.tp_world == 1 && c.numerics == TL_NUMERICS_FAST),
+               "one_kernel_decode needs a single GPU and fast numerics");
     if (c.numerics == TL_NUMERICS_FAST) {
-        TL_REQUIRE(c.dim % 8 == 0 && (c.hidden_dim / c.tp_world) % 8 == 0 && ((c.dim / c.n_heads) * (c.n_heads / c.tp_world)) % 8 == 0,
-                   "fast numerics needs dim, local hidden_dim and local attention width to be multiples of 8");
-        TL_REQUIRE(c.dim <= 16384 && c.hidden_dim / c.tp_world <= 16384, "fast numerics: reduction length above 16384");
+        TL_REQUIRE(c.dim % 16 == 0 && (c.hidden_dim / c.tp_world) % 16 == 0 && ((c.dim / c.n_heads) * (c.n_heads / c.tp_world)) % 16 == 0,
+                   "fast numerics needs dim, local hidden_dim and local attention width to be multiples of 16");
+        TL_REQUIRE(c.dim <= 12288 && c.hidden_dim / c.tp_world <= 12288, "fast numerics: reduction length above 12288");
         TL_REQUIRE(c.dim / c.n_heads <= 256, "fast numerics: head_dim above 256");
     }
     tl_llama2* m = new (std::nothrow) tl_llama2{nullptr, nullptr};
@@ -395,6 +397,13 @@ int tl_rmsnorm_gateup_swiglu_f16(const tl_half* x, const tl_half* norm_w, float 
     a.W[0] = H(w1); a.W[1] = H(w3); a.n_mats = 2; a.N_each = hidden; a.K = dim;
     a.epilogue = EPI_SWIGLU; a.y = H(out); a.pdl = false;
     return launch_fused_gemv(a, as_stream(stream));
+}
+
+int tl_llama2_decode_profile(tl_llama2* m, int start_pos, int cta, unsigned long long* stamps_host, int capacity,
+                             int* n_phases) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m, "null model");
+    return m->eng->decode_profile(start_pos, cta, stamps_host, capacity, n_phases);
 }
 
 int tl_llama2_tensor(tl_llama2* m, const char* name, int layer, void** dptr, int* rows, int* cols) {

@@ -7,9 +7,13 @@
 // online-softmax state (max, sum, acc[hd]) in fp32 for its slice of the sequence, writes it to a
 // scratch slot, and the last CTA to finish a head merges the slots. HBM-bound on the KV bytes:
 // 2 * S * H * hd * 2 bytes per call.
+#include <cooperative_groups.h>
+
 #include <mutex>
 
 #include "kernels.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace tlb {
 
@@ -231,6 +235,156 @@ __global__ void k_transpose_v(__half* vt, const __half* v, int S, int H, int hd,
 }
 
 }  // namespace
+
+// Same attention, splits merged through distributed shared memory: the `splits` CTAs of a head
+// form one thread-block cluster; each leaves its (max, sum, acc) in its own shared memory, and
+// after a cluster barrier the first CTA of the cluster reads its peers' partials over DSMEM and
+// writes the head's output. No scratch buffer, no atomics, no global-memory round trips in the
+// merge, which is most of the kernel's latency at decode-sized contexts.
+namespace {
+constexpr int CL_WARPS = 8;
+constexpr int CL_THREADS = CL_WARPS * 32;
+
+__global__ void __launch_bounds__(CL_THREADS) k_decode_attn_cluster(AttnArgs p) {
+    __shared__ float sm_m[CL_WARPS], sm_l[CL_WARPS];
+    __shared__ float sm_acc[CL_WARPS][MAX_HD];
+    __shared__ float cta_out[MAX_HD + 2];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int h = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hd = p.hd;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int S = p.pos_ptr ? (*p.pos_ptr + 1) : p.seq_len;
+    const int per = (S + p.splits - 1) / p.splits;
+    const int s_begin = split * per, s_end = min(S, s_begin + per);
+
+    float2 qf[HD_ITERS];
+#pragma unroll
+    for (int i = 0; i < HD_ITERS; i++) {
+        int d = 2 * lane + 64 * i;
+        qf[i] = d < hd ? __half22float2(*reinterpret_cast<const __half2*>(p.q + (size_t)h * hd + d))
+                       : make_float2(0.f, 0.f);
+    }
+    float m = -INFINITY, l = 0.f;
+    float2 acc[HD_ITERS];
+#pragma unroll
+    for (int i = 0; i < HD_ITERS; i++) acc[i] = make_float2(0.f, 0.f);
+
+    constexpr int U = 4;
+    for (int s0 = s_begin + warp * U; s0 < s_end; s0 += CL_WARPS * U) {
+        __half2 kv[U][HD_ITERS], vv[U][HD_ITERS];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int s = s0 + u;
+            const size_t base = (size_t)s * p.pitch + (size_t)h * hd;
+#pragma unroll
+            for (int i = 0; i < HD_ITERS; i++) {
+                int d = 2 * lane + 64 * i;
+                bool ok = s < s_end && d < hd;
+                kv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.kc + base + d) : __half2half2(__float2half(0.f));
+                vv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.vc + base + d) : __half2half2(__float2half(0.f));
+            }
+        }
+        float sc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD_ITERS; i++) {
+                float2 kf = __half22float2(kv[u][i]);
+                d = fmaf(qf[i].x, kf.x, d);
+                d = fmaf(qf[i].y, kf.y, d);
+            }
+            sc[u] = d;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (s0 + u < s_end) {
+                const float x = sc[u] * p.scale;
+                const float mn = fmaxf(m, x);
+                const float corr = __expf(m - mn), pe = __expf(x - mn);
+                l = l * corr + pe;
+#pragma unroll
+                for (int i = 0; i < HD_ITERS; i++) {
+                    float2 vf = __half22float2(vv[u][i]);
+                    acc[i].x = fmaf(pe, vf.x, acc[i].x * corr);
+                    acc[i].y = fmaf(pe, vf.y, acc[i].y * corr);
+                }
+                m = mn;
+            }
+        }
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < HD_ITERS; i++) {
+        int d = 2 * lane + 64 * i;
+        if (d < hd) { sm_acc[warp][d] = acc[i].x; sm_acc[warp][d + 1] = acc[i].y; }
+    }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < CL_WARPS; w++) M = fmaxf(M, sm_m[w]);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < CL_WARPS; w++) L += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * __expf(sm_m[w] - M);
+    for (int d = threadIdx.x; d < hd; d += CL_THREADS) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < CL_WARPS; w++)
+            a += sm_m[w] == -INFINITY ? 0.f : sm_acc[w][d] * __expf(sm_m[w] - M);
+        cta_out[2 + d] = a;
+    }
+    if (threadIdx.x == 0) { cta_out[0] = M; cta_out[1] = L; }
+    cluster.sync();   // every split's partial is in its CTA's shared memory
+    if (cluster.block_rank() == 0) {
+        const int n = (int)cluster.num_blocks();
+        float GM = -INFINITY;
+        for (int r = 0; r < n; r++) GM = fmaxf(GM, cluster.map_shared_rank(cta_out, r)[0]);
+        float GL = 0.f;
+        for (int r = 0; r < n; r++) {
+            const float* rem = cluster.map_shared_rank(cta_out, r);
+            if (rem[0] != -INFINITY) GL += rem[1] * __expf(rem[0] - GM);
+        }
+        for (int d = threadIdx.x; d < hd; d += CL_THREADS) {
+            float a = 0.f;
+            for (int r = 0; r < n; r++) {
+                const float* rem = cluster.map_shared_rank(cta_out, r);
+                if (rem[0] != -INFINITY) a += rem[2 + d] * __expf(rem[0] - GM);
+            }
+            p.out[(size_t)h * hd + d] = __float2half_rn(a / GL);
+        }
+    }
+    cluster.sync();   // peers keep their shared memory alive until the reader is done
+}
+}  // namespace
+
+int launch_decode_attn_cluster(const DecodeAttn& q, cudaStream_t st) {
+    TL_REQUIRE(q.head_dim > 0 && q.head_dim <= MAX_HD && q.head_dim % 2 == 0, "decode attention: head_dim %d unsupported", q.head_dim);
+    TL_REQUIRE(q.H > 0 && q.splits >= 1 && q.splits <= 8, "decode attention (cluster): splits must be 1..8");
+    AttnArgs a{q.q, q.k_cache, q.v_cache, q.out, nullptr, nullptr, q.H, q.head_dim, q.seq_len,
+               q.splits, q.pos_ptr, q.kv_pitch, 1.0f / sqrtf((float)q.head_dim)};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(q.H, q.splits);
+    cfg.blockDim = dim3(CL_THREADS);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = q.splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = q.pdl ? 2 : 1;
+    TL_CUDA(cudaLaunchKernelEx(&cfg, k_decode_attn_cluster, a));
+    return TL_OK;
+}
 
 int launch_decode_attn(const DecodeAttn& q, cudaStream_t st) {
     TL_REQUIRE(q.head_dim > 0 && q.head_dim <= MAX_HD && q.head_dim % 2 == 0, "decode attention: head_dim %d unsupported", q.head_dim);

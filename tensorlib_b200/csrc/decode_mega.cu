@@ -109,8 +109,24 @@ constexpr int CONSUMER_THREADS = CONSUMERS * 32;
 constexpr int MEGA_THREADS = CONSUMER_THREADS + 32;   // + one producer warp
 constexpr int KC = 1024;                              // halfs per row-chunk
 constexpr int CHUNK_BYTES = KC * 2;
-constexpr int STAGE_BYTES = CONSUMERS * 2 * CHUNK_BYTES;  // 64 KB
+constexpr int ROW_STRIDE = CHUNK_BYTES + 16;          // +16 B: conflict-free ldmatrix row addresses
+constexpr int STAGE_ROWS = CONSUMERS * 2;
+constexpr int STAGE_BYTES = STAGE_ROWS * ROW_STRIDE;  // 66,048 B
 constexpr int NSTAGES = 3;
+constexpr int STEPS_PER_WARP = KC / 16 / CONSUMERS;   // k16 steps of a chunk each warp multiplies
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                 : "r"(saddr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 constexpr int ATT_GROUPS = 4, ATT_WARPS = 4;          // 4 groups x 4 warps
 constexpr int MAX_HD = 256, HD_ITERS = MAX_HD / 64;
 constexpr int ATT_SMEM_PER_GROUP = (2 * ATT_WARPS + ATT_WARPS * MAX_HD + 4) * 4;
@@ -144,9 +160,10 @@ __device__ __forceinline__ void unit_rows_rt(const MegaPhase& p, int unit, const
 }
 
 struct Ctx {
-    unsigned char* stages; uint4* xs; float* red; uint32_t full0, empty0;
-    int warp, lane, ctid;
+    unsigned char* stages; uint4* xs; float* red; float* partials; uint32_t full0, empty0;
+    int warp, lane, ctid, tile_parity;
     int tok, pos;
+    float rinv;            // 1/rms of the current phase's input (1 when the phase has no RMSNorm)
     int it;                // ring iteration counter of this role
     unsigned int bar_target;
     bool ok;
@@ -154,16 +171,18 @@ struct Ctx {
 
 // Grid-wide barrier among the consumer warps of all CTAs (the producers never join it).
 __device__ __forceinline__ void grid_barrier(const MegaArgs& a, Ctx& c) {
+    // bar.sync orders every consumer thread's stores before thread 0's release-add (cumulative at
+    // gpu scope); the acquire-load that sees the last arrival orders the other CTAs' stores before
+    // everything after the second bar.sync. No return value is needed from the add, so it is a
+    // fire-and-forget reduction rather than an atomic round trip.
     named_bar_sync(1, CONSUMER_THREADS);
     if (c.ctid == 0) {
         c.bar_target += gridDim.x;
-        __threadfence();
-        atomicAdd(a.grid_bar, 1u);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.grid_bar) : "memory");
         bool done = false;
         for (uint32_t i = 0; i < (1u << 24); i++)
             if (ld_acquire_u32(a.grid_bar) >= c.bar_target) { done = true; break; }
         if (!done) atomicExch(a.status, TL_ERR_TIMEOUT);
-        __threadfence();
     }
     named_bar_sync(1, CONSUMER_THREADS);
 }
@@ -174,11 +193,22 @@ __device__ __forceinline__ void stage_x(const MegaArgs& a, const MegaPhase& p, C
     const __half* xsrc = p.x ? p.x : a.emb + (long long)c.tok * a.dim;
     const uint4* x4 = reinterpret_cast<const uint4*>(xsrc);
     if (p.norm_w) {
+        // RMSNorm in one pass: the vector staged is x * w (fp16); the scalar 1/rms is applied to
+        // the finished dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk),
+        // so no second pass over x has to wait for the reduction.
         float ss = 0.f;
+        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
         for (int i = c.ctid; i < K8; i += CONSUMER_THREADS) {
-            uint4 v = __ldcg(x4 + i);
-            c.xs[i] = v;
+            uint4 v = __ldcg(x4 + i), g = nw4[i];
             ss += sumsq8(v);
+            __half2* vh = reinterpret_cast<__half2*>(&v);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float2 vf = __half22float2(vh[j]), gf = __half22float2(gh[j]);
+                vh[j] = __floats2half2_rn(vf.x * gf.x, vf.y * gf.y);
+            }
+            c.xs[i] = v;
         }
         ss = warp_sum(ss);
         if (c.lane == 0) c.red[c.warp] = ss;
@@ -186,23 +216,12 @@ __device__ __forceinline__ void stage_x(const MegaArgs& a, const MegaPhase& p, C
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < CONSUMERS; w++) tot += c.red[w];
-        const float rinv = rsqrtf(tot / (float)p.K + a.eps);
-        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
-        for (int i = c.ctid; i < K8; i += CONSUMER_THREADS) {
-            uint4 v = c.xs[i], g = nw4[i];
-            __half2* vh = reinterpret_cast<__half2*>(&v);
-            const __half2* gh = reinterpret_cast<const __half2*>(&g);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float2 vf = __half22float2(vh[j]), gf = __half22float2(gh[j]);
-                vh[j] = __floats2half2_rn(vf.x * rinv * gf.x, vf.y * rinv * gf.y);
-            }
-            c.xs[i] = v;
-        }
+        c.rinv = rsqrtf(tot / (float)p.K + a.eps);
     } else {
         for (int i = c.ctid; i < K8; i += CONSUMER_THREADS) c.xs[i] = __ldcg(x4 + i);
+        c.rinv = 1.0f;
+        named_bar_sync(1, CONSUMER_THREADS);
     }
-    named_bar_sync(1, CONSUMER_THREADS);
 }
 
 template <int EPI>
@@ -212,39 +231,70 @@ __device__ __forceinline__ void gemv_consume(const MegaArgs& a, const MegaPhase&
     const int n_units = u_end - u_begin;
     const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
     const int nk = (p.K + KC - 1) / KC;
+    // Tensor-core dot products (mma.sync m16n8k16, fp32 accumulate): the 32 rows of a stage are two
+    // m16 tiles, the activation vector is column 0 of B; warp w multiplies k16 steps
+    // [w*STEPS_PER_WARP, +STEPS_PER_WARP) of every chunk for all rows; the per-warp partial row
+    // sums meet in shared memory at the end of a tile and warp 0 finishes the rows.
+    const int lane = c.lane, g = lane >> 2, t = lane & 3;
+    const uint32_t lm_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + (lane >> 4) * 16);
+    const __half* xh = reinterpret_cast<const __half*>(c.xs);
     for (int tile = 0; tile < n_tiles && c.ok; tile++) {
         const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
-        const bool mine = c.warp < units_here;
-        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+        // warp 0 finishes the rows of this tile: fetch what its epilogue needs from L2 now, so the
+        // latency overlaps the multiply instead of following it
+        __half res_a = __float2half_rn(0.f), res_b = res_a;
+        if (EPI == EPI_RESIDUAL && c.warp == 0 && !(lane & 1) && (lane >> 1) < units_here) {
+            const __half *ra, *rb; int mat, r;
+            unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
+            const __half* res = p.residual ? p.residual : a.emb + (long long)c.tok * a.dim;
+            res_a = ldcg_half(res + r);
+            res_b = ldcg_half(res + r + 1);
+        }
         for (int chunk = 0; chunk < nk; chunk++, c.it++) {
             const int s = c.it % NSTAGES, use = c.it / NSTAGES;
             c.ok = mbar_wait(c.full0 + 8 * s, use & 1);
             c.ok = __all_sync(0xffffffffu, c.ok);
             if (!c.ok) break;
-            if (mine) {
-                const int kc8 = min(KC, p.K - chunk * KC) >> 3;
-                const uint4* wa = reinterpret_cast<const uint4*>(c.stages + (size_t)s * STAGE_BYTES + (size_t)(2 * c.warp) * CHUNK_BYTES);
-                const uint4* wb = wa + CHUNK_BYTES / 16;
-                const uint4* xc = c.xs + chunk * (KC / 8);
+            const int steps = min(KC, p.K - chunk * KC) >> 4;
+            const uint32_t sbase = smem_u32(c.stages + (size_t)s * STAGE_BYTES) + lm_off;
 #pragma unroll
-                for (int j = 0; j < KC / 8 / 32; j++) {
-                    const int idx = c.lane + 32 * j;
-                    if (idx < kc8) {
-                        const uint4 xv = xc[idx], va = wa[idx], vb = wb[idx];
-                        if (j & 1) { a1 = dot8(va, xv, a1); b1 = dot8(vb, xv, b1); }
-                        else       { a0 = dot8(va, xv, a0); b0 = dot8(vb, xv, b0); }
-                    }
+            for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
+                const int step = c.warp * STEPS_PER_WARP + kk;
+                if (step < steps) {
+                    uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+                    ldmatrix_x4(sbase + step * 32, a0, a1, a2, a3);
+                    ldmatrix_x4(sbase + 16 * ROW_STRIDE + step * 32, e0, e1, e2, e3);
+                    const __half* xk = xh + chunk * KC + step * 16 + 2 * t;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xk);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xk + 8);
+                    mma_16816(acc0, a0, a1, a2, a3, b0, b1);
+                    mma_16816(acc1, e0, e1, e2, e3, b0, b1);
                 }
             }
             __syncwarp();
-            if (c.lane == 0) mbar_arrive(c.empty0 + 8 * s);
+            if (lane == 0) mbar_arrive(c.empty0 + 8 * s);
         }
-        if (!c.ok || !mine) continue;
-        const float sa = warp_sum(a0 + a1), sb = warp_sum(b0 + b1);
-        if (c.lane != 0) continue;
+        if (!c.ok) break;
+        float* part = c.partials + (c.tile_parity & 1) * (CONSUMERS * STAGE_ROWS);
+        c.tile_parity ^= 1;
+        if (t == 0) {
+            part[c.warp * STAGE_ROWS + g] = acc0[0];
+            part[c.warp * STAGE_ROWS + g + 8] = acc0[2];
+            part[c.warp * STAGE_ROWS + 16 + g] = acc1[0];
+            part[c.warp * STAGE_ROWS + 24 + g] = acc1[2];
+        }
+        named_bar_sync(1, CONSUMER_THREADS);
+        if (c.warp != 0) continue;
+        float rowsum = 0.f;   // lane = row slot of the stage: slots 2u, 2u+1 are the rows of unit u
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; w++) rowsum += part[w * STAGE_ROWS + lane];
+        const float other = __shfl_xor_sync(0xffffffffu, rowsum, 1);
+        if ((lane & 1) || (lane >> 1) >= units_here) continue;
+        const float sa = rowsum * c.rinv, sb = other * c.rinv;
         const __half ha = __float2half_rn(sa), hb = __float2half_rn(sb);
         const __half *ra, *rb; int mat, r;
-        unit_rows<EPI>(p, u_begin + tile * CONSUMERS + c.warp, ra, rb, mat, r);
+        unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
         if (EPI == EPI_STORE) {
             p.y[(long long)mat * p.N_each + r] = ha;
             p.y[(long long)mat * p.N_each + r + 1] = hb;
@@ -252,9 +302,8 @@ __device__ __forceinline__ void gemv_consume(const MegaArgs& a, const MegaPhase&
             p.y32[(long long)mat * p.N_each + r] = sa;
             p.y32[(long long)mat * p.N_each + r + 1] = sb;
         } else if (EPI == EPI_RESIDUAL) {
-            const __half* res = p.residual ? p.residual : a.emb + (long long)c.tok * a.dim;
-            p.y[r] = hadd_ref(ldcg_half(res + r), ha);
-            p.y[r + 1] = hadd_ref(ldcg_half(res + r + 1), hb);
+            p.y[r] = hadd_ref(res_a, ha);
+            p.y[r + 1] = hadd_ref(res_b, hb);
         } else if (EPI == EPI_QKV_ROPE) {
             if (mat == 2) {
                 __half* vo = p.v_cache + (long long)c.pos * a.kv_pitch;
@@ -413,6 +462,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
     c.xs = reinterpret_cast<uint4*>(smem + NSTAGES * STAGE_BYTES);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGES * STAGE_BYTES + a.x_bytes);
     c.red = reinterpret_cast<float*>(bars + 2 * NSTAGES);
+    c.partials = c.red + CONSUMERS;   // [2][CONSUMERS][STAGE_ROWS]
+    c.tile_parity = 0;
     c.full0 = smem_u32(bars);
     c.empty0 = smem_u32(bars + NSTAGES);
     c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31; c.ctid = threadIdx.x;
@@ -433,6 +484,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
         const int lane = c.lane;
         bool ok = true;
         int it = 0;
+        // (An L2 prefetch running ahead of the ring with cp.async.bulk.prefetch.L2 was measured and
+        // dropped: phase times grew by ~50 %, the extra bulk requests compete with the ring's own.)
         for (int ph = 0; ph < a.n_phases && ok; ph++) {
             const MegaPhase& p = a.phases[ph];
             if (p.kind != PH_GEMV) continue;
@@ -458,7 +511,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
                     if (lane == 0) mbar_arrive_expect_tx(c.full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
                     __syncwarp();
                     if (lane < rows_in_tile)
-                        tma_load_1d(smem_u32(c.stages + (size_t)s * STAGE_BYTES + (size_t)lane * CHUNK_BYTES),
+                        tma_load_1d(smem_u32(c.stages + (size_t)s * STAGE_BYTES + (size_t)lane * ROW_STRIDE),
                                     row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), c.full0 + 8 * s, pol);
                 }
             }
@@ -471,14 +524,21 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
     c.tok = __ldcg(a.d_next);
     c.pos = __ldcg(a.d_pos);
     if (c.tok < 0 || c.tok >= a.vocab) c.tok = 0;
+    // optional per-phase timestamps (ns) of one CTA: [phase][0] work start (barrier passed),
+    // [1] activation vector staged, [2] phase work done
+    const bool prof = a.prof != nullptr && blockIdx.x == a.prof_cta && c.ctid == 0;
+    auto now = []() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
     for (int ph = 0; ph < a.n_phases; ph++) {
         const MegaPhase& p = a.phases[ph];
         if (ph > 0) grid_barrier(a, c);
+        if (prof) a.prof[3 * ph] = now();
         if (p.kind == PH_ATTN) {
             attn_phase(a, p, c);
+            if (prof) a.prof[3 * ph + 1] = a.prof[3 * ph + 2] = now();
             continue;
         }
         stage_x(a, p, c);
+        if (prof) a.prof[3 * ph + 1] = now();
         switch (p.epilogue) {
             case EPI_STORE: gemv_consume<EPI_STORE>(a, p, c); break;
             case EPI_STORE_F32: gemv_consume<EPI_STORE_F32>(a, p, c); break;
@@ -486,6 +546,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
             case EPI_QKV_ROPE: gemv_consume<EPI_QKV_ROPE>(a, p, c); break;
             default: gemv_consume<EPI_SWIGLU>(a, p, c); break;
         }
+        if (prof) a.prof[3 * ph + 2] = now();
     }
     if (!c.ok && c.lane == 0) atomicExch(a.status, TL_ERR_TIMEOUT);
     grid_barrier(a, c);
@@ -525,7 +586,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
 int mega_smem_bytes(int max_k) {
     int x_bytes = std::max((max_k * 2 + 127) & ~127, ATT_GROUPS * ATT_SMEM_PER_GROUP);
     x_bytes = (x_bytes + 127) & ~127;
-    return NSTAGES * STAGE_BYTES + x_bytes + 2 * NSTAGES * 8 + CONSUMERS * 4 + 64;
+    return NSTAGES * STAGE_BYTES + x_bytes + 2 * NSTAGES * 8 + CONSUMERS * 4 + 2 * CONSUMERS * STAGE_ROWS * 4 + 64;
 }
 
 int launch_decode_mega(const MegaArgs& args, int grid, int smem, cudaStream_t st) {

@@ -27,6 +27,8 @@ struct MegaArgs {
     const __half* logits; int* d_next; int* d_pos; int* d_generated;
     unsigned int* grid_bar; int* status; float eps;
     int x_bytes;            // shared-memory bytes reserved for the activation vector / attention scratch
+    unsigned long long* prof;  // optional [n_phases][3] globaltimer stamps written by CTA prof_cta
+    int prof_cta;
 };
 
 

@@ -113,8 +113,8 @@ int Llama2Engine::allocate() {
     TL_PROPAGATE(rope_table(hd_, (int)S, &cos_t_, &sin_t_));
     // decode attention: enough CTAs to cover the SMs
     attn_splits_ = 1;
-    while (H_local_ * attn_splits_ < sm_count() && attn_splits_ < 16) attn_splits_ *= 2;
-    TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * attn_splits_ * (hd_ + 2) * sizeof(float)));
+    while (H_local_ * attn_splits_ < sm_count() && attn_splits_ < 8) attn_splits_ *= 2;  // <= 8: one cluster per head
+    TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * 16 * (hd_ + 2) * sizeof(float)));
     allocs_.push_back(d);
     attn_scratch_ = static_cast<float*>(d);
     TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * sizeof(unsigned int)));
@@ -320,7 +320,7 @@ int Llama2Engine::forward(int T, int start_pos, bool all_logits, cudaStream_t st
         // same launch sequence as the graph, position passed through *d_pos_
         TL_CUDA(cudaMemcpyAsync(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice, st));
         TL_CUDA(cudaMemcpyAsync(d_next_, d_tokens_, sizeof(int), cudaMemcpyDeviceToDevice, st));
-        if (!coll_) {
+        if (use_mega()) {
             TL_PROPAGATE(ensure_mega());
             return decode_step_mega(st);
         }
@@ -450,7 +450,7 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
 
         DecodeAttn at{q_, w.cache_k, w.cache_v, att_, attn_scratch_, attn_counters_, H_local_, hd_, 0,
                       attn_splits_, d_pos_, dl, pdl};
-        TL_PROPAGATE(launch_decode_attn(at, st)); n++;
+        TL_PROPAGATE(launch_decode_attn_cluster(at, st)); n++;
 
         FusedGemv o{};
         o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
@@ -510,7 +510,7 @@ int Llama2Engine::sample_last(int T, cudaStream_t st) {
 int Llama2Engine::ensure_decode_graph(cudaStream_t st) {
     if (decode_graph_) return TL_OK;
     TL_REQUIRE(cfg_.numerics == TL_NUMERICS_FAST, "the decode graph exists for fast numerics only");
-    if (!coll_) return ensure_mega();  // single GPU decodes with the one-kernel step, no graph
+    if (use_mega()) return ensure_mega();  // the one-kernel step needs no graph
     TL_REQUIRE(!coll_ || coll_->graph_capturable(), "collective is not capturable");
     TL_PROPAGATE(ensure_activations(1, 0));
     cudaStream_t cap = st;
@@ -597,8 +597,24 @@ int Llama2Engine::ensure_mega() {
     return TL_OK;
 }
 
-int Llama2Engine::decode_step_mega(cudaStream_t st) {
+int Llama2Engine::decode_profile(int start_pos, int cta, unsigned long long* out_host, int capacity, int* n_phases) {
+    TL_REQUIRE(use_mega(), "phase timestamps exist for the one-kernel decode step only (one_kernel_decode = 1)");
+    TL_PROPAGATE(ensure_mega());
+    TL_REQUIRE(out_host && n_phases && capacity >= 3 * mega_n_phases_, "timestamp buffer needs %d entries", 3 * mega_n_phases_);
+    unsigned long long* d = nullptr;
+    TL_CUDA(cudaMalloc(&d, (size_t)3 * mega_n_phases_ * sizeof(unsigned long long)));
+    TL_CUDA(cudaMemcpy(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice));
+    int rc = decode_step_mega(nullptr, d, cta);
+    if (rc == TL_OK && cudaMemcpy(out_host, d, (size_t)3 * mega_n_phases_ * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+        rc = set_error(TL_ERR_CUDA, "timestamp copy failed");
+    cudaFree(d);
+    *n_phases = mega_n_phases_;
+    return rc;
+}
+
+int Llama2Engine::decode_step_mega(cudaStream_t st, unsigned long long* prof, int prof_cta) {
     MegaArgs a{};
+    a.prof = prof; a.prof_cta = prof_cta;
     a.phases = static_cast<const MegaPhase*>(mega_phases_); a.n_phases = mega_n_phases_;
     a.emb = emb_; a.dim = cfg_.dim; a.vocab = cfg_.vocab_size;
     a.H = H_local_; a.hd = hd_; a.splits = mega_splits_; a.max_seq = cfg_.max_seq_len; a.kv_pitch = dim_local_;
@@ -614,7 +630,7 @@ int Llama2Engine::decode_steps(int start_pos, int steps, cudaStream_t st) {
     TL_REQUIRE(steps >= 0 && start_pos >= 0 && start_pos + steps <= cfg_.max_seq_len,
                "decode: positions [%d,%d) exceed max_seq_len=%d", start_pos, start_pos + steps, cfg_.max_seq_len);
     TL_CUDA(cudaMemcpyAsync(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice, st));
-    if (cfg_.numerics == TL_NUMERICS_FAST && !coll_) {
+    if (use_mega()) {
         // single GPU: the whole step is one persistent kernel
         TL_PROPAGATE(ensure_mega());
         for (int i = 0; i < steps; i++) TL_PROPAGATE(decode_step_mega(st));

@@ -53,6 +53,8 @@ public:
     int vocab_local() const { return vocab_local_; }
     void set_collective(Collective* c) { coll_ = c; }
     int tensor(const char* name, int layer, void** dptr, int* rows, int* cols) const;
+    // one decode step with per-phase device timestamps of CTA `cta`: out_host[n_phases][3] in ns
+    int decode_profile(int start_pos, int cta, unsigned long long* out_host, int capacity, int* n_phases);
 
 private:
     int ensure_activations(int T, int S);
@@ -85,8 +87,9 @@ private:
     const __half *cos_t_ = nullptr, *sin_t_ = nullptr;
 
     // one-kernel decode step (single GPU, fast numerics): phase list in device memory
+    bool use_mega() const { return cfg_.one_kernel_decode != 0 && coll_ == nullptr && cfg_.numerics == TL_NUMERICS_FAST; }
     int ensure_mega();
-    int decode_step_mega(cudaStream_t st);
+    int decode_step_mega(cudaStream_t st, unsigned long long* prof = nullptr, int prof_cta = 0);
     void* mega_phases_ = nullptr;
     unsigned int* grid_bar_ = nullptr;
     int mega_n_phases_ = 0, mega_grid_ = 0, mega_smem_ = 0, mega_splits_ = 1, mega_x_bytes_ = 0;

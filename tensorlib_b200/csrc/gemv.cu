@@ -108,12 +108,31 @@ __device__ __forceinline__ void consumer_bar_sync(int threads) {  // the consume
 // ---------------------------------------------------------------------------------------------
 // k_gemv_ring
 // ---------------------------------------------------------------------------------------------
-constexpr int CONSUMERS = 16;                      // consumer warps == units per stage
+constexpr int CONSUMERS = 16;                      // consumer warps; a stage holds 16 units = 32 rows
 constexpr int RING_THREADS = (CONSUMERS + 1) * 32; // + one producer warp
 constexpr int KC = 1024;                           // halfs per row-chunk
 constexpr int CHUNK_BYTES = KC * 2;                // 2 KB
-constexpr int STAGE_BYTES = CONSUMERS * 2 * CHUNK_BYTES;  // 64 KB
+// rows sit 2 KB + 16 B apart so that the 8 row addresses of an ldmatrix phase fall into
+// different banks
+constexpr int ROW_STRIDE = CHUNK_BYTES + 16;
+constexpr int STAGE_ROWS = CONSUMERS * 2;
+constexpr int STAGE_BYTES = STAGE_ROWS * ROW_STRIDE;  // 66,048 B
 constexpr int NSTAGES = 3;
+constexpr int STEPS_PER_WARP = KC / 16 / CONSUMERS;   // k16 steps of a chunk each warp multiplies
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                 : "r"(saddr));
+}
+// D(16x8, fp32) += A(16x16 fp16, row) * B(16x8 fp16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 struct RingArgs {
     const __half* x; const __half* norm_w; float eps;
@@ -152,6 +171,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
     const int K8 = p.K >> 3;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGES * STAGE_BYTES + (((size_t)p.K * 2 + 127) & ~(size_t)127));
     float* red = reinterpret_cast<float*>(bars + 2 * NSTAGES);
+    float* partials = red + CONSUMERS;  // [2][CONSUMERS][STAGE_ROWS] per-warp partial row sums, double buffered
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NSTAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -199,7 +219,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
             if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
             __syncwarp();
             if (lane < rows_in_tile)
-                tma_load_1d(smem_u32(stages + (size_t)s * STAGE_BYTES + (size_t)lane * CHUNK_BYTES),
+                tma_load_1d(smem_u32(stages + (size_t)s * STAGE_BYTES + (size_t)lane * ROW_STRIDE),
                             row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), full0 + 8 * s, pol);
         }
         if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
@@ -210,12 +230,24 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
     pdl_wait();  // activations written by the previous kernel are visible from here on
     const int ctid = threadIdx.x;  // 0..255
     const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
-    if (NORM) {  // RMSNorm: fp32 sum of squares, xs = half(x * rinv * w)
+    float rinv = 1.0f;
+    if (NORM) {
+        // RMSNorm in one pass: the staged vector is x * w (fp16); the scalar 1/rms multiplies the
+        // finished dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk), so
+        // no second pass over x has to wait for the block-wide sum of squares.
         float ss = 0.f;
+        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
         for (int c = ctid; c < K8; c += CONSUMERS * 32) {
-            uint4 v = x4[c];
-            xs[c] = v;
+            uint4 v = x4[c], g = nw4[c];
             ss += sumsq8(v);
+            __half2* vh = reinterpret_cast<__half2*>(&v);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 vf = __half22float2(vh[i]), gf = __half22float2(gh[i]);
+                vh[i] = __floats2half2_rn(vf.x * gf.x, vf.y * gf.y);
+            }
+            xs[c] = v;
         }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
@@ -223,59 +255,72 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < CONSUMERS; w++) tot += red[w];
-        const float rinv = rsqrtf(tot / (float)p.K + p.eps);
-        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
-        for (int c = ctid; c < K8; c += CONSUMERS * 32) {
-            uint4 v = xs[c], g = nw4[c];
-            __half2* vh = reinterpret_cast<__half2*>(&v);
-            const __half2* gh = reinterpret_cast<const __half2*>(&g);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                float2 vf = __half22float2(vh[i]), gf = __half22float2(gh[i]);
-                vh[i] = __floats2half2_rn(vf.x * rinv * gf.x, vf.y * rinv * gf.y);
-            }
-            xs[c] = v;
-        }
+        rinv = rsqrtf(tot / (float)p.K + p.eps);
     } else {
         for (int c = ctid; c < K8; c += CONSUMERS * 32) xs[c] = x4[c];
+        consumer_bar_sync(CONSUMERS * 32);
     }
-    consumer_bar_sync(CONSUMERS * 32);
 
+    // Main loop. A stage is a 32-row x 1024-k slab of weights. The dot products run on the tensor
+    // cores (mma.sync m16n8k16, fp32 accumulate): the slab's rows are the M dimension (two m16
+    // tiles), the activation vector is column 0 of the B operand. Warp w multiplies the k16 steps
+    // [w*STEPS_PER_WARP, +STEPS_PER_WARP) of every chunk for all 32 rows; at the end of a tile the
+    // 16 per-warp partial sums of each row meet in shared memory and warp 0 finishes the rows.
+    // This keeps the consumers' instruction count ~8x below a SIMT FMA loop, so they outrun HBM and
+    // the ring can absorb prologue and barrier time.
     bool ok = true;
     int it = 0;
+    const int g = lane >> 2, t = lane & 3;
+    // ldmatrix row addresses: lanes 0-7 rows 0-7 (k 0-7), 8-15 rows 8-15, 16-23 rows 0-7 (k 8-15), 24-31 rows 8-15
+    const uint32_t lm_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + (lane >> 4) * 16);
+    const __half* xh = reinterpret_cast<const __half*>(xs);
     for (int tile = 0; tile < n_tiles && ok; tile++) {
         const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
-        const bool mine = warp < units_here;
-        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
         for (int chunk = 0; chunk < nk; chunk++, it++) {
             const int s = it % NSTAGES, use = it / NSTAGES;
             ok = mbar_wait(full0 + 8 * s, use & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (mine) {
-                const int kc8 = min(KC, p.K - chunk * KC) >> 3;
-                const uint4* wa = reinterpret_cast<const uint4*>(stages + (size_t)s * STAGE_BYTES + (size_t)(2 * warp) * CHUNK_BYTES);
-                const uint4* wb = wa + CHUNK_BYTES / 16;
-                const uint4* xc = xs + chunk * (KC / 8);
+            const int steps = min(KC, p.K - chunk * KC) >> 4;
+            const uint32_t sbase = smem_u32(stages + (size_t)s * STAGE_BYTES) + lm_off;
 #pragma unroll
-                for (int j = 0; j < KC / 8 / 32; j++) {
-                    const int idx = lane + 32 * j;
-                    if (idx < kc8) {
-                        const uint4 xv = xc[idx], va = wa[idx], vb = wb[idx];
-                        if (j & 1) { a1 = dot8(va, xv, a1); b1 = dot8(vb, xv, b1); }
-                        else       { a0 = dot8(va, xv, a0); b0 = dot8(vb, xv, b0); }
-                    }
+            for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
+                const int step = warp * STEPS_PER_WARP + kk;
+                if (step < steps) {
+                    uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+                    ldmatrix_x4(sbase + step * 32, a0, a1, a2, a3);
+                    ldmatrix_x4(sbase + 16 * ROW_STRIDE + step * 32, c0, c1, c2, c3);
+                    const __half* xk = xh + chunk * KC + step * 16 + 2 * t;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xk);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xk + 8);
+                    mma_16816(acc0, a0, a1, a2, a3, b0, b1);
+                    mma_16816(acc1, c0, c1, c2, c3, b0, b1);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
-        if (!ok || !mine) continue;
-        const float sa = warp_sum(a0 + a1), sb = warp_sum(b0 + b1);
-        if (lane != 0) continue;
+        if (!ok) break;
+        // column 0 of the accumulators lives in the lanes with t == 0: rows g and g+8 of each m16 tile
+        float* part = partials + (tile & 1) * (CONSUMERS * STAGE_ROWS);
+        if (t == 0) {
+            part[warp * STAGE_ROWS + g] = acc0[0];
+            part[warp * STAGE_ROWS + g + 8] = acc0[2];
+            part[warp * STAGE_ROWS + 16 + g] = acc1[0];
+            part[warp * STAGE_ROWS + 24 + g] = acc1[2];
+        }
+        consumer_bar_sync(CONSUMERS * 32);
+        if (warp != 0) continue;
+        float rowsum = 0.f;   // lane = row slot of the stage: slots 2u, 2u+1 are the two rows of unit u
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; w++) rowsum += part[w * STAGE_ROWS + lane];
+        const float other = __shfl_xor_sync(0xffffffffu, rowsum, 1);
+        if ((lane & 1) || (lane >> 1) >= units_here) continue;
+        const float sa = rowsum * rinv, sb = other * rinv;
         const __half ha = __float2half_rn(sa), hb = __float2half_rn(sb);
         const __half *ra, *rb; int mat, r;
-        unit_rows<EPI>(p, u_begin + tile * CONSUMERS + warp, ra, rb, mat, r);
+        unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
         if (EPI == EPI_STORE) {
             p.y[(long long)mat * p.N_each + r] = ha;
             p.y[(long long)mat * p.N_each + r + 1] = hb;
@@ -410,7 +455,7 @@ bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, 
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
                 long long ldx, long long ldy, cudaStream_t st) {
     TL_REQUIRE(gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0, "gemv: unsupported shape or alignment");
-    if (M == 1 && ldw == K && N % 2 == 0 && K <= 16384) {  // the decode kernel, plain store epilogue
+    if (M == 1 && ldw == K && N % 2 == 0 && K % 16 == 0 && K <= 12288) {  // the decode kernel, plain store epilogue
         FusedGemv f{};
         f.x = x; f.W[0] = W; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = y; f.pdl = false;
         return launch_fused_gemv(f, st);
@@ -433,7 +478,7 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
 
 int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     auto al16 = [](const void* v) { return (reinterpret_cast<uintptr_t>(v) & 15) == 0; };
-    TL_REQUIRE(q.K >= 8 && q.K % 8 == 0 && q.K <= 16384, "fused gemv: K=%d must be a multiple of 8, <= 16384", q.K);
+    TL_REQUIRE(q.K >= 16 && q.K % 16 == 0 && q.K <= 12288, "fused gemv: K=%d must be a multiple of 16, <= 12288", q.K);
     TL_REQUIRE(q.N_each > 0 && q.N_each % 2 == 0, "fused gemv: N must be even");
     TL_REQUIRE(al16(q.x) && al16(q.W[0]) && (!q.norm_w || al16(q.norm_w)), "fused gemv: 16-byte alignment required");
     for (int i = 1; i < q.n_mats; i++) TL_REQUIRE(al16(q.W[i]), "fused gemv: 16-byte alignment required");
@@ -458,7 +503,7 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     // one persistent CTA per SM; small problems get one CTA per stage-full of units
     const int grid = std::max(1, std::min(sm_count(), (a.total_units + CONSUMERS - 1) / CONSUMERS));
     const size_t smem = (size_t)NSTAGES * STAGE_BYTES + (((size_t)q.K * 2 + 127) & ~(size_t)127) +
-                        2 * NSTAGES * sizeof(uint64_t) + CONSUMERS * sizeof(float) + 64;
+                        2 * NSTAGES * sizeof(uint64_t) + CONSUMERS * sizeof(float) + 2 * CONSUMERS * STAGE_ROWS * sizeof(float) + 64;
     const bool norm = q.norm_w != nullptr;
 #define TL_FUSED(E) (norm ? launch_ring<E, true>(a, smem, grid, st, q.pdl) : launch_ring<E, false>(a, smem, grid, st, q.pdl))
     switch (q.epilogue) {

@@ -90,6 +90,9 @@ struct DecodeAttn {
     bool pdl;
 };
 int launch_decode_attn(const DecodeAttn& p, cudaStream_t st);
+// the same with the splits of a head merged over distributed shared memory (cluster of <= 8 CTAs);
+// scratch and counters are not used
+int launch_decode_attn_cluster(const DecodeAttn& p, cudaStream_t st);
 // causal softmax over materialised scores (H,T,S) with scale, fp32 internals, in place
 int launch_softmax_causal_fast(__half* scores, int H, int T, int S, int pos, float scale,
                                cudaStream_t st);

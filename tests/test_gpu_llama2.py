@@ -108,6 +108,29 @@ def test_fast_generate_graph_and_host_loop_agree(tl, golden_tiny, tiny_payload):
     m.close(); m2.close()
 
 
+def test_one_kernel_decode_step_matches_the_graph_of_kernels(tl, oracle, golden_tiny, tiny_payload):
+    """one_kernel_decode=1 runs the whole step as one persistent cooperative kernel; same
+    arithmetic up to fp32 summation order, so the logits agree within the fast-mode tolerance and
+    stay within it against the oracle."""
+    a = make_model(tl, tiny_payload, tl.FAST)
+    b = tl.Llama2(synth.TINY, numerics=tl.FAST, one_kernel_decode=True)
+    b.load_payload(tiny_payload, shared_classifier=True)
+    mo = oracle.llama2(synth.TINY, tiny_payload)
+    forced = golden_tiny["forced_tokens"]
+    for m in (a, b, mo):
+        m.forward(forced[:16], 0, *(() if m is not mo else (1,)))
+    for i in range(16, 24):
+        la = a.forward(forced[i:i + 1], i, all_logits=True).astype(np.float32)
+        lb = b.forward(forced[i:i + 1], i, all_logits=True).astype(np.float32)
+        lo = mo.forward(forced[i:i + 1], i, 1).astype(np.float32)
+        assert np.abs(la - lb).max() <= 1e-2
+        assert np.abs(lb - lo).max() <= 2e-2
+    b.forward(forced[:16], 0, all_logits=False)
+    ids = b.decode_device(16, 20)
+    assert ids.shape == (20,) and tl.device_status() == 0
+    a.close(); b.close()
+
+
 def test_context_limits(tl, tiny_payload):
     m = make_model(tl, tiny_payload, tl.FAST)
     tok = synth.token_ids(5, 1, 256, synth.TINY.vocab_size)
