@@ -228,6 +228,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world > 1:
         from tensorlib_b200 import tp
         tp.attach(model, rank, world, dist)
+        if args.tp_exchange == "fused":
+            tp.open_fused_exchange(model, rank, world, dist)
     model.init_random(SEED, 0.02)
 
     n_ctx = 128 if world == 1 else 512
@@ -298,7 +300,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": workload_name(world) + ("" if cfg.n_layers == CFG.n_layers else f" [PROFILING ONLY: {cfg.n_layers} layers]"),
                            "context_at_start": n_ctx + W,
-                           "parallelism": f"tp{world}", "numerics": "fp16 storage, fp32 accumulate",
+                           "parallelism": f"tp{world}",
+                           "tp_exchange": (args.tp_exchange if world > 1 else "none"), "numerics": "fp16 storage, fp32 accumulate",
                            "l2": "inputs larger than L2 (weights streamed per token >> 126 MB)",
                            "weight_bytes_per_token_per_gpu": step_bytes},
                 "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4,
@@ -312,6 +315,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                               "classifier rows (1/32 of a token each), extrapolated x32"}
     # the compute-bound companion numbers: one 2048-token prefill (all ranks take part)
     prefill = prefill_2048(model, cfg, world, torch, dist) if cfg.n_layers == CFG.n_layers else None
+    if world > 1 and args.tp_exchange == "fused":
+        from tensorlib_b200 import tp
+        tp.close_fused_exchange(model, dist)
     model.close()
     if rank == 0:
         line["prefill_2048"] = prefill
@@ -411,6 +417,9 @@ def main():
     ap.add_argument("--layers", type=int, default=CFG.n_layers, help="profiling only: fewer layers of the 7B shape")
     ap.add_argument("--skip-prefill", action="store_true", help="profiling only: decode without a prompt pass")
     ap.add_argument("--sweep-only", default="", help="profiling only: time one matmul point 'M,K,N' and exit")
+    ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
+                    help="N>1 decode: partial sums exchanged by peer stores inside the GEMV kernels (default) "
+                         "or by ncclAllReduce between them")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -241,6 +241,16 @@ TL_API int tl_tp_init(const void* unique_id, int nbytes, int rank, int world);
 TL_API int tl_tp_attach(tl_llama2* m);
 TL_API int tl_tp_allreduce_f32(float* buf, size_t n, tl_stream stream);
 TL_API int tl_tp_destroy(void);
+/* Fused exchange for the decode step: instead of an NCCL allreduce after wo and w2, the GEMV
+ * kernels store their fp32 partial sums into a receive region in every rank's memory (peer
+ * stores over NVLink) and the next GEMV's prologue sums them in rank order; the classifier
+ * slices travel the same way. Set-up: every rank exports a 64-byte handle of its region, the
+ * handles are gathered out of band (rank order, world*64 bytes), every rank opens them; all
+ * ranks must pass a host barrier before the first decode step and before closing. Device-side
+ * waits are bounded (TL_ERR_TIMEOUT in the device status word). Prefill keeps using NCCL. */
+TL_API int tl_tp_exchange_export(tl_llama2* m, void* handle64, int nbytes);
+TL_API int tl_tp_exchange_open(tl_llama2* m, const void* handles, int world);
+TL_API int tl_tp_exchange_close(tl_llama2* m);
 /* Host-only: the block of a [rows, cols] checkpoint tensor that rank `rank` of `world` keeps.
  * kind 0 = replicated, 1 = split by rows, 2 = split by columns. */
 TL_API int tl_tp_shard(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows,

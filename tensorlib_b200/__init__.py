@@ -86,6 +86,9 @@ _SIGS = {
     "tl_tp_attach": [_vp],
     "tl_tp_allreduce_f32": [_vp, _sz, _vp],
     "tl_tp_destroy": [],
+    "tl_tp_exchange_export": [_vp, _vp, _int],
+    "tl_tp_exchange_open": [_vp, _vp, _int],
+    "tl_tp_exchange_close": [_vp],
     "tl_tp_shard": [_int] * 5 + [C.POINTER(_int)] * 4,
 }
 _OTHER_RESTYPE = {"tl_strerror": (C.c_char_p, [_int]), "tl_last_error": (C.c_char_p, []),

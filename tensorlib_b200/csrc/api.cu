@@ -251,9 +251,9 @@ int tl_llama2_forward(tl_llama2* m, const int* tokens_host, int T, int start_pos
     TL_PROPAGATE(e.forward(T, start_pos, logits_host != nullptr, nullptr));
     TL_PROPAGATE(e.sample_last(T, nullptr));
     if (logits_host)
-        TL_CUDA(cudaMemcpyAsync(logits_host, e.logits(), (size_t)T * V * 2, cudaMemcpyDeviceToHost, nullptr));
+        TL_CUDA(cudaMemcpyAsync(logits_host, T == 1 ? e.last_logits() : e.logits(), (size_t)T * V * 2, cudaMemcpyDeviceToHost, nullptr));
     if (last_logits_host)
-        TL_CUDA(cudaMemcpyAsync(last_logits_host, e.logits() + (size_t)(T - 1) * V, (size_t)V * 2, cudaMemcpyDeviceToHost, nullptr));
+        TL_CUDA(cudaMemcpyAsync(last_logits_host, e.last_logits(), (size_t)V * 2, cudaMemcpyDeviceToHost, nullptr));
     TL_CUDA(cudaStreamSynchronize(nullptr));
     return TL_OK;
 }

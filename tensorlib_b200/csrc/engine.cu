@@ -50,6 +50,7 @@ Llama2Engine::Llama2Engine(const tl_llama2_config& cfg) : cfg_(cfg) {
 Llama2Engine::~Llama2Engine() { free_all(); }
 
 int Llama2Engine::free_all() {
+    xch_close();
     if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
     mega_ready_ = false;
     for (void* p : allocs_) cudaFree(p);
@@ -315,6 +316,7 @@ int Llama2Engine::forward(int T, int start_pos, bool all_logits, cudaStream_t st
                "forward: T=%d start_pos=%d exceeds max_seq_len=%d", T, start_pos, cfg_.max_seq_len);
     const bool exact = cfg_.numerics == TL_NUMERICS_REFERENCE_ORDER;
     TL_PROPAGATE(ensure_activations(T, (exact || T > 1) ? start_pos + T : 0));
+    last_logits_ = logits_ + (size_t)(T - 1) * cfg_.vocab_size;
     if (exact) return forward_reference_order(T, start_pos, all_logits, st);
     if (T == 1) {
         // same launch sequence as the graph, position passed through *d_pos_
@@ -434,9 +436,200 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
 //   [wo GEMV + residual] -> [RMSNorm + w1|w3 GEMV + SiLU*up] -> [w2 GEMV + residual]
 // then [RMSNorm + classifier GEMV] -> argmax -> advance. Token and position are read from device
 // memory so the same launches can be replayed from a CUDA graph.
+// ---- fused tensor-parallel exchange -----------------------------------------------------------------
+namespace {
+// greedy sampling over logits that the ranks pushed slice by slice: wait for every rank's flag
+// (bounded), then the usual lowest-index argmax
+__global__ void k_argmax_after_exchange(int* out_idx, const __half* logits, int cols, const unsigned int* flags,
+                                        int world, const unsigned int* step_ptr, int phases_per_step,
+                                        int phase_id, int* status) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const unsigned int epoch = __ldcg(step_ptr) * (unsigned)phases_per_step + (unsigned)phase_id + 1u;
+    if ((int)threadIdx.x < world) {   // one watcher per source rank
+        bool seen = false;
+        const unsigned int* flag = flags + threadIdx.x * TL_XCH_FLAG_STRIDE;
+        for (unsigned i = 0; i < (1u << 22) && !seen; i++) {
+            unsigned int v;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            seen = (int)(v - epoch) >= 0;
+        }
+        if (!seen) atomicExch(status, TL_ERR_TIMEOUT);
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+    }
+    __syncthreads();
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(logits) + j);
+        float v = __half2float(__ushort_as_half(raw));
+        if (bi == 0x7fffffff || v > bv) { bv = v; bi = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+        out_idx[0] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+__global__ void k_advance_tp(int* pos, const int* next, int* generated, int max_seq, unsigned int* step) {
+    int p = *pos;
+    if (p >= 0 && p < max_seq) generated[p] = *next;
+    *pos = p + 1;
+    *step = *step + 1;
+}
+}  // namespace
+
+int Llama2Engine::xch_export(cudaIpcMemHandle_t* out) {
+    TL_REQUIRE(out && cfg_.tp_world > 1 && cfg_.tp_world <= TL_MAX_TP, "exchange needs 2..%d ranks", TL_MAX_TP);
+    if (!xch_base_) {
+        const size_t dim = cfg_.dim, W = cfg_.tp_world;
+        size_t off = 0;
+        auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) & ~(size_t)255; return o; };
+        xch_off_part_[0] = take(W * dim * sizeof(float));
+        xch_off_part_[1] = take(W * dim * sizeof(float));
+        xch_off_logits_ = take((size_t)cfg_.vocab_size * sizeof(__half));
+        xch_off_flags_ = take((size_t)3 * TL_MAX_TP * TL_XCH_FLAG_STRIDE * sizeof(unsigned int));
+        xch_off_done_ = take(3 * sizeof(unsigned int));
+        xch_off_step_ = take(sizeof(unsigned int));
+        xch_bytes_ = off;
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, xch_bytes_));
+        TL_CUDA(cudaMemset(d, 0, xch_bytes_));
+        TL_CUDA(cudaDeviceSynchronize());
+        allocs_.push_back(d);
+        xch_base_ = static_cast<unsigned char*>(d);
+    }
+    TL_CUDA(cudaIpcGetMemHandle(out, xch_base_));
+    return TL_OK;
+}
+
+int Llama2Engine::xch_open(const cudaIpcMemHandle_t* handles, int world) {
+    TL_REQUIRE(handles && world == cfg_.tp_world && xch_base_, "exchange: export first, then open with %d handles", cfg_.tp_world);
+    for (int r = 0; r < world; r++) {
+        if (r == cfg_.tp_rank) { xch_peer_[r] = xch_base_; continue; }
+        void* p = nullptr;
+        TL_CUDA(cudaIpcOpenMemHandle(&p, handles[r], cudaIpcMemLazyEnablePeerAccess));
+        xch_peer_[r] = static_cast<unsigned char*>(p);
+    }
+    if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
+    xch_ready_ = true;
+    return TL_OK;
+}
+
+int Llama2Engine::xch_close() {
+    if (!xch_ready_) return TL_OK;
+    cudaDeviceSynchronize();
+    if (decode_graph_) { cudaGraphExecDestroy(decode_graph_); decode_graph_ = nullptr; }
+    for (int r = 0; r < cfg_.tp_world; r++)
+        if (r != cfg_.tp_rank && xch_peer_[r]) cudaIpcCloseMemHandle(xch_peer_[r]);
+    xch_ready_ = false;
+    return TL_OK;
+}
+
+// buf 0: wo partials, 1: w2 partials (fp32, dim per rank); 2: classifier slices (fp16, vocab/world per rank)
+PeerExchange Llama2Engine::make_exchange(int buf, int phase_id) const {
+    PeerExchange e{};
+    e.world = cfg_.tp_world; e.rank = cfg_.tp_rank;
+    const size_t slot_bytes = buf < 2 ? (size_t)cfg_.dim * sizeof(float) : (size_t)vocab_local_ * sizeof(__half);
+    const size_t base_off = buf < 2 ? xch_off_part_[buf] : xch_off_logits_;
+    e.n = buf < 2 ? cfg_.dim : vocab_local_;
+    e.done_counter = reinterpret_cast<unsigned int*>(xch_base_ + xch_off_done_) + buf;
+    e.local_slots = xch_base_ + base_off;
+    e.local_flags = reinterpret_cast<const unsigned int*>(xch_base_ + xch_off_flags_) + (size_t)buf * TL_MAX_TP * TL_XCH_FLAG_STRIDE;
+    for (int d = 0; d < e.world; d++) {
+        e.peer_slot[d] = xch_peer_[d] + base_off + (size_t)e.rank * slot_bytes;
+        e.peer_flag[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + xch_off_flags_) +
+                         ((size_t)buf * TL_MAX_TP + e.rank) * TL_XCH_FLAG_STRIDE;
+    }
+    e.step_ptr = reinterpret_cast<const unsigned int*>(xch_base_ + xch_off_step_);
+    e.phases_per_step = 2 * cfg_.n_layers + 1;
+    e.phase_id = phase_id;
+    return e;
+}
+
+// The tensor-parallel decode step with the exchanges fused into the GEMV kernels: same five
+// kernels per layer as on one GPU, no collective launches. wo and w2 push fp32 partial sums to
+// every rank; the next GEMV's prologue waits for all ranks, sums in rank order and adds the
+// residual. The classifier pushes its logit slice; the sampling kernel waits for all slices.
+int Llama2Engine::decode_step_tp_fused(cudaStream_t st, bool pdl) {
+    const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_, L = cfg_.n_layers;
+    long long n = 0;
+    TL_PROPAGATE(launch_embedding(x_, emb_, d_next_, 1, dim, cfg_.vocab_size, st)); n++;
+    for (int l = 0; l < L; l++) {
+        const LayerWeights& w = layers_[l];
+        PeerExchange in_w2{};
+        FusedGemv a{};
+        a.x = x_; a.norm_w = w.attn_norm; a.eps = 1e-5f;
+        a.W[0] = w.wq; a.W[1] = w.wk; a.W[2] = w.wv; a.n_mats = 3; a.N_each = dl; a.K = dim;
+        a.epilogue = EPI_QKV_ROPE; a.y = q_; a.k_out = w.cache_k; a.v_out = w.cache_v;
+        a.cos_row = cos_t_; a.sin_row = sin_t_; a.head_dim = hd_; a.pos_ptr = d_pos_; a.kv_pitch = dl;
+        a.pdl = pdl;
+        if (l > 0) {  // x = h + sum of the previous layer's w2 partials
+            in_w2 = make_exchange(1, 2 * (l - 1) + 1);
+            in_w2.residual = h_; in_w2.sum_out = x_;
+            a.xin = &in_w2;
+        }
+        TL_PROPAGATE(launch_fused_gemv(a, st)); n++;
+
+        DecodeAttn at{q_, w.cache_k, w.cache_v, att_, attn_scratch_, attn_counters_, H_local_, hd_, 0,
+                      attn_splits_, d_pos_, dl, pdl};
+        TL_PROPAGATE(launch_decode_attn_cluster(at, st)); n++;
+
+        PeerExchange out_wo = make_exchange(0, 2 * l);
+        FusedGemv o{};
+        o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
+        o.epilogue = EPI_PUSH_F32; o.xout = &out_wo;
+        TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
+
+        PeerExchange in_wo = make_exchange(0, 2 * l);
+        in_wo.residual = x_; in_wo.sum_out = h_;
+        FusedGemv f{};
+        f.x = x_; f.norm_w = w.ffn_norm; f.eps = 1e-5f; f.xin = &in_wo;
+        f.W[0] = w.w1; f.W[1] = w.w3; f.n_mats = 2; f.N_each = hl; f.K = dim;
+        f.epilogue = EPI_SWIGLU; f.y = g_; f.pdl = pdl;
+        TL_PROPAGATE(launch_fused_gemv(f, st)); n++;
+
+        PeerExchange out_w2 = make_exchange(1, 2 * l + 1);
+        FusedGemv d{};
+        d.x = g_; d.W[0] = w.w2; d.n_mats = 1; d.N_each = dim; d.K = hl; d.pdl = pdl;
+        d.epilogue = EPI_PUSH_F32; d.xout = &out_w2;
+        TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
+    }
+    PeerExchange in_last = make_exchange(1, 2 * (L - 1) + 1);
+    in_last.residual = h_; in_last.sum_out = x_;
+    PeerExchange out_cls = make_exchange(2, 2 * L);
+    FusedGemv c{};
+    c.x = x_; c.norm_w = final_norm_; c.eps = 1e-5f; c.xin = &in_last;
+    c.W[0] = wcls_; c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_PUSH_F16; c.xout = &out_cls;
+    c.pdl = pdl;
+    TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
+    const __half* lg = reinterpret_cast<const __half*>(xch_base_ + xch_off_logits_);
+    k_argmax_after_exchange<<<1, 1024, 0, st>>>(d_next_, lg, cfg_.vocab_size, out_cls.local_flags, cfg_.tp_world,
+                                                out_cls.step_ptr, out_cls.phases_per_step,
+                                                out_cls.phase_id, device_status_word()); n++;
+    TL_LAUNCH_CHECK();
+    k_advance_tp<<<1, 1, 0, st>>>(d_pos_, d_next_, d_generated_, cfg_.max_seq_len,
+                                  reinterpret_cast<unsigned int*>(xch_base_ + xch_off_step_)); n++;
+    TL_LAUNCH_CHECK();
+    last_logits_ = lg;
+    decode_step_launches_ = n;
+    launches_ += n;
+    return TL_OK;
+}
+
 int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
+    if (xch_ready_) return decode_step_tp_fused(st, pdl);
     const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_;
     long long n = 0;
+    last_logits_ = logits_;
     TL_PROPAGATE(launch_embedding(x_, emb_, d_next_, 1, dim, cfg_.vocab_size, st)); n++;
     for (int l = 0; l < cfg_.n_layers; l++) {
         const LayerWeights& w = layers_[l];
@@ -504,7 +697,8 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
 
 int Llama2Engine::sample_last(int T, cudaStream_t st) {
     launches_++;
-    return launch_argmax(d_next_, logits_ + (size_t)(T - 1) * cfg_.vocab_size, 1, cfg_.vocab_size, st);
+    (void)T;
+    return launch_argmax(d_next_, last_logits_, 1, cfg_.vocab_size, st);
 }
 
 int Llama2Engine::ensure_decode_graph(cudaStream_t st) {
@@ -615,6 +809,7 @@ int Llama2Engine::decode_profile(int start_pos, int cta, unsigned long long* out
 int Llama2Engine::decode_step_mega(cudaStream_t st, unsigned long long* prof, int prof_cta) {
     MegaArgs a{};
     a.prof = prof; a.prof_cta = prof_cta;
+    last_logits_ = logits_;
     a.phases = static_cast<const MegaPhase*>(mega_phases_); a.n_phases = mega_n_phases_;
     a.emb = emb_; a.dim = cfg_.dim; a.vocab = cfg_.vocab_size;
     a.H = H_local_; a.hd = hd_; a.splits = mega_splits_; a.max_seq = cfg_.max_seq_len; a.kv_pitch = dim_local_;

@@ -52,6 +52,13 @@ public:
     long long weight_bytes() const { return weight_bytes_; }
     int vocab_local() const { return vocab_local_; }
     void set_collective(Collective* c) { coll_ = c; }
+    // Fused tensor-parallel exchange (see PeerExchange): allocate this rank's receive region and
+    // export it; then map every rank's region. After xch_open the decode step needs no collective
+    // library call.
+    int xch_export(cudaIpcMemHandle_t* out);
+    int xch_open(const cudaIpcMemHandle_t* handles, int world);
+    int xch_close();
+    const __half* last_logits() const { return last_logits_; }
     int tensor(const char* name, int layer, void** dptr, int* rows, int* cols) const;
     // one decode step with per-phase device timestamps of CTA `cta`: out_host[n_phases][3] in ns
     int decode_profile(int start_pos, int cta, unsigned long long* out_host, int capacity, int* n_phases);
@@ -100,6 +107,14 @@ private:
     long long launches_ = 0;
     long long decode_step_launches_ = 0;
     Collective* coll_ = nullptr;
+    // exchange region: [part0: world*dim f32][part1: world*dim f32][logits: vocab f16][flags 3*8 u32][done 3 u32][step u32]
+    int decode_step_tp_fused(cudaStream_t st, bool pdl);
+    PeerExchange make_exchange(int buf, int phase_id) const;
+    unsigned char* xch_base_ = nullptr;
+    unsigned char* xch_peer_[TL_MAX_TP] = {};
+    size_t xch_off_part_[2] = {0, 0}, xch_off_logits_ = 0, xch_off_flags_ = 0, xch_off_done_ = 0, xch_off_step_ = 0, xch_bytes_ = 0;
+    bool xch_ready_ = false;
+    const __half* last_logits_ = nullptr;
 };
 
 // Which block of a [rows, cols] checkpoint tensor rank `rank` of `world` keeps.

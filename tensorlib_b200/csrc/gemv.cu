@@ -143,7 +143,21 @@ struct RingArgs {
     const int* pos_ptr; long long kv_pitch;
     const __half* silu_tab;
     int* status;                  // device status word: set on a timed-out wait
+    int has_xin;                  // the activation vector is residual + sum of pushed partials
+    PeerExchange xin, xout;
 };
+
+__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int exchange_epoch(const PeerExchange& e) {
+    return __ldcg(e.step_ptr) * (unsigned)e.phases_per_step + (unsigned)e.phase_id + 1u;
+}
 
 template <int EPI>
 __device__ __forceinline__ void unit_rows(const RingArgs& p, int unit, const __half*& ra, const __half*& rb,
@@ -231,6 +245,39 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
     const int ctid = threadIdx.x;  // 0..255
     const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
     float rinv = 1.0f;
+    if (p.has_xin) {
+        // Tensor-parallel input: wait (bounded) until every rank has pushed its partial vector of
+        // this step into the local slots, then x = residual + sum over ranks, in rank order.
+        const PeerExchange& e = p.xin;
+        const unsigned int epoch = exchange_epoch(e);
+        if (ctid < e.world) {   // one watcher per source rank
+            bool seen = false;
+            for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+                if ((int)(ld_relaxed_sys(e.local_flags + ctid * TL_XCH_FLAG_STRIDE) - epoch) >= 0) { seen = true; break; }
+            if (!seen) atomicExch(p.status, TL_ERR_TIMEOUT);
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // the pushed data is read after the flags
+        }
+        consumer_bar_sync(CONSUMERS * 32);
+    }
+    // one 16-byte group of the activation vector (plain, or reduced over the ranks)
+    auto load_x = [&](int c) -> uint4 {
+        if (!p.has_xin) return x4[c];
+        const PeerExchange& e = p.xin;
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < e.world; r++) {
+            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(e.local_slots) + (size_t)r * e.n) + 2 * c;
+            const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+            s[0] += lo.x; s[1] += lo.y; s[2] += lo.z; s[3] += lo.w;
+            s[4] += hi.x; s[5] += hi.y; s[6] += hi.z; s[7] += hi.w;
+        }
+        uint4 res = __ldcg(reinterpret_cast<const uint4*>(e.residual) + c), out;
+        const __half* rh = reinterpret_cast<const __half*>(&res);
+        __half* oh = reinterpret_cast<__half*>(&out);
+#pragma unroll
+        for (int i = 0; i < 8; i++) oh[i] = hadd_ref(rh[i], __float2half_rn(s[i]));
+        if (blockIdx.x == 0 && e.sum_out) reinterpret_cast<uint4*>(e.sum_out)[c] = out;
+        return out;
+    };
     if (NORM) {
         // RMSNorm in one pass: the staged vector is x * w (fp16); the scalar 1/rms multiplies the
         // finished dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk), so
@@ -238,7 +285,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         float ss = 0.f;
         const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
         for (int c = ctid; c < K8; c += CONSUMERS * 32) {
-            uint4 v = x4[c], g = nw4[c];
+            uint4 v = load_x(c), g = nw4[c];
             ss += sumsq8(v);
             __half2* vh = reinterpret_cast<__half2*>(&v);
             const __half2* gh = reinterpret_cast<const __half2*>(&g);
@@ -257,7 +304,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         for (int w = 0; w < CONSUMERS; w++) tot += red[w];
         rinv = rsqrtf(tot / (float)p.K + p.eps);
     } else {
-        for (int c = ctid; c < K8; c += CONSUMERS * 32) xs[c] = x4[c];
+        for (int c = ctid; c < K8; c += CONSUMERS * 32) xs[c] = load_x(c);
         consumer_bar_sync(CONSUMERS * 32);
     }
 
@@ -327,6 +374,14 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         } else if (EPI == EPI_STORE_F32) {
             p.y32[(long long)mat * p.N_each + r] = sa;
             p.y32[(long long)mat * p.N_each + r + 1] = sb;
+        } else if (EPI == EPI_PUSH_F32) {  // K-split partial sums into slot [rank] on every rank
+#pragma unroll 1
+            for (int d = 0; d < p.xout.world; d++)
+                *reinterpret_cast<float2*>(static_cast<float*>(p.xout.peer_slot[d]) + r) = make_float2(sa, sb);
+        } else if (EPI == EPI_PUSH_F16) {  // row-split results (classifier slice) onto every rank
+#pragma unroll 1
+            for (int d = 0; d < p.xout.world; d++)
+                *reinterpret_cast<__half2*>(static_cast<__half*>(p.xout.peer_slot[d]) + r) = __halves2half2(ha, hb);
         } else if (EPI == EPI_RESIDUAL) {  // h = x + linear(...), fp16 add like Tensor::EwiseAdd
             p.y[r] = hadd_ref(p.residual[r], ha);
             p.y[r + 1] = hadd_ref(p.residual[r + 1], hb);
@@ -351,6 +406,24 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         }
     }
     if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+    if (EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16) {
+        // All of this CTA's peer stores are issued (warp 0 made them). bar.sync orders them before
+        // thread 0's fence + counter increment (gpu scope); the CTA that sees the full count issues
+        // one system-scope fence, which is cumulative over every CTA's stores, and raises this
+        // rank's flag on every rank. (Per-CTA flags were measured: polling world*grid flags in
+        // every consumer CTA costs more than this counter.)
+        consumer_bar_sync(CONSUMERS * 32);
+        if (ctid == 0) {
+            __threadfence();
+            const unsigned int prev = atomicAdd(p.xout.done_counter, 1u);
+            if (prev == gridDim.x - 1) {
+                atomicExch(p.xout.done_counter, 0u);
+                const unsigned int epoch = exchange_epoch(p.xout);
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                for (int d = 0; d < p.xout.world; d++) st_relaxed_sys(p.xout.peer_flag[d], epoch);
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -476,6 +549,11 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
     return TL_OK;
 }
 
+int fused_gemv_grid(int total_rows) {
+    const int units = total_rows / 2;
+    return std::max(1, std::min(sm_count(), (units + CONSUMERS - 1) / CONSUMERS));
+}
+
 int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     auto al16 = [](const void* v) { return (reinterpret_cast<uintptr_t>(v) & 15) == 0; };
     TL_REQUIRE(q.K >= 16 && q.K % 16 == 0 && q.K <= 12288, "fused gemv: K=%d must be a multiple of 16, <= 12288", q.K);
@@ -491,6 +569,16 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     a.pos_ptr = q.pos_ptr; a.kv_pitch = q.kv_pitch;
     a.silu_tab = tables().silu_float_tab;
     a.status = device_status_word();
+    a.has_xin = q.xin != nullptr;
+    if (q.xin) {
+        TL_REQUIRE(q.xin->world >= 1 && q.xin->world <= TL_MAX_TP && q.xin->n == q.K && q.xin->residual,
+                   "fused gemv: bad exchange input");
+        a.xin = *q.xin;
+    }
+    if (q.epilogue == EPI_PUSH_F32 || q.epilogue == EPI_PUSH_F16) {
+        TL_REQUIRE(q.xout && q.n_mats == 1 && q.xout->world >= 1 && q.xout->world <= TL_MAX_TP, "fused gemv: bad exchange output");
+        a.xout = *q.xout;
+    }
     if (q.epilogue == EPI_SWIGLU) {
         TL_REQUIRE(q.n_mats == 2, "swiglu epilogue needs w1 and w3");
         a.total_units = q.N_each;
@@ -509,6 +597,8 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     switch (q.epilogue) {
         case EPI_STORE: return TL_FUSED(EPI_STORE);
         case EPI_STORE_F32: return TL_FUSED(EPI_STORE_F32);
+        case EPI_PUSH_F32: return TL_FUSED(EPI_PUSH_F32);
+        case EPI_PUSH_F16: return TL_FUSED(EPI_PUSH_F16);
         case EPI_RESIDUAL: return TL_FUSED(EPI_RESIDUAL);
         case EPI_QKV_ROPE: return TL_FUSED(EPI_QKV_ROPE);
         case EPI_SWIGLU: return TL_FUSED(EPI_SWIGLU);

@@ -54,7 +54,36 @@ bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, 
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
                 long long ldx, long long ldy, cudaStream_t st);
 
-enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3, EPI_STORE_F32 = 4 };
+enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3, EPI_STORE_F32 = 4,
+                    EPI_PUSH_F32 = 5, EPI_PUSH_F16 = 6 };
+
+// Tensor-parallel exchange fused into the GEMV kernels (no collective library call in between).
+// Producer side (a K-split matmul: wo, w2; or the vocabulary-split classifier): the epilogue
+// stores its results straight into slot [my_rank] of a receive buffer in EVERY rank's memory
+// (plain peer stores over NVLink); the last CTA to finish then raises flag [my_rank] on every
+// rank to this step's epoch. Consumer side (the prologue of the next GEMV): wait, with a bound,
+// until all `world` flags of the local buffer have reached the epoch, then sum the `world`
+// partial vectors in rank order in fp32, round once to fp16 and add the residual in fp16, i.e. the
+// arithmetic of the single-GPU path up to fp32 summation order. Data is pushed into the
+// consumer's own memory; nothing is ever loaded from a peer, and no TMA multicast is involved.
+// One flag per (buffer, source rank), each on its own 128-byte line; a grid-wide counter in local
+// memory elects the last producing CTA (a per-CTA flag variant measured 10 % slower: the consumer
+// then polls world * grid flags instead of world).
+constexpr int TL_MAX_TP = 8;
+constexpr int TL_XCH_FLAG_STRIDE = 32;   // unsigned ints between two flags (one 128-byte line each)
+struct PeerExchange {
+    int world, rank;
+    int n;                               // elements per rank slot
+    // consumer view (local memory): slots [world][n] and flags [world] (stride TL_XCH_FLAG_STRIDE)
+    const void* local_slots; const unsigned int* local_flags;
+    // producer view: for every destination rank d, the address of slot [my rank] / flag [my rank] there
+    void* peer_slot[TL_MAX_TP]; unsigned int* peer_flag[TL_MAX_TP];
+    unsigned int* done_counter;          // local: CTAs of the producing kernel that finished their stores
+    const unsigned int* step_ptr;        // local: decode step counter (same value on every rank)
+    int phases_per_step, phase_id;       // epoch = *step_ptr * phases_per_step + phase_id + 1
+    // consumer extras
+    const __half* residual; __half* sum_out;   // x = residual + sum; CTA 0 also writes it to sum_out
+};
 struct FusedGemv {
     // input vector (M = 1) and optional RMSNorm prologue
     const __half* x;            // [K]
@@ -73,8 +102,12 @@ struct FusedGemv {
     // kernel adds (*pos_ptr) * kv_pitch to k_out / v_out and (*pos_ptr) * head_dim/2 to cos/sin
     const int* pos_ptr; long long kv_pitch;
     bool pdl;                   // launch with programmatic stream serialization
+    const PeerExchange* xin;    // prologue: x = residual + sum over ranks of a pushed partial vector
+    const PeerExchange* xout;   // EPI_PUSH_F32 / EPI_PUSH_F16: where the results go on every rank
 };
 int launch_fused_gemv(const FusedGemv& p, cudaStream_t st);
+// number of CTAs launch_fused_gemv uses for `total_rows` weight rows (units of two rows)
+int fused_gemv_grid(int total_rows);
 
 // ---- attn.cu: attention, fast numerics -----------------------------------------------------------
 struct DecodeAttn {

@@ -85,6 +85,29 @@ int tl_tp_allreduce_f32(float* buf, size_t n, tl_stream stream) {
     return g_coll.allreduce_sum_f32(buf, n, as_stream(stream));
 }
 
+// Fused exchange: every rank exports its receive region (64-byte IPC handle), the handles travel
+// out of band, every rank opens all of them. From then on the decode step pushes partial sums
+// with peer stores from inside the GEMV kernels instead of calling ncclAllReduce.
+int tl_tp_exchange_export(tl_llama2* m, void* handle64, int nbytes) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && handle64 && nbytes >= (int)sizeof(cudaIpcMemHandle_t), "handle buffer needs %zu bytes", sizeof(cudaIpcMemHandle_t));
+    cudaIpcMemHandle_t h;
+    TL_PROPAGATE(m->eng->xch_export(&h));
+    memcpy(handle64, &h, sizeof h);
+    return TL_OK;
+}
+int tl_tp_exchange_open(tl_llama2* m, const void* handles, int world) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(m && handles && world >= 2 && world <= TL_MAX_TP, "bad argument");
+    cudaIpcMemHandle_t h[TL_MAX_TP];
+    memcpy(h, handles, sizeof(cudaIpcMemHandle_t) * world);
+    return m->eng->xch_open(h, world);
+}
+int tl_tp_exchange_close(tl_llama2* m) {
+    TL_REQUIRE(m, "null model");
+    return m->eng->xch_close();
+}
+
 int tl_tp_destroy(void) {
     if (g_coll.comm) {
         ncclCommDestroy(g_coll.comm);

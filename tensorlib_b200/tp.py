@@ -43,5 +43,26 @@ def attach(model: "tl.Llama2", rank: int, world: int, dist) -> None:
     tl.check(lib.tl_tp_attach(model.h), "tl_tp_attach")
 
 
+def open_fused_exchange(model: "tl.Llama2", rank: int, world: int, dist) -> None:
+    """Switch the decode step from NCCL allreduces to the exchange fused into the GEMV kernels:
+    every rank exports its receive region, the 64-byte IPC handles are gathered over `dist`,
+    every rank maps all regions. Collective on the host side (all ranks must call it)."""
+    lib = tl.load()
+    buf = (C.c_ubyte * 64)()
+    tl.check(lib.tl_tp_exchange_export(model.h, buf, 64), "tl_tp_exchange_export")
+    gathered = [None] * world
+    dist.all_gather_object(gathered, bytes(buf))
+    allh = (C.c_ubyte * (64 * world)).from_buffer_copy(b"".join(gathered))
+    tl.check(lib.tl_tp_exchange_open(model.h, allh, world), "tl_tp_exchange_open")
+    dist.barrier()
+
+
+def close_fused_exchange(model: "tl.Llama2", dist) -> None:
+    tl.synchronize()
+    dist.barrier()           # nobody unmaps while a peer may still push
+    tl.load().tl_tp_exchange_close(model.h)
+    dist.barrier()
+
+
 def destroy() -> None:
     tl.load().tl_tp_destroy()

@@ -43,13 +43,21 @@ def _worker(rank: int, world: int, port: int, q):
         ids = m.decode_device(16, 12)                       # CUDA-graph decode with NCCL inside the graph
         status = tl.device_status()
         dist.barrier()
+        # the same decode with the exchange fused into the GEMV kernels (peer stores, no NCCL)
+        tp.open_fused_exchange(m, rank, world, dist)
+        m.forward(prompt, 0, all_logits=False)               # prefill still reduces over NCCL
+        lg_fused = np.concatenate([m.forward(forced[i:i + 1], 16 + i, all_logits=True) for i in range(6)])
+        m.forward(prompt, 0, all_logits=False)
+        ids_fused = m.decode_device(16, 12)
+        status |= tl.device_status()
+        tp.close_fused_exchange(m, dist)
         m.close()
         tp.destroy()
         dist.destroy_process_group()
-        q.put((rank, "ok", lg_prefill, lg_decode, ids, status))
+        q.put((rank, "ok", lg_prefill, lg_decode, ids, status, lg_fused, ids_fused))
     except Exception as e:  # pragma: no cover
         import traceback
-        q.put((rank, traceback.format_exc() + str(e), None, None, None, None))
+        q.put((rank, traceback.format_exc() + str(e), None, None, None, None, None, None))
 
 
 def test_two_rank_tensor_parallel_matches_single_gpu(tl, tiny_payload):
@@ -76,9 +84,13 @@ def test_two_rank_tensor_parallel_matches_single_gpu(tl, tiny_payload):
         p.join(timeout=60)
     for rank, msg, *_ in results:
         assert msg == "ok", f"rank {rank}: {msg}"
-    for rank, _, lp, ld, ids, status in results:
+    for rank, _, lp, ld, ids, status, lf, ids_f in results:
         assert status == 0
         assert np.abs(lp.astype(np.float32) - want_prefill).max() <= 2e-2
         assert np.abs(ld.astype(np.float32) - want_decode).max() <= 2e-2
+        assert np.abs(lf.astype(np.float32) - want_decode).max() <= 2e-2, "fused exchange"
     assert np.array_equal(results[0][4], results[1][4]), "ranks sampled different ids"
     assert np.array_equal(results[0][2].view(np.uint16), results[1][2].view(np.uint16)), "ranks disagree on logits"
+    # fused exchange: every rank sums the same partials in the same (rank) order -> identical bits
+    assert np.array_equal(results[0][6].view(np.uint16), results[1][6].view(np.uint16)), "ranks disagree (fused)"
+    assert np.array_equal(results[0][7], results[1][7]), "ranks sampled different ids (fused)"
