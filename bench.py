@@ -201,14 +201,19 @@ def roofline_gateup(tl, model, stream, torch, n_layers):
     bytes_per_launch = 2 * hid * dim * 2 + 2 * dim * 2 + hid * 2   # w1+w3, x + norm weight, out
     peak, peak_src = measured_peaks()
     achieved = bytes_per_launch / sec / 1e9
-    return {"bound": "hbm", "kernel": "k_gemv_fused<SWIGLU,NORM> (RMSNorm + w1|w3 GEMV + SiLU*up)",
+    traffic = NCU_TRAFFIC_GATEUP // model.c.tp_world   # weight rows per launch scale as 1 / ranks
+    return {"bound": "hbm", "kernel": "k_gemv_ring<SWIGLU,NORM> (RMSNorm + w1|w3 GEMV + SiLU*up)",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-            "bytes_per_launch": bytes_per_launch, "us_per_launch": sec * 1e6, "traffic": NCU_TRAFFIC_GATEUP}
+            "bytes_per_launch": bytes_per_launch, "us_per_launch": sec * 1e6, "traffic": traffic,
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch "
+                              "(profiles/gemv_ring_decode_llama2_7b.md)" + ("" if model.c.tp_world == 1 else
+                                                                            f", divided by {model.c.tp_world} ranks")}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel from the ncu
-# capture summarised under profiles/ (None until a capture exists)
-NCU_TRAFFIC_GATEUP = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel (2 x 11008 x 4096
+# fp16 weights) from the ncu capture summarised in profiles/gemv_ring_decode_llama2_7b.md:
+# 180,431,872 B read + 3,465,984 B written
+NCU_TRAFFIC_GATEUP = 183_897_856
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
