@@ -162,6 +162,16 @@ TL_API int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl
 TL_API int tl_attn_decode_f16_noalloc(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache,
                                       tl_half* out, int n_heads, int head_dim, int seq_len, int splits,
                                       tl_stream stream);
+/* causal attention of T query rows at positions start_pos .. start_pos+T-1 over positions
+ * [0, start_pos+T) of the caches, in one kernel (Transformer.cpp:56-109 for T > 1: per-head
+ * matmul, ScalarDiv, mask, softmax, per-head matmul). q, out: (T, n_heads*head_dim); caches:
+ * (max_seq, n_heads*head_dim) read in place. vt_scratch: n_heads*head_dim * ((start_pos+T+7)&~7)
+ * halfs of caller-owned device memory (receives V transposed per head). head_dim must be 128;
+ * other head sizes return TL_ERR_UNSUPPORTED (the caller composes tl_matmul_batched_f16 and
+ * tl_softmax_f16 instead, as the model path does). */
+TL_API int tl_attn_prefill_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
+                        tl_half* vt_scratch, int T, int start_pos, int n_heads, int head_dim,
+                        tl_stream stream);
 /* y[n] = residual[n] + sum_k x[k] W[n,k]  (wo / w2 GEMV + EwiseAdd, Transformer.cpp:111+:169,
  * :143+:175). y may alias residual. */
 TL_API int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,

@@ -79,6 +79,7 @@ _SIGS = {
     "tl_rmsnorm_qkv_rope_f16": [_vp, _vp, C.c_float] + [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16": [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16_noalloc": [_vp] * 4 + [_int, _int, _int, _int, _vp],
+    "tl_attn_prefill_f16": [_vp] * 5 + [_int, _int, _int, _int, _vp],
     "tl_gemv_residual_f16": [_vp, _vp, _vp, _vp, _int, _int, _vp],
     "tl_rmsnorm_gateup_swiglu_f16": [_vp, _vp, C.c_float, _vp, _vp, _vp, _int, _int, _vp],
     "tl_tp_unique_id": [_vp, _int],
@@ -294,6 +295,21 @@ def embedding(table: np.ndarray, tokens: np.ndarray) -> np.ndarray:
     dt, dk, dy = DeviceBuffer.from_numpy(table), DeviceBuffer.from_numpy(tok), DeviceBuffer(max(tok.size * D * 2, 2))
     check(load().tl_embedding_f16(dy.ptr, dt.ptr, dk.ptr, tok.size, D, V, None), "tl_embedding_f16")
     return dy.to_numpy(np.float16, (tok.size, D))
+
+
+def attn_prefill(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, start_pos: int, n_heads: int) -> np.ndarray:
+    """Causal attention of T query rows (T, n_heads*hd) at positions start_pos.. over the first
+    start_pos+T rows of the caches (max_seq, n_heads*hd): tl_attn_prefill_f16."""
+    T, width = q.shape
+    hd = width // n_heads
+    S = start_pos + T
+    dq, dk, dv = (DeviceBuffer.from_numpy(np.ascontiguousarray(a, dtype=np.float16)) for a in (q, k_cache, v_cache))
+    out = DeviceBuffer(T * width * 2)
+    vt = DeviceBuffer(width * ((S + 7) & ~7) * 2)
+    check(load().tl_attn_prefill_f16(dq.ptr, dk.ptr, dv.ptr, out.ptr, vt.ptr, T, start_pos, n_heads, hd, None),
+          "tl_attn_prefill_f16")
+    synchronize()
+    return out.to_numpy(np.float16, (T, width))
 
 
 def host_lookup_tables():

@@ -378,6 +378,22 @@ int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl_half* 
     return launch_decode_attn(a, as_stream(stream));
 }
 
+int tl_attn_prefill_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
+                        tl_half* vt_scratch, int T, int start_pos, int n_heads, int head_dim,
+                        tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(q && k_cache && v_cache && out && vt_scratch, "null pointer");
+    TL_REQUIRE(T > 0 && start_pos >= 0 && n_heads > 0 && head_dim > 0, "bad shape");
+    const int S = start_pos + T;
+    const long long pitch = (long long)n_heads * head_dim, vt_pitch = (S + 7) & ~7;
+    if (!flash_prefill_supported(q, k_cache, vt_scratch, out, T, S, start_pos, n_heads, head_dim, pitch, pitch,
+                                 vt_pitch, pitch))
+        return set_error(TL_ERR_UNSUPPORTED, "tl_attn_prefill_f16: head_dim %d (128 only) or unaligned pointers", head_dim);
+    TL_PROPAGATE(launch_transpose_v(H(vt_scratch), H(v_cache), S, n_heads, head_dim, pitch, vt_pitch, as_stream(stream)));
+    return launch_flash_prefill(H(q), H(k_cache), H(vt_scratch), H(out), T, S, start_pos, n_heads, head_dim, pitch,
+                                pitch, vt_pitch, pitch, as_stream(stream));
+}
+
 int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,
                          int N, int K, tl_stream stream) {
     TL_CHECK_INIT();

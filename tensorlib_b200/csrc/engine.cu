@@ -135,7 +135,7 @@ int Llama2Engine::allocate() {
 // the (H,T,S) score buffers only exist for multi-token passes.
 int Llama2Engine::ensure_activations(int T, int S) {
     // score buffers are sized for the whole context once they are needed at all
-    const bool need_scores = S > 0 && (scores_ == nullptr || T > act_T_);
+    const bool need_scores = S > 0 && (vt_ == nullptr || T > act_T_);
     if (T <= act_T_ && !need_scores) return TL_OK;
     if (S > 0 || act_S_ > 0) S = cfg_.max_seq_len;
     TL_CUDA(cudaDeviceSynchronize());
@@ -165,9 +165,14 @@ int Llama2Engine::ensure_activations(int T, int S) {
     TL_PROPAGATE(alloc(&logits_, (size_t)Tn * cfg_.vocab_size));
     scores_ = probs_ = vt_ = nullptr;
     if (Sn > 0) {
-        TL_PROPAGATE(alloc(&scores_, (size_t)H_local_ * Tn * Sn));
-        TL_PROPAGATE(alloc(&probs_, (size_t)H_local_ * Tn * Sn));
-        TL_PROPAGATE(alloc(&vt_, (size_t)dim_local_ * Sn));
+        // the fused prefill attention (fast numerics, head_dim 128) keeps the scores on the SM
+        const bool fused_attn = cfg_.numerics != TL_NUMERICS_REFERENCE_ORDER && hd_ == 128 &&
+                                tensor_map_encode_available();
+        if (!fused_attn) {
+            TL_PROPAGATE(alloc(&scores_, (size_t)H_local_ * Tn * Sn));
+            TL_PROPAGATE(alloc(&probs_, (size_t)H_local_ * Tn * Sn));
+        }
+        TL_PROPAGATE(alloc(&vt_, (size_t)dim_local_ * (Sn + 8)));
     }
     act_T_ = Tn;
     act_S_ = Sn;
@@ -393,7 +398,13 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
         TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dl, k_, T, dl, dl, st));
         TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dl, v_, T, dl, dl, st));
         // scores[h] = q_h . K_h^T ; softmax (scale + causal mask inside) ; att_h = P_h . V_h
-        if (hgemm_supported(q_, w.cache_k, scores_, T, S, hd_, dl, dl, S) &&
+        const long long vt_pitch = (S + 7) & ~7;
+        if (flash_prefill_supported(q_, w.cache_k, vt_, att_, T, S, pos, H, hd_, dl, dl, vt_pitch, dl)) {
+            // one kernel, scores stay in tensor memory / registers
+            launches_ -= 2;
+            TL_PROPAGATE(launch_transpose_v(vt_, w.cache_v, S, H, hd_, dl, vt_pitch, st));
+            TL_PROPAGATE(launch_flash_prefill(q_, w.cache_k, vt_, att_, T, S, pos, H, hd_, dl, dl, vt_pitch, dl, st));
+        } else if (hgemm_supported(q_, w.cache_k, scores_, T, S, hd_, dl, dl, S) &&
             hgemm_supported(scores_, vt_, att_, T, hd_, S, S, S, dl)) {
             TL_PROPAGATE(launch_hgemm(q_, w.cache_k, scores_, H, T, S, hd_, dl, dl, S, hd_, hd_, (long long)T * S, st));
             TL_PROPAGATE(launch_softmax_causal_fast(scores_, H, T, S, pos, scale, st));

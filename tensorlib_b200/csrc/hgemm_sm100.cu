@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "kernels.cuh"
+#include "sm100.cuh"
 
 namespace tlb {
 
@@ -27,83 +28,7 @@ constexpr int BM = 128, BK = 64, STAGES = 4;
 constexpr int GEMM_THREADS = 256;
 constexpr int A_BYTES = BM * BK * 2;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-// Bounded wait that also gives up as soon as another role of the CTA has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 63 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 bytes apart,
-// groups of 8 rows (one swizzle atom) 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address
-    d |= (uint64_t)1 << 16;                     // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                     // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor, kind::f16: A, B fp16 K-major, D fp32, M=128, N=n
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+using namespace sm100;
 
 struct GemmArgs {
     __half* C;
@@ -270,6 +195,15 @@ EncodeTiledFn encode_fn() {
 // rows x K fp16 operand with row pitch `ld` and batch stride `stride` (elements), box 64 x box_rows
 int make_map(CUtensorMap* map, const __half* base, int rows, int K, long long ld, long long stride, int batch,
              int box_rows) {
+    return make_tensor_map_f16(map, base, rows, K, ld, stride, batch, box_rows);
+}
+
+}  // namespace
+
+bool tensor_map_encode_available() { return encode_fn() != nullptr; }
+
+int make_tensor_map_f16(CUtensorMap* map, const __half* base, int rows, int K, long long ld, long long stride,
+                        int batch, int box_rows) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return set_error(TL_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
     const bool batched = stride != 0 && batch > 1;
@@ -283,6 +217,8 @@ int make_map(CUtensorMap* map, const __half* base, int rows, int K, long long ld
     if (r != CUDA_SUCCESS) return set_error(TL_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return TL_OK;
 }
+
+namespace {
 
 template <int BN>
 int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {

@@ -138,6 +138,14 @@ int launch_swiglu_fast(__half* out, const __half* gate, const __half* up, size_t
 int launch_transpose_v(__half* vt, const __half* v, int S, int H, int hd, long long v_pitch,
                        long long vt_pitch_s, cudaStream_t st);
 
+// ---- attn_sm100.cu: prefill attention on tcgen05 / TMEM / TMA (head_dim 128) ----------------------
+bool flash_prefill_supported(const void* q, const void* k, const void* vt, const void* out, int T, int S, int pos0,
+                             int heads, int head_dim, long long ldq, long long ldk, long long ldvt, long long ldo);
+int launch_flash_prefill(const __half* q, const __half* k, const __half* vt, __half* out, int T, int S, int pos0,
+                         int heads, int head_dim, long long ldq, long long ldk, long long ldvt, long long ldo,
+                         cudaStream_t st);
+bool tensor_map_encode_available();
+
 // ---- hgemm_sm100.cu: prefill HGEMM on tcgen05 / TMEM / TMA -----------------------------------------
 bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K,
                      size_t lda, size_t ldb, size_t ldc);

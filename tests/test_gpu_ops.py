@@ -186,3 +186,51 @@ def test_fast_softmax_and_norm_close(tl, oracle):
     xf = xn.astype(np.float64)
     want = xf / np.sqrt((xf * xf).mean(axis=1, keepdims=True) + 1e-5) * w.astype(np.float64)
     assert np.abs(got - want).max() <= 1e-2
+
+
+# ---- fused prefill attention (tcgen05 / TMEM), head_dim 128 ---------------------------------------------
+def _attention_f64(q, k, v, start_pos, n_heads):
+    """softmax(q k^T / sqrt(hd) + causal mask) v in float64 on the fp16 inputs."""
+    T, width = q.shape
+    hd, S = width // n_heads, start_pos + q.shape[0]
+    out = np.empty((T, width))
+    for h in range(n_heads):
+        qh, kh, vh = (a[:, h * hd:(h + 1) * hd].astype(np.float64) for a in (q, k[:S], v[:S]))
+        s = qh @ kh.T / np.sqrt(hd)
+        s[np.arange(S)[None, :] > (start_pos + np.arange(T))[:, None]] = -np.inf
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        out[:, h * hd:(h + 1) * hd] = (p / p.sum(axis=1, keepdims=True)) @ vh
+    return out
+
+
+@pytest.mark.parametrize("T,start_pos,n_heads", [(128, 0, 2), (200, 0, 3), (64, 0, 1), (1, 0, 2), (130, 77, 2),
+                                                  (333, 190, 2), (512, 0, 4)])
+def test_fused_prefill_attention(tl, T, start_pos, n_heads):
+    hd, S = 128, start_pos + T
+    max_seq = S + 5
+    q = synth.normal_f16(51, 1, T * n_heads * hd, 1.0).reshape(T, n_heads * hd)
+    k = synth.normal_f16(51, 2, max_seq * n_heads * hd, 1.0).reshape(max_seq, n_heads * hd)
+    v = synth.normal_f16(51, 3, max_seq * n_heads * hd, 1.0).reshape(max_seq, n_heads * hd)
+    got = tl.attn_prefill(q, k, v, start_pos, n_heads).astype(np.float64)
+    want = _attention_f64(q, k, v, start_pos, n_heads)
+    assert tl.device_status() == 0
+    # fp16 probabilities and an fp16 result: absolute error against unit-variance values
+    assert np.abs(got - want).max() <= 8e-3, (T, start_pos, np.abs(got - want).max())
+
+
+def test_fused_prefill_attention_peaked_scores_rescale(tl):
+    """Scores that keep growing along the sequence force the running-max rescale of the accumulator."""
+    T, n_heads, hd = 256, 1, 128
+    q = np.full((T, hd), 0.25, np.float16)
+    k = (np.linspace(0.0, 3.0, T, dtype=np.float64)[:, None] * np.ones((1, hd))).astype(np.float16)
+    v = synth.normal_f16(52, 3, T * hd, 1.0).reshape(T, hd)
+    got = tl.attn_prefill(q, k, v, 0, n_heads).astype(np.float64)
+    want = _attention_f64(q, k, v, 0, n_heads)
+    assert tl.device_status() == 0
+    assert np.abs(got - want).max() <= 8e-3
+
+
+def test_fused_prefill_attention_rejects_other_head_sizes(tl):
+    d = tl.DeviceBuffer(1 << 16)
+    rc = tl.load().tl_attn_prefill_f16(d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, 4, 0, 2, 48, None)
+    assert rc == 4  # TL_ERR_UNSUPPORTED
