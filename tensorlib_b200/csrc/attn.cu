@@ -173,6 +173,41 @@ __global__ void k_rmsnorm_fast(__half* out, const __half* in, const __half* w, f
         out[(size_t)t * hidden + j] = __float2half_rn(__half2float(x[j]) * rinv * __half2float(w[j]));
 }
 
+// The same arithmetic with one 128-thread block per token and 16-byte loads (hidden % 8 == 0,
+// 16-byte aligned rows): the multi-token (prefill) form, bound by HBM at 4 bytes per element.
+__global__ void __launch_bounds__(128) k_rmsnorm_fast_vec(__half* out, const __half* in, const __half* w, float eps, int hidden) {
+    __shared__ float red[4];
+    const size_t t = blockIdx.x;
+    const uint4* x4 = reinterpret_cast<const uint4*>(in + t * hidden);
+    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+    uint4* o4 = reinterpret_cast<uint4*>(out + t * hidden);
+    const int n8 = hidden >> 3;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < n8; j += 128) {
+        const uint4 v = x4[j];
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h[i]); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float rinv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)hidden + eps);
+    for (int j = threadIdx.x; j < n8; j += 128) {
+        const uint4 v = x4[j], wv = w4[j];
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = __half22float2(h[i]), g = __half22float2(wh[i]);
+            oh[i] = __floats2half2_rn(f.x * rinv * g.x, f.y * rinv * g.y);
+        }
+        o4[j] = o;
+    }
+}
+
 // softmax over the last dim with fp32 internals; optional scale and causal mask (col > pos + t)
 __global__ void k_softmax_fast(__half* out, const __half* in, size_t cols, int T, int pos, float scale, bool causal) {
     __shared__ float red[32];
@@ -477,6 +512,13 @@ namespace tlb {
 int launch_rmsnorm_fast(__half* out, const __half* in, const __half* w, float eps, int hidden,
                         int tokens, cudaStream_t st) {
     if (tokens <= 0) return TL_OK;
+    const bool vec = hidden % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in) |
+                                          reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    if (vec && tokens >= 16) {
+        k_rmsnorm_fast_vec<<<(unsigned)tokens, 128, 0, st>>>(out, in, w, eps, hidden);
+        TL_LAUNCH_CHECK();
+        return TL_OK;
+    }
     k_rmsnorm_fast<<<(unsigned)ceil_div(tokens, 8), 256, 0, st>>>(out, in, w, eps, hidden, tokens);
     TL_LAUNCH_CHECK();
     return TL_OK;

@@ -380,53 +380,89 @@ int Llama2Engine::forward_reference_order(int T, int pos, bool all_logits, cudaS
     return linear(xn_ + (size_t)t0 * dim, cls, logits_ + (size_t)t0 * cfg_.vocab_size, tn, cfg_.vocab_size, dim, st);
 }
 
-// Multi-token pass, fast numerics: unfused operators around the matmuls.
+// Multi-token pass, fast numerics. With 32-column-aligned shapes the operators next to a matmul run
+// in its epilogue: [norm] [wq|wk|wv + RoPE + KV-cache write] [attention] [wo + residual] [norm]
+// [w1|w3 + SiLU*up] [w2 + residual] = 7 launches per layer (+1 for the V transpose the fused
+// attention reads). Other shapes (and the K-split matmuls under tensor parallelism, which need the
+// allreduce between matmul and residual) take the operator-by-operator sequence.
 int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStream_t st) {
     const int dim = cfg_.dim, S = pos + T, H = H_local_, dl = dim_local_, hl = hidden_local_;
     const float scale = 1.0f / sqrtf((float)hd_);
+    const bool fused = T > 8 && tensor_map_encode_available() && hd_ % 32 == 0 && dl % 64 == 0 && hl % 32 == 0 &&
+                       dim % 32 == 0;
+    const bool fused_residual = fused && coll_ == nullptr;
     launches_++;
     TL_PROPAGATE(launch_embedding(x_, emb_, d_tokens_, T, dim, cfg_.vocab_size, st));
     for (int l = 0; l < cfg_.n_layers; l++) {
         const LayerWeights& w = layers_[l];
-        launches_ += 12;
         TL_PROPAGATE(launch_rmsnorm_fast(xn_, x_, w.attn_norm, 1e-5f, dim, T, st));
-        TL_PROPAGATE(linear(xn_, w.wq, q_, T, dl, dim, st));
-        TL_PROPAGATE(linear(xn_, w.wk, k_, T, dl, dim, st));
-        TL_PROPAGATE(linear(xn_, w.wv, v_, T, dl, dim, st));
-        TL_PROPAGATE(launch_rope(q_, q_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
-        TL_PROPAGATE(launch_rope(k_, k_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
-        TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dl, k_, T, dl, dl, st));
-        TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dl, v_, T, dl, dl, st));
+        if (fused) {
+            launches_ += 2;
+            const size_t half_hd = (size_t)hd_ / 2;
+            TL_PROPAGATE(launch_hgemm_qkv_rope(xn_, w.wq, w.wk, w.wv, q_, w.cache_k + (size_t)pos * dl,
+                                               w.cache_v + (size_t)pos * dl, T, dl, dim, dim, dim, dl, dl,
+                                               cos_t_ + (size_t)pos * half_hd, sin_t_ + (size_t)pos * half_hd, hd_, st));
+        } else {
+            launches_ += 5;   // linear() counts its own launches
+            TL_PROPAGATE(linear(xn_, w.wq, q_, T, dl, dim, st));
+            TL_PROPAGATE(linear(xn_, w.wk, k_, T, dl, dim, st));
+            TL_PROPAGATE(linear(xn_, w.wv, v_, T, dl, dim, st));
+            TL_PROPAGATE(launch_rope(q_, q_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
+            TL_PROPAGATE(launch_rope(k_, k_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
+            TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dl, k_, T, dl, dl, st));
+            TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dl, v_, T, dl, dl, st));
+        }
         // scores[h] = q_h . K_h^T ; softmax (scale + causal mask inside) ; att_h = P_h . V_h
         const long long vt_pitch = (S + 7) & ~7;
         if (flash_prefill_supported(q_, w.cache_k, vt_, att_, T, S, pos, H, hd_, dl, dl, vt_pitch, dl)) {
             // one kernel, scores stay in tensor memory / registers
-            launches_ -= 2;
+            launches_ += 2;
             TL_PROPAGATE(launch_transpose_v(vt_, w.cache_v, S, H, hd_, dl, vt_pitch, st));
             TL_PROPAGATE(launch_flash_prefill(q_, w.cache_k, vt_, att_, T, S, pos, H, hd_, dl, dl, vt_pitch, dl, st));
         } else if (hgemm_supported(q_, w.cache_k, scores_, T, S, hd_, dl, dl, S) &&
-            hgemm_supported(scores_, vt_, att_, T, hd_, S, S, S, dl)) {
+                   hgemm_supported(scores_, vt_, att_, T, hd_, S, S, S, dl)) {
+            launches_ += 4;
             TL_PROPAGATE(launch_hgemm(q_, w.cache_k, scores_, H, T, S, hd_, dl, dl, S, hd_, hd_, (long long)T * S, st));
             TL_PROPAGATE(launch_softmax_causal_fast(scores_, H, T, S, pos, scale, st));
             TL_PROPAGATE(launch_transpose_v(vt_, w.cache_v, S, H, hd_, dl, S, st));
             TL_PROPAGATE(launch_hgemm(scores_, vt_, att_, H, T, hd_, S, S, S, dl, (long long)T * S, (long long)hd_ * S, hd_, st));
         } else {
+            launches_ += 3;
             SeqMatmul qk{q_, w.cache_k, scores_, H, T, S, hd_, dl, 1, dl, 1, S, hd_, hd_, (long long)T * S};
             TL_PROPAGATE(launch_matmul_seq(qk, st));
             TL_PROPAGATE(launch_softmax_causal_fast(scores_, H, T, S, pos, scale, st));
             SeqMatmul pv{scores_, w.cache_v, att_, H, T, hd_, S, S, 1, 1, dl, dl, (long long)T * S, hd_, hd_};
             TL_PROPAGATE(launch_matmul_seq(pv, st));
         }
-        TL_PROPAGATE(linear(att_, w.wo, ao_, T, dim, dl, st));
-        if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
-        TL_PROPAGATE(launch_binary(h_, x_, ao_, (size_t)T * dim, 0, st));
+        if (fused_residual) {
+            launches_++;
+            TL_PROPAGATE(launch_hgemm_residual(att_, w.wo, x_, h_, T, dim, dl, dl, dl, dim, dim, st));
+        } else {
+            launches_++;
+            TL_PROPAGATE(linear(att_, w.wo, ao_, T, dim, dl, st));
+            if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
+            TL_PROPAGATE(launch_binary(h_, x_, ao_, (size_t)T * dim, 0, st));
+        }
+        launches_++;
         TL_PROPAGATE(launch_rmsnorm_fast(xn_, h_, w.ffn_norm, 1e-5f, dim, T, st));
-        TL_PROPAGATE(linear(xn_, w.w1, g_, T, hl, dim, st));
-        TL_PROPAGATE(linear(xn_, w.w3, u_, T, hl, dim, st));
-        TL_PROPAGATE(launch_swiglu_fast(g_, g_, u_, (size_t)T * hl, st));
-        TL_PROPAGATE(linear(g_, w.w2, ao_, T, dim, hl, st));
-        if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
-        TL_PROPAGATE(launch_binary(x_, h_, ao_, (size_t)T * dim, 0, st));
+        if (fused) {
+            launches_++;
+            TL_PROPAGATE(launch_hgemm_swiglu(xn_, w.w1, w.w3, g_, T, hl, dim, dim, dim, hl, st));
+        } else {
+            launches_++;
+            TL_PROPAGATE(linear(xn_, w.w1, g_, T, hl, dim, st));
+            TL_PROPAGATE(linear(xn_, w.w3, u_, T, hl, dim, st));
+            TL_PROPAGATE(launch_swiglu_fast(g_, g_, u_, (size_t)T * hl, st));
+        }
+        if (fused_residual) {
+            launches_++;
+            TL_PROPAGATE(launch_hgemm_residual(g_, w.w2, h_, x_, T, dim, hl, hl, hl, dim, dim, st));
+        } else {
+            launches_++;
+            TL_PROPAGATE(linear(g_, w.w2, ao_, T, dim, hl, st));
+            if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
+            TL_PROPAGATE(launch_binary(x_, h_, ao_, (size_t)T * dim, 0, st));
+        }
     }
     launches_ += 1;
     const int t0 = all_logits ? 0 : T - 1, tn = all_logits ? T : 1;

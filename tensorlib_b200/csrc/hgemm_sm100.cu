@@ -11,6 +11,15 @@
 // the (batch, m-tile, n-tile) list. Warp roles: 0 TMA producer, 1 MMA issuer, 2 TMEM allocator,
 // 4-7 epilogue. Bound: tensor pipe for M >= ~512 (2*M*N*K flops), HBM (the B operand) below.
 //
+// Epilogues fused for the Llama2 block (the operators the reference launches right after the
+// matmul, model/llama2_7b/src/Transformer.cpp):
+//   RESIDUAL  C = half(A B^T) + R                 wo / w2 matmul + EwiseAdd            (:111+:169, :143+:175)
+//   SWIGLU    C = silu(A W1^T) * (A W3^T)         w1, w3 matmuls + silu + EwiseMul     (:136-141)
+//             the B tile is 128 rows of W1 next to the same 128 rows of W3 (two TMA loads), so
+//             gate and up of one output column sit in one accumulator row
+//   QKV_ROPE  q, k, v = A [Wq|Wk|Wv]^T; rotary embedding on q and k; k, v written straight into
+//             the KV cache rows of their positions                                    (:35-53)
+//
 // Every mbarrier wait is bounded; when one gives up the CTA raises an abort flag, every role
 // leaves its loop, TMEM is freed and TL_ERR_TIMEOUT is recorded in the device status word.
 #include <cuda.h>
@@ -30,20 +39,91 @@ constexpr int A_BYTES = BM * BK * 2;
 
 using namespace sm100;
 
+enum { GEPI_STORE = 0, GEPI_RESIDUAL = 1, GEPI_SWIGLU = 2, GEPI_QKV_ROPE = 3 };
+
 struct GemmArgs {
     __half* C;
     int M, N, K, batch;
     long long ldc, sC;
     int a_batched, b_batched;   // 0: the operand is shared by all batches (batch coordinate 0)
     int* status;
+    // RESIDUAL
+    const __half* R; long long ldr;
+    // QKV_ROPE: N = n_each columns per matrix; q -> C, k -> kc, v -> vc (row t = position pos0 + t,
+    // the pointers already point at position pos0); cos/sin rows [t][head_dim / 2] likewise
+    __half* kc; __half* vc; long long ld_kv;
+    const __half* cos_t; const __half* sin_t;
+    int head_dim;
 };
 
-template <int BN>
+// 32 consecutive columns of one output row: fp32 accumulators -> fp16 -> 64 bytes
+__device__ __forceinline__ void store32(__half* dst, const uint32_t* r) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            oh[j] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+        *reinterpret_cast<uint4*>(dst + v * 8) = o;
+    }
+}
+__device__ __forceinline__ void store32_residual(__half* dst, const __half* res, const uint32_t* r) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        uint4 o, rr = *reinterpret_cast<const uint4*>(res + v * 8);
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+        const __half2* rh = reinterpret_cast<const __half2*>(&rr);
+#pragma unroll
+        for (int j = 0; j < 4; j++)   // the matmul result is rounded to fp16 first, then added in fp16
+            oh[j] = __hadd2(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1])), rh[j]);
+        *reinterpret_cast<uint4*>(dst + v * 8) = o;
+    }
+}
+// interleaved-pair rotation (x0, x1) -> (x0 c - x1 s, x0 s + x1 c), every product and sum rounded
+// to fp16 like the reference's apply_rotary_emb (tensorLib/src/device/CPU.cpp:427-461)
+__device__ __forceinline__ void store32_rope(__half* dst, const __half* cosr, const __half* sinr, const uint32_t* r) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        uint2 cc = *reinterpret_cast<const uint2*>(cosr + v * 4), ss = *reinterpret_cast<const uint2*>(sinr + v * 4);
+        const __half* ch = reinterpret_cast<const __half*>(&cc);
+        const __half* sh = reinterpret_cast<const __half*>(&ss);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 x = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+            const __half2 t1 = __hmul2(x, __half2half2(ch[j]));                          // (x0 c, x1 c)
+            const __half2 t2 = __hmul2(__lowhigh2highlow(x), __half2half2(sh[j]));       // (x1 s, x0 s)
+            oh[j] = __halves2half2(__hsub(__low2half(t1), __low2half(t2)), __hadd(__high2half(t2), __high2half(t1)));
+        }
+        *reinterpret_cast<uint4*>(dst + v * 8) = o;
+    }
+}
+// silu(gate) * up with the gate through float: g / (1 + exp(-g)), rounded to fp16, then an fp16 product
+__device__ __forceinline__ void store32_swiglu(__half* dst, const uint32_t* g, const uint32_t* u) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        uint4 o;
+        __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float gf = __half2float(__float2half_rn(__uint_as_float(g[v * 8 + j])));
+            const __half s = __float2half_rn(gf / (1.f + __expf(-gf)));
+            oh[j] = __hmul(s, __float2half_rn(__uint_as_float(u[v * 8 + j])));
+        }
+        *reinterpret_cast<uint4*>(dst + v * 8) = o;
+    }
+}
+
+template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
+k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+        const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmB3, GemmArgs p) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = 2 * BN;      // two accumulator buffers
+    constexpr int OUT_COLS = EPI == GEPI_SWIGLU ? BN / 2 : BN;   // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -54,7 +134,9 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int mt_count = (p.M + BM - 1) / BM, nt_count = (p.N + BN - 1) / BN;
+    const int mt_count = (p.M + BM - 1) / BM;
+    const int nt_each = (p.N + OUT_COLS - 1) / OUT_COLS;                 // column tiles per weight matrix
+    const int nt_count = EPI == GEPI_QKV_ROPE ? 3 * nt_each : nt_each;
     const int tiles_per_batch = mt_count * nt_count;
     const int total_tiles = tiles_per_batch * p.batch;
     const int nkb = (p.K + BK - 1) / BK;
@@ -65,10 +147,7 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 2) {  // TMEM allocation: one warp, result written to shared memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    if (warp == 2) tmem_alloc<TMEM_COLS>(tmem_slot);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -78,18 +157,27 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         // ---------------- TMA producer ---------------------------------------------------------
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        if (EPI == GEPI_SWIGLU || EPI == GEPI_QKV_ROPE) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB2) : "memory");
+        if (EPI == GEPI_QKV_ROPE) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB3) : "memory");
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
             const int mt = idx % mt_count, nt = idx / mt_count;
+            const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
+            const CUtensorMap* mb = which == 0 ? &tmB : (which == 1 ? &tmB2 : &tmB3);
             for (int kb = 0; kb < nkb; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
                 if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
                 const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
                 mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_3d(sa, &tmA, kb * BK, mt * BM, p.a_batched ? b : 0, full0 + 8 * s);
-                tma_load_3d(sb, &tmB, kb * BK, nt * BN, p.b_batched ? b : 0, full0 + 8 * s);
+                if (EPI == GEPI_SWIGLU) {   // rows [0, BN/2): W1, rows [BN/2, BN): the same rows of W3
+                    tma_load_3d(sb, &tmB, kb * BK, ntl * OUT_COLS, 0, full0 + 8 * s);
+                    tma_load_3d(sb + B_BYTES / 2, &tmB2, kb * BK, ntl * OUT_COLS, 0, full0 + 8 * s);
+                } else {
+                    tma_load_3d(sb, mb, kb * BK, ntl * BN, p.b_batched ? b : 0, full0 + 8 * s);
+                }
             }
         }
         if (!ok) {  // let copies already in flight land before the CTA goes away
@@ -121,7 +209,7 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
             if (ok) umma_commit(tfull0 + 8 * buf);  // accumulator complete
         }
     } else if (warp >= 4) {
-        // ---------------- epilogue: TMEM -> registers -> fp16 -> global -----------------------------
+        // ---------------- epilogue: TMEM -> registers -> fp16 (+ fused operator) -> global -------------
         const int q = warp & 3;                   // TMEM lane quarter this warp may access
         int tcount = 0;
         bool ok = true;
@@ -129,30 +217,45 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tcount++) {
             const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
             const int mt = idx % mt_count, nt = idx / mt_count;
+            const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
             const int buf = tcount & 1, use = tcount >> 1;
             ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             const int row = mt * BM + q * 32 + lane;
+            const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
+            if (EPI == GEPI_SWIGLU) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c), r);
-                tmem_ld_wait();
-                const int col0 = nt * BN + c;
-                if (row < p.M && col0 < p.N) {
-                    if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++) {
-                            uint4 o;
-                            __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-                            for (int j = 0; j < 4; j++)
-                                oh[j] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-                            *reinterpret_cast<uint4*>(crow + col0 + v * 8) = o;
+                for (int c = 0; c < OUT_COLS; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(tbase + (uint32_t)c, g);
+                    tmem_ld32(tbase + (uint32_t)(OUT_COLS + c), u);
+                    tmem_ld_wait();
+                    const int col0 = ntl * OUT_COLS + c;
+                    if (row < p.M && col0 < p.N) store32_swiglu(crow + col0, g, u);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tbase + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    const int col0 = ntl * BN + c;
+                    if (row >= p.M || col0 >= p.N) continue;
+                    if (EPI == GEPI_RESIDUAL) {
+                        store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
+                    } else if (EPI == GEPI_QKV_ROPE) {
+                        if (which == 2) {
+                            store32(p.vc + (long long)row * p.ld_kv + col0, r);
+                        } else {
+                            const int half_dim = p.head_dim >> 1, d2 = (col0 % p.head_dim) >> 1;
+                            __half* dst = which == 0 ? crow + col0 : p.kc + (long long)row * p.ld_kv + col0;
+                            store32_rope(dst, p.cos_t + (long long)row * half_dim + d2, p.sin_t + (long long)row * half_dim + d2, r);
                         }
+                    } else if (vec_ok && col0 + 32 <= p.N) {
+                        store32(crow + col0, r);
                     } else {
                         for (int j = 0; j < 32 && col0 + j < p.N; j++)
                             crow[col0 + j] = __float2half_rn(__uint_as_float(r[j]));
@@ -169,7 +272,7 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     __syncthreads();
     if (warp == 2) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        tmem_dealloc<TMEM_COLS>(tmem_base);
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
@@ -190,12 +293,6 @@ EncodeTiledFn encode_fn() {
             g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     });
     return g_encode;
-}
-
-// rows x K fp16 operand with row pitch `ld` and batch stride `stride` (elements), box 64 x box_rows
-int make_map(CUtensorMap* map, const __half* base, int rows, int K, long long ld, long long stride, int batch,
-             int box_rows) {
-    return make_tensor_map_f16(map, base, rows, K, ld, stride, batch, box_rows);
 }
 
 }  // namespace
@@ -220,25 +317,34 @@ int make_tensor_map_f16(CUtensorMap* map, const __half* base, int rows, int K, l
 
 namespace {
 
-template <int BN>
-int launch_bn(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {
+template <int BN, int EPI>
+int launch_k(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
+             const GemmArgs& a, int tiles, cudaStream_t st) {
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
     static bool configured = false;
     if (!configured) {
-        TL_CUDA(cudaFuncSetAttribute(k_hgemm<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TL_CUDA(cudaFuncSetAttribute(k_hgemm<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     const int grid = std::max(1, std::min(tiles, sm_count()));
-    k_hgemm<BN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, a);
+    k_hgemm<BN, EPI><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mb2, mb3, a);
     TL_LAUNCH_CHECK();
     return TL_OK;
 }
+template <int EPI>
+int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
+                  const GemmArgs& a, int tiles, cudaStream_t st) {
+    if (bn == 256) return launch_k<256, EPI>(ma, mb, mb2, mb3, a, tiles, st);
+    if (bn == 128) return launch_k<128, EPI>(ma, mb, mb2, mb3, a, tiles, st);
+    return launch_k<64, EPI>(ma, mb, mb2, mb3, a, tiles, st);
+}
+
+inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
 }  // namespace
 
 bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
                      size_t ldb, size_t ldc) {
-    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     (void)C; (void)ldc;
     return M >= 1 && N >= 1 && K >= 8 && lda % 8 == 0 && ldb % 8 == 0 && al16(A) && al16(B) && encode_fn() != nullptr;
 }
@@ -253,14 +359,77 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     int bn = 256;
     while (bn > 64 && (long long)mt * ((N + bn - 1) / bn) * batch < sm_count()) bn >>= 1;
     CUtensorMap ma, mb;
-    TL_PROPAGATE(make_map(&ma, A, M, K, lda, sA, batch, BM));
-    TL_PROPAGATE(make_map(&mb, B, N, K, ldb, sB, batch, bn));
-    GemmArgs a{C, M, N, K, batch, ldc, sC, (sA != 0 && batch > 1) ? 1 : 0, (sB != 0 && batch > 1) ? 1 : 0,
-               device_status_word()};
+    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
+    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, bn));
+    GemmArgs a{};
+    a.C = C; a.M = M; a.N = N; a.K = K; a.batch = batch; a.ldc = ldc; a.sC = sC;
+    a.a_batched = (sA != 0 && batch > 1) ? 1 : 0; a.b_batched = (sB != 0 && batch > 1) ? 1 : 0;
+    a.status = device_status_word();
     const int tiles = mt * ((N + bn - 1) / bn) * batch;
-    if (bn == 256) return launch_bn<256>(ma, mb, a, tiles, st);
-    if (bn == 128) return launch_bn<128>(ma, mb, a, tiles, st);
-    return launch_bn<64>(ma, mb, a, tiles, st);
+    return launch_any_bn<GEPI_STORE>(bn, ma, mb, mb, mb, a, tiles, st);
+}
+
+// The fused forms need full 32-column chunks and 16-byte aligned rows everywhere.
+bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
+                           size_t ldb, size_t ldc) {
+    return hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc) && N % 32 == 0 && ldc % 8 == 0 && al16(C);
+}
+
+// C = half(A B^T) + R
+int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __half* C, int M, int N, int K,
+                          long long lda, long long ldb, long long ldr, long long ldc, cudaStream_t st) {
+    TL_REQUIRE(hgemm_fused_supported(A, B, C, M, N, K, lda, ldb, ldc) && R && al16(R) && ldr % 8 == 0,
+               "hgemm+residual: unsupported shape or alignment");
+    const int mt = (M + BM - 1) / BM;
+    int bn = 256;
+    while (bn > 64 && (long long)mt * ((N + bn - 1) / bn) < sm_count()) bn >>= 1;
+    CUtensorMap ma, mb;
+    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
+    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, bn));
+    GemmArgs a{};
+    a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
+    a.R = R; a.ldr = ldr;
+    return launch_any_bn<GEPI_RESIDUAL>(bn, ma, mb, mb, mb, a, mt * ((N + bn - 1) / bn), st);
+}
+
+// C[M, N] = silu(A W1^T) * (A W3^T); W1, W3: [N, K]
+int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __half* C, int M, int N, int K,
+                        long long lda, long long ldb, long long ldc, cudaStream_t st) {
+    TL_REQUIRE(hgemm_fused_supported(A, W1, C, M, N, K, lda, ldb, ldc) && W3 && al16(W3),
+               "hgemm+swiglu: unsupported shape or alignment");
+    const int mt = (M + BM - 1) / BM, nt = (N + 127) / 128;
+    CUtensorMap ma, m1, m3;
+    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
+    TL_PROPAGATE(make_tensor_map_f16(&m1, W1, N, K, ldb, 0, 1, 128));
+    TL_PROPAGATE(make_tensor_map_f16(&m3, W3, N, K, ldb, 0, 1, 128));
+    GemmArgs a{};
+    a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
+    return launch_k<256, GEPI_SWIGLU>(ma, m1, m3, m3, a, mt * nt, st);
+}
+
+// q[M, n_each] = rope(A Wq^T) -> q_out; rope(A Wk^T) -> k_rows; A Wv^T -> v_rows. Row t of k_rows /
+// v_rows / cos_rows / sin_rows belongs to the position of token t (the caller offsets the bases).
+int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, const __half* Wv, __half* q_out,
+                          __half* k_rows, __half* v_rows, int M, int n_each, int K, long long lda, long long ldb,
+                          long long ldq, long long ld_kv, const __half* cos_rows, const __half* sin_rows,
+                          int head_dim, cudaStream_t st) {
+    TL_REQUIRE(hgemm_fused_supported(A, Wq, q_out, M, n_each, K, lda, ldb, ldq) && al16(Wk) && al16(Wv) &&
+                   al16(k_rows) && al16(v_rows) && ld_kv % 8 == 0 && head_dim % 32 == 0 && n_each % head_dim == 0 &&
+                   n_each % 64 == 0 && cos_rows && sin_rows && (reinterpret_cast<uintptr_t>(cos_rows) & 7) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sin_rows) & 7) == 0,
+               "hgemm+qkv+rope: unsupported shape or alignment");
+    const int mt = (M + BM - 1) / BM;
+    int bn = 256;
+    while (bn > 64 && (n_each % bn != 0 || (long long)mt * 3 * (n_each / bn) < sm_count())) bn >>= 1;
+    CUtensorMap ma, mq, mk, mv;
+    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
+    TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, bn));
+    TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, bn));
+    TL_PROPAGATE(make_tensor_map_f16(&mv, Wv, n_each, K, ldb, 0, 1, bn));
+    GemmArgs a{};
+    a.C = q_out; a.M = M; a.N = n_each; a.K = K; a.batch = 1; a.ldc = ldq; a.status = device_status_word();
+    a.kc = k_rows; a.vc = v_rows; a.ld_kv = ld_kv; a.cos_t = cos_rows; a.sin_t = sin_rows; a.head_dim = head_dim;
+    return launch_any_bn<GEPI_QKV_ROPE>(bn, ma, mq, mk, mv, a, mt * 3 * (n_each / bn), st);
 }
 
 }  // namespace tlb

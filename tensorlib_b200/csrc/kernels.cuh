@@ -153,4 +153,16 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
                  long long lda, long long ldb, long long ldc, long long sA, long long sB,
                  long long sC, cudaStream_t st);
 
+// fused epilogues of the prefill HGEMM (N % 32 == 0, 16-byte aligned rows)
+bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
+                           size_t ldb, size_t ldc);
+int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __half* C, int M, int N, int K,
+                          long long lda, long long ldb, long long ldr, long long ldc, cudaStream_t st);
+int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __half* C, int M, int N, int K,
+                        long long lda, long long ldb, long long ldc, cudaStream_t st);
+int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, const __half* Wv, __half* q_out,
+                          __half* k_rows, __half* v_rows, int M, int n_each, int K, long long lda, long long ldb,
+                          long long ldq, long long ld_kv, const __half* cos_rows, const __half* sin_rows,
+                          int head_dim, cudaStream_t st);
+
 }  // namespace tlb

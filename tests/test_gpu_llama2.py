@@ -155,3 +155,35 @@ def test_checkpoint_file_loader(tl, tmp_path, golden_tiny, tiny_payload):
     with pytest.raises(tl.TLError):
         m.load_file(str(tmp_path / "missing.bin"))
     m.close()
+
+
+# head_dim 128 and 32-column-aligned widths: the shapes that take the fused prefill path
+# (matmul epilogues with RoPE / KV write / residual / SiLU*up, attention in one kernel)
+MID = synth.LlamaConfig(dim=512, hidden_dim=1408, n_layers=2, n_heads=4, vocab_size=1000, seq_len=384)
+
+
+@pytest.mark.parametrize("T,tail", [(200, 3), (20, 2), (300, 2)])
+def test_fast_fused_prefill_matches_oracle_at_head_dim_128(tl, oracle, T, tail):
+    payload = synth.llama2c_payload(MID, 777)
+    tokens = synth.token_ids(777, 5, T + tail, MID.vocab_size)
+    m = tl.Llama2(MID, numerics=tl.FAST)
+    m.load_payload(payload, shared_classifier=True)
+    mo = oracle.llama2(MID, payload)
+    got = [m.forward(tokens[:T], 0, all_logits=True)]
+    want = [mo.forward(tokens[:T], 0, 1)]
+    # a chunked continuation (start_pos > 0, T > 1) and single-token decode steps over the same cache
+    got.append(m.forward(tokens[T:T + tail - 1], T, all_logits=True) if tail > 2 else np.zeros((0, MID.vocab_size), np.float16))
+    want.append(mo.forward(tokens[T:T + tail - 1], T, 1) if tail > 2 else np.zeros((0, MID.vocab_size), np.float16))
+    p = T + (tail - 1 if tail > 2 else 0)
+    while p < T + tail:
+        got.append(m.forward(tokens[p:p + 1], p, all_logits=True))
+        want.append(mo.forward(tokens[p:p + 1], p, 1))
+        p += 1
+    got, want = np.concatenate(got).astype(np.float32), np.concatenate(want).astype(np.float32)
+    assert tl.device_status() == 0
+    err = np.abs(got - want).max()
+    assert err <= 2e-2, f"max abs logit error {err} (logits are O(1))"
+    s = np.sort(want, axis=1)
+    clear = (s[:, -1] - s[:, -2]) > 2 * err
+    assert np.array_equal(got.argmax(1)[clear], want.argmax(1)[clear])
+    m.close()
