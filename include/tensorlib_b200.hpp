@@ -1,0 +1,197 @@
+// C++ host mirror of the reference's user-visible API for the matmul -> Llama2 forward path, over
+// the C ABI of tensorlib_b200.h. Header-only, C++17, no CUDA headers needed by the includer.
+//
+//   reference (DavidZyy/tensorLib)                              here (namespace tlb200)
+//   Tensor<half>::matmul(other, result_opt)   Tensor.hpp:90     Tensor::matmul(other, result_opt)
+//   Tensor<half>::transpose(0, 1) view        Tensor.cpp:277+   Tensor::transpose()  (last two dims)
+//   nn::Linear<half>::forward(x, result_opt)  nn/linear.hpp:13  nn::Linear::forward(x, result_opt)
+//   ModelArgs                                 Transformer.hpp:13 ModelArgs
+//   Transformer<half>::forward(tokens, start_pos, buf)  Transformer.hpp:80
+//                                                               Transformer::forward(tokens, start_pos)
+//   Llama2<half>::generate(prompt_tokens)     llama2.hpp:19     Llama2::generate(prompt_tokens, max_new)
+//
+// Error behaviour follows the reference: argument/shape errors throw std::invalid_argument
+// (matmul.cpp:209-221); CUDA failures, which the reference answers with exit(1) (CUDA.cuh:131-151),
+// throw tlb200::Error so that an embedding application can decide.
+// Tensors live in device memory ("cuda" is the only device type: there is no CPU path).
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "tensorlib_b200.h"
+
+namespace tlb200 {
+
+class Error : public std::runtime_error {
+public:
+    Error(int status, const std::string& what) : std::runtime_error(what), status(status) {}
+    int status;
+};
+
+inline void check(int status) {
+    if (status == TL_OK) return;
+    const std::string msg = tl_last_error();
+    if (status == TL_ERR_INVALID_ARGUMENT) throw std::invalid_argument(msg);
+    throw Error(status, msg);
+}
+
+inline void init(int device = 0) { check(tl_init(device)); }
+
+// fp16 tensor in device memory: contiguous row-major storage, plus an optional "last two
+// dimensions swapped" view (what the reference's transpose(0,1) of a 2-D weight produces).
+class Tensor {
+public:
+    Tensor() = default;
+    explicit Tensor(const std::vector<int>& shape) : shape_(shape) {
+        void* p = nullptr;
+        check(tl_malloc(&p, bytes()));
+        data_ = std::shared_ptr<void>(p, [](void* q) { tl_free(q); });
+    }
+    // copy `numel()` fp16 values (raw 16-bit patterns) from host memory
+    Tensor(const std::vector<int>& shape, const uint16_t* host) : Tensor(shape) {
+        check(tl_memcpy_h2d(data_.get(), host, bytes(), nullptr));
+        check(tl_stream_synchronize(nullptr));
+    }
+    const std::vector<int>& shape() const { return shape_; }
+    size_t numel() const {
+        size_t n = 1;
+        for (int d : shape_) n *= (size_t)d;
+        return n;
+    }
+    size_t bytes() const { return numel() * sizeof(uint16_t); }
+    tl_half* data() const { return static_cast<tl_half*>(data_.get()); }
+    bool is_transposed_view() const { return transposed_; }
+    std::vector<uint16_t> to_host() const {
+        if (transposed_) throw std::invalid_argument("to_host: make the view contiguous first");
+        std::vector<uint16_t> out(numel());
+        check(tl_memcpy_d2h(out.data(), data_.get(), bytes(), nullptr));
+        check(tl_stream_synchronize(nullptr));
+        return out;
+    }
+    // view with the last two dimensions swapped; shares storage (Tensor.cpp:277-304)
+    Tensor transpose() const {
+        if (shape_.size() < 2) throw std::invalid_argument("transpose: needs at least 2 dimensions");
+        Tensor v = *this;
+        std::swap(v.shape_[v.shape_.size() - 1], v.shape_[v.shape_.size() - 2]);
+        v.transposed_ = !transposed_;
+        return v;
+    }
+    // this: (..., M, K) contiguous; other: a transposed view of (..., N, K) storage, i.e. logical
+    // (..., K, N) — the form every matmul on the Llama2 path has (Linear: x . W^T,
+    // attention: q . k^T). Leading dimensions of `other` broadcast when it has none.
+    // result_opt: caller-owned output of shape (..., M, N), returned (Tensor.hpp:90).
+    Tensor matmul(const Tensor& other, std::optional<Tensor> result_opt = std::nullopt,
+                  int numerics = TL_NUMERICS_FAST) const {
+        if (transposed_) throw std::invalid_argument("matmul: left operand must be contiguous");
+        if (!other.transposed_)
+            throw std::invalid_argument("matmul: right operand must be a transposed view of (N, K) row-major storage");
+        if (shape_.size() < 2 || other.shape_.size() < 2) throw std::invalid_argument("matmul: operands need 2 dimensions");
+        const size_t M = (size_t)shape_[shape_.size() - 2], K = (size_t)shape_.back();
+        const size_t Kb = (size_t)other.shape_[other.shape_.size() - 2], N = (size_t)other.shape_.back();
+        if (K != Kb) throw std::invalid_argument("matmul: inner dimensions differ");   // matmul.cpp:209-221
+        size_t batch = 1, batch_b = 1;
+        for (size_t i = 0; i + 2 < shape_.size(); i++) batch *= (size_t)shape_[i];
+        for (size_t i = 0; i + 2 < other.shape_.size(); i++) batch_b *= (size_t)other.shape_[i];
+        if (batch_b != 1 && batch_b != batch) throw std::invalid_argument("matmul: batch dimensions do not broadcast");
+        std::vector<int> out_shape(shape_.begin(), shape_.end() - 1);
+        out_shape.push_back((int)N);
+        Tensor out = result_opt ? *result_opt : Tensor(out_shape);
+        if (out.transposed_ || out.numel() != batch * M * N) throw std::invalid_argument("matmul: result has the wrong size");
+        check(tl_matmul_batched_f16(data(), other.data(), out.data(), batch, M, N, K, K, K, N, M * K,
+                                    batch_b == 1 ? 0 : N * K, M * N, numerics, nullptr));
+        out.shape_ = out_shape;
+        return out;
+    }
+
+private:
+    std::vector<int> shape_;
+    std::shared_ptr<void> data_;
+    bool transposed_ = false;
+};
+
+namespace nn {
+// weight [out_features, in_features] as in the checkpoint (linear.cpp:10-14)
+class Linear {
+public:
+    Linear() = default;
+    Linear(int in_features, int out_features, Tensor weight)
+        : in_features(in_features), out_features(out_features), weight(std::move(weight)) {
+        if (this->weight.shape() != std::vector<int>{out_features, in_features})
+            throw std::invalid_argument("Linear: weight must be (out_features, in_features)");
+    }
+    // x.matmul(weight.transpose(0, 1), result_opt)   (linear.cpp:43-49)
+    Tensor forward(const Tensor& input, std::optional<Tensor> result_opt = std::nullopt) const {
+        return input.matmul(weight.transpose(), std::move(result_opt));
+    }
+    int in_features = 0, out_features = 0;
+    Tensor weight;
+};
+}  // namespace nn
+
+struct ModelArgs {          // Transformer.hpp:13-24
+    int dim = 0, hidden_dim = 0, n_layers = 0, n_heads = 0, vocab_size = 0, n_kv_heads = 0;
+    int max_batch_size = 1, max_seq_len = 0;
+};
+
+// Llama2 decoder. forward() takes token ids on the host and returns the logits of every position
+// (T, vocab) on the host, like the reference's Transformer::forward followed by the caller's copy
+// (Transformer.cpp:264-299); activation buffers are owned by the model, not passed in.
+class Transformer {
+public:
+    explicit Transformer(const ModelArgs& args, int numerics = TL_NUMERICS_FAST, bool silu_via_float = true) : args(args) {
+        tl_llama2_config c{};
+        c.dim = args.dim; c.hidden_dim = args.hidden_dim; c.n_layers = args.n_layers; c.n_heads = args.n_heads;
+        c.n_kv_heads = args.n_kv_heads ? args.n_kv_heads : args.n_heads; c.vocab_size = args.vocab_size;
+        c.max_seq_len = args.max_seq_len; c.numerics = numerics; c.silu_via_float = silu_via_float ? 1 : 0;
+        c.tp_rank = 0; c.tp_world = 1; c.one_kernel_decode = 0;
+        tl_llama2* h = nullptr;
+        check(tl_llama2_create(&c, &h));
+        handle_ = std::shared_ptr<tl_llama2>(h, [](tl_llama2* q) { tl_llama2_destroy(q); });
+    }
+    // read_checkpoint + read_weights (main.cpp:195-228, :36-190): a llama2.c file, header included
+    void load_checkpoint(const std::string& path) { check(tl_llama2_load_file(handle_.get(), path.c_str())); }
+    std::vector<uint16_t> forward(const std::vector<int>& tokens, int start_pos) const {
+        std::vector<uint16_t> logits(tokens.size() * (size_t)args.vocab_size);
+        check(tl_llama2_forward(handle_.get(), tokens.data(), (int)tokens.size(), start_pos,
+                                reinterpret_cast<tl_half*>(logits.data()), nullptr));
+        return logits;
+    }
+    tl_llama2* handle() const { return handle_.get(); }
+    ModelArgs args;
+
+private:
+    std::shared_ptr<tl_llama2> handle_;
+};
+
+struct GenerateResult {
+    std::vector<int> tokens;          // generated ids (without the prompt)
+    double prefill_seconds = 0, decode_seconds = 0;
+    double tokens_per_second() const { return decode_seconds > 0 ? (tokens.size() - 1) / decode_seconds : 0; }
+};
+
+// Llama2::generate (llama2.cpp:15-101): prefill, then greedy steps; stops early on id 1 or 2 when
+// stop_on_eos is set (llama2.cpp:88-91). The tokenizer and chat loop are outside this path.
+class Llama2 {
+public:
+    Llama2(const ModelArgs& args, const std::string& checkpoint_path, int numerics = TL_NUMERICS_FAST)
+        : model(args, numerics) {
+        model.load_checkpoint(checkpoint_path);
+    }
+    GenerateResult generate(const std::vector<int>& prompt_tokens, int max_new = 256, bool stop_on_eos = true) {
+        GenerateResult r;
+        r.tokens.resize((size_t)max_new);
+        int n_out = 0;
+        check(tl_llama2_generate(model.handle(), prompt_tokens.data(), (int)prompt_tokens.size(), max_new,
+                                 stop_on_eos ? 1 : 0, r.tokens.data(), &n_out, &r.prefill_seconds, &r.decode_seconds));
+        r.tokens.resize((size_t)n_out);
+        return r;
+    }
+    Transformer model;
+};
+
+}  // namespace tlb200

@@ -30,6 +30,8 @@ int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t
     TL_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31) && batch < (1u << 31), "dimension too large");
     cudaStream_t st = as_stream(stream);
     if (numerics == TL_NUMERICS_FAST && K > 0) {
+        if (batch == 1 && M >= 2 && M <= 128 && skinny_supported(A, B, M, N, K, lda, ldb))
+            return launch_skinny(H(A), H(B), H(C), (int)M, (int)N, (int)K, lda, ldb, ldc, st);
         if (M > 8 && hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc))
             return launch_hgemm(H(A), H(B), H(C), (int)batch, (int)M, (int)N, (int)K, lda, ldb, ldc,
                                 strideA, strideB, strideC, st);

@@ -299,6 +299,10 @@ int Llama2Engine::linear(const __half* x, const __half* W, __half* y, int T, int
         launches_++;
         return launch_matmul_seq(p, st);
     }
+    if (T >= 2 && T <= 128 && skinny_supported(x, W, T, N, K, K, K)) {
+        launches_++;
+        return launch_skinny(x, W, y, T, N, K, K, K, N, st);
+    }
     if (T > 8 && hgemm_supported(x, W, y, T, N, K, K, K, N)) {
         launches_++;
         return launch_hgemm(x, W, y, 1, T, N, K, K, K, N, 0, 0, 0, st);
@@ -388,7 +392,8 @@ int Llama2Engine::forward_reference_order(int T, int pos, bool all_logits, cudaS
 int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStream_t st) {
     const int dim = cfg_.dim, S = pos + T, H = H_local_, dl = dim_local_, hl = hidden_local_;
     const float scale = 1.0f / sqrtf((float)hd_);
-    const bool fused = T > 8 && tensor_map_encode_available() && hd_ % 32 == 0 && dl % 64 == 0 && hl % 32 == 0 &&
+    // up to 128 rows the matmuls are bound by the weight stream and run on the skinny kernel
+    const bool fused = T > 128 && tensor_map_encode_available() && hd_ % 32 == 0 && dl % 64 == 0 && hl % 32 == 0 &&
                        dim % 32 == 0;
     const bool fused_residual = fused && coll_ == nullptr;
     launches_++;

@@ -341,6 +341,24 @@ int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CU
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
+// N-tile width with the smallest estimated time: waves of tiles over the SMs times the cost of one
+// k-block of a tile, which is the larger of its MMA time (2 cycles per accumulator column) and
+// the time to bring its operands into shared memory (16 KB of A + BN * 128 B of B at the roughly
+// 64 bytes per cycle one SM sustains from L2; measured: the 128x256 tile runs the tensor pipe
+// at 69 %, i.e. it is fill-bound, 48 KB per 512 MMA cycles).
+int pick_bn(int mt, int N, int batch) {
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn = 256; bn >= 64; bn >>= 1) {
+        const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
+        const long long waves = (tiles + sm_count() - 1) / sm_count();
+        const long long per_kb = std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
+        const long long cost = waves * per_kb;
+        if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+    }
+    return best;
+}
+
 }  // namespace
 
 bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
@@ -354,10 +372,8 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     TL_REQUIRE(hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc), "hgemm: unsupported shape or alignment");
     TL_REQUIRE(sA % 8 == 0 && sB % 8 == 0, "hgemm: batch strides must be multiples of 8 elements");
     if (batch <= 0) return TL_OK;
-    // widest N tile that still gives every SM a tile
     const int mt = (M + BM - 1) / BM;
-    int bn = 256;
-    while (bn > 64 && (long long)mt * ((N + bn - 1) / bn) * batch < sm_count()) bn >>= 1;
+    const int bn = pick_bn(mt, N, batch);
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
     TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, bn));
@@ -381,8 +397,7 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     TL_REQUIRE(hgemm_fused_supported(A, B, C, M, N, K, lda, ldb, ldc) && R && al16(R) && ldr % 8 == 0,
                "hgemm+residual: unsupported shape or alignment");
     const int mt = (M + BM - 1) / BM;
-    int bn = 256;
-    while (bn > 64 && (long long)mt * ((N + bn - 1) / bn) < sm_count()) bn >>= 1;
+    const int bn = pick_bn(mt, N, 1);
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
     TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, bn));

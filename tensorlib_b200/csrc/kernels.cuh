@@ -153,6 +153,11 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
                  long long lda, long long ldb, long long ldc, long long sA, long long sB,
                  long long sC, cudaStream_t st);
 
+// ---- skinny_sm100.cu: 2 <= M <= 128, weights streamed once (swap-AB tcgen05, stream-K split) --------
+bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K, size_t lda, size_t ldw);
+int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int K, long long lda, long long ldw,
+                  long long ldc, cudaStream_t st);
+
 // fused epilogues of the prefill HGEMM (N % 32 == 0, 16-byte aligned rows)
 bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
                            size_t ldb, size_t ldc);
