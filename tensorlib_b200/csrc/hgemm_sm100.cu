@@ -24,6 +24,8 @@
 // leaves its loop, TMEM is freed and TL_ERR_TIMEOUT is recorded in the device status word.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -277,6 +279,185 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
 
+// ---- CTA-pair variant: 256 x 256 tile per 2-CTA cluster ------------------------------------------
+// The 128x256 tile above is limited by the rate at which one SM can fill its shared memory
+// (48 KB per 512 MMA cycles: the tensor pipe measures 69 % active). With cta_group::2 the two CTAs
+// of a cluster share one MMA of M = 256: each CTA loads its own 128 rows of A and only HALF of the
+// B tile (128 of the 256 weight rows), 32 KB per 512 MMA cycles, and keeps its 128 rows of the
+// accumulator in its own TMEM. The leader CTA (cluster rank 0) issues the MMAs and owns the "full"
+// barriers (the loads of both CTAs complete there); "empty" and "accumulator ready" are
+// signalled to each CTA's own barrier by a separate commit; the peer's epilogue warps release
+// the accumulator on the leader's barrier with a remote arrive. No multicast anywhere.
+// For SWIGLU the split of B by halves is exactly W1 | W3: rank 0 loads the W1 rows, rank 1 the
+// W3 rows of the same output columns.
+constexpr int PAIR_BN = 256, PAIR_STAGES = 6;
+constexpr int PAIR_B_BYTES = (PAIR_BN / 2) * BK * 2;                  // this CTA's half of the B tile
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;             // 32 KB
+constexpr size_t PAIR_SMEM = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+             const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmB3, GemmArgs p) {
+    constexpr int BN = PAIR_BN, STAGES = PAIR_STAGES, STAGE_BYTES = PAIR_STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr int OUT_COLS = EPI == GEPI_SWIGLU ? BN / 2 : BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                              // 0: leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int mt_count = (p.M + 2 * BM - 1) / (2 * BM);                   // 256-row tiles
+    const int nt_each = (p.N + OUT_COLS - 1) / OUT_COLS;
+    const int nt_count = EPI == GEPI_QKV_ROPE ? 3 * nt_each : nt_each;
+    const int tiles_per_batch = mt_count * nt_count;
+    const int total_tiles = tiles_per_batch * p.batch;
+    const int nkb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }   // 4 warps x 2 CTAs
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) tmem_alloc_pair<TMEM_COLS>(tmem_slot);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // both CTAs' barriers exist before anything is signalled across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------------------------------------
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        if (EPI == GEPI_SWIGLU || EPI == GEPI_QKV_ROPE) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB2) : "memory");
+        if (EPI == GEPI_QKV_ROPE) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB3) : "memory");
+        int it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+            const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
+            const int mt = idx % mt_count, nt = idx / mt_count;
+            const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
+            const CUtensorMap* mb = EPI == GEPI_SWIGLU ? (rank == 0 ? &tmB : &tmB2)
+                                                       : (which == 0 ? &tmB : (which == 1 ? &tmB2 : &tmB3));
+            const int brow = EPI == GEPI_SWIGLU ? ntl * OUT_COLS : ntl * BN + (int)rank * (BN / 2);
+            for (int kb = 0; kb < nkb; kb++, it++) {
+                const int s = it % STAGES, use = it / STAGES;
+                if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+                const uint32_t leader_full = map_to_cta(full0 + 8 * s, 0);
+                if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // both CTAs' bytes
+                tma_load_3d_pair(sa, &tmA, kb * BK, (mt * 2 + (int)rank) * BM, p.a_batched ? b : 0, leader_full);
+                tma_load_3d_pair(sb, mb, kb * BK, brow, p.b_batched ? b : 0, leader_full);
+            }
+        }
+        // Copies in flight complete on the leader's barrier; before leaving, wait (bounded) until
+        // the MMAs that read this CTA's last stages are done: its "empty" barriers say so.
+        if (ok) {
+            for (int j = max(0, it - STAGES); j < it; j++)
+                if (!mbar_wait(empty0 + 8 * (j % STAGES), (j / STAGES) & 1, abort_flag)) break;
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------- MMA issuer (leader only) ------------------------------------------------
+        constexpr uint32_t idesc = make_idesc_pair(BN);
+        int it = 0, tcount = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tcount++) {
+            const int buf = tcount & 1, use = tcount >> 1;
+            if (use > 0 && !(ok = mbar_wait(tempty0 + 8 * buf, (use - 1) & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+            for (int kb = 0; kb < nkb; kb++, it++) {
+                const int s = it % STAGES, use_s = it / STAGES;
+                if (!(ok = mbar_wait(full0 + 8 * s, use_s & 1, abort_flag))) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)
+                    umma_pair(d_tmem, make_desc(sa + k * 32), make_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit_pair(empty0 + 8 * s);                   // my stage is reusable
+                umma_commit_pair(map_to_cta(empty0 + 8 * s, 1));    // and the peer's
+            }
+            if (ok) {
+                umma_commit_pair(tfull0 + 8 * buf);
+                umma_commit_pair(map_to_cta(tfull0 + 8 * buf, 1));
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue (both CTAs, own 128 rows) ----------------------------------------
+        const int q = warp & 3;
+        int tcount = 0;
+        bool ok = true;
+        const uint32_t leader_tempty0 = map_to_cta(tempty0, 0);
+        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tcount++) {
+            const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
+            const int mt = idx % mt_count, nt = idx / mt_count;
+            const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
+            const int buf = tcount & 1, use = tcount >> 1;
+            ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = (mt * 2 + (int)rank) * BM + q * 32 + lane;
+            const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
+            if (EPI == GEPI_SWIGLU) {
+#pragma unroll 1
+                for (int c = 0; c < OUT_COLS; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(tbase + (uint32_t)c, g);
+                    tmem_ld32(tbase + (uint32_t)(OUT_COLS + c), u);
+                    tmem_ld_wait();
+                    const int col0 = ntl * OUT_COLS + c;
+                    if (row < p.M && col0 < p.N) store32_swiglu(crow + col0, g, u);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tbase + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    const int col0 = ntl * BN + c;
+                    if (row >= p.M || col0 >= p.N) continue;
+                    if (EPI == GEPI_RESIDUAL) {
+                        store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
+                    } else if (EPI == GEPI_QKV_ROPE) {
+                        if (which == 2) {
+                            store32(p.vc + (long long)row * p.ld_kv + col0, r);
+                        } else {
+                            const int half_dim = p.head_dim >> 1, d2 = (col0 % p.head_dim) >> 1;
+                            __half* dst = which == 0 ? crow + col0 : p.kc + (long long)row * p.ld_kv + col0;
+                            store32_rope(dst, p.cos_t + (long long)row * half_dim + d2, p.sin_t + (long long)row * half_dim + d2, r);
+                        }
+                    } else {
+                        store32(crow + col0, r);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * buf);
+        }
+    }
+    // ---------------- teardown: nobody frees TMEM or leaves while the pair may still use it -----------
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc_pair<TMEM_COLS>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
+}
+
 // ---- host side: tensor maps --------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -339,7 +520,41 @@ int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CU
     return launch_k<64, EPI>(ma, mb, mb2, mb3, a, tiles, st);
 }
 
+template <int EPI>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
+                const GemmArgs& a, int pair_tiles, cudaStream_t st) {
+    static bool configured = false;
+    if (!configured) {
+        TL_CUDA(cudaFuncSetAttribute(k_hgemm_pair<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+        configured = true;
+    }
+    const int grid = 2 * std::max(1, std::min(pair_tiles, sm_count() / 2));
+    k_hgemm_pair<EPI><<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(ma, mb, mb2, mb3, a);
+    TL_LAUNCH_CHECK();
+    return TL_OK;
+}
+
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
+
+// estimated cost (cycles per k-block x waves) of the CTA-pair kernel: 256 x 256 tiles over sm/2 pairs,
+// 512 MMA cycles per k-block, operands arrive at 32 KB per CTA per k-block (not the limit)
+long long pair_cost(int M, int n_tiles_256, int batch) {
+    // TL_HGEMM_PAIR=always|never overrides the estimate (tests force both kernels onto small shapes)
+    static const int forced = [] {
+        const char* e = getenv("TL_HGEMM_PAIR");
+        return !e ? 0 : (!strcmp(e, "always") ? 1 : (!strcmp(e, "never") ? 2 : 0));
+    }();
+    if (forced == 1) return -1;
+    if (forced == 2) return (1ll << 60);
+    const long long tiles = (long long)((M + 255) / 256) * n_tiles_256 * batch;
+    const long long pairs = std::max(1, sm_count() / 2);
+    return ((tiles + pairs - 1) / pairs) * 512;
+}
+long long single_cost(int mt, int N, int batch, int bn) {
+    const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
+    const long long waves = (tiles + sm_count() - 1) / sm_count();
+    return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
+}
 
 // N-tile width with the smallest estimated time: waves of tiles over the SMs times the cost of one
 // k-block of a tile, which is the larger of its MMA time (2 cycles per accumulator column) and
@@ -374,13 +589,18 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     if (batch <= 0) return TL_OK;
     const int mt = (M + BM - 1) / BM;
     const int bn = pick_bn(mt, N, batch);
-    CUtensorMap ma, mb;
-    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
-    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, bn));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = batch; a.ldc = ldc; a.sC = sC;
     a.a_batched = (sA != 0 && batch > 1) ? 1 : 0; a.b_batched = (sB != 0 && batch > 1) ? 1 : 0;
     a.status = device_status_word();
+    CUtensorMap ma, mb;
+    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
+    const bool vec_c = ldc % 8 == 0 && sC % 8 == 0 && al16(C) && N % 32 == 0;   // the pair epilogue stores 64-byte chunks
+    if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch) < single_cost(mt, N, batch, bn)) {
+        TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, 128));
+        return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, ((M + 255) / 256) * ((N + 255) / 256) * batch, st);
+    }
+    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, bn));
     const int tiles = mt * ((N + bn - 1) / bn) * batch;
     return launch_any_bn<GEPI_STORE>(bn, ma, mb, mb, mb, a, tiles, st);
 }
@@ -400,10 +620,14 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     const int bn = pick_bn(mt, N, 1);
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
-    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, bn));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
     a.R = R; a.ldr = ldr;
+    if (M > BM && pair_cost(M, (N + 255) / 256, 1) < single_cost(mt, N, 1, bn)) {
+        TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
+        return launch_pair<GEPI_RESIDUAL>(ma, mb, mb, mb, a, ((M + 255) / 256) * ((N + 255) / 256), st);
+    }
+    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, bn));
     return launch_any_bn<GEPI_RESIDUAL>(bn, ma, mb, mb, mb, a, mt * ((N + bn - 1) / bn), st);
 }
 
@@ -419,6 +643,8 @@ int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __h
     TL_PROPAGATE(make_tensor_map_f16(&m3, W3, N, K, ldb, 0, 1, 128));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
+    if (M > BM && pair_cost(M, nt, 1) < single_cost(mt, N, 1, 128) * 768 / 512)   // single: 128 output columns per 256-wide tile
+        return launch_pair<GEPI_SWIGLU>(ma, m1, m3, m3, a, ((M + 255) / 256) * nt, st);
     return launch_k<256, GEPI_SWIGLU>(ma, m1, m3, m3, a, mt * nt, st);
 }
 
@@ -438,6 +664,15 @@ int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, c
     while (bn > 64 && (n_each % bn != 0 || (long long)mt * 3 * (n_each / bn) < sm_count())) bn >>= 1;
     CUtensorMap ma, mq, mk, mv;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
+    if (M > BM && n_each % 256 == 0 && pair_cost(M, 3 * (n_each / 256), 1) < single_cost(mt, 3 * n_each, 1, bn)) {
+        TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, 128));
+        TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, 128));
+        TL_PROPAGATE(make_tensor_map_f16(&mv, Wv, n_each, K, ldb, 0, 1, 128));
+        GemmArgs a2{};
+        a2.C = q_out; a2.M = M; a2.N = n_each; a2.K = K; a2.batch = 1; a2.ldc = ldq; a2.status = device_status_word();
+        a2.kc = k_rows; a2.vc = v_rows; a2.ld_kv = ld_kv; a2.cos_t = cos_rows; a2.sin_t = sin_rows; a2.head_dim = head_dim;
+        return launch_pair<GEPI_QKV_ROPE>(ma, mq, mk, mv, a2, ((M + 255) / 256) * 3 * (n_each / 256), st);
+    }
     TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, bn));
     TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, bn));
     TL_PROPAGATE(make_tensor_map_f16(&mv, Wv, n_each, K, ldb, 0, 1, bn));

@@ -234,3 +234,36 @@ def test_fused_prefill_attention_rejects_other_head_sizes(tl):
     d = tl.DeviceBuffer(1 << 16)
     rc = tl.load().tl_attn_prefill_f16(d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, 4, 0, 2, 48, None)
     assert rc == 4  # TL_ERR_UNSUPPORTED
+
+
+# ---- CTA-pair HGEMM (cta_group::2): forced onto small shapes in a child process -------------------------
+_PAIR_CHILD = r"""
+import sys, numpy as np
+sys.path.insert(0, sys.argv[1])
+import tensorlib_b200 as tl
+from tensorlib_b200 import synth
+tl.init(0)
+worst = 0.0
+for (M, N, K) in ((512, 1024, 512), (384, 768, 200), (2048, 512, 4096), (300, 256, 1032), (129, 512, 64)):
+    A = synth.normal_f16(71, 1, M * K, 1.0).reshape(M, K)
+    W = synth.normal_f16(71, 2, N * K, 0.02).reshape(N, K)
+    got = tl.matmul2d(A, W, numerics=tl.FAST).astype(np.float64)
+    want = A.astype(np.float64) @ W.astype(np.float64).T
+    scale = np.sqrt((want * want).mean(axis=-1, keepdims=True)) + 1e-30
+    worst = max(worst, float((np.abs(got - want) / np.maximum(np.abs(want), scale)).max()))
+assert tl.device_status() == 0
+print("WORST", worst)
+"""
+
+
+@pytest.mark.parametrize("mode", ["always", "never"])
+def test_hgemm_pair_and_single_kernels_agree_with_float64(tl, mode, tmp_path):
+    import subprocess
+    script = tmp_path / "child.py"
+    script.write_text(_PAIR_CHILD)
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+    env = dict(os.environ, TL_HGEMM_PAIR=mode)
+    r = subprocess.run([sys.executable, str(script), root], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    worst = float(r.stdout.strip().split("WORST")[-1])
+    assert worst <= 2e-3, worst      # fp16 rounding of the result only: both kernels accumulate in fp32
