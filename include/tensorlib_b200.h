@@ -165,13 +165,11 @@ TL_API int tl_attn_decode_f16_noalloc(const tl_half* q, const tl_half* k_cache, 
 /* causal attention of T query rows at positions start_pos .. start_pos+T-1 over positions
  * [0, start_pos+T) of the caches, in one kernel (Transformer.cpp:56-109 for T > 1: per-head
  * matmul, ScalarDiv, mask, softmax, per-head matmul). q, out: (T, n_heads*head_dim); caches:
- * (max_seq, n_heads*head_dim) read in place. vt_scratch: n_heads*head_dim * ((start_pos+T+7)&~7)
- * halfs of caller-owned device memory (receives V transposed per head). head_dim must be 128;
- * other head sizes return TL_ERR_UNSUPPORTED (the caller composes tl_matmul_batched_f16 and
- * tl_softmax_f16 instead, as the model path does). */
+ * (max_seq, n_heads*head_dim), read in place. head_dim must be 128; other head sizes return
+ * TL_ERR_UNSUPPORTED (the caller composes tl_matmul_batched_f16 and tl_softmax_f16 instead, as
+ * the model path does). */
 TL_API int tl_attn_prefill_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
-                        tl_half* vt_scratch, int T, int start_pos, int n_heads, int head_dim,
-                        tl_stream stream);
+                        int T, int start_pos, int n_heads, int head_dim, tl_stream stream);
 /* y[n] = residual[n] + sum_k x[k] W[n,k]  (wo / w2 GEMV + EwiseAdd, Transformer.cpp:111+:169,
  * :143+:175). y may alias residual. */
 TL_API int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,
@@ -218,6 +216,12 @@ TL_API int tl_llama2_forward(tl_llama2* m, const int* tokens_host, int T, int st
 TL_API int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int max_new,
                        int stop_on_eos, int* out_tokens_host, int* n_out, double* prefill_seconds,
                        double* decode_seconds);
+/* The same, continuing a conversation: the prompt tokens occupy positions start_pos .. and attend
+ * to everything already in the KV cache below start_pos (the reference's multi-turn chat keeps a
+ * running total_len this way, llama2.cpp:13, :51-52). tl_llama2_generate is start_pos = 0. */
+TL_API int tl_llama2_generate_at(tl_llama2* m, int start_pos, const int* prompt_host, int n_prompt, int max_new,
+                          int stop_on_eos, int* out_tokens_host, int* n_out, double* prefill_seconds,
+                          double* decode_seconds);
 /* Device-resident greedy decode: `steps` tokens starting from the id in the model's device-side
  * token slot (left there by a previous forward/generate/decode call), one CUDA-graph replay per
  * token, no host round trip. out_tokens_host (optional) is filled after the last step. Runs on

@@ -70,6 +70,8 @@ _SIGS = {
     "tl_llama2_forward": [_vp, _vp, _int, _int, _vp, _vp],
     "tl_llama2_generate": [_vp, _vp, _int, _int, _int, _vp, C.POINTER(_int), C.POINTER(C.c_double),
                            C.POINTER(C.c_double)],
+    "tl_llama2_generate_at": [_vp, _int, _vp, _int, _int, _int, _vp, C.POINTER(_int), C.POINTER(C.c_double),
+                              C.POINTER(C.c_double)],
     "tl_llama2_decode_device": [_vp, _int, _int, _vp, _vp],
     "tl_llama2_set_next_token": [_vp, _int],
     "tl_llama2_kernel_launches": [_vp, C.POINTER(C.c_longlong)],
@@ -79,7 +81,7 @@ _SIGS = {
     "tl_rmsnorm_qkv_rope_f16": [_vp, _vp, C.c_float] + [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16": [_vp] * 6 + [_int, _int, _int, _int, _vp],
     "tl_attn_decode_f16_noalloc": [_vp] * 4 + [_int, _int, _int, _int, _vp],
-    "tl_attn_prefill_f16": [_vp] * 5 + [_int, _int, _int, _int, _vp],
+    "tl_attn_prefill_f16": [_vp] * 4 + [_int, _int, _int, _int, _vp],
     "tl_gemv_residual_f16": [_vp, _vp, _vp, _vp, _int, _int, _vp],
     "tl_rmsnorm_gateup_swiglu_f16": [_vp, _vp, C.c_float, _vp, _vp, _vp, _int, _int, _vp],
     "tl_tp_unique_id": [_vp, _int],
@@ -305,8 +307,7 @@ def attn_prefill(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, start_
     S = start_pos + T
     dq, dk, dv = (DeviceBuffer.from_numpy(np.ascontiguousarray(a, dtype=np.float16)) for a in (q, k_cache, v_cache))
     out = DeviceBuffer(T * width * 2)
-    vt = DeviceBuffer(width * ((S + 7) & ~7) * 2)
-    check(load().tl_attn_prefill_f16(dq.ptr, dk.ptr, dv.ptr, out.ptr, vt.ptr, T, start_pos, n_heads, hd, None),
+    check(load().tl_attn_prefill_f16(dq.ptr, dk.ptr, dv.ptr, out.ptr, T, start_pos, n_heads, hd, None),
           "tl_attn_prefill_f16")
     synchronize()
     return out.to_numpy(np.float16, (T, width))
@@ -363,13 +364,15 @@ class Llama2:
                   "tl_llama2_forward")
         return out
 
-    def generate(self, prompt, max_new: int, stop_on_eos: bool = False):
+    def generate(self, prompt, max_new: int, stop_on_eos: bool = False, start_pos: int = 0):
+        """Prefill `prompt` at start_pos (0: a fresh conversation; > 0: continue over the KV cache of
+        earlier turns), then greedy decode. Returns (ids, prefill seconds, decode seconds)."""
         p = np.ascontiguousarray(prompt, dtype=np.int32)
         out = np.empty(max_new, dtype=np.int32)
         n = _int(0)
         tp, td = C.c_double(0), C.c_double(0)
-        check(load().tl_llama2_generate(self.h, _np_ptr(p), p.size, max_new, int(stop_on_eos), _np_ptr(out),
-                                        C.byref(n), C.byref(tp), C.byref(td)), "tl_llama2_generate")
+        check(load().tl_llama2_generate_at(self.h, int(start_pos), _np_ptr(p), p.size, max_new, int(stop_on_eos),
+                                           _np_ptr(out), C.byref(n), C.byref(tp), C.byref(td)), "tl_llama2_generate_at")
         return out[: n.value].copy(), tp.value, td.value
 
     def set_next_token(self, token: int) -> None:

@@ -225,12 +225,16 @@ int tl_llama2_load_file(tl_llama2* m, const char* path) {
     const size_t d = c.dim, h = c.hidden_dim, L = c.n_layers, V = c.vocab_size;
     size_t n = V * d + L * (2 * d + 4 * d * d + 3 * d * h) + d;
     if (!shared) n += (size_t)c.max_seq_len * (d / c.n_heads) + V * d;
-    std::vector<tl_half> buf;
-    try { buf.resize(n); } catch (...) { fclose(f); return set_error(TL_ERR_OUT_OF_MEMORY, "host buffer of %zu halfs", n); }
-    size_t got = fread(buf.data(), sizeof(tl_half), n, f);
+    // refuse a truncated file before anything is uploaded
+    if (fseeko(f, 0, SEEK_END) != 0) { fclose(f); return set_error(TL_ERR_IO, "cannot seek in %s", path); }
+    const long long size = ftello(f);
+    if (size < (long long)(7 * sizeof(int) + n * sizeof(tl_half))) {
+        fclose(f);
+        return set_error(TL_ERR_IO, "checkpoint %s is truncated: %lld of %zu bytes", path, size, 7 * sizeof(int) + n * sizeof(tl_half));
+    }
+    const int rc = m->eng->load_payload_stream(f, (long long)(7 * sizeof(int)), shared);
     fclose(f);
-    if (got != n) return set_error(TL_ERR_IO, "checkpoint %s is truncated: %zu of %zu values", path, got, n);
-    return m->eng->load_payload_host(H(buf.data()), shared);
+    return rc;
 }
 
 int tl_llama2_init_random(tl_llama2* m, uint64_t seed, float std) {
@@ -271,12 +275,19 @@ int tl_llama2_set_next_token(tl_llama2* m, int token) {
 int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int max_new,
                        int stop_on_eos, int* out_tokens_host, int* n_out, double* prefill_seconds,
                        double* decode_seconds) {
+    return tl_llama2_generate_at(m, 0, prompt_host, n_prompt, max_new, stop_on_eos, out_tokens_host, n_out,
+                                 prefill_seconds, decode_seconds);
+}
+
+int tl_llama2_generate_at(tl_llama2* m, int start_pos, const int* prompt_host, int n_prompt, int max_new,
+                          int stop_on_eos, int* out_tokens_host, int* n_out, double* prefill_seconds,
+                          double* decode_seconds) {
     TL_CHECK_INIT();
     TL_REQUIRE(m && prompt_host && out_tokens_host && n_out, "null argument");
     Llama2Engine& e = *m->eng;
     const int V = e.cfg().vocab_size;
-    TL_REQUIRE(n_prompt > 0 && max_new > 0 && n_prompt + max_new - 1 <= e.cfg().max_seq_len,
-               "prompt (%d) + generation (%d) exceeds max_seq_len", n_prompt, max_new);
+    TL_REQUIRE(start_pos >= 0 && n_prompt > 0 && max_new > 0 && start_pos + n_prompt + max_new - 1 <= e.cfg().max_seq_len,
+               "start (%d) + prompt (%d) + generation (%d) exceeds max_seq_len", start_pos, n_prompt, max_new);
     for (int i = 0; i < n_prompt; i++) TL_REQUIRE(prompt_host[i] >= 0 && prompt_host[i] < V, "token id out of range");
     using clk = std::chrono::high_resolution_clock;
     cudaStream_t st = nullptr;
@@ -286,7 +297,7 @@ int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int m
     auto t0 = clk::now();
     memcpy(tok, prompt_host, (size_t)n_prompt * sizeof(int));
     TL_PROPAGATE(e.set_tokens(tok, n_prompt, st));
-    TL_PROPAGATE(e.forward(n_prompt, 0, false, st));
+    TL_PROPAGATE(e.forward(n_prompt, start_pos, false, st));
     TL_PROPAGATE(e.sample_last(n_prompt, st));
     TL_CUDA(cudaMemcpyAsync(tok, e.d_next(), sizeof(int), cudaMemcpyDeviceToHost, st));
     TL_CUDA(cudaStreamSynchronize(st));
@@ -297,7 +308,7 @@ int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int m
     const bool fast = e.cfg().numerics == TL_NUMERICS_FAST;
     if (fast && max_new > 1) TL_PROPAGATE(e.ensure_decode_graph(st));
     auto t1 = clk::now();
-    int pos = n_prompt;
+    int pos = start_pos + n_prompt;
     while (*n_out < max_new) {
         if (stop_on_eos && (next == 1 || next == 2)) break;
         tok[0] = next;
@@ -380,20 +391,17 @@ int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl_half* 
     return launch_decode_attn(a, as_stream(stream));
 }
 
-int tl_attn_prefill_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out,
-                        tl_half* vt_scratch, int T, int start_pos, int n_heads, int head_dim,
-                        tl_stream stream) {
+int tl_attn_prefill_f16(const tl_half* q, const tl_half* k_cache, const tl_half* v_cache, tl_half* out, int T,
+                        int start_pos, int n_heads, int head_dim, tl_stream stream) {
     TL_CHECK_INIT();
-    TL_REQUIRE(q && k_cache && v_cache && out && vt_scratch, "null pointer");
+    TL_REQUIRE(q && k_cache && v_cache && out, "null pointer");
     TL_REQUIRE(T > 0 && start_pos >= 0 && n_heads > 0 && head_dim > 0, "bad shape");
     const int S = start_pos + T;
-    const long long pitch = (long long)n_heads * head_dim, vt_pitch = (S + 7) & ~7;
-    if (!flash_prefill_supported(q, k_cache, vt_scratch, out, T, S, start_pos, n_heads, head_dim, pitch, pitch,
-                                 vt_pitch, pitch))
+    const long long pitch = (long long)n_heads * head_dim;
+    if (!flash_prefill_supported(q, k_cache, v_cache, out, T, S, start_pos, n_heads, head_dim, pitch, pitch, pitch, pitch))
         return set_error(TL_ERR_UNSUPPORTED, "tl_attn_prefill_f16: head_dim %d (128 only) or unaligned pointers", head_dim);
-    TL_PROPAGATE(launch_transpose_v(H(vt_scratch), H(v_cache), S, n_heads, head_dim, pitch, vt_pitch, as_stream(stream)));
-    return launch_flash_prefill(H(q), H(k_cache), H(vt_scratch), H(out), T, S, start_pos, n_heads, head_dim, pitch,
-                                pitch, vt_pitch, pitch, as_stream(stream));
+    return launch_flash_prefill(H(q), H(k_cache), H(v_cache), H(out), T, S, start_pos, n_heads, head_dim, pitch,
+                                pitch, pitch, pitch, as_stream(stream));
 }
 
 int tl_gemv_residual_f16(const tl_half* x, const tl_half* W, const tl_half* residual, tl_half* y,

@@ -6,7 +6,7 @@
 //
 // One CTA per (head, 128 query rows); two CTAs per SM so that one CTA's softmax overlaps the
 // other's MMAs. Inside a CTA, per 64-column KV tile j:
-//   warp 0   TMA: Q once, K tiles (2 stages), V^T tiles (1 stage), 128-byte swizzle, zero fill
+//   warp 0   TMA: Q once, K tiles (2 stages), V tiles (1 stage), 128-byte swizzle, zero fill
 //   warp 1   tcgen05.mma: S[j&1] = Q K_j^T (TMEM, 64 fp32 columns), then O += P_{j-1} V_{j-1}
 //            (TMEM, 128 columns); issuing S_j before the P.V of tile j-1 keeps the tensor core
 //            busy while the softmax warps work on tile j-1
@@ -14,7 +14,8 @@
 //            (exp2 domain), P as fp16 into the swizzled shared tile the second MMA reads as its
 //            A operand. The accumulator is rescaled (tcgen05.ld/st) only when the running max
 //            grew by more than 2^8 since the last rescale; P stays below 2^8 in between.
-// V is read through a (heads, hd, S) transposed copy so that both MMA operands are K-major.
+// V is read in place from the cache: (kv, head_dim) rows are the N x K operand of the second MMA in
+// MN-major form (head_dim contiguous), so no transposed copy exists.
 // Bound: tensor pipe / MUFU (exp2), not HBM: 4 * T * S * hd flops per head against
 // 2 * (T + 2 S) * hd bytes.
 //
@@ -35,7 +36,7 @@ constexpr int BQ = 128, BKV = 64, HD = 128;
 constexpr int FA_THREADS = 192;
 constexpr int Q_BYTES = BQ * HD * 2;          // two swizzle atoms of 64 columns
 constexpr int K_BYTES = BKV * HD * 2;         // two atoms, 64 rows each
-constexpr int V_BYTES = HD * BKV * 2;         // V^T tile: hd rows x 64 kv columns, one atom
+constexpr int V_BYTES = BKV * HD * 2;         // V tile as stored: 64 kv rows, two 64-column halves
 constexpr int P_BYTES = BQ * BKV * 2;         // one atom
 constexpr int K_STAGES = 2;
 constexpr uint32_t TMEM_COLS = 256;           // S0 | S1 (64 each) | O (128)
@@ -121,7 +122,8 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (j + 1 < n_tiles && !(ok = issue_k(j + 1))) break;
             if (j >= 1 && !(ok = mbar_wait(BAR(6), (j - 1) & 1, abort_flag))) break;   // P.V of tile j-1 has read V
             mbar_arrive_expect_tx(BAR(5), V_BYTES);
-            tma_load_3d(smem_u32(sV), &tmV, j * BKV, 0, head, BAR(5));
+            tma_load_3d(smem_u32(sV), &tmV, 0, j * BKV, head, BAR(5));
+            tma_load_3d(smem_u32(sV) + V_BYTES / 2, &tmV, 64, j * BKV, head, BAR(5));
             v_issued++;
         }
         if (!ok) {  // let copies already in flight land before the CTA goes away
@@ -133,7 +135,7 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ------------------------------------------------------------
-        constexpr uint32_t idesc_s = make_idesc(BKV), idesc_o = make_idesc(HD);
+        constexpr uint32_t idesc_s = make_idesc(BKV), idesc_o = make_idesc(HD) | IDESC_B_MN_MAJOR;
         bool ok = mbar_wait(BAR(0), 0, abort_flag);
         const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aV = smem_u32(sV);
         auto issue_pv = [&](int t) -> bool {   // O += P_t V_t
@@ -142,7 +144,8 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < BKV / 16; k++)
-                umma(tmem_base + O_COL, make_desc(aP + k * 32), make_desc(aV + k * 32), idesc_o, (t > 0 || k > 0) ? 1u : 0u);
+                umma(tmem_base + O_COL, make_desc(aP + k * 32), make_desc_mn(aV + k * 2048, V_BYTES / 2, 1024), idesc_o,
+                     (t > 0 || k > 0) ? 1u : 0u);
             umma_commit(BAR(6));
             return true;
         };
@@ -276,21 +279,21 @@ constexpr size_t FA_SMEM = (size_t)Q_BYTES + K_STAGES * K_BYTES + V_BYTES + P_BY
 
 }  // namespace
 
-bool flash_prefill_supported(const void* q, const void* k, const void* vt, const void* out, int T, int S, int pos0,
-                             int heads, int head_dim, long long ldq, long long ldk, long long ldvt, long long ldo) {
+bool flash_prefill_supported(const void* q, const void* k, const void* v, const void* out, int T, int S, int pos0,
+                             int heads, int head_dim, long long ldq, long long ldk, long long ldv, long long ldo) {
     auto al16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
     return head_dim == HD && T >= 1 && S >= 1 && pos0 >= 0 && pos0 + T <= S && heads >= 1 && ldq % 8 == 0 &&
-           ldk % 8 == 0 && ldvt % 8 == 0 && ldo % 8 == 0 && al16(q) && al16(k) && al16(vt) && al16(out) &&
+           ldk % 8 == 0 && ldv % 8 == 0 && ldo % 8 == 0 && al16(q) && al16(k) && al16(v) && al16(out) &&
            tensor_map_encode_available();
 }
 
-// q: (T, heads, hd) pitch ldq; k: (S, heads, hd) pitch ldk (the cache, positions 0..S-1);
-// vt: (heads, hd, S) with row pitch ldvt; out: (T, heads, hd) pitch ldo. Query row t sits at
-// position pos0 + t and attends to cache positions 0 .. pos0 + t.
-int launch_flash_prefill(const __half* q, const __half* k, const __half* vt, __half* out, int T, int S, int pos0,
-                         int heads, int head_dim, long long ldq, long long ldk, long long ldvt, long long ldo,
+// q: (T, heads, hd) pitch ldq; k, v: (S, heads, hd) pitch ldk / ldv (the caches, positions 0..S-1);
+// out: (T, heads, hd) pitch ldo. Query row t sits at position pos0 + t and attends to cache
+// positions 0 .. pos0 + t.
+int launch_flash_prefill(const __half* q, const __half* k, const __half* v, __half* out, int T, int S, int pos0,
+                         int heads, int head_dim, long long ldq, long long ldk, long long ldv, long long ldo,
                          cudaStream_t st) {
-    TL_REQUIRE(flash_prefill_supported(q, k, vt, out, T, S, pos0, heads, head_dim, ldq, ldk, ldvt, ldo),
+    TL_REQUIRE(flash_prefill_supported(q, k, v, out, T, S, pos0, heads, head_dim, ldq, ldk, ldv, ldo),
                "flash prefill: unsupported shape or alignment (head_dim must be %d)", HD);
     static bool configured = false;
     if (!configured) {
@@ -302,7 +305,7 @@ int launch_flash_prefill(const __half* q, const __half* k, const __half* vt, __h
     CUtensorMap mq, mk, mv;
     TL_PROPAGATE(make_tensor_map_f16(&mq, q, T, HD, ldq, HD, heads, BQ));
     TL_PROPAGATE(make_tensor_map_f16(&mk, k, S, HD, ldk, HD, heads, BKV));
-    TL_PROPAGATE(make_tensor_map_f16(&mv, vt, HD, S, ldvt, (long long)HD * ldvt, heads, HD));
+    TL_PROPAGATE(make_tensor_map_f16(&mv, v, S, HD, ldv, HD, heads, BKV));
     FlashArgs a{out, ldo, T, S, pos0, heads, 1.4426950408889634f / sqrtf((float)head_dim), device_status_word()};
     dim3 grid((unsigned)heads, (unsigned)((T + BQ - 1) / BQ));
     k_flash_prefill<<<grid, FA_THREADS, FA_SMEM, st>>>(mq, mk, mv, a);

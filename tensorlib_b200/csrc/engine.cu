@@ -2,6 +2,7 @@
 #include "engine.cuh"
 #include "decode_mega.cuh"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <vector>
@@ -216,6 +217,73 @@ int Llama2Engine::load_payload_host(const __half* payload, bool shared_classifie
     return TL_OK;
 }
 
+// The same tensor order read from a file without holding the checkpoint in host memory
+// (read_weights, main.cpp:36-190, freads every tensor group into one pageable buffer and copies it
+// with a blocking cudaMemcpy). Two pinned 64 MB staging buffers: while chunk i travels to the
+// device (cudaMemcpy2DAsync, which also cuts this rank's column block out of wo / w2 rows), chunk
+// i+1 is read from the file. Row-split tensors only read their own rows.
+int Llama2Engine::load_payload_stream(FILE* f, long long payload_offset_bytes, bool shared_classifier) {
+    const size_t dim = cfg_.dim, hid = cfg_.hidden_dim, L = cfg_.n_layers, V = cfg_.vocab_size;
+    shared_classifier_ = shared_classifier;
+    constexpr size_t CAP = (size_t)64 << 20;
+    __half* stage[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaStream_t st = nullptr;
+    int rc = TL_OK;
+    auto cleanup = [&]() {
+        if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+        for (int i = 0; i < 2; i++) { if (done[i]) cudaEventDestroy(done[i]); if (stage[i]) cudaFreeHost(stage[i]); }
+    };
+    for (int i = 0; i < 2 && rc == TL_OK; i++) {
+        if (cudaMallocHost(&stage[i], CAP) != cudaSuccess) rc = set_error(TL_ERR_OUT_OF_MEMORY, "pinned staging buffer of %zu bytes", CAP);
+        else if (cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) != cudaSuccess) rc = set_error(TL_ERR_CUDA, "event creation failed");
+    }
+    if (rc == TL_OK && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) rc = set_error(TL_ERR_CUDA, "stream creation failed");
+    int cur = 0;
+    // copy this rank's block of the [nrows_full, ncols_full] tensor that starts `elem_off` elements into the payload
+    auto put = [&](__half* dst, size_t elem_off, int kind, size_t nrows_full, size_t ncols_full) -> int {
+        int r0, nr, c0, nc;
+        TL_PROPAGATE(shard_block(kind, (int)nrows_full, (int)ncols_full, cfg_.tp_rank, cfg_.tp_world, &r0, &nr, &c0, &nc));
+        const size_t rows_per_chunk = std::max<size_t>(1, CAP / (ncols_full * sizeof(__half)));
+        TL_REQUIRE(ncols_full * sizeof(__half) <= CAP, "checkpoint row of %zu bytes exceeds the staging buffer", ncols_full * sizeof(__half));
+        for (size_t row = 0; row < (size_t)nr; row += rows_per_chunk) {
+            const size_t rows = std::min(rows_per_chunk, (size_t)nr - row);
+            TL_CUDA(cudaEventSynchronize(done[cur]));            // the previous copy out of this buffer has finished
+            const long long pos = payload_offset_bytes + (long long)((elem_off + ((size_t)r0 + row) * ncols_full) * sizeof(__half));
+            if (fseeko(f, pos, SEEK_SET) != 0) return set_error(TL_ERR_IO, "seek to %lld failed", pos);
+            const size_t want = rows * ncols_full;
+            if (fread(stage[cur], sizeof(__half), want, f) != want) return set_error(TL_ERR_IO, "checkpoint is truncated (tensor at element %zu)", elem_off);
+            TL_CUDA(cudaMemcpy2DAsync(dst + row * (size_t)nc, (size_t)nc * sizeof(__half), stage[cur] + c0,
+                                      ncols_full * sizeof(__half), (size_t)nc * sizeof(__half), rows, cudaMemcpyHostToDevice, st));
+            TL_CUDA(cudaEventRecord(done[cur], st));
+            cur ^= 1;
+        }
+        return TL_OK;
+    };
+    auto run = [&]() -> int {
+        size_t off = 0;
+        const size_t emb_off = off;
+        TL_PROPAGATE(put(emb_, off, 0, V, dim)); off += V * dim;
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].attn_norm, off, 0, 1, dim)); off += dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wq, off, 1, dim, dim)); off += dim * dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wk, off, 1, dim, dim)); off += dim * dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wv, off, 1, dim, dim)); off += dim * dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].wo, off, 2, dim, dim)); off += dim * dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].ffn_norm, off, 0, 1, dim)); off += dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].w1, off, 1, hid, dim)); off += hid * dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].w2, off, 2, dim, hid)); off += hid * dim; }
+        for (size_t l = 0; l < L; l++) { TL_PROPAGATE(put(layers_[l].w3, off, 1, hid, dim)); off += hid * dim; }
+        TL_PROPAGATE(put(final_norm_, off, 0, 1, dim)); off += dim;
+        if (shared_classifier) return put(wcls_, emb_off, 1, V, dim);
+        off += (size_t)cfg_.max_seq_len * hd_;  // RoPE values the reference skips (main.cpp:175-177)
+        return put(wcls_, off, 1, V, dim);
+    };
+    if (rc == TL_OK) rc = run();
+    if (rc == TL_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = set_error(TL_ERR_CUDA, "checkpoint upload failed");
+    cleanup();
+    return rc;
+}
+
 int Llama2Engine::init_random(uint64_t seed, float std) {
     const size_t dim = cfg_.dim, L = cfg_.n_layers;
     unsigned long long id = 0;
@@ -418,12 +486,10 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dl, v_, T, dl, dl, st));
         }
         // scores[h] = q_h . K_h^T ; softmax (scale + causal mask inside) ; att_h = P_h . V_h
-        const long long vt_pitch = (S + 7) & ~7;
-        if (flash_prefill_supported(q_, w.cache_k, vt_, att_, T, S, pos, H, hd_, dl, dl, vt_pitch, dl)) {
-            // one kernel, scores stay in tensor memory / registers
-            launches_ += 2;
-            TL_PROPAGATE(launch_transpose_v(vt_, w.cache_v, S, H, hd_, dl, vt_pitch, st));
-            TL_PROPAGATE(launch_flash_prefill(q_, w.cache_k, vt_, att_, T, S, pos, H, hd_, dl, dl, vt_pitch, dl, st));
+        if (flash_prefill_supported(q_, w.cache_k, w.cache_v, att_, T, S, pos, H, hd_, dl, dl, dl, dl)) {
+            // one kernel, scores stay in tensor memory / registers, K and V read in place from the caches
+            launches_ += 1;
+            TL_PROPAGATE(launch_flash_prefill(q_, w.cache_k, w.cache_v, att_, T, S, pos, H, hd_, dl, dl, dl, dl, st));
         } else if (hgemm_supported(q_, w.cache_k, scores_, T, S, hd_, dl, dl, S) &&
                    hgemm_supported(scores_, vt_, att_, T, hd_, S, S, S, dl)) {
             launches_ += 4;

@@ -3,6 +3,7 @@
 // FeedForward / TransformerBlock (model/llama2_7b/src/Transformer.cpp) and ActivationBuffer
 // (model/llama2_7b/include/ActivationBuffer.hpp) of the reference.
 #pragma once
+#include <cstdio>
 
 #include <vector>
 
@@ -30,6 +31,9 @@ public:
     ~Llama2Engine();
     int allocate();
     int load_payload_host(const __half* payload, bool shared_classifier);
+    // stream a llama2.c checkpoint (positioned after its 28-byte header) through two pinned staging
+    // buffers: the read of chunk i+1 overlaps the host-to-device copy of chunk i
+    int load_payload_stream(FILE* f, long long payload_offset_bytes, bool shared_classifier);
     int init_random(uint64_t seed, float std);
 
     // Transformer::forward. Token ids must already be in d_tokens_[0..T) (see set_tokens).

@@ -139,10 +139,10 @@ int launch_transpose_v(__half* vt, const __half* v, int S, int H, int hd, long l
                        long long vt_pitch_s, cudaStream_t st);
 
 // ---- attn_sm100.cu: prefill attention on tcgen05 / TMEM / TMA (head_dim 128) ----------------------
-bool flash_prefill_supported(const void* q, const void* k, const void* vt, const void* out, int T, int S, int pos0,
-                             int heads, int head_dim, long long ldq, long long ldk, long long ldvt, long long ldo);
-int launch_flash_prefill(const __half* q, const __half* k, const __half* vt, __half* out, int T, int S, int pos0,
-                         int heads, int head_dim, long long ldq, long long ldk, long long ldvt, long long ldo,
+bool flash_prefill_supported(const void* q, const void* k, const void* v, const void* out, int T, int S, int pos0,
+                             int heads, int head_dim, long long ldq, long long ldk, long long ldv, long long ldo);
+int launch_flash_prefill(const __half* q, const __half* k, const __half* v, __half* out, int T, int S, int pos0,
+                         int heads, int head_dim, long long ldq, long long ldk, long long ldv, long long ldo,
                          cudaStream_t st);
 bool tensor_map_encode_available();
 

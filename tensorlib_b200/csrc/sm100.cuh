@@ -59,6 +59,20 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
     return d;
 }
+// The same for an MN-major operand (the matrix is stored with its M/N index contiguous, e.g. V as
+// (kv, head_dim) used as the N x K operand with N = head_dim): a 64-element x 8-row swizzle atom is
+// 1024 bytes, atoms follow each other along K every `k_group_bytes` (8 rows) and along MN every
+// `mn_block_bytes` (the next 64 elements).
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr, uint32_t mn_block_bytes, uint32_t k_group_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset
+    d |= (uint64_t)((k_group_bytes >> 4) & 0x3FFF) << 32;    // stride byte offset
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+constexpr uint32_t IDESC_B_MN_MAJOR = 1u << 16;
 // Instruction descriptor, kind::f16: A, B fp16 K-major, D fp32, M=128, N=n
 __host__ __device__ constexpr uint32_t make_idesc(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);

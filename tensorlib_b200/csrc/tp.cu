@@ -6,21 +6,63 @@
 // columns (each rank produces a full-width partial sum -> allreduce), classifier by vocabulary
 // rows (allgather of the logit slices). Decode partial sums travel as fp32 and are rounded to
 // fp16 once after the sum, so a p-GPU run differs from the 1-GPU run only by fp32 summation order.
+//
+// NCCL is bound at run time (dlopen in the first tl_tp_* call), not at link time: a single-GPU
+// process never maps it, and in a process that already holds an NCCL (PyTorch bundles its own,
+// newer than the system copy) the loader hands back that same library instead of a second one
+// with the same soname, which would otherwise shadow the symbols of whoever loads it later.
+#include <dlfcn.h>
 #include <nccl.h>
 
 #include <cstring>
+#include <mutex>
 
 #include "engine.cuh"
 
 namespace tlb {
 namespace {
 
-#define TL_NCCL(expr)                                                                         \
+struct NcclApi {
+    decltype(&::ncclGetUniqueId) GetUniqueId = nullptr;
+    decltype(&::ncclCommInitRank) CommInitRank = nullptr;
+    decltype(&::ncclCommDestroy) CommDestroy = nullptr;
+    decltype(&::ncclAllReduce) AllReduce = nullptr;
+    decltype(&::ncclAllGather) AllGather = nullptr;
+    decltype(&::ncclGetErrorString) GetErrorString = nullptr;
+    bool ok = false;
+    char why[256] = {0};
+};
+NcclApi g_nccl;
+std::once_flag g_nccl_once;
+
+const NcclApi& nccl() {
+    std::call_once(g_nccl_once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
+        if (!h) { snprintf(g_nccl.why, sizeof g_nccl.why, "libnccl.so.2 not found: %s", dlerror()); return; }
+        auto sym = [&](const char* name) { void* p = dlsym(h, name); if (!p) snprintf(g_nccl.why, sizeof g_nccl.why, "%s missing in libnccl", name); return p; };
+        g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(sym("ncclGetUniqueId"));
+        g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(sym("ncclCommInitRank"));
+        g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(sym("ncclCommDestroy"));
+        g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(sym("ncclAllReduce"));
+        g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(sym("ncclAllGather"));
+        g_nccl.GetErrorString = reinterpret_cast<decltype(g_nccl.GetErrorString)>(sym("ncclGetErrorString"));
+        g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllReduce &&
+                    g_nccl.AllGather && g_nccl.GetErrorString;
+    });
+    return g_nccl;
+}
+
+#define TL_NCCL_READY()                                                                       \
     do {                                                                                      \
-        ncclResult_t _r = (expr);                                                             \
+        if (!nccl().ok) return ::tlb::set_error(TL_ERR_COMM, "NCCL is not available: %s", nccl().why); \
+    } while (0)
+#define TL_NCCL(call, ...)                                                                    \
+    do {                                                                                      \
+        ncclResult_t _r = nccl().call(__VA_ARGS__);                                           \
         if (_r != ncclSuccess)                                                                \
-            return ::tlb::set_error(TL_ERR_COMM, "%s failed: %s (%s:%d)", #expr,              \
-                                    ncclGetErrorString(_r), __FILE__, __LINE__);              \
+            return ::tlb::set_error(TL_ERR_COMM, "nccl%s failed: %s (%s:%d)", #call,          \
+                                    nccl().GetErrorString(_r), __FILE__, __LINE__);           \
     } while (0)
 
 class NcclCollective : public Collective {
@@ -28,15 +70,15 @@ public:
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     int allreduce_sum_f16(__half* buf, size_t n, cudaStream_t st) override {
-        TL_NCCL(ncclAllReduce(buf, buf, n, ncclHalf, ncclSum, comm, st));
+        TL_NCCL(AllReduce, buf, buf, n, ncclHalf, ncclSum, comm, st);
         return TL_OK;
     }
     int allreduce_sum_f32(float* buf, size_t n, cudaStream_t st) override {
-        TL_NCCL(ncclAllReduce(buf, buf, n, ncclFloat, ncclSum, comm, st));
+        TL_NCCL(AllReduce, buf, buf, n, ncclFloat, ncclSum, comm, st);
         return TL_OK;
     }
     int allgather_f16(const __half* send, __half* recv, size_t n_per_rank, cudaStream_t st) override {
-        TL_NCCL(ncclAllGather(send, recv, n_per_rank, ncclHalf, comm, st));
+        TL_NCCL(AllGather, send, recv, n_per_rank, ncclHalf, comm, st);
         return TL_OK;
     }
     bool graph_capturable() const override { return true; }
@@ -53,8 +95,9 @@ extern "C" {
 
 int tl_tp_unique_id(void* out, int nbytes) {
     TL_REQUIRE(out && nbytes >= (int)sizeof(ncclUniqueId), "unique id buffer needs %zu bytes", sizeof(ncclUniqueId));
+    TL_NCCL_READY();
     ncclUniqueId id;
-    TL_NCCL(ncclGetUniqueId(&id));
+    TL_NCCL(GetUniqueId, &id);
     memcpy(out, &id, sizeof id);
     return TL_OK;
 }
@@ -65,7 +108,8 @@ int tl_tp_init(const void* unique_id, int nbytes, int rank, int world) {
     TL_REQUIRE(g_coll.comm == nullptr, "tensor-parallel group already initialised");
     ncclUniqueId id;
     memcpy(&id, unique_id, sizeof id);
-    TL_NCCL(ncclCommInitRank(&g_coll.comm, world, id, rank));
+    TL_NCCL_READY();
+    TL_NCCL(CommInitRank, &g_coll.comm, world, id, rank);
     g_coll.rank = rank;
     g_coll.world = world;
     return TL_OK;
@@ -110,7 +154,7 @@ int tl_tp_exchange_close(tl_llama2* m) {
 
 int tl_tp_destroy(void) {
     if (g_coll.comm) {
-        ncclCommDestroy(g_coll.comm);
+        if (nccl().ok) nccl().CommDestroy(g_coll.comm);
         g_coll.comm = nullptr;
     }
     return TL_OK;

@@ -154,7 +154,34 @@ def test_checkpoint_file_loader(tl, tmp_path, golden_tiny, tiny_payload):
     assert_bit_equal(lg[0], golden_tiny["logits_B"][0], "logits after loading from a file")
     with pytest.raises(tl.TLError):
         m.load_file(str(tmp_path / "missing.bin"))
+    # a truncated file is refused before anything is uploaded: the weights stay as loaded
+    short = str(tmp_path / "short.bin")
+    with open(short, "wb") as f:
+        f.write(synth.TINY.header())
+        tiny_payload[: tiny_payload.size // 2].tofile(f)
+    with pytest.raises(tl.TLError, match="truncated"):
+        m.load_file(short)
+    assert_bit_equal(m.forward(golden_tiny["prompt"], 0, all_logits=False)[0], golden_tiny["logits_B"][0], "after refusal")
     m.close()
+
+
+def test_checkpoint_file_loader_untied_classifier_streams_in_chunks(tl, tmp_path):
+    """Untied checkpoint (negative vocab in the header, RoPE block before wcls, main.cpp:160-190) with an
+    embedding larger than one 64 MB staging chunk; file and in-memory loads must give the same logits."""
+    cfg = synth.LlamaConfig(dim=1024, hidden_dim=2816, n_layers=1, n_heads=8, vocab_size=40000, seq_len=64,
+                            shared_classifier=False)
+    payload = synth.llama2c_payload(cfg, 99)
+    path = str(tmp_path / "untied.bin")
+    with open(path, "wb") as f:
+        f.write(cfg.header())
+        payload.tofile(f)
+    tokens = synth.token_ids(99, 3, 24, cfg.vocab_size)
+    a = tl.Llama2(cfg, numerics=tl.FAST)
+    a.load_file(path)
+    b = tl.Llama2(cfg, numerics=tl.FAST)
+    b.load_payload(payload, shared_classifier=False)
+    assert_bit_equal(a.forward(tokens, 0, all_logits=True), b.forward(tokens, 0, all_logits=True), "file vs memory")
+    a.close(); b.close()
 
 
 # head_dim 128 and 32-column-aligned widths: the shapes that take the fused prefill path
@@ -187,3 +214,22 @@ def test_fast_fused_prefill_matches_oracle_at_head_dim_128(tl, oracle, T, tail):
     clear = (s[:, -1] - s[:, -2]) > 2 * err
     assert np.array_equal(got.argmax(1)[clear], want.argmax(1)[clear])
     m.close()
+
+
+def test_multi_turn_generation_continues_over_the_kv_cache(tl, golden_tiny, tiny_payload):
+    """Two turns (llama2.cpp keeps total_len across generate calls) equal one forward over the
+    concatenated token stream, bit for bit in reference-order numerics."""
+    m = make_model(tl, tiny_payload, tl.REFERENCE_ORDER)
+    prompt = golden_tiny["prompt"]
+    ids1, _, _ = m.generate(prompt, 5)
+    assert np.array_equal(ids1, golden_tiny["ids_B"][:5])
+    turn2 = synth.token_ids(SEED, 77, 4, synth.TINY.vocab_size)
+    start = len(prompt) + len(ids1) - 1          # the last sampled id of turn 1 was never fed back
+    ids2, _, _ = m.generate(np.concatenate([ids1[-1:], turn2]), 3, start_pos=start)
+    whole = np.concatenate([prompt, ids1, turn2])
+    m2 = make_model(tl, tiny_payload, tl.REFERENCE_ORDER)
+    lg = m2.forward(whole, 0, all_logits=True)
+    assert int(lg[-1].astype(np.float32).argmax()) == int(ids2[0])
+    with pytest.raises(tl.TLError):
+        m.generate(prompt, 8, start_pos=synth.TINY.seq_len - 4)
+    m.close(); m2.close()

@@ -232,7 +232,7 @@ def test_fused_prefill_attention_peaked_scores_rescale(tl):
 
 def test_fused_prefill_attention_rejects_other_head_sizes(tl):
     d = tl.DeviceBuffer(1 << 16)
-    rc = tl.load().tl_attn_prefill_f16(d.ptr, d.ptr, d.ptr, d.ptr, d.ptr, 4, 0, 2, 48, None)
+    rc = tl.load().tl_attn_prefill_f16(d.ptr, d.ptr, d.ptr, d.ptr, 4, 0, 2, 48, None)
     assert rc == 4  # TL_ERR_UNSUPPORTED
 
 
