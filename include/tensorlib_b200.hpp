@@ -9,6 +9,8 @@
 //   Transformer<half>::forward(tokens, start_pos, buf)  Transformer.hpp:80
 //                                                               Transformer::forward(tokens, start_pos)
 //   Llama2<half>::generate(prompt_tokens)     llama2.hpp:19     Llama2::generate(prompt_tokens, max_new)
+//   Tokenizer::encode / decode                Tokenizer.hpp:33  Tokenizer::encode / decode (host only)
+//   Llama2<half>::text_completion(prompt)     llama2.hpp:20     Llama2::text_completion(tokenizer, prompt)
 //
 // Error behaviour follows the reference: argument/shape errors throw std::invalid_argument
 // (matmul.cpp:209-221); CUDA failures, which the reference answers with exit(1) (CUDA.cuh:131-151),
@@ -17,10 +19,13 @@
 #pragma once
 
 #include <cstdint>
+#include <cstdio>
+#include <fstream>
 #include <memory>
 #include <optional>
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "tensorlib_b200.h"
@@ -168,6 +173,101 @@ private:
     std::shared_ptr<tl_llama2> handle_;
 };
 
+// Byte-pair tokenizer over a llama2.c `tokenizer.bin` (int32 max_token_length, then per entry:
+// float score, int32 length, bytes), the format and algorithm of the reference's Tokenizer
+// (model/llama2_7b/src/Tokenizer.cpp, itself a restatement of llama2.c's): optional BOS (id 1), a
+// " " prefix token for non-empty text, one lookup per UTF-8 code point with byte fallback (byte + 3),
+// then repeatedly merging the adjacent pair whose concatenation has the highest score; optional
+// EOS (id 2). Host only. Two deliberate differences from the reference: decode() does not edit
+// the vocabulary in place (Tokenizer.cpp:155-167 assigns through a reference, so a piece decoded
+// once after BOS loses its leading space for good), and an empty token list does not underflow
+// the merge loop's bound (Tokenizer.cpp:131).
+class Tokenizer {
+public:
+    Tokenizer(const std::string& tokenizer_file, int vocab_size) : vocab_(vocab_size), scores_(vocab_size) {
+        std::ifstream f(tokenizer_file, std::ios::binary);
+        if (!f) throw std::runtime_error("couldn't load " + tokenizer_file);
+        int32_t max_len = 0;
+        f.read(reinterpret_cast<char*>(&max_len), sizeof max_len);
+        for (int i = 0; i < vocab_size; i++) {
+            int32_t len = 0;
+            f.read(reinterpret_cast<char*>(&scores_[i]), sizeof(float));
+            f.read(reinterpret_cast<char*>(&len), sizeof len);
+            if (!f || len < 0 || len > (1 << 20)) throw std::runtime_error("tokenizer file is truncated or corrupt");
+            vocab_[i].resize((size_t)len);
+            f.read(&vocab_[i][0], len);
+            if (!f) throw std::runtime_error("tokenizer file is truncated");
+            index_.emplace(vocab_[i], i);          // first id wins for a repeated piece
+        }
+    }
+    int vocab_size() const { return (int)vocab_.size(); }
+
+    std::vector<int> encode(const std::string& text, bool bos, bool eos) const {
+        std::vector<int> tokens;
+        if (bos) tokens.push_back(1);
+        if (!text.empty()) {
+            const int space = lookup(" ");
+            if (space < 0) throw std::invalid_argument("tokenizer vocabulary has no \" \" piece");
+            tokens.push_back(space);
+        }
+        std::string cp;                               // bytes of the current code point
+        for (size_t i = 0; i < text.size(); i++) {
+            const unsigned char c = (unsigned char)text[i];
+            if ((c & 0xC0) != 0x80) cp.clear();       // a lead byte starts a new code point
+            cp.push_back((char)c);
+            const unsigned char next = i + 1 < text.size() ? (unsigned char)text[i + 1] : 0;
+            if ((next & 0xC0) == 0x80 && cp.size() < 4) continue;
+            const int id = lookup(cp);
+            if (id >= 0) tokens.push_back(id);
+            else for (unsigned char b : cp) tokens.push_back((int)b + 3);
+            cp.clear();
+        }
+        while (tokens.size() >= 2) {
+            float best_score = -1e10f;
+            int best_id = -1;
+            size_t best_at = 0;
+            for (size_t i = 0; i + 1 < tokens.size(); i++) {
+                const int id = lookup(vocab_[(size_t)tokens[i]] + vocab_[(size_t)tokens[i + 1]]);
+                if (id >= 0 && scores_[(size_t)id] > best_score) { best_score = scores_[(size_t)id]; best_id = id; best_at = i; }
+            }
+            if (best_id < 0) break;
+            tokens[best_at] = best_id;
+            tokens.erase(tokens.begin() + (long)best_at + 1);
+        }
+        if (eos) tokens.push_back(2);
+        return tokens;
+    }
+
+    // the text of `token` given its predecessor: no leading space right after BOS; <0xHH> pieces
+    // are the raw byte (byte 0 decodes to the empty string, as a C string would)
+    std::string decode(int prev_token, int token) const {
+        if (token < 0 || token >= (int)vocab_.size()) throw std::invalid_argument("token id out of range");
+        std::string piece = vocab_[(size_t)token];
+        if (prev_token == 1 && !piece.empty() && piece[0] == ' ') piece.erase(0, 1);
+        unsigned int byte = 0;
+        int digits = 0;
+        if (piece.size() >= 4 && piece.compare(0, 3, "<0x") == 0) {
+            for (size_t i = 3; i < piece.size() && digits < 2; i++, digits++) {
+                const char ch = piece[i];
+                const int v = ch >= '0' && ch <= '9' ? ch - '0' : ch >= 'a' && ch <= 'f' ? ch - 'a' + 10 : ch >= 'A' && ch <= 'F' ? ch - 'A' + 10 : -1;
+                if (v < 0) break;
+                byte = byte * 16 + (unsigned)v;
+            }
+        }
+        if (digits > 0) return byte == 0 ? std::string() : std::string(1, (char)byte);
+        return piece;
+    }
+
+private:
+    int lookup(const std::string& s) const {
+        auto it = index_.find(s);
+        return it == index_.end() ? -1 : it->second;
+    }
+    std::vector<std::string> vocab_;
+    std::vector<float> scores_;
+    std::unordered_map<std::string, int> index_;
+};
+
 struct GenerateResult {
     std::vector<int> tokens;          // generated ids (without the prompt)
     double prefill_seconds = 0, decode_seconds = 0;
@@ -190,6 +290,19 @@ public:
                                  stop_on_eos ? 1 : 0, r.tokens.data(), &n_out, &r.prefill_seconds, &r.decode_seconds));
         r.tokens.resize((size_t)n_out);
         return r;
+    }
+    // Llama2::text_completion (llama2.cpp:104-107): encode with BOS, generate, decode piece by piece
+    std::string text_completion(const Tokenizer& tokenizer, const std::string& prompt, int max_new = 256) {
+        const std::vector<int> ids = tokenizer.encode(prompt, true, false);
+        const GenerateResult r = generate(ids, max_new, true);
+        std::string out;
+        int prev = ids.empty() ? 1 : ids.back();
+        for (int t : r.tokens) {
+            if (t == 1 || t == 2) break;
+            out += tokenizer.decode(prev, t);
+            prev = t;
+        }
+        return out;
     }
     Transformer model;
 };

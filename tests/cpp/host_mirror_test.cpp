@@ -101,14 +101,52 @@ static int run_gpu(const char* ckpt, const char* case_path) {
     return failures;
 }
 
+// tokenizer <tokenizer.bin> <cases.txt>: cases.txt holds, per case,
+//   bos eos n_text_bytes bytes... n_ids ids... n_dec {prev tok n_bytes bytes...}...
+// with the ids / pieces the reference's own Tokenizer produced (tests/golden/tokenizer_cases.json)
+static int run_tokenizer(const char* vocab_path, const char* cases_path) {
+    std::ifstream in(cases_path);
+    int vocab_size = 0, n_cases = 0, failures = 0;
+    in >> vocab_size >> n_cases;
+    Tokenizer tok(vocab_path, vocab_size);
+    for (int c = 0; c < n_cases; c++) {
+        int bos, eos, nb, ni, nd;
+        in >> bos >> eos >> nb;
+        std::string text((size_t)nb, '\0');
+        for (int i = 0; i < nb; i++) { int v; in >> v; text[(size_t)i] = (char)v; }
+        in >> ni;
+        std::vector<int> want((size_t)ni);
+        for (int& v : want) in >> v;
+        const std::vector<int> got = tok.encode(text, bos != 0, eos != 0);
+        if (got != want) { std::printf("FAIL encode case %d\n", c); failures++; }
+        in >> nd;
+        for (int d = 0; d < nd; d++) {
+            int prev, t, len;
+            in >> prev >> t >> len;
+            std::string piece((size_t)len, '\0');
+            for (int i = 0; i < len; i++) { int v; in >> v; piece[(size_t)i] = (char)v; }
+            if (tok.decode(prev, t) != piece) { std::printf("FAIL decode case %d token %d\n", c, t); failures++; }
+        }
+    }
+    if (!in) { std::puts("FAIL cases file truncated"); return 1; }
+    // decode must not change later encodes (the reference edits its vocabulary in place)
+    const std::vector<int> before = tok.encode(" the", true, false);
+    for (int t : before) tok.decode(1, t);
+    if (tok.encode(" the", true, false) != before) { std::puts("FAIL decode changed the vocabulary"); failures++; }
+    if (!tok.encode("", false, false).empty()) { std::puts("FAIL empty text"); failures++; }
+    if (!failures) std::printf("OK tokenizer: %d cases identical to the reference\n", n_cases);
+    return failures;
+}
+
 int main(int argc, char** argv) {
     try {
+        if (argc >= 4 && !std::strcmp(argv[1], "tokenizer")) return run_tokenizer(argv[2], argv[3]) ? 1 : 0;
         if (argc >= 2 && !std::strcmp(argv[1], "nogpu")) return run_nogpu() ? 1 : 0;
         if (argc >= 4 && !std::strcmp(argv[1], "gpu")) return run_gpu(argv[2], argv[3]) ? 1 : 0;
     } catch (const std::exception& e) {
         std::printf("FAIL unexpected exception: %s\n", e.what());
         return 1;
     }
-    std::puts("usage: host_mirror_test nogpu | gpu <checkpoint> <case>");
+    std::puts("usage: host_mirror_test nogpu | gpu <checkpoint> <case> | tokenizer <tokenizer.bin> <cases>");
     return 2;
 }

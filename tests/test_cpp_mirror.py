@@ -39,6 +39,27 @@ def test_cpp_mirror_compiles_and_refuses_without_a_device(mirror_binary):
     assert "no CPU path" in r.stdout and "FAIL" not in r.stdout
 
 
+def test_cpp_tokenizer_matches_the_reference_tokenizer(mirror_binary, tmp_path):
+    """Host only: every encoding and decoded piece of the committed fixture, which
+    tests/golden/make_tokenizer_golden.py produced with the reference's own Tokenizer."""
+    import json
+    golden = os.path.join(ROOT, "tests", "golden")
+    with open(os.path.join(golden, "tokenizer_cases.json")) as f:
+        g = json.load(f)
+    lines = [f"{g['vocab_size']} {len(g['cases'])}"]
+    for c in g["cases"]:
+        tb = list(c["text"].encode())
+        parts = [c["bos"], c["eos"], len(tb), *tb, len(c["ids"]), *c["ids"], len(c["decode"])]
+        for prev, tok, piece in c["decode"]:
+            parts += [prev, tok, len(piece), *piece]
+        lines.append(" ".join(str(int(v)) for v in parts))
+    cases = tmp_path / "tok_cases.txt"
+    cases.write_text("\n".join(lines) + "\n")
+    r = subprocess.run([mirror_binary, "tokenizer", os.path.join(golden, "tokenizer.bin"), str(cases)],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "OK tokenizer" in r.stdout, r.stdout + r.stderr
+
+
 @pytest.mark.gpu
 def test_cpp_mirror_matches_reference_on_tiny_config(mirror_binary, oracle, golden_tiny, tmp_path):
     cfg = synth.TINY
