@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 #include <string>
@@ -116,6 +117,10 @@ int Llama2Engine::allocate() {
     // decode attention: enough CTAs to cover the SMs
     attn_splits_ = 1;
     while (H_local_ * attn_splits_ < sm_count() && attn_splits_ < 8) attn_splits_ *= 2;  // <= 8: one cluster per head
+    if (const char* e = getenv("TL_ATTN_SPLITS")) {   // experiments: 1, 2, 4 or 8
+        const int v = atoi(e);
+        if (v == 1 || v == 2 || v == 4 || v == 8) attn_splits_ = v;
+    }
     TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * 16 * (hd_ + 2) * sizeof(float)));
     allocs_.push_back(d);
     attn_scratch_ = static_cast<float*>(d);

@@ -10,7 +10,7 @@ import numpy as np
 import tensorlib_b200 as tl
 
 SHARD_REPLICATED, SHARD_ROWS, SHARD_COLS = 0, 1, 2
-# how each checkpoint tensor of the Llama2 block is split (SURVEY: wq/wk/wv/w1/w3 by output rows,
+# how each checkpoint tensor of the Llama2 block is split (Megatron scheme: wq/wk/wv/w1/w3 by output rows,
 # wo/w2 by input columns, classifier by vocabulary rows, embedding and norms replicated)
 SHARD_KIND = {"tok_embeddings": SHARD_REPLICATED, "attention_norm": SHARD_REPLICATED, "ffn_norm": SHARD_REPLICATED,
               "norm": SHARD_REPLICATED, "wq": SHARD_ROWS, "wk": SHARD_ROWS, "wv": SHARD_ROWS, "w1": SHARD_ROWS,

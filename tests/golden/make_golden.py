@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this folder from the REFERENCE ITSELF.
 
 Runs the reference's own CPU code (oracle/_ref/libtl_ref.so, built by oracle/Makefile from the
-unmodified sources under /root/reference) on seeded synthetic inputs and stores small outputs:
+unmodified reference sources, variable REF there) on seeded synthetic inputs and stores small outputs:
 
   tiny_llama2.npz   config 0 of the benchmark spec: tiny Llama2 (dim 288, hidden 768, 6 layers,
                     6 heads, vocab 32000, seq 256), weights N(0, 0.02) seed 20240229, norms = 1,
@@ -15,7 +15,7 @@ unmodified sources under /root/reference) on seeded synthetic inputs and stores 
   matmul_sweep.npz  the four (K, N) pairs of the sweep at M = 1 and 8: SHA-256 of the outputs and
                     the first 64 values of each.
 
-Only this script needs /root/reference (through the built library); the tests read the .npz
+Only this script needs the reference checkout (through the built library); the tests read the .npz
 files. Usage:  make -C oracle ref && python tests/golden/make_golden.py
 """
 from __future__ import annotations
