@@ -295,12 +295,11 @@ int launch_flash_prefill(const __half* q, const __half* k, const __half* v, __ha
                          cudaStream_t st) {
     TL_REQUIRE(flash_prefill_supported(q, k, v, out, T, S, pos0, heads, head_dim, ldq, ldk, ldv, ldo),
                "flash prefill: unsupported shape or alignment (head_dim must be %d)", HD);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_flash_prefill, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM));
         TL_CUDA(cudaFuncSetAttribute(k_flash_prefill, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      (int)cudaSharedmemCarveoutMaxShared));
-        configured = true;
     }
     CUtensorMap mq, mk, mv;
     TL_PROPAGATE(make_tensor_map_f16(&mq, q, T, HD, ldq, HD, heads, BQ));

@@ -19,6 +19,19 @@ int set_error(int status, const char* fmt, ...);
 bool initialized();
 int sm_count();
 
+// Kernel attributes (opt-in shared-memory size) belong to a device: a process that moves between
+// devices with tl_init must set them once on each. One of these per kernel instantiation.
+struct PerDeviceOnce {
+    unsigned long long done = 0;   // bit d: configured on device d (d < 64)
+    bool needed() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+        if (done & (1ull << dev)) return false;
+        done |= 1ull << dev;
+        return true;
+    }
+};
+
 #define TL_REQUIRE(cond, ...)                                              \
     do {                                                                   \
         if (!(cond)) return ::tlb::set_error(TL_ERR_INVALID_ARGUMENT, __VA_ARGS__); \

@@ -590,10 +590,9 @@ int mega_smem_bytes(int max_k) {
 }
 
 int launch_decode_mega(const MegaArgs& args, int grid, int smem, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
     }
     TL_CUDA(cudaMemsetAsync(args.grid_bar, 0, sizeof(unsigned int), st));
     cudaLaunchConfig_t cfg{};

@@ -561,33 +561,32 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
 // memory so the same launches can be replayed from a CUDA graph.
 // ---- fused tensor-parallel exchange -----------------------------------------------------------------
 namespace {
-// greedy sampling over logits that the ranks pushed slice by slice: wait for every rank's flag
-// (bounded), then the usual lowest-index argmax
-__global__ void k_argmax_after_exchange(int* out_idx, const __half* logits, int cols, const unsigned int* flags,
-                                        int world, const unsigned int* step_ptr, int phases_per_step,
-                                        int phase_id, int* status) {
+// greedy sampling over logits that the ranks pushed slice by slice as (two fp16 logits, epoch)
+// words: wait (bounded) for every word of this step, unpack into the plain logits row, then the
+// usual lowest-index argmax
+__global__ void k_argmax_after_exchange(int* out_idx, const unsigned long long* words, __half* logits, int cols,
+                                        const unsigned int* step_ptr, int phases_per_step, int phase_id, int* status) {
     __shared__ float sv[32];
     __shared__ int si[32];
     const unsigned int epoch = __ldcg(step_ptr) * (unsigned)phases_per_step + (unsigned)phase_id + 1u;
-    if ((int)threadIdx.x < world) {   // one watcher per source rank
-        bool seen = false;
-        const unsigned int* flag = flags + threadIdx.x * TL_XCH_FLAG_STRIDE;
-        for (unsigned i = 0; i < (1u << 22) && !seen; i++) {
-            unsigned int v;
-            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            seen = (int)(v - epoch) >= 0;
-        }
-        if (!seen) atomicExch(status, TL_ERR_TIMEOUT);
-        asm volatile("fence.acq_rel.sys;" ::: "memory");
-    }
-    __syncthreads();
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
-        unsigned short raw = __ldcg(reinterpret_cast<const unsigned short*>(logits) + j);
-        float v = __half2float(__ushort_as_half(raw));
-        if (bi == 0x7fffffff || v > bv) { bv = v; bi = j; }
+    bool timed_out = false;
+    for (int j = threadIdx.x; 2 * j < cols; j += blockDim.x) {
+        unsigned int data = 0, flag = 0;
+        bool here = false;
+        for (unsigned i = 0; i < (1u << 18) && !here; i++) {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(data), "=r"(flag) : "l"(words + j) : "memory");
+            here = flag == epoch;
+        }
+        timed_out |= !here;
+        *reinterpret_cast<unsigned int*>(logits + 2 * j) = data;
+        const __half2 h = *reinterpret_cast<const __half2*>(&data);
+        const float v0 = __low2float(h), v1 = __high2float(h);
+        if (bi == 0x7fffffff || v0 > bv) { bv = v0; bi = 2 * j; }
+        if (2 * j + 1 < cols && v1 > bv) { bv = v1; bi = 2 * j + 1; }
     }
+    if (timed_out) atomicExch(status, TL_ERR_TIMEOUT);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -612,15 +611,15 @@ __global__ void k_advance_tp(int* pos, const int* next, int* generated, int max_
 
 int Llama2Engine::xch_export(cudaIpcMemHandle_t* out) {
     TL_REQUIRE(out && cfg_.tp_world > 1 && cfg_.tp_world <= TL_MAX_TP, "exchange needs 2..%d ranks", TL_MAX_TP);
+    TL_REQUIRE(vocab_local_ % 2 == 0 && cfg_.dim % 8 == 0, "exchange needs an even vocabulary slice and dim %% 8 == 0");
     if (!xch_base_) {
         const size_t dim = cfg_.dim, W = cfg_.tp_world;
         size_t off = 0;
         auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) & ~(size_t)255; return o; };
-        xch_off_part_[0] = take(W * dim * sizeof(float));
-        xch_off_part_[1] = take(W * dim * sizeof(float));
-        xch_off_logits_ = take((size_t)cfg_.vocab_size * sizeof(__half));
-        xch_off_flags_ = take((size_t)3 * TL_MAX_TP * TL_XCH_FLAG_STRIDE * sizeof(unsigned int));
-        xch_off_done_ = take(3 * sizeof(unsigned int));
+        // every payload travels as an 8-byte (payload, epoch) word
+        xch_off_part_[0] = take(W * dim * sizeof(unsigned long long));
+        xch_off_part_[1] = take(W * dim * sizeof(unsigned long long));
+        xch_off_logits_ = take(((size_t)cfg_.vocab_size / 2 + 1) * sizeof(unsigned long long));
         xch_off_step_ = take(sizeof(unsigned int));
         xch_bytes_ = off;
         void* d = nullptr;
@@ -661,17 +660,13 @@ int Llama2Engine::xch_close() {
 PeerExchange Llama2Engine::make_exchange(int buf, int phase_id) const {
     PeerExchange e{};
     e.world = cfg_.tp_world; e.rank = cfg_.tp_rank;
-    const size_t slot_bytes = buf < 2 ? (size_t)cfg_.dim * sizeof(float) : (size_t)vocab_local_ * sizeof(__half);
+    // words per rank slot: one per fp32 partial sum, one per pair of fp16 logits
+    const size_t slot_words = buf < 2 ? (size_t)cfg_.dim : (size_t)vocab_local_ / 2;
     const size_t base_off = buf < 2 ? xch_off_part_[buf] : xch_off_logits_;
     e.n = buf < 2 ? cfg_.dim : vocab_local_;
-    e.done_counter = reinterpret_cast<unsigned int*>(xch_base_ + xch_off_done_) + buf;
-    e.local_slots = xch_base_ + base_off;
-    e.local_flags = reinterpret_cast<const unsigned int*>(xch_base_ + xch_off_flags_) + (size_t)buf * TL_MAX_TP * TL_XCH_FLAG_STRIDE;
-    for (int d = 0; d < e.world; d++) {
-        e.peer_slot[d] = xch_peer_[d] + base_off + (size_t)e.rank * slot_bytes;
-        e.peer_flag[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + xch_off_flags_) +
-                         ((size_t)buf * TL_MAX_TP + e.rank) * TL_XCH_FLAG_STRIDE;
-    }
+    e.local_slots = reinterpret_cast<const unsigned long long*>(xch_base_ + base_off);
+    for (int d = 0; d < e.world; d++)
+        e.peer_slot[d] = reinterpret_cast<unsigned long long*>(xch_peer_[d] + base_off) + (size_t)e.rank * slot_words;
     e.step_ptr = reinterpret_cast<const unsigned int*>(xch_base_ + xch_off_step_);
     e.phases_per_step = 2 * cfg_.n_layers + 1;
     e.phase_id = phase_id;
@@ -734,15 +729,13 @@ int Llama2Engine::decode_step_tp_fused(cudaStream_t st, bool pdl) {
     c.W[0] = wcls_; c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_PUSH_F16; c.xout = &out_cls;
     c.pdl = pdl;
     TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
-    const __half* lg = reinterpret_cast<const __half*>(xch_base_ + xch_off_logits_);
-    k_argmax_after_exchange<<<1, 1024, 0, st>>>(d_next_, lg, cfg_.vocab_size, out_cls.local_flags, cfg_.tp_world,
-                                                out_cls.step_ptr, out_cls.phases_per_step,
-                                                out_cls.phase_id, device_status_word()); n++;
+    k_argmax_after_exchange<<<1, 1024, 0, st>>>(d_next_, out_cls.local_slots, logits_, cfg_.vocab_size, out_cls.step_ptr,
+                                                out_cls.phases_per_step, out_cls.phase_id, device_status_word()); n++;
     TL_LAUNCH_CHECK();
     k_advance_tp<<<1, 1, 0, st>>>(d_pos_, d_next_, d_generated_, cfg_.max_seq_len,
                                   reinterpret_cast<unsigned int*>(xch_base_ + xch_off_step_)); n++;
     TL_LAUNCH_CHECK();
-    last_logits_ = lg;
+    last_logits_ = logits_;
     decode_step_launches_ = n;
     launches_ += n;
     return TL_OK;

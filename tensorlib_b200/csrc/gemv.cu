@@ -147,13 +147,17 @@ struct RingArgs {
     PeerExchange xin, xout;
 };
 
-__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// 16 bytes = two (payload, epoch) words, one volatile access (served by L2, where peer stores land)
+__device__ __forceinline__ uint4 ld_words2(const unsigned long long* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_words2(unsigned long long* p, unsigned int d0, unsigned int d1, unsigned int epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(epoch), "r"(d1), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ void st_word(unsigned long long* p, unsigned int d, unsigned int epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(d), "r"(epoch) : "memory");
 }
 __device__ __forceinline__ unsigned int exchange_epoch(const PeerExchange& e) {
     return __ldcg(e.step_ptr) * (unsigned)e.phases_per_step + (unsigned)e.phase_id + 1u;
@@ -245,31 +249,32 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
     const int ctid = threadIdx.x;  // 0..255
     const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
     float rinv = 1.0f;
-    if (p.has_xin) {
-        // Tensor-parallel input: wait (bounded) until every rank has pushed its partial vector of
-        // this step into the local slots, then x = residual + sum over ranks, in rank order.
-        const PeerExchange& e = p.xin;
-        const unsigned int epoch = exchange_epoch(e);
-        if (ctid < e.world) {   // one watcher per source rank
-            bool seen = false;
-            for (uint32_t i = 0; i < WAIT_LIMIT; i++)
-                if ((int)(ld_relaxed_sys(e.local_flags + ctid * TL_XCH_FLAG_STRIDE) - epoch) >= 0) { seen = true; break; }
-            if (!seen) atomicExch(p.status, TL_ERR_TIMEOUT);
-            asm volatile("fence.acq_rel.sys;" ::: "memory");   // the pushed data is read after the flags
-        }
-        consumer_bar_sync(CONSUMERS * 32);
-    }
+    // Tensor-parallel input (has_xin): x = residual + sum over ranks of the partial vectors the ranks
+    // pushed into the local slots; a word counts once its epoch is this step's (bounded retries).
+    const unsigned int xin_epoch = p.has_xin ? exchange_epoch(p.xin) : 0u;
+    const unsigned int xout_epoch = (EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16) ? exchange_epoch(p.xout) : 0u;
     // one 16-byte group of the activation vector (plain, or reduced over the ranks)
     auto load_x = [&](int c) -> uint4 {
         if (!p.has_xin) return x4[c];
         const PeerExchange& e = p.xin;
-        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < e.world; r++) {
-            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(e.local_slots) + (size_t)r * e.n) + 2 * c;
-            const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
-            s[0] += lo.x; s[1] += lo.y; s[2] += lo.z; s[3] += lo.w;
-            s[4] += hi.x; s[5] += hi.y; s[6] += hi.z; s[7] += hi.w;
+        float s[8];
+        bool all_here = false;
+        for (uint32_t tries = 0; tries < (WAIT_LIMIT >> 4) && !all_here; tries++) {
+            all_here = true;
+#pragma unroll
+            for (int i = 0; i < 8; i++) s[i] = 0.f;
+            for (int r = 0; r < e.world; r++) {   // no branch inside: the loads of all ranks are in flight together
+                const unsigned long long* src = e.local_slots + (size_t)r * e.n + 8 * c;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint4 w = ld_words2(src + 2 * q);
+                    s[2 * q] += __uint_as_float(w.x);
+                    s[2 * q + 1] += __uint_as_float(w.z);
+                    all_here &= (w.y == xin_epoch) & (w.w == xin_epoch);
+                }
+            }
         }
+        if (!all_here) atomicExch(p.status, TL_ERR_TIMEOUT);
         uint4 res = __ldcg(reinterpret_cast<const uint4*>(e.residual) + c), out;
         const __half* rh = reinterpret_cast<const __half*>(&res);
         __half* oh = reinterpret_cast<__half*>(&out);
@@ -377,11 +382,12 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         } else if (EPI == EPI_PUSH_F32) {  // K-split partial sums into slot [rank] on every rank
 #pragma unroll 1
             for (int d = 0; d < p.xout.world; d++)
-                *reinterpret_cast<float2*>(static_cast<float*>(p.xout.peer_slot[d]) + r) = make_float2(sa, sb);
+                st_words2(p.xout.peer_slot[d] + r, __float_as_uint(sa), __float_as_uint(sb), xout_epoch);
         } else if (EPI == EPI_PUSH_F16) {  // row-split results (classifier slice) onto every rank
 #pragma unroll 1
+            const __half2 pair = __halves2half2(ha, hb);
             for (int d = 0; d < p.xout.world; d++)
-                *reinterpret_cast<__half2*>(static_cast<__half*>(p.xout.peer_slot[d]) + r) = __halves2half2(ha, hb);
+                st_word(p.xout.peer_slot[d] + (r >> 1), *reinterpret_cast<const unsigned int*>(&pair), xout_epoch);
         } else if (EPI == EPI_RESIDUAL) {  // h = x + linear(...), fp16 add like Tensor::EwiseAdd
             p.y[r] = hadd_ref(p.residual[r], ha);
             p.y[r + 1] = hadd_ref(p.residual[r + 1], hb);
@@ -406,24 +412,6 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         }
     }
     if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
-    if (EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16) {
-        // All of this CTA's peer stores are issued (warp 0 made them). bar.sync orders them before
-        // thread 0's fence + counter increment (gpu scope); the CTA that sees the full count issues
-        // one system-scope fence, which is cumulative over every CTA's stores, and raises this
-        // rank's flag on every rank. (Per-CTA flags were measured: polling world*grid flags in
-        // every consumer CTA costs more than this counter.)
-        consumer_bar_sync(CONSUMERS * 32);
-        if (ctid == 0) {
-            __threadfence();
-            const unsigned int prev = atomicAdd(p.xout.done_counter, 1u);
-            if (prev == gridDim.x - 1) {
-                atomicExch(p.xout.done_counter, 0u);
-                const unsigned int epoch = exchange_epoch(p.xout);
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                for (int d = 0; d < p.xout.world; d++) st_relaxed_sys(p.xout.peer_flag[d], epoch);
-            }
-        }
-    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -510,10 +498,9 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, b
 
 template <int EPI, bool NORM>
 int launch_ring(const RingArgs& a, size_t smem, int grid, cudaStream_t st, bool pdl) {
-    static bool configured = false;  // per instantiation
-    if (!configured) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_gemv_ring<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
     }
     return launch_pdl(k_gemv_ring<EPI, NORM>, dim3(grid), dim3(RING_THREADS), smem, st, pdl, a);
 }

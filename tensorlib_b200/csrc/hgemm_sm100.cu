@@ -502,10 +502,9 @@ template <int BN, int EPI>
 int launch_k(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
              const GemmArgs& a, int tiles, cudaStream_t st) {
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_hgemm<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
     }
     const int grid = std::max(1, std::min(tiles, sm_count()));
     k_hgemm<BN, EPI><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mb2, mb3, a);
@@ -523,10 +522,9 @@ int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CU
 template <int EPI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
                 const GemmArgs& a, int pair_tiles, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_hgemm_pair<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
-        configured = true;
     }
     const int grid = 2 * std::max(1, std::min(pair_tiles, sm_count() / 2));
     k_hgemm_pair<EPI><<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(ma, mb, mb2, mb3, a);

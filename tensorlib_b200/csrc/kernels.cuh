@@ -60,29 +60,26 @@ enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGL
 // Tensor-parallel exchange fused into the GEMV kernels (no collective library call in between).
 // Producer side (a K-split matmul: wo, w2; or the vocabulary-split classifier): the epilogue
 // stores its results straight into slot [my_rank] of a receive buffer in EVERY rank's memory
-// (plain peer stores over NVLink); the last CTA to finish then raises flag [my_rank] on every
-// rank to this step's epoch. Consumer side (the prologue of the next GEMV): wait, with a bound,
-// until all `world` flags of the local buffer have reached the epoch, then sum the `world`
-// partial vectors in rank order in fp32, round once to fp16 and add the residual in fp16, i.e. the
-// arithmetic of the single-GPU path up to fp32 summation order. Data is pushed into the
-// consumer's own memory; nothing is ever loaded from a peer, and no TMA multicast is involved.
-// One flag per (buffer, source rank), each on its own 128-byte line; a grid-wide counter in local
-// memory elects the last producing CTA (a per-CTA flag variant measured 10 % slower: the consumer
-// then polls world * grid flags instead of world).
+// (plain peer stores over NVLink). Every 8-byte word carries 4 bytes of payload (one fp32
+// partial sum, or two fp16 logits) and the 4-byte epoch of this step and phase, written by one
+// 8- or 16-byte store, so a word is valid exactly when its epoch matches: no flags, no fences,
+// no counters, and the latency of an exchange is one store's flight over NVLink.
+// Consumer side (the prologue of the next GEMV): read the `world` slots, retry (bounded) any
+// word whose epoch is not this step's yet, sum in rank order in fp32, round once to fp16 and add
+// the residual in fp16, i.e. the arithmetic of the single-GPU path up to fp32 summation order.
+// Data is pushed into the consumer's own memory; nothing is ever loaded from a peer.
+// Slots are reused every step without a second handshake: a rank can only reach the next writer
+// of a slot after consuming data its peers produce after their reads of that slot.
 constexpr int TL_MAX_TP = 8;
-constexpr int TL_XCH_FLAG_STRIDE = 32;   // unsigned ints between two flags (one 128-byte line each)
 struct PeerExchange {
     int world, rank;
-    int n;                               // elements per rank slot
-    // consumer view (local memory): slots [world][n] and flags [world] (stride TL_XCH_FLAG_STRIDE)
-    const void* local_slots; const unsigned int* local_flags;
-    // producer view: for every destination rank d, the address of slot [my rank] / flag [my rank] there
-    void* peer_slot[TL_MAX_TP]; unsigned int* peer_flag[TL_MAX_TP];
-    unsigned int* done_counter;          // local: CTAs of the producing kernel that finished their stores
-    const unsigned int* step_ptr;        // local: decode step counter (same value on every rank)
-    int phases_per_step, phase_id;       // epoch = *step_ptr * phases_per_step + phase_id + 1
+    int n;                                       // payload elements per rank slot (fp32 sums or fp16 logits)
+    const unsigned long long* local_slots;       // consumer view: [world][words per slot]
+    unsigned long long* peer_slot[TL_MAX_TP];    // producer view: slot [my rank] in rank d's memory
+    const unsigned int* step_ptr;                // local: decode step counter (same value on every rank)
+    int phases_per_step, phase_id;               // epoch = *step_ptr * phases_per_step + phase_id + 1
     // consumer extras
-    const __half* residual; __half* sum_out;   // x = residual + sum; CTA 0 also writes it to sum_out
+    const __half* residual; __half* sum_out;     // x = residual + sum; CTA 0 also writes it to sum_out
 };
 struct FusedGemv {
     // input vector (M = 1) and optional RMSNorm prologue

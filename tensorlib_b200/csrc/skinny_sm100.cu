@@ -263,10 +263,9 @@ int workspace_for(cudaStream_t st, Workspace* out) {
 
 template <int NB>
 int launch_nb(const CUtensorMap& mw, const CUtensorMap& mx, const SkinnyArgs& a, int grid, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_skinny<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SkinnyCfg<NB>::SMEM));
-        configured = true;
     }
     k_skinny<NB><<<grid, SK_THREADS, SkinnyCfg<NB>::SMEM, st>>>(mw, mx, a);
     TL_LAUNCH_CHECK();
