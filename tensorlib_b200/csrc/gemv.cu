@@ -19,6 +19,9 @@
 //
 //  k_gemv (M = 1..8, tl_matmul2d_f16): activations staged in shared memory, each warp owns two
 //  rows and streams them with 128-bit non-allocating loads, 16 of them in flight per lane.
+#include <cstdlib>
+#include <cstring>
+
 #include "kernels.cuh"
 
 namespace tlb {
@@ -108,17 +111,31 @@ __device__ __forceinline__ void consumer_bar_sync(int threads) {  // the consume
 // ---------------------------------------------------------------------------------------------
 // k_gemv_ring
 // ---------------------------------------------------------------------------------------------
-constexpr int CONSUMERS = 16;                      // consumer warps; a stage holds 16 units = 32 rows
-constexpr int RING_THREADS = (CONSUMERS + 1) * 32; // + one producer warp
 constexpr int KC = 1024;                           // halfs per row-chunk
-constexpr int CHUNK_BYTES = KC * 2;                // 2 KB
+constexpr int CHUNK_BYTES = KC * 2;                // 2 KB: the smallest copy that keeps the TMA request rate off the critical path
 // rows sit 2 KB + 16 B apart so that the 8 row addresses of an ldmatrix phase fall into
 // different banks
 constexpr int ROW_STRIDE = CHUNK_BYTES + 16;
-constexpr int STAGE_ROWS = CONSUMERS * 2;
-constexpr int STAGE_BYTES = STAGE_ROWS * ROW_STRIDE;  // 66,048 B
-constexpr int NSTAGES = 3;
-constexpr int STEPS_PER_WARP = KC / 16 / CONSUMERS;   // k16 steps of a chunk each warp multiplies
+// Two shapes of the same kernel. CW = consumer warps, NST = ring stages; a stage holds CW units =
+// 2*CW weight rows (CW/8 m16 MMA tiles).
+//   <16, 3>  one CTA per SM, 3 x 64.5 KB ring
+//   <8, 3>, <8, 2>  two CTAs per SM (3 or 2 stages of 32 KB, by the size of the staged vector):
+//            the same 16 consumer warps and ~190 KB of ring per SM, but a CTA that finishes
+//            hands its half of the SM to a CTA of the NEXT kernel, which starts streaming its
+//            weights while the other half is still working: the weight stream does not pause at
+//            kernel boundaries.
+template <int CW, int NST> struct RingCfg {
+    static constexpr int THREADS = (CW + 1) * 32;          // + one producer warp
+    static constexpr int STAGE_ROWS = CW * 2;
+    static constexpr int STAGE_BYTES = STAGE_ROWS * ROW_STRIDE;
+    static constexpr int STEPS_PER_WARP = KC / 16 / CW;    // k16 steps of a chunk each warp multiplies
+    static constexpr int M16 = STAGE_ROWS / 16;            // m16 tiles per stage
+    static constexpr int CTAS_PER_SM = CW == 16 ? 1 : 2;
+    static size_t smem_bytes(int K) {
+        return (size_t)NST * STAGE_BYTES + (((size_t)K * 2 + 127) & ~(size_t)127) + 2 * NST * sizeof(uint64_t) +
+               CW * sizeof(float) + 2 * CW * STAGE_ROWS * sizeof(float) + 64;
+    }
+};
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -180,8 +197,11 @@ __device__ __forceinline__ void unit_rows(const RingArgs& p, int unit, const __h
     }
 }
 
-template <int EPI, bool NORM>
-__global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
+template <int EPI, bool NORM, int CW, int NST>
+__global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::CTAS_PER_SM) k_gemv_ring(RingArgs p) {
+    using Cfg = RingCfg<CW, NST>;
+    constexpr int CONSUMERS = CW, NSTAGES = NST, STAGE_ROWS = Cfg::STAGE_ROWS, STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int STEPS_PER_WARP = Cfg::STEPS_PER_WARP;
     extern __shared__ __align__(128) unsigned char smem[];
     // layout: [NSTAGES stages][x: K halfs][full barriers][empty barriers][reduction scratch]
     unsigned char* stages = smem;
@@ -328,7 +348,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
     const __half* xh = reinterpret_cast<const __half*>(xs);
     for (int tile = 0; tile < n_tiles && ok; tile++) {
         const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
-        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};   // acc1: second m16 tile (CW = 16 only)
         for (int chunk = 0; chunk < nk; chunk++, it++) {
             const int s = it % NSTAGES, use = it / NSTAGES;
             ok = mbar_wait(full0 + 8 * s, use & 1);
@@ -340,14 +360,17 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
             for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
                 const int step = warp * STEPS_PER_WARP + kk;
                 if (step < steps) {
-                    uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+                    uint32_t a0, a1, a2, a3;
                     ldmatrix_x4(sbase + step * 32, a0, a1, a2, a3);
-                    ldmatrix_x4(sbase + 16 * ROW_STRIDE + step * 32, c0, c1, c2, c3);
                     const __half* xk = xh + chunk * KC + step * 16 + 2 * t;
                     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xk);
                     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xk + 8);
                     mma_16816(acc0, a0, a1, a2, a3, b0, b1);
-                    mma_16816(acc1, c0, c1, c2, c3, b0, b1);
+                    if (Cfg::M16 == 2) {
+                        uint32_t c0, c1, c2, c3;
+                        ldmatrix_x4(sbase + 16 * ROW_STRIDE + step * 32, c0, c1, c2, c3);
+                        mma_16816(acc1, c0, c1, c2, c3, b0, b1);
+                    }
                 }
             }
             __syncwarp();
@@ -359,14 +382,16 @@ __global__ void __launch_bounds__(RING_THREADS, 1) k_gemv_ring(RingArgs p) {
         if (t == 0) {
             part[warp * STAGE_ROWS + g] = acc0[0];
             part[warp * STAGE_ROWS + g + 8] = acc0[2];
-            part[warp * STAGE_ROWS + 16 + g] = acc1[0];
-            part[warp * STAGE_ROWS + 24 + g] = acc1[2];
+            if (Cfg::M16 == 2) {
+                part[warp * STAGE_ROWS + 16 + g] = acc1[0];
+                part[warp * STAGE_ROWS + 24 + g] = acc1[2];
+            }
         }
         consumer_bar_sync(CONSUMERS * 32);
         if (warp != 0) continue;
         float rowsum = 0.f;   // lane = row slot of the stage: slots 2u, 2u+1 are the two rows of unit u
 #pragma unroll
-        for (int w = 0; w < CONSUMERS; w++) rowsum += part[w * STAGE_ROWS + lane];
+        for (int w = 0; w < CONSUMERS; w++) rowsum += part[w * STAGE_ROWS + (lane & (STAGE_ROWS - 1))];
         const float other = __shfl_xor_sync(0xffffffffu, rowsum, 1);
         if ((lane & 1) || (lane >> 1) >= units_here) continue;
         const float sa = rowsum * rinv, sb = other * rinv;
@@ -496,13 +521,42 @@ int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, b
     return TL_OK;
 }
 
-template <int EPI, bool NORM>
-int launch_ring(const RingArgs& a, size_t smem, int grid, cudaStream_t st, bool pdl) {
+template <int EPI, bool NORM, int CW, int NST>
+int launch_ring_cfg(const RingArgs& a, cudaStream_t st, bool pdl) {
+    using Cfg = RingCfg<CW, NST>;
     static PerDeviceOnce once;
     if (once.needed()) {
-        TL_CUDA(cudaFuncSetAttribute(k_gemv_ring<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        TL_CUDA(cudaFuncSetAttribute(k_gemv_ring<EPI, NORM, CW, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     CW == 16 ? 227 * 1024 : 113 * 1024));
+        if (CW != 16)
+            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring<EPI, NORM, CW, NST>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         (int)cudaSharedmemCarveoutMaxShared));
     }
-    return launch_pdl(k_gemv_ring<EPI, NORM>, dim3(grid), dim3(RING_THREADS), smem, st, pdl, a);
+    // persistent CTAs; small problems get one CTA per stage-full of units
+    const int grid = std::max(1, std::min(sm_count() * Cfg::CTAS_PER_SM, (a.total_units + CW - 1) / CW));
+    return launch_pdl(k_gemv_ring<EPI, NORM, CW, NST>, dim3(grid), dim3(Cfg::THREADS), Cfg::smem_bytes(a.K), st, pdl, a);
+}
+
+// 0: one CTA per SM; 1: two half-size CTAs per SM. Measured on the 7B decode step: half-size CTAs
+// gain 1.5 % on one GPU (2.478 -> 2.440 ms per token) but lose 13 % under 2-GPU tensor parallelism
+// (every CTA sums all ranks' partial vectors in its prologue, and there are twice as many CTAs),
+// so launches that take part in an exchange keep the full shape. TL_RING=full|half overrides.
+int ring_shape_choice(const RingArgs& a, bool pushes) {
+    static const int forced = [] {
+        const char* e = getenv("TL_RING");
+        return !e ? -1 : (!strcmp(e, "half") ? 1 : (!strcmp(e, "full") ? 0 : -1));
+    }();
+    if (forced >= 0) return forced;
+    return (a.has_xin || pushes) ? 0 : 1;
+}
+
+template <int EPI, bool NORM>
+int launch_ring(const RingArgs& a, cudaStream_t st, bool pdl) {
+    if (ring_shape_choice(a, EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16 || EPI == EPI_STORE_F32) == 1) {
+        if (RingCfg<8, 3>::smem_bytes(a.K) <= 113 * 1024) return launch_ring_cfg<EPI, NORM, 8, 3>(a, st, pdl);
+        if (RingCfg<8, 2>::smem_bytes(a.K) <= 113 * 1024) return launch_ring_cfg<EPI, NORM, 8, 2>(a, st, pdl);
+    }
+    return launch_ring_cfg<EPI, NORM, 16, 3>(a, st, pdl);
 }
 
 }  // namespace
@@ -534,11 +588,6 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
 #undef TL_GEMV_CASE
     TL_LAUNCH_CHECK();
     return TL_OK;
-}
-
-int fused_gemv_grid(int total_rows) {
-    const int units = total_rows / 2;
-    return std::max(1, std::min(sm_count(), (units + CONSUMERS - 1) / CONSUMERS));
 }
 
 int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
@@ -575,12 +624,8 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
         if (q.epilogue == EPI_RESIDUAL) TL_REQUIRE(q.n_mats == 1 && q.residual, "residual epilogue: one matrix and a residual");
         a.total_units = q.n_mats * q.N_each / 2;
     }
-    // one persistent CTA per SM; small problems get one CTA per stage-full of units
-    const int grid = std::max(1, std::min(sm_count(), (a.total_units + CONSUMERS - 1) / CONSUMERS));
-    const size_t smem = (size_t)NSTAGES * STAGE_BYTES + (((size_t)q.K * 2 + 127) & ~(size_t)127) +
-                        2 * NSTAGES * sizeof(uint64_t) + CONSUMERS * sizeof(float) + 2 * CONSUMERS * STAGE_ROWS * sizeof(float) + 64;
     const bool norm = q.norm_w != nullptr;
-#define TL_FUSED(E) (norm ? launch_ring<E, true>(a, smem, grid, st, q.pdl) : launch_ring<E, false>(a, smem, grid, st, q.pdl))
+#define TL_FUSED(E) (norm ? launch_ring<E, true>(a, st, q.pdl) : launch_ring<E, false>(a, st, q.pdl))
     switch (q.epilogue) {
         case EPI_STORE: return TL_FUSED(EPI_STORE);
         case EPI_STORE_F32: return TL_FUSED(EPI_STORE_F32);

@@ -103,8 +103,6 @@ struct FusedGemv {
     const PeerExchange* xout;   // EPI_PUSH_F32 / EPI_PUSH_F16: where the results go on every rank
 };
 int launch_fused_gemv(const FusedGemv& p, cudaStream_t st);
-// number of CTAs launch_fused_gemv uses for `total_rows` weight rows (units of two rows)
-int fused_gemv_grid(int total_rows);
 
 // ---- attn.cu: attention, fast numerics -----------------------------------------------------------
 struct DecodeAttn {
