@@ -177,6 +177,8 @@ __global__ void k_rmsnorm_fast(__half* out, const __half* in, const __half* w, f
 // 16-byte aligned rows): the multi-token (prefill) form, bound by HBM at 4 bytes per element.
 __global__ void __launch_bounds__(128) k_rmsnorm_fast_vec(__half* out, const __half* in, const __half* w, float eps, int hidden) {
     __shared__ float red[4];
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t t = blockIdx.x;
     const uint4* x4 = reinterpret_cast<const uint4*>(in + t * hidden);
     const uint4* w4 = reinterpret_cast<const uint4*>(w);
@@ -515,9 +517,7 @@ int launch_rmsnorm_fast(__half* out, const __half* in, const __half* w, float ep
     const bool vec = hidden % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in) |
                                           reinterpret_cast<uintptr_t>(w)) & 15) == 0;
     if (vec && tokens >= 16) {
-        k_rmsnorm_fast_vec<<<(unsigned)tokens, 128, 0, st>>>(out, in, w, eps, hidden);
-        TL_LAUNCH_CHECK();
-        return TL_OK;
+        return launch_pdl(k_rmsnorm_fast_vec, dim3((unsigned)tokens), dim3(128), 0, st, true, out, in, w, eps, hidden);
     }
     k_rmsnorm_fast<<<(unsigned)ceil_div(tokens, 8), 256, 0, st>>>(out, in, w, eps, hidden, tokens);
     TL_LAUNCH_CHECK();

@@ -95,6 +95,10 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done (barriers, TMEM): let the next kernel of the stream start its own set-up, then wait
+    // for the previous one before any operand is read or any result written
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ---------------------------------------------------------
@@ -307,9 +311,7 @@ int launch_flash_prefill(const __half* q, const __half* k, const __half* v, __ha
     TL_PROPAGATE(make_tensor_map_f16(&mv, v, S, HD, ldv, HD, heads, BKV));
     FlashArgs a{out, ldo, T, S, pos0, heads, 1.4426950408889634f / sqrtf((float)head_dim), device_status_word()};
     dim3 grid((unsigned)heads, (unsigned)((T + BQ - 1) / BQ));
-    k_flash_prefill<<<grid, FA_THREADS, FA_SMEM, st>>>(mq, mk, mv, a);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return launch_pdl(k_flash_prefill, grid, dim3(FA_THREADS), FA_SMEM, st, true, mq, mk, mv, a);
 }
 
 }  // namespace tlb

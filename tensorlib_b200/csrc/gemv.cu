@@ -160,6 +160,7 @@ struct RingArgs {
     const int* pos_ptr; long long kv_pitch;
     const __half* silu_tab;
     int* status;                  // device status word: set on a timed-out wait
+    int wait_weights;             // the weight stream also waits for the previous kernel (generic entry point)
     int has_xin;                  // the activation vector is residual + sum of pushed partials
     PeerExchange xin, xout;
 };
@@ -232,7 +233,9 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
     pdl_launch_dependents();
 
     if (warp == CONSUMERS) {
-        // ---------------- producer: weights only, independent of the previous kernel ----------
+        // ---------------- producer: weights only; in the model they never depend on the previous
+        // kernel, a caller of the plain matmul entry point may have just written them ------------
+        if (p.wait_weights) pdl_wait();
         const uint64_t pol = policy_evict_first();
         const __half* row_ptr = nullptr;
         int cur_tile = -1, rows_in_tile = 0;
@@ -505,22 +508,6 @@ __global__ void __launch_bounds__(THREADS) k_gemv(const __half* __restrict__ x, 
     }
 }
 
-template <typename Kern, typename... Args>
-int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    TL_CUDA(cudaLaunchKernelEx(&cfg, kern, args...));
-    return TL_OK;
-}
-
 template <int EPI, bool NORM, int CW, int NST>
 int launch_ring_cfg(const RingArgs& a, cudaStream_t st, bool pdl) {
     using Cfg = RingCfg<CW, NST>;
@@ -571,7 +558,8 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
     TL_REQUIRE(gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0, "gemv: unsupported shape or alignment");
     if (M == 1 && ldw == K && N % 2 == 0 && K % 16 == 0 && K <= 12288) {  // the decode kernel, plain store epilogue
         FusedGemv f{};
-        f.x = x; f.W[0] = W; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = y; f.pdl = false;
+        f.x = x; f.W[0] = W; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = y;
+        f.pdl = true; f.weights_may_change = true;
         return launch_fused_gemv(f, st);
     }
     int KT = 16384 / M;                 // halfs per tile so that M*KT*2 <= 32 KB
@@ -605,6 +593,7 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     a.pos_ptr = q.pos_ptr; a.kv_pitch = q.kv_pitch;
     a.silu_tab = tables().silu_float_tab;
     a.status = device_status_word();
+    a.wait_weights = q.weights_may_change ? 1 : 0;
     a.has_xin = q.xin != nullptr;
     if (q.xin) {
         TL_REQUIRE(q.xin->world >= 1 && q.xin->world <= TL_MAX_TP && q.xin->n == q.K && q.xin->residual,

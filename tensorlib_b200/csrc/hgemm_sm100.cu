@@ -154,6 +154,10 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done (barriers, TMEM): let the next kernel of the stream start its own set-up, then wait
+    // for the previous one before any operand is read or any result written
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ---------------------------------------------------------
@@ -332,6 +336,10 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     cluster_sync_all();          // both CTAs' barriers exist before anything is signalled across the pair
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done (barriers, TMEM): let the next kernel of the stream start its own set-up, then wait
+    // for the previous one before any operand is read or any result written
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer (both CTAs) ----------------------------------------------
@@ -507,9 +515,7 @@ int launch_k(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb
         TL_CUDA(cudaFuncSetAttribute(k_hgemm<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
     const int grid = std::max(1, std::min(tiles, sm_count()));
-    k_hgemm<BN, EPI><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mb2, mb3, a);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return launch_pdl(k_hgemm<BN, EPI>, dim3(grid), dim3(GEMM_THREADS), smem, st, true, ma, mb, mb2, mb3, a);
 }
 template <int EPI>
 int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
@@ -527,9 +533,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
         TL_CUDA(cudaFuncSetAttribute(k_hgemm_pair<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
     }
     const int grid = 2 * std::max(1, std::min(pair_tiles, sm_count() / 2));
-    k_hgemm_pair<EPI><<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(ma, mb, mb2, mb3, a);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return launch_pdl(k_hgemm_pair<EPI>, dim3(grid), dim3(GEMM_THREADS), PAIR_SMEM, st, true, ma, mb, mb2, mb3, a);
 }
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }

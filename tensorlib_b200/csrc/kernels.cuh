@@ -99,6 +99,7 @@ struct FusedGemv {
     // kernel adds (*pos_ptr) * kv_pitch to k_out / v_out and (*pos_ptr) * head_dim/2 to cos/sin
     const int* pos_ptr; long long kv_pitch;
     bool pdl;                   // launch with programmatic stream serialization
+    bool weights_may_change;    // the previous kernel of the stream may have written W: stream it after the wait
     const PeerExchange* xin;    // prologue: x = residual + sum over ranks of a pushed partial vector
     const PeerExchange* xout;   // EPI_PUSH_F32 / EPI_PUSH_F16: where the results go on every rank
 };

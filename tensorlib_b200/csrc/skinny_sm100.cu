@@ -82,6 +82,10 @@ k_skinny(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done (barriers, TMEM): let the next kernel of the stream start its own set-up, then wait
+    // for the previous one before any operand is read or any result written
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ---------------------------------------------------------
@@ -267,9 +271,7 @@ int launch_nb(const CUtensorMap& mw, const CUtensorMap& mx, const SkinnyArgs& a,
     if (once.needed()) {
         TL_CUDA(cudaFuncSetAttribute(k_skinny<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SkinnyCfg<NB>::SMEM));
     }
-    k_skinny<NB><<<grid, SK_THREADS, SkinnyCfg<NB>::SMEM, st>>>(mw, mx, a);
-    TL_LAUNCH_CHECK();
-    return TL_OK;
+    return launch_pdl(k_skinny<NB>, dim3(grid), dim3(SK_THREADS), SkinnyCfg<NB>::SMEM, st, true, mw, mx, a);
 }
 
 }  // namespace
