@@ -40,6 +40,7 @@ struct SkinnyArgs {
     long long ldc;
     int M, N, K;
     int tiles, nkb, per;        // W-row tiles, k-blocks per tile, k-blocks per CTA
+    int per_cluster;            // cluster variant: CTAs (k-splits) per tile
     float* ws;                  // [2 * grid][NB][TW] fp32 partial tiles
     unsigned int* counters;     // [tiles], zero between launches
     int* status;
@@ -240,6 +241,146 @@ k_skinny(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
 
+// ---- cluster variant: the sharers of a W tile are one thread-block cluster -------------------------
+// When a whole number of CTAs per tile fills the GPU (few W tiles, e.g. N = 4096), the k-range of a
+// tile is split evenly over the `splits` CTAs of a cluster. Each leaves its fp32 partial tile in
+// its own shared memory (the drained operand ring); after one cluster barrier every CTA adds up
+// its share of the token columns from all sharers over distributed shared memory, in rank order,
+// and writes fp16. No workspace, no atomics, no global-memory round trip, and the reduction is
+// spread over all sharers instead of falling on the last one to arrive.
+template <int NB>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+k_skinny_cluster(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, SkinnyArgs p) {
+    using Cfg = SkinnyCfg<NB>;
+    constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = NB < 32 ? 32 : NB;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t tfull = smem_u32(bars + 2 * STAGES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* part = reinterpret_cast<float*>(smem);       // [NB][TW] once the ring has drained
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int splits = p.per_cluster;                    // cluster size = sharers per tile
+    const int rank = (int)cluster_ctarank();
+    const int t = (int)blockIdx.x / splits;
+    const int kb0 = min(p.nkb, rank * p.per), kb1 = min(p.nkb, kb0 + p.per), len = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tfull, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) tmem_alloc<TMEM_COLS>(tmem_slot);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
+        bool ok = true;
+        int it = 0;
+        for (int kb = kb0; kb < kb1 && ok; kb++, it++) {
+            const int s = it % STAGES, use = it / STAGES;
+            if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
+            const uint32_t sw = smem_u32(smem + s * STAGE_BYTES), sx = sw + W_BYTES;
+            mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_3d(sw, &tmW, kb * BK, t * TW, 0, full0 + 8 * s);
+            tma_load_3d(sx, &tmX, kb * BK, 0, 0, full0 + 8 * s);
+        }
+        if (!ok) {
+            for (int j = max(0, it - STAGES); j < it; j++)
+                for (uint32_t i = 0; i < (1u << 16); i++)
+                    if (mbar_try_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1)) break;
+        }
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = make_idesc(NB);
+        bool ok = true;
+        for (int i = 0; i < len && ok; i++) {
+            const int s = i % STAGES, use_s = i / STAGES;
+            if (!(ok = mbar_wait(full0 + 8 * s, use_s & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t sw = smem_u32(smem + s * STAGE_BYTES), sx = sw + W_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / 16; k++)
+                umma(tmem_base, make_desc(sw + k * 32), make_desc(sx + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(empty0 + 8 * s);
+        }
+        if (ok && len > 0) umma_commit(tfull);
+    } else if (warp >= 4) {
+        // this CTA's partial tile: TMEM -> registers -> own shared memory, [token][W row]
+        const int q = warp & 3, r = q * 32 + lane;
+        bool ok = true;
+        if (len > 0) {
+            ok = mbar_wait(tfull, 0, abort_flag);       // all MMAs done: the ring is drained too
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && len > 0) {
+            tc_fence_after();
+            const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < NB; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tbase + (uint32_t)c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j++) part[(c + j) * TW + r] = __uint_as_float(v[j]);
+            }
+        } else {
+            for (int m = 0; m < NB; m++) part[m * TW + r] = 0.f;   // empty k-range (or gave up): contributes nothing
+        }
+    }
+    // every thread of every sharer: partials are complete and visible cluster-wide
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 4) {
+        const int r = (warp & 3) * 32 + lane, n = t * TW + r;
+        const int mper = (p.M + splits - 1) / splits;
+        const int m0 = rank * mper, m1 = min(p.M, m0 + mper);
+        if (n < p.N) {
+            const uint32_t my_part = smem_u32(part);
+            for (int mb = m0; mb < m1; mb += 16) {
+                float acc[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) acc[i] = 0.f;
+                for (int c = 0; c < splits; c++) {           // rank order: a fixed summation order
+                    const uint32_t remote = map_to_cta(my_part, (uint32_t)c);
+                    float v[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        v[i] = 0.f;
+                        if (mb + i < m1)
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[i]) : "r"(remote + (uint32_t)(((mb + i) * TW + r) * 4)) : "memory");
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) acc[i] += v[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if (mb + i < m1) p.C[(long long)(mb + i) * p.ldc + n] = __float2half_rn(acc[i]);
+            }
+        }
+    }
+    // nobody leaves (and frees its shared memory) while a sharer may still read it
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 // One workspace per (device, stream): calls on different streams may overlap on the GPU.
 struct Workspace { float* ws = nullptr; unsigned int* counters = nullptr; };
@@ -274,6 +415,28 @@ int launch_nb(const CUtensorMap& mw, const CUtensorMap& mx, const SkinnyArgs& a,
     return launch_pdl(k_skinny<NB>, dim3(grid), dim3(SK_THREADS), SkinnyCfg<NB>::SMEM, st, true, mw, mx, a);
 }
 
+template <int NB>
+int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const SkinnyArgs& a, int grid, int cluster, cudaStream_t st) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
+        TL_CUDA(cudaFuncSetAttribute(k_skinny_cluster<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SkinnyCfg<NB>::SMEM));
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(SK_THREADS);
+    cfg.dynamicSmemBytes = SkinnyCfg<NB>::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    TL_CUDA(cudaLaunchKernelEx(&cfg, k_skinny_cluster<NB>, mw, mx, a));
+    return TL_OK;
+}
+
 }  // namespace
 
 bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K, size_t lda, size_t ldw) {
@@ -294,10 +457,14 @@ int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int
     int per = (int)((total + max_grid - 1) / max_grid);
     if (per < 4) per = (int)std::min<long long>(4, total);
     // few W tiles: give every tile the same whole number of sharers when that still fills >= 85 %
-    // of the SMs (one segment per CTA, fewer partials than ranges that straddle tile boundaries)
+    // of the SMs; the sharers then form a cluster and reduce over distributed shared memory
+    int cluster_splits = 0;
     if (tiles <= max_grid) {
-        const int sp = std::max(1, std::min(max_grid / tiles, std::max(1, nkb / 4)));
-        if ((long long)tiles * sp * 100 >= (long long)max_grid * 85) per = (nkb + sp - 1) / sp;
+        const int sp = std::max(1, std::min(std::min(max_grid / tiles, 8), std::max(1, nkb / 4)));
+        if ((long long)tiles * sp * 100 >= (long long)max_grid * 85) {
+            per = (nkb + sp - 1) / sp;
+            if (sp >= 2) cluster_splits = sp;
+        }
     }
     const int grid = (int)((total + per - 1) / per);
     Workspace w;
@@ -305,7 +472,12 @@ int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int
     CUtensorMap mw, mx;
     TL_PROPAGATE(make_tensor_map_f16(&mw, W, N, K, ldw, 0, 1, TW));
     TL_PROPAGATE(make_tensor_map_f16(&mx, A, M, K, lda, 0, 1, nb));
-    SkinnyArgs a{C, ldc, M, N, K, tiles, nkb, per, w.ws, w.counters, device_status_word()};
+    SkinnyArgs a{C, ldc, M, N, K, tiles, nkb, per, cluster_splits, w.ws, w.counters, device_status_word()};
+    if (cluster_splits >= 2) {
+        if (nb == 32) return launch_cluster<32>(mw, mx, a, tiles * cluster_splits, cluster_splits, st);
+        if (nb == 64) return launch_cluster<64>(mw, mx, a, tiles * cluster_splits, cluster_splits, st);
+        return launch_cluster<128>(mw, mx, a, tiles * cluster_splits, cluster_splits, st);
+    }
     if (nb == 32) return launch_nb<32>(mw, mx, a, grid, st);
     if (nb == 64) return launch_nb<64>(mw, mx, a, grid, st);
     return launch_nb<128>(mw, mx, a, grid, st);

@@ -267,3 +267,14 @@ def test_hgemm_pair_and_single_kernels_agree_with_float64(tl, mode, tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     worst = float(r.stdout.strip().split("WORST")[-1])
     assert worst <= 2e-3, worst      # fp16 rounding of the result only: both kernels accumulate in fp32
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 4096, 1024), (32, 4224, 1032), (100, 4096, 2048), (128, 8192, 512), (2, 5000, 4096)])
+def test_skinny_matmul_cluster_reduction_shapes(tl, oracle, M, N, K):
+    """Shapes whose weight tiles split evenly over the SMs: the sharers of a tile reduce through
+    distributed shared memory (ragged K, a last tile beyond N, M not a multiple of the split)."""
+    A = synth.normal_f16(81, 1, M * K, 1.0).reshape(M, K)
+    W = synth.normal_f16(81, 2, N * K, 0.02).reshape(N, K)
+    got, want = tl.matmul2d(A, W, numerics=tl.FAST), oracle.matmul2d(A, W)
+    assert tl.device_status() == 0
+    assert max_rel_err(got, want) <= MATMUL_RTOL, (M, N, K)
