@@ -97,6 +97,14 @@ TL_API int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_
 TL_API int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t batch, size_t M,
                           size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, size_t strideA,
                           size_t strideB, size_t strideC, int numerics, tl_stream stream);
+/* Host-only introspection (no device needed): the kernel tl_matmul2d_f16 selects in fast numerics for
+ * 16-byte aligned operands on a device with sm_count SMs, and how the work is cut: CTAs launched,
+ * tile width along N (the padded batch for the skinny kernels), k-blocks of 64 per CTA (skinny
+ * kernels), CTAs per cluster (0 = no clusters). */
+enum { TL_PLAN_REFERENCE_ORDER = 0, TL_PLAN_GEMV_RING = 1, TL_PLAN_GEMV_SMALL = 2, TL_PLAN_SKINNY_STREAMK = 3,
+       TL_PLAN_SKINNY_CLUSTER = 4, TL_PLAN_HGEMM = 5, TL_PLAN_HGEMM_PAIR = 6 };
+TL_API int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int* grid, int* tile_n,
+                   int* k_blocks_per_cta, int* cluster);
 /* Same contract as tl_matmul2d_f16 with HOST buffers: copies A and B in, C out, synchronises. */
 TL_API int tl_matmul2d_f16_host(const tl_half* A_host, const tl_half* B_host, tl_half* C_host, size_t M,
                          size_t N, size_t K, int numerics);

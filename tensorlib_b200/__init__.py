@@ -67,6 +67,7 @@ _SIGS = {
     "tl_llama2_load_payload_host": [_vp, _vp, _int],
     "tl_llama2_load_file": [_vp, C.c_char_p],
     "tl_llama2_init_random": [_vp, C.c_uint64, C.c_float],
+    "tl_matmul_plan": [C.c_size_t, C.c_size_t, C.c_size_t, _int] + [C.POINTER(_int)] * 5,
     "tl_llama2_forward": [_vp, _vp, _int, _int, _vp, _vp],
     "tl_llama2_generate": [_vp, _vp, _int, _int, _int, _vp, C.POINTER(_int), C.POINTER(C.c_double),
                            C.POINTER(C.c_double)],
@@ -311,6 +312,18 @@ def attn_prefill(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, start_
           "tl_attn_prefill_f16")
     synchronize()
     return out.to_numpy(np.float16, (T, width))
+
+
+PLAN_NAMES = {0: "reference_order", 1: "gemv_ring", 2: "gemv_small", 3: "skinny_streamk", 4: "skinny_cluster",
+              5: "hgemm", 6: "hgemm_pair"}
+
+
+def matmul_plan(M: int, N: int, K: int, sm_count: int = 148) -> dict:
+    """Host-only: the kernel and work split tl_matmul2d_f16 would use (tl_matmul_plan)."""
+    out = [_int(0) for _ in range(5)]
+    check(load().tl_matmul_plan(M, N, K, sm_count, *[C.byref(o) for o in out]), "tl_matmul_plan")
+    k, grid, tile_n, per, cluster = (o.value for o in out)
+    return {"kernel": PLAN_NAMES[k], "grid": grid, "tile_n": tile_n, "k_blocks_per_cta": per, "cluster": cluster}
 
 
 def host_lookup_tables():

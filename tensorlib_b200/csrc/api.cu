@@ -7,6 +7,8 @@
 #include <new>
 #include <vector>
 
+#include <algorithm>
+
 #include "engine.cuh"
 
 using namespace tlb;
@@ -55,6 +57,33 @@ int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t
         q.M = (int)(M - m0 < 65535 ? M - m0 : 65535);
         TL_PROPAGATE(launch_matmul_seq(q, st));
     }
+    return TL_OK;
+}
+
+// Host-only: which kernel tl_matmul2d_f16 picks in fast numerics for aligned operands on a device
+// with `sm_count` SMs, and how it cuts the work. No device is touched.
+int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int* grid, int* tile_n, int* k_blocks_per_cta,
+                   int* cluster) {
+    TL_REQUIRE(kernel && grid && tile_n && k_blocks_per_cta && cluster, "null output");
+    TL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && sm_count >= 1 && M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "bad shape");
+    *grid = *tile_n = *k_blocks_per_cta = *cluster = 0;
+    if (M == 1 && N % 2 == 0 && K % 16 == 0 && K <= 12288) { *kernel = TL_PLAN_GEMV_RING; return TL_OK; }
+    if (M >= 2 && M <= 128 && K % 8 == 0) {
+        const SkinnyPlan pl = skinny_plan((int)M, (int)N, (int)K, sm_count);
+        *kernel = pl.cluster_splits >= 2 ? TL_PLAN_SKINNY_CLUSTER : TL_PLAN_SKINNY_STREAMK;
+        *grid = pl.grid; *tile_n = pl.nb; *k_blocks_per_cta = pl.per; *cluster = pl.cluster_splits;
+        return TL_OK;
+    }
+    if (M > 8 && K % 8 == 0) {
+        int kind = 0, bn = 0;
+        hgemm_plan((int)M, (int)N, 1, sm_count, &kind, &bn);
+        *kernel = kind == 1 ? TL_PLAN_HGEMM_PAIR : TL_PLAN_HGEMM;
+        *tile_n = bn; *cluster = kind == 1 ? 2 : 0;
+        const long long tiles = kind == 1 ? (long long)((M + 255) / 256) * ((N + 255) / 256) : (long long)((M + 127) / 128) * ((N + bn - 1) / bn);
+        *grid = (int)std::min<long long>(tiles * (kind == 1 ? 2 : 1), kind == 1 ? (sm_count / 2) * 2 : sm_count);
+        return TL_OK;
+    }
+    *kernel = M <= 8 && K % 8 == 0 ? TL_PLAN_GEMV_SMALL : TL_PLAN_REFERENCE_ORDER;
     return TL_OK;
 }
 

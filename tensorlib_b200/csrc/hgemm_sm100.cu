@@ -538,6 +538,9 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
+int g_plan_sms = 0;   // when non-zero, the planning functions use it instead of the device's SM count
+int plan_sms() { return g_plan_sms > 0 ? g_plan_sms : sm_count(); }
+
 // estimated cost (cycles per k-block x waves) of the CTA-pair kernel: 256 x 256 tiles over sm/2 pairs,
 // 512 MMA cycles per k-block, operands arrive at 32 KB per CTA per k-block (not the limit)
 long long pair_cost(int M, int n_tiles_256, int batch) {
@@ -549,12 +552,12 @@ long long pair_cost(int M, int n_tiles_256, int batch) {
     if (forced == 1) return -1;
     if (forced == 2) return (1ll << 60);
     const long long tiles = (long long)((M + 255) / 256) * n_tiles_256 * batch;
-    const long long pairs = std::max(1, sm_count() / 2);
+    const long long pairs = std::max(1, plan_sms() / 2);
     return ((tiles + pairs - 1) / pairs) * 512;
 }
 long long single_cost(int mt, int N, int batch, int bn) {
     const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
-    const long long waves = (tiles + sm_count() - 1) / sm_count();
+    const long long waves = (tiles + plan_sms() - 1) / plan_sms();
     return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
 }
 
@@ -568,7 +571,7 @@ int pick_bn(int mt, int N, int batch) {
     long long best_cost = -1;
     for (int bn = 256; bn >= 64; bn >>= 1) {
         const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
-        const long long waves = (tiles + sm_count() - 1) / sm_count();
+        const long long waves = (tiles + plan_sms() - 1) / plan_sms();
         const long long per_kb = std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
         const long long cost = waves * per_kb;
         if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
@@ -577,6 +580,17 @@ int pick_bn(int mt, int N, int batch) {
 }
 
 }  // namespace
+
+void hgemm_plan(int M, int N, int batch, int sms, int* kind, int* bn) {
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    g_plan_sms = sms;
+    const int mt = (M + BM - 1) / BM;
+    *bn = pick_bn(mt, N, batch);
+    *kind = (M > BM && N % 32 == 0 && pair_cost(M, (N + 255) / 256, batch) < single_cost(mt, N, batch, *bn)) ? 1 : 0;
+    if (*kind == 1) *bn = 256;
+    g_plan_sms = 0;
+}
 
 bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
                      size_t ldb, size_t ldc) {

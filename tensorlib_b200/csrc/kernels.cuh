@@ -151,8 +151,13 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
 
 // ---- skinny_sm100.cu: 2 <= M <= 128, weights streamed once (swap-AB tcgen05, stream-K split) --------
 bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K, size_t lda, size_t ldw);
+struct SkinnyPlan { int nb, tiles, nkb, per, grid, cluster_splits; };
+SkinnyPlan skinny_plan(int M, int N, int K, int sms);
 int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int K, long long lda, long long ldw,
                   long long ldc, cudaStream_t st);
+
+// which tile the plain HGEMM would use on `sms` SMs: kind 0 = single-CTA tile of width *bn, 1 = CTA-pair 256x256
+void hgemm_plan(int M, int N, int batch, int sms, int* kind, int* bn);
 
 // fused epilogues of the prefill HGEMM (N % 32 == 0, 16-byte aligned rows)
 bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,

@@ -445,28 +445,39 @@ bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K
            (N + TW - 1) / TW <= (size_t)MAX_TILES && tensor_map_encode_available();
 }
 
-int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int K, long long lda, long long ldw,
-                  long long ldc, cudaStream_t st) {
-    TL_REQUIRE(skinny_supported(A, W, M, N, K, lda, ldw), "skinny matmul: unsupported shape or alignment");
-    const int nb = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
-    const int tiles = (N + TW - 1) / TW, nkb = (K + BK - 1) / BK;
-    const long long total = (long long)tiles * nkb;
+// Host-side planning (no device needed): how the (W tile, k-block) space of an M x N x K problem is
+// cut for `sms` SMs.
+SkinnyPlan skinny_plan(int M, int N, int K, int sms) {
+    SkinnyPlan pl{};
+    pl.nb = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    pl.tiles = (N + TW - 1) / TW;
+    pl.nkb = (K + BK - 1) / BK;
+    const long long total = (long long)pl.tiles * pl.nkb;
     // equal contiguous k-block ranges, one per SM; at least 4 k-blocks each so that tiny problems
     // do not pay a partial-tile exchange per k-block
-    const int max_grid = std::min(sm_count(), MAX_GRID);
+    const int max_grid = std::max(1, std::min(sms, MAX_GRID));
     int per = (int)((total + max_grid - 1) / max_grid);
     if (per < 4) per = (int)std::min<long long>(4, total);
     // few W tiles: give every tile the same whole number of sharers when that still fills >= 85 %
     // of the SMs; the sharers then form a cluster and reduce over distributed shared memory
-    int cluster_splits = 0;
-    if (tiles <= max_grid) {
-        const int sp = std::max(1, std::min(std::min(max_grid / tiles, 8), std::max(1, nkb / 4)));
-        if ((long long)tiles * sp * 100 >= (long long)max_grid * 85) {
-            per = (nkb + sp - 1) / sp;
-            if (sp >= 2) cluster_splits = sp;
+    pl.cluster_splits = 0;
+    if (pl.tiles <= max_grid) {
+        const int sp = std::max(1, std::min(std::min(max_grid / pl.tiles, 8), std::max(1, pl.nkb / 4)));
+        if ((long long)pl.tiles * sp * 100 >= (long long)max_grid * 85) {
+            per = (pl.nkb + sp - 1) / sp;
+            if (sp >= 2) pl.cluster_splits = sp;
         }
     }
-    const int grid = (int)((total + per - 1) / per);
+    pl.per = per;
+    pl.grid = pl.cluster_splits >= 2 ? pl.tiles * pl.cluster_splits : (int)((total + per - 1) / per);
+    return pl;
+}
+
+int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int K, long long lda, long long ldw,
+                  long long ldc, cudaStream_t st) {
+    TL_REQUIRE(skinny_supported(A, W, M, N, K, lda, ldw), "skinny matmul: unsupported shape or alignment");
+    const SkinnyPlan pl = skinny_plan(M, N, K, sm_count());
+    const int nb = pl.nb, tiles = pl.tiles, nkb = pl.nkb, per = pl.per, cluster_splits = pl.cluster_splits, grid = pl.grid;
     Workspace w;
     TL_PROPAGATE(workspace_for(st, &w));
     CUtensorMap mw, mx;

@@ -112,3 +112,54 @@ def test_checkpoint_layout(tmp_path):
     assert np.all(body[V * d: V * d + L * d] == 1.0)  # attention_norm weights follow the embedding
     assert_bit_equal(body[:V * d], synth.normal_f16(1, synth.TID_EMB, V * d, 0.02), "embedding first")
     assert_bit_equal(body[-V * d:], synth.normal_f16(1, synth.TID_WCLS, V * d, 0.02), "classifier last")
+
+
+# ---- matmul dispatch and work split (host logic, no device) ------------------------------------------
+def test_matmul_plan_picks_the_kernel_each_regime_is_built_for():
+    import tensorlib_b200 as tl
+    assert tl.matmul_plan(1, 4096, 4096)["kernel"] == "gemv_ring"                # decode GEMV
+    assert tl.matmul_plan(1, 32000, 4096)["kernel"] == "gemv_ring"
+    for M in (2, 8, 32, 128):                                                   # weights streamed once
+        assert tl.matmul_plan(M, 11008, 4096)["kernel"].startswith("skinny"), M
+    assert tl.matmul_plan(32, 4096, 4096) == {"kernel": "skinny_cluster", "grid": 128, "tile_n": 32,
+                                              "k_blocks_per_cta": 16, "cluster": 4}
+    assert tl.matmul_plan(512, 4096, 4096)["kernel"] == "hgemm"
+    for N, K in ((4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)):   # prefill shapes: CTA pairs
+        p = tl.matmul_plan(2048, N, K)
+        assert p["kernel"] == "hgemm_pair" and p["grid"] == 148 and p["cluster"] == 2, (N, K, p)
+    assert tl.matmul_plan(3, 1000, 300)["kernel"] == "reference_order"          # K % 8 != 0: any-shape kernel
+    with pytest.raises(tl.TLError):
+        tl.matmul_plan(0, 8, 8)
+
+
+@pytest.mark.parametrize("sms", [148, 132, 64, 7])
+def test_skinny_split_covers_every_k_block_exactly_once(sms):
+    """The stream-K ranges (CTA c owns k-blocks [c*per, (c+1)*per) of the flattened (tile, k-block)
+    space) and the cluster split (tile = cta // splits, k-range by rank) must tile the space without
+    gaps or overlaps for every shape, and stay inside the workspace the kernels were given."""
+    import tensorlib_b200 as tl
+    for M, N, K in ((2, 128, 64), (8, 4096, 4096), (32, 11008, 4096), (128, 4096, 11008), (100, 32000, 4096),
+                    (5, 513, 1032), (64, 127, 8), (17, 9472, 520), (128, 8192, 512)):
+        p = tl.matmul_plan(M, N, K, sms)
+        assert p["kernel"].startswith("skinny")
+        tiles, nkb, per = -(-N // 128), -(-K // 64), p["k_blocks_per_cta"]
+        assert p["tile_n"] in (32, 64, 128) and p["tile_n"] >= M and per >= 1
+        covered = np.zeros(tiles * nkb, np.int32)
+        if p["kernel"] == "skinny_cluster":
+            sp = p["cluster"]
+            assert 2 <= sp <= 8 and p["grid"] == tiles * sp and p["grid"] <= sms
+            for cta in range(p["grid"]):
+                t, r = divmod(cta, sp)
+                kb0, kb1 = min(nkb, r * per), min(nkb, r * per + per)
+                covered[t * nkb + kb0:t * nkb + kb1] += 1
+        else:
+            assert p["grid"] <= min(sms, 256) or per == 4      # one CTA per SM, except tiny-per problems
+            assert p["grid"] * per >= tiles * nkb > (p["grid"] - 1) * per
+            for cta in range(p["grid"]):
+                covered[cta * per:min(tiles * nkb, (cta + 1) * per)] += 1
+            # sharers of a tile: consecutive CTAs first..last; at most two partial segments per CTA
+            for t in range(tiles):
+                first, last = (t * nkb) // per, ((t + 1) * nkb - 1) // per
+                slots = {2 * c if c * per > t * nkb else 2 * c + 1 for c in range(first, last + 1)}
+                assert len(slots) == last - first + 1 and max(slots) < 2 * 256
+        assert (covered == 1).all(), (M, N, K, sms, p)
