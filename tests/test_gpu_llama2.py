@@ -233,3 +233,25 @@ def test_multi_turn_generation_continues_over_the_kv_cache(tl, golden_tiny, tiny
     with pytest.raises(tl.TLError):
         m.generate(prompt, 8, start_pos=synth.TINY.seq_len - 4)
     m.close(); m2.close()
+
+
+def test_long_context_decode_agrees_with_prefill_of_the_same_tokens(tl):
+    """Context of ~2000 positions at head_dim 128: the decode path (GEMV ring + split attention over
+    the in-place caches) must give the logits the fused prefill gives for the same token stream."""
+    cfg = synth.LlamaConfig(dim=512, hidden_dim=1408, n_layers=2, n_heads=4, vocab_size=1000, seq_len=2048)
+    payload = synth.llama2c_payload(cfg, 4242)
+    tokens = synth.token_ids(4242, 9, 2043, cfg.vocab_size)
+    a = tl.Llama2(cfg, numerics=tl.FAST)
+    a.load_payload(payload, shared_classifier=True)
+    a.forward(tokens[:2040], 0, all_logits=False)
+    dec = np.concatenate([a.forward(tokens[p:p + 1], p, all_logits=True) for p in range(2040, 2043)]).astype(np.float32)
+    ids = a.decode_device(2043, 3)            # graph path up to the last position of the context
+    b = tl.Llama2(cfg, numerics=tl.FAST)
+    b.load_payload(payload, shared_classifier=True)
+    ref = b.forward(tokens, 0, all_logits=True)[2040:2043].astype(np.float32)
+    assert tl.device_status() == 0
+    assert np.abs(dec - ref).max() <= 2e-2
+    assert ids.shape == (3,)
+    with pytest.raises(tl.TLError):
+        a.decode_device(2046, 3)              # would run past max_seq_len
+    a.close(); b.close()
