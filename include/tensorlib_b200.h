@@ -88,7 +88,13 @@ TL_API int tl_free_host(void* hptr);
 /* ---- matmul: the drop-in boundary --------------------------------------------------------- */
 /* Device<half>::matmul2d (tensorLib/include/device/Device.hpp:22; CUDA implementation
  * tensorLib/src/device/cuda/gemm.cu:153-172): C[M,N] = A[M,K] * B[N,K]^T, all row-major
- * contiguous. Dispatches on M: GEMV (M<=8), skinny, tcgen05 HGEMM. */
+ * contiguous. Dispatches on M in fast numerics: M = 1 the streaming GEMV, 2..128 the skinny
+ * tensor-core kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair
+ * tiles); operands that are not 16-byte aligned or K % 8 != 0 take the any-shape kernel.
+ * All kernels are launched with programmatic stream serialization and wait on the device for the
+ * previous kernel of `stream` before touching A, B or C, so back-to-back calls overlap their
+ * set-up, never their data. The first skinny call on a given stream allocates a 34 MB workspace
+ * for that stream (kept until exit): make it before starting a stream capture. */
 TL_API int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t M, size_t N, size_t K,
                     int numerics, tl_stream stream);
 /* The per-batch loop of ops::matmul::call2 (tensorLib/src/ops/matmul.cpp:297-321) as one call:
