@@ -343,6 +343,40 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
     // 16 per-warp partial sums of each row meet in shared memory and warp 0 finishes the rows.
     // This keeps the consumers' instruction count ~8x below a SIMT FMA loop, so they outrun HBM and
     // the ring can absorb prologue and barrier time.
+    // QKV epilogue: the rotary factors of this lane's rows depend only on the position and the row,
+    // so warp 0 fetches them now (up to ROPE_PRE tiles) instead of on the critical path of each tile
+    constexpr int ROPE_PRE = 4;
+    __half2 rope_cs[ROPE_PRE];
+    int rope_pos = 0;
+    if (EPI == EPI_QKV_ROPE && warp == 0) {
+        rope_pos = p.pos_ptr ? *p.pos_ptr : 0;
+        const int half_dim = p.head_dim >> 1;
+#pragma unroll
+        for (int tt = 0; tt < ROPE_PRE; tt++) {
+            rope_cs[tt] = __half2half2(__float2half(0.f));
+            const int unit = u_begin + tt * CONSUMERS + (lane >> 1);
+            if (tt < n_tiles && !(lane & 1) && unit < u_end) {
+                const __half *ra, *rb; int mat, r;
+                unit_rows<EPI>(p, unit, ra, rb, mat, r);
+                if (mat < 2) {
+                    const int d2 = (r % p.head_dim) >> 1;
+                    rope_cs[tt] = __halves2half2(p.cos_t[(long long)rope_pos * half_dim + d2],
+                                                 p.sin_t[(long long)rope_pos * half_dim + d2]);
+                }
+            }
+        }
+    }
+    // residual epilogue: the two residual values of this lane's rows, fetched ahead the same way
+    __half2 res_pre[ROPE_PRE];
+    if (EPI == EPI_RESIDUAL && warp == 0) {
+#pragma unroll
+        for (int tt = 0; tt < ROPE_PRE; tt++) {
+            res_pre[tt] = __half2half2(__float2half(0.f));
+            const int unit = u_begin + tt * CONSUMERS + (lane >> 1);
+            if (tt < n_tiles && !(lane & 1) && unit < u_end)
+                res_pre[tt] = *reinterpret_cast<const __half2*>(p.residual + 2 * unit);   // rows 2u, 2u+1 of the single matrix
+        }
+    }
     bool ok = true;
     int it = 0;
     const int g = lane >> 2, t = lane & 3;
@@ -417,18 +451,35 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
             for (int d = 0; d < p.xout.world; d++)
                 st_word(p.xout.peer_slot[d] + (r >> 1), *reinterpret_cast<const unsigned int*>(&pair), xout_epoch);
         } else if (EPI == EPI_RESIDUAL) {  // h = x + linear(...), fp16 add like Tensor::EwiseAdd
-            p.y[r] = hadd_ref(p.residual[r], ha);
-            p.y[r + 1] = hadd_ref(p.residual[r + 1], hb);
+            __half r0, r1;
+            if (tile < ROPE_PRE) {
+                __half2 rr = res_pre[0];
+#pragma unroll
+                for (int tt = 1; tt < ROPE_PRE; tt++) if (tile == tt) rr = res_pre[tt];
+                r0 = __low2half(rr); r1 = __high2half(rr);
+            } else {
+                r0 = p.residual[r]; r1 = p.residual[r + 1];
+            }
+            p.y[r] = hadd_ref(r0, ha);
+            p.y[r + 1] = hadd_ref(r1, hb);
         } else if (EPI == EPI_QKV_ROPE) {
-            const int pos = p.pos_ptr ? *p.pos_ptr : 0;
+            const int pos = rope_pos;
             if (mat == 2) {                // v: straight into the cache row of this position
                 __half* vo = p.v_out + (long long)pos * p.kv_pitch;
                 vo[r] = ha; vo[r + 1] = hb;
             } else {                       // q, k: interleaved-pair rotation, fp16 rounding per op
                 const int half_dim = p.head_dim >> 1;
                 const int d2 = (r % p.head_dim) >> 1;
-                const __half c = p.cos_t[(long long)pos * half_dim + d2];
-                const __half s = p.sin_t[(long long)pos * half_dim + d2];
+                __half c, s;
+                if (tile < ROPE_PRE) {
+                    __half2 cs = rope_cs[0];
+#pragma unroll
+                    for (int tt = 1; tt < ROPE_PRE; tt++) if (tile == tt) cs = rope_cs[tt];
+                    c = __low2half(cs); s = __high2half(cs);
+                } else {
+                    c = p.cos_t[(long long)pos * half_dim + d2];
+                    s = p.sin_t[(long long)pos * half_dim + d2];
+                }
                 const __half o0 = hsub_ref(hmul_ref(ha, c), hmul_ref(hb, s));
                 const __half o1 = hadd_ref(hmul_ref(ha, s), hmul_ref(hb, c));
                 __half* dst = mat == 0 ? p.y : p.k_out + (long long)pos * p.kv_pitch;
@@ -519,27 +570,29 @@ int launch_ring_cfg(const RingArgs& a, cudaStream_t st, bool pdl) {
             TL_CUDA(cudaFuncSetAttribute(k_gemv_ring<EPI, NORM, CW, NST>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                          (int)cudaSharedmemCarveoutMaxShared));
     }
-    // persistent CTAs; small problems get one CTA per stage-full of units
-    const int grid = std::max(1, std::min(sm_count() * Cfg::CTAS_PER_SM, (a.total_units + CW - 1) / CW));
+    // persistent CTAs, each with a contiguous share of the units balanced to +-1; a CTA's last stage may
+    // be partly filled (it streams only its own rows), so every SM gets work as soon as there is half
+    // a stage of units per CTA: N = 4096 spreads over all 148 SMs instead of 128 full stages
+    const int grid = std::max(1, std::min(sm_count() * Cfg::CTAS_PER_SM, (a.total_units + CW / 2 - 1) / (CW / 2)));
     return launch_pdl(k_gemv_ring<EPI, NORM, CW, NST>, dim3(grid), dim3(Cfg::THREADS), Cfg::smem_bytes(a.K), st, pdl, a);
 }
 
-// 0: one CTA per SM; 1: two half-size CTAs per SM. Measured on the 7B decode step: half-size CTAs
-// gain 1.5 % on one GPU (2.478 -> 2.440 ms per token) but lose 13 % under 2-GPU tensor parallelism
-// (every CTA sums all ranks' partial vectors in its prologue, and there are twice as many CTAs),
-// so launches that take part in an exchange keep the full shape. TL_RING=full|half overrides.
-int ring_shape_choice(const RingArgs& a, bool pushes) {
+// 0: one CTA per SM (default); 1: two half-size CTAs per SM (TL_RING=half). Measured on the 7B decode
+// step with both shapes spreading N = 4096 over all SMs: 2.459 ms per token for the full shape,
+// 2.483 ms for the half shape on one GPU, and -13 % for the half shape under 2-GPU tensor
+// parallelism (every CTA sums all ranks' partial vectors in its prologue, and there are twice as
+// many CTAs). The half shape stays selectable for experiments.
+int ring_shape_choice() {
     static const int forced = [] {
         const char* e = getenv("TL_RING");
-        return !e ? -1 : (!strcmp(e, "half") ? 1 : (!strcmp(e, "full") ? 0 : -1));
+        return !e ? 0 : (!strcmp(e, "half") ? 1 : 0);
     }();
-    if (forced >= 0) return forced;
-    return (a.has_xin || pushes) ? 0 : 1;
+    return forced;
 }
 
 template <int EPI, bool NORM>
 int launch_ring(const RingArgs& a, cudaStream_t st, bool pdl) {
-    if (ring_shape_choice(a, EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16 || EPI == EPI_STORE_F32) == 1) {
+    if (ring_shape_choice() == 1) {
         if (RingCfg<8, 3>::smem_bytes(a.K) <= 113 * 1024) return launch_ring_cfg<EPI, NORM, 8, 3>(a, st, pdl);
         if (RingCfg<8, 2>::smem_bytes(a.K) <= 113 * 1024) return launch_ring_cfg<EPI, NORM, 8, 2>(a, st, pdl);
     }
