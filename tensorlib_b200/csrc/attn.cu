@@ -292,10 +292,38 @@ __global__ void __launch_bounds__(CL_THREADS) k_decode_attn_cluster(AttnArgs p) 
     const int hd = p.hd;
 
     pdl_launch_dependents();
-    pdl_wait();
+    // In the decode step (pos_ptr set) the position counter and every cache row below the current
+    // position were written by kernels of EARLIER steps, long finished; only the newest row (and q)
+    // come from the kernel just before this one. So the first chunk of old rows is fetched before
+    // the dependency wait and its L2 latency overlaps that kernel's tail.
+    const bool early = p.pos_ptr != nullptr;
+    if (!early) pdl_wait();
     const int S = p.pos_ptr ? (*p.pos_ptr + 1) : p.seq_len;
+    const int newest = early ? S - 1 : -1;
     const int per = (S + p.splits - 1) / p.splits;
     const int s_begin = split * per, s_end = min(S, s_begin + per);
+
+    constexpr int U = 4;
+    auto load_rows = [&](__half2 (&kv)[U][HD_ITERS], __half2 (&vv)[U][HD_ITERS], int s0, bool skip_newest) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int s = s0 + u;
+            const size_t base = (size_t)s * p.pitch + (size_t)h * hd;
+#pragma unroll
+            for (int i = 0; i < HD_ITERS; i++) {
+                const int d = 2 * lane + 64 * i;
+                const bool ok = s < s_end && d < hd && !(skip_newest && s == newest);
+                kv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.kc + base + d) : __half2half2(__float2half(0.f));
+                vv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.vc + base + d) : __half2half2(__float2half(0.f));
+            }
+        }
+    };
+    __half2 kv[U][HD_ITERS], vv[U][HD_ITERS];
+    const int s_first = s_begin + warp * U;
+    if (early) {
+        if (s_first < s_end) load_rows(kv, vv, s_first, true);
+        pdl_wait();
+    }
 
     float2 qf[HD_ITERS];
 #pragma unroll
@@ -309,19 +337,24 @@ __global__ void __launch_bounds__(CL_THREADS) k_decode_attn_cluster(AttnArgs p) 
 #pragma unroll
     for (int i = 0; i < HD_ITERS; i++) acc[i] = make_float2(0.f, 0.f);
 
-    constexpr int U = 4;
-    for (int s0 = s_begin + warp * U; s0 < s_end; s0 += CL_WARPS * U) {
-        __half2 kv[U][HD_ITERS], vv[U][HD_ITERS];
+    for (int s0 = s_first; s0 < s_end; s0 += CL_WARPS * U) {
+        if (!early || s0 != s_first) {
+            load_rows(kv, vv, s0, false);
+        } else if (newest >= s0 && newest < s0 + U && newest < s_end) {
+            // the one row the previous kernel wrote, if it falls into the prefetched chunk
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int s = s0 + u;
-            const size_t base = (size_t)s * p.pitch + (size_t)h * hd;
+            for (int u = 0; u < U; u++) {
+                if (s0 + u == newest) {
+                    const size_t base = (size_t)newest * p.pitch + (size_t)h * hd;
 #pragma unroll
-            for (int i = 0; i < HD_ITERS; i++) {
-                int d = 2 * lane + 64 * i;
-                bool ok = s < s_end && d < hd;
-                kv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.kc + base + d) : __half2half2(__float2half(0.f));
-                vv[u][i] = ok ? *reinterpret_cast<const __half2*>(p.vc + base + d) : __half2half2(__float2half(0.f));
+                    for (int i = 0; i < HD_ITERS; i++) {
+                        const int d = 2 * lane + 64 * i;
+                        if (d < hd) {
+                            kv[u][i] = *reinterpret_cast<const __half2*>(p.kc + base + d);
+                            vv[u][i] = *reinterpret_cast<const __half2*>(p.vc + base + d);
+                        }
+                    }
+                }
             }
         }
         float sc[U];
