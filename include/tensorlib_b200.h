@@ -272,7 +272,8 @@ TL_API int tl_tp_destroy(void);
 /* Fused exchange for the decode step: instead of an NCCL allreduce after wo and w2, the GEMV
  * kernels store their fp32 partial sums into a receive region in every rank's memory (peer
  * stores over NVLink) and the next GEMV's prologue sums them in rank order; the classifier
- * slices travel the same way. Set-up: every rank exports a 64-byte handle of its region, the
+ * slices travel the same way. Every 8-byte word carries its payload and the epoch of the step, so
+ * validity needs no separate flag or fence. Needs an even vocabulary slice per rank. Set-up: every rank exports a 64-byte handle of its region, the
  * handles are gathered out of band (rank order, world*64 bytes), every rank opens them; all
  * ranks must pass a host barrier before the first decode step and before closing. Device-side
  * waits are bounded (TL_ERR_TIMEOUT in the device status word). Prefill keeps using NCCL. */

@@ -111,7 +111,8 @@ private:
     long long launches_ = 0;
     long long decode_step_launches_ = 0;
     Collective* coll_ = nullptr;
-    // exchange region: [part0: world*dim f32][part1: world*dim f32][logits: vocab f16][flags 3*8 u32][done 3 u32][step u32]
+    // exchange region, all payloads as 8-byte (payload, epoch) words:
+    // [part0: world*dim words][part1: world*dim words][logits: vocab/2 words][step u32]
     int decode_step_tp_fused(cudaStream_t st, bool pdl);
     PeerExchange make_exchange(int buf, int phase_id) const;
     unsigned char* xch_base_ = nullptr;
