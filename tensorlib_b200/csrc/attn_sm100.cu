@@ -192,22 +192,30 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (lane == 0) mbar_arrive(BAR(9 + b));     // this score buffer may be overwritten
             const int c0 = j * BKV;
             const bool need_mask = c0 + BKV - 1 > p.pos0 + q0;
-            float mloc = -INFINITY;
+            // running maximum on the raw scores (the scale is positive); the scale is applied inside
+            // the exponent's FFMA: p = 2^(s * scale - m)
+            float mraw = -INFINITY;
+            if (need_mask) {
 #pragma unroll
-            for (int c = 0; c < BKV; c++) {
-                float x = __uint_as_float(s[c]) * p.scale_log2;
-                if (need_mask && c0 + c > rowpos) x = -INFINITY;
-                s[c] = __float_as_uint(x);
-                mloc = fmaxf(mloc, x);
+                for (int c = 0; c < BKV; c++) {
+                    if (c0 + c > rowpos) s[c] = 0xff800000u;   // -inf
+                    mraw = fmaxf(mraw, __uint_as_float(s[c]));
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < BKV; c++) mraw = fmaxf(mraw, __uint_as_float(s[c]));
             }
+            const float mloc = mraw * p.scale_log2;
             const bool grow = mloc > m_ref + RESCALE_THRESHOLD;   // always true for the first tile
             const float alpha = grow ? ex2(m_ref - mloc) : 1.0f;
             if (grow) m_ref = mloc;
+            const float neg_m = -m_ref;
             uint32_t pk[BKV / 2];
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < BKV; c += 2) {
-                const float p0 = ex2(__uint_as_float(s[c]) - m_ref), p1 = ex2(__uint_as_float(s[c + 1]) - m_ref);
+                const float p0 = ex2(fmaf(__uint_as_float(s[c]), p.scale_log2, neg_m));
+                const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, neg_m));
                 sum += p0 + p1;
                 __half2 h = __floats2half2_rn(p0, p1);
                 pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);

@@ -19,6 +19,7 @@
 // status word).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -458,12 +459,16 @@ SkinnyPlan skinny_plan(int M, int N, int K, int sms) {
     const int max_grid = std::max(1, std::min(sms, MAX_GRID));
     int per = (int)((total + max_grid - 1) / max_grid);
     if (per < 4) per = (int)std::min<long long>(4, total);
-    // few W tiles: give every tile the same whole number of sharers when that still fills >= 85 %
-    // of the SMs; the sharers then form a cluster and reduce over distributed shared memory
+    // few W tiles: give every tile the same whole number of sharers when that still fills enough of
+    // the SMs; two or more sharers form a cluster and reduce over distributed shared memory
     pl.cluster_splits = 0;
     if (pl.tiles <= max_grid) {
         const int sp = std::max(1, std::min(std::min(max_grid / pl.tiles, 8), std::max(1, pl.nkb / 4)));
-        if ((long long)pl.tiles * sp * 100 >= (long long)max_grid * 85) {
+        // measured at N = 11008 (86 tiles on 148 SMs): whole tiles beat the stream-K ranges once the
+        // fp32 partial tiles are large (M = 128: 30.2 against 33.9 us; M = 64: 26.5 against 27.4) and
+        // lose for narrow ones (M = 8: 23.6 against 22.0)
+        const int fill_pct = pl.nb >= 64 ? 55 : 85;
+        if ((long long)pl.tiles * sp * 100 >= (long long)max_grid * fill_pct) {
             per = (pl.nkb + sp - 1) / sp;
             if (sp >= 2) pl.cluster_splits = sp;
         }

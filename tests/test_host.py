@@ -121,6 +121,8 @@ def test_matmul_plan_picks_the_kernel_each_regime_is_built_for():
     assert tl.matmul_plan(1, 32000, 4096)["kernel"] == "gemv_ring"
     for M in (2, 8, 32, 128):                                                   # weights streamed once
         assert tl.matmul_plan(M, 11008, 4096)["kernel"].startswith("skinny"), M
+    assert tl.matmul_plan(32, 11008, 4096)["grid"] == 145                       # stream-K ranges
+    assert tl.matmul_plan(128, 11008, 4096)["grid"] == 86                       # whole tiles: no partial-tile exchange
     assert tl.matmul_plan(32, 4096, 4096) == {"kernel": "skinny_cluster", "grid": 128, "tile_n": 32,
                                               "k_blocks_per_cta": 16, "cluster": 4}
     assert tl.matmul_plan(512, 4096, 4096)["kernel"] == "hgemm"
