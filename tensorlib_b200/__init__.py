@@ -315,7 +315,7 @@ def attn_prefill(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, start_
 
 
 PLAN_NAMES = {0: "reference_order", 1: "gemv_ring", 2: "gemv_small", 3: "skinny_streamk", 4: "skinny_cluster",
-              5: "hgemm", 6: "hgemm_pair"}
+              5: "hgemm", 6: "hgemm_pair", 7: "hgemm_pair512"}
 
 
 def matmul_plan(M: int, N: int, K: int, sm_count: int = 148) -> dict:

@@ -294,17 +294,25 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
 // the accumulator on the leader's barrier with a remote arrive. No multicast anywhere.
 // For SWIGLU the split of B by halves is exactly W1 | W3: rank 0 loads the W1 rows, rank 1 the
 // W3 rows of the same output columns.
-constexpr int PAIR_BN = 256, PAIR_STAGES = 6;
+// MSUB = 2 gives every CTA TWO 128-row sub-tiles of A against the same half B tile (a 512 x 256 tile per
+// pair, two accumulators = all 512 TMEM columns, so no accumulator double buffering): 48 KB of
+// operands per CTA for twice the MMA work, i.e. 24 KB per 512 MMA cycles. That moves the kernel
+// from the shared-memory fill limit (measured ~72 B/clk per SM) to the tensor pipe.
+constexpr int PAIR_BN = 256;
 constexpr int PAIR_B_BYTES = (PAIR_BN / 2) * BK * 2;                  // this CTA's half of the B tile
-constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;             // 32 KB
-constexpr size_t PAIR_SMEM = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+template <int MSUB> struct PairCfg {
+    static constexpr int STAGE_BYTES = MSUB * A_BYTES + PAIR_B_BYTES;   // 32 KB / 48 KB
+    static constexpr int STAGES = MSUB == 1 ? 6 : 4;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int THREADS = GEMM_THREADS + (MSUB - 1) * 128;     // four epilogue warps per sub-tile
+};
 
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+template <int EPI, int MSUB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<MSUB>::THREADS, 1)
 k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmB3, GemmArgs p) {
-    constexpr int BN = PAIR_BN, STAGES = PAIR_STAGES, STAGE_BYTES = PAIR_STAGE_BYTES;
-    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr int BN = PAIR_BN, STAGES = PairCfg<MSUB>::STAGES, STAGE_BYTES = PairCfg<MSUB>::STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;      // MSUB 1: two buffers of one accumulator; MSUB 2: one buffer of two
     constexpr int OUT_COLS = EPI == GEPI_SWIGLU ? BN / 2 : BN;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -317,7 +325,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();                              // 0: leader
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int mt_count = (p.M + 2 * BM - 1) / (2 * BM);                   // 256-row tiles
+    const int mt_count = (p.M + 2 * MSUB * BM - 1) / (2 * MSUB * BM);     // 256- or 512-row tiles
     const int nt_each = (p.N + OUT_COLS - 1) / OUT_COLS;
     const int nt_count = EPI == GEPI_QKV_ROPE ? 3 * nt_each : nt_each;
     const int tiles_per_batch = mt_count * nt_count;
@@ -326,7 +334,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }   // 4 warps x 2 CTAs
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8 * MSUB); }   // epilogue warps x 2 CTAs
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -359,10 +367,13 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             for (int kb = 0; kb < nkb; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
                 if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
-                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + MSUB * A_BYTES;
                 const uint32_t leader_full = map_to_cta(full0 + 8 * s, 0);
                 if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // both CTAs' bytes
-                tma_load_3d_pair(sa, &tmA, kb * BK, (mt * 2 + (int)rank) * BM, p.a_batched ? b : 0, leader_full);
+#pragma unroll
+                for (int ms = 0; ms < MSUB; ms++)   // sub-tile ms of this CTA: rows ((mt * 2 + rank) * MSUB + ms) * 128 ...
+                    tma_load_3d_pair(sa + ms * A_BYTES, &tmA, kb * BK, ((mt * 2 + (int)rank) * MSUB + ms) * BM,
+                                     p.a_batched ? b : 0, leader_full);
                 tma_load_3d_pair(sb, mb, kb * BK, brow, p.b_batched ? b : 0, leader_full);
             }
         }
@@ -378,7 +389,8 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         int it = 0, tcount = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tcount++) {
-            const int buf = tcount & 1, use = tcount >> 1;
+            // MSUB 1: accumulator buffers alternate; MSUB 2: both accumulators form the single buffer 0
+            const int buf = MSUB == 1 ? (tcount & 1) : 0, use = MSUB == 1 ? (tcount >> 1) : tcount;
             if (use > 0 && !(ok = mbar_wait(tempty0 + 8 * buf, (use - 1) & 1, abort_flag))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
@@ -386,10 +398,13 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 const int s = it % STAGES, use_s = it / STAGES;
                 if (!(ok = mbar_wait(full0 + 8 * s, use_s & 1, abort_flag))) break;
                 tc_fence_after();
-                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + MSUB * A_BYTES;
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++)
-                    umma_pair(d_tmem, make_desc(sa + k * 32), make_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int ms = 0; ms < MSUB; ms++)
+                        umma_pair(d_tmem + (uint32_t)(ms * BN), make_desc(sa + ms * A_BYTES + k * 32), make_desc(sb + k * 32), idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
                 umma_commit_pair(empty0 + 8 * s);                   // my stage is reusable
                 umma_commit_pair(map_to_cta(empty0 + 8 * s, 1));    // and the peer's
             }
@@ -408,13 +423,15 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
             const int mt = idx % mt_count, nt = idx / mt_count;
             const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
-            const int buf = tcount & 1, use = tcount >> 1;
+            const int buf = MSUB == 1 ? (tcount & 1) : 0, use = MSUB == 1 ? (tcount >> 1) : tcount;
             ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const int row = (mt * 2 + (int)rank) * BM + q * 32 + lane;
-            const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+            {
+            const int ms = (warp - 4) >> 2;            // warps 4..7 drain sub-tile 0, warps 8..11 sub-tile 1
+            const int row = ((mt * 2 + (int)rank) * MSUB + ms) * BM + q * 32 + lane;
+            const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf + ms) * BN);
             __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
             if (EPI == GEPI_SWIGLU) {
 #pragma unroll 1
@@ -448,6 +465,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         store32(crow + col0, r);
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -525,15 +543,24 @@ int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CU
     return launch_k<64, EPI>(ma, mb, mb2, mb3, a, tiles, st);
 }
 
-template <int EPI>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
-                const GemmArgs& a, int pair_tiles, cudaStream_t st) {
+template <int EPI, int MSUB>
+int launch_pair_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
+                    const GemmArgs& a, int pair_tiles, cudaStream_t st) {
     static PerDeviceOnce once;
     if (once.needed()) {
-        TL_CUDA(cudaFuncSetAttribute(k_hgemm_pair<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+        TL_CUDA(cudaFuncSetAttribute(k_hgemm_pair<EPI, MSUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg<MSUB>::SMEM));
     }
     const int grid = 2 * std::max(1, std::min(pair_tiles, sm_count() / 2));
-    return launch_pdl(k_hgemm_pair<EPI>, dim3(grid), dim3(GEMM_THREADS), PAIR_SMEM, st, true, ma, mb, mb2, mb3, a);
+    return launch_pdl(k_hgemm_pair<EPI, MSUB>, dim3(grid), dim3(PairCfg<MSUB>::THREADS), PairCfg<MSUB>::SMEM, st, true, ma, mb, mb2, mb3, a);
+}
+// `n_tiles` = column tiles (per batch); rows come in 256- or 512-row tiles by what fills the pairs better
+int pair_msub(int M, long long n_tiles, int epi);
+template <int EPI>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
+                const GemmArgs& a, int n_col_tiles, cudaStream_t st) {
+    const long long nt = (long long)n_col_tiles * a.batch;
+    if (pair_msub(a.M, nt, EPI) == 2) return launch_pair_cfg<EPI, 2>(ma, mb, mb2, mb3, a, (int)(((a.M + 511) / 512) * nt), st);
+    return launch_pair_cfg<EPI, 1>(ma, mb, mb2, mb3, a, (int)(((a.M + 255) / 256) * nt), st);
 }
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
@@ -541,19 +568,38 @@ inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) =
 int g_plan_sms = 0;   // when non-zero, the planning functions use it instead of the device's SM count
 int plan_sms() { return g_plan_sms > 0 ? g_plan_sms : sm_count(); }
 
-// estimated cost (cycles per k-block x waves) of the CTA-pair kernel: 256 x 256 tiles over sm/2 pairs,
-// 512 MMA cycles per k-block, operands arrive at 32 KB per CTA per k-block (not the limit)
-long long pair_cost(int M, int n_tiles_256, int batch) {
-    // TL_HGEMM_PAIR=always|never overrides the estimate (tests force both kernels onto small shapes)
+// Estimated cost (cycles per k-block x rounds of tiles over the sm/2 pairs) of the CTA-pair kernel in its
+// two shapes. Per k-block a 256 x 256 pair tile measures ~590 cycles (512 of MMA stretched by the
+// shared-memory fill running at its limit beside them), a 512 x 256 tile ~1090 (1024 of MMA, the fill
+// no longer the limit).
+// TL_HGEMM_PAIR=always|always512|never overrides the estimate (tests force every kernel onto small shapes)
+int pair_forced() {
     static const int forced = [] {
         const char* e = getenv("TL_HGEMM_PAIR");
-        return !e ? 0 : (!strcmp(e, "always") ? 1 : (!strcmp(e, "never") ? 2 : 0));
+        return !e ? 0 : (!strcmp(e, "always") ? 1 : (!strcmp(e, "never") ? 2 : (!strcmp(e, "always512") ? 3 : 0)));
     }();
-    if (forced == 1) return -1;
-    if (forced == 2) return (1ll << 60);
-    const long long tiles = (long long)((M + 255) / 256) * n_tiles_256 * batch;
+    return forced;
+}
+long long pair_cost_msub(int M, long long n_tiles, int msub) {
+    const long long tiles = (long long)((M + 256 * msub - 1) / (256 * msub)) * n_tiles;
     const long long pairs = std::max(1, plan_sms() / 2);
-    return ((tiles + pairs - 1) / pairs) * 512;
+    return ((tiles + pairs - 1) / pairs) * (msub == 1 ? 590 : 1090);
+}
+// The 512-row tile has no second accumulator buffer, so its epilogue is not hidden behind the next
+// tile's MMAs. The rotary epilogue (per-row factor loads, three destinations) is long enough that the
+// 256-row tile with its hidden epilogue wins for the fused QKV projection (2048 tokens of the 7B model:
+// 1.7 ms of 24.5 over 32 layers); the other epilogues gain from the larger tile.
+int pair_msub(int M, long long n_tiles, int epi) {
+    if (pair_forced() == 1) return 1;
+    if (pair_forced() == 3) return 2;
+    if (epi == GEPI_QKV_ROPE) return 1;
+    return pair_cost_msub(M, n_tiles, 2) < pair_cost_msub(M, n_tiles, 1) ? 2 : 1;
+}
+long long pair_cost(int M, int n_tiles_256, int batch, int epi = GEPI_STORE) {
+    if (pair_forced() == 1 || pair_forced() == 3) return -1;
+    if (pair_forced() == 2) return (1ll << 60);
+    const long long nt = (long long)n_tiles_256 * batch;
+    return pair_cost_msub(M, nt, pair_msub(M, nt, epi));
 }
 long long single_cost(int mt, int N, int batch, int bn) {
     const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
@@ -588,7 +634,10 @@ void hgemm_plan(int M, int N, int batch, int sms, int* kind, int* bn) {
     const int mt = (M + BM - 1) / BM;
     *bn = pick_bn(mt, N, batch);
     *kind = (M > BM && N % 32 == 0 && pair_cost(M, (N + 255) / 256, batch) < single_cost(mt, N, batch, *bn)) ? 1 : 0;
-    if (*kind == 1) *bn = 256;
+    if (*kind == 1) {                     // 1: 256-row pair tiles, 2: 512-row pair tiles
+        *bn = 256;
+        *kind = pair_msub(M, (long long)((N + 255) / 256) * batch, GEPI_STORE);
+    }
     g_plan_sms = 0;
 }
 
@@ -614,7 +663,7 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     const bool vec_c = ldc % 8 == 0 && sC % 8 == 0 && al16(C) && N % 32 == 0;   // the pair epilogue stores 64-byte chunks
     if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch) < single_cost(mt, N, batch, bn)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, 128));
-        return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, ((M + 255) / 256) * ((N + 255) / 256) * batch, st);
+        return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, (N + 255) / 256, st);
     }
     TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, bn));
     const int tiles = mt * ((N + bn - 1) / bn) * batch;
@@ -641,7 +690,7 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     a.R = R; a.ldr = ldr;
     if (M > BM && pair_cost(M, (N + 255) / 256, 1) < single_cost(mt, N, 1, bn)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
-        return launch_pair<GEPI_RESIDUAL>(ma, mb, mb, mb, a, ((M + 255) / 256) * ((N + 255) / 256), st);
+        return launch_pair<GEPI_RESIDUAL>(ma, mb, mb, mb, a, (N + 255) / 256, st);
     }
     TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, bn));
     return launch_any_bn<GEPI_RESIDUAL>(bn, ma, mb, mb, mb, a, mt * ((N + bn - 1) / bn), st);
@@ -660,7 +709,7 @@ int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __h
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
     if (M > BM && pair_cost(M, nt, 1) < single_cost(mt, N, 1, 128) * 768 / 512)   // single: 128 output columns per 256-wide tile
-        return launch_pair<GEPI_SWIGLU>(ma, m1, m3, m3, a, ((M + 255) / 256) * nt, st);
+        return launch_pair<GEPI_SWIGLU>(ma, m1, m3, m3, a, nt, st);
     return launch_k<256, GEPI_SWIGLU>(ma, m1, m3, m3, a, mt * nt, st);
 }
 
@@ -680,14 +729,14 @@ int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, c
     while (bn > 64 && (n_each % bn != 0 || (long long)mt * 3 * (n_each / bn) < sm_count())) bn >>= 1;
     CUtensorMap ma, mq, mk, mv;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
-    if (M > BM && n_each % 256 == 0 && pair_cost(M, 3 * (n_each / 256), 1) < single_cost(mt, 3 * n_each, 1, bn)) {
+    if (M > BM && n_each % 256 == 0 && pair_cost(M, 3 * (n_each / 256), 1, GEPI_QKV_ROPE) < single_cost(mt, 3 * n_each, 1, bn)) {
         TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, 128));
         TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, 128));
         TL_PROPAGATE(make_tensor_map_f16(&mv, Wv, n_each, K, ldb, 0, 1, 128));
         GemmArgs a2{};
         a2.C = q_out; a2.M = M; a2.N = n_each; a2.K = K; a2.batch = 1; a2.ldc = ldq; a2.status = device_status_word();
         a2.kc = k_rows; a2.vc = v_rows; a2.ld_kv = ld_kv; a2.cos_t = cos_rows; a2.sin_t = sin_rows; a2.head_dim = head_dim;
-        return launch_pair<GEPI_QKV_ROPE>(ma, mq, mk, mv, a2, ((M + 255) / 256) * 3 * (n_each / 256), st);
+        return launch_pair<GEPI_QKV_ROPE>(ma, mq, mk, mv, a2, 3 * (n_each / 256), st);
     }
     TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, bn));
     TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, bn));

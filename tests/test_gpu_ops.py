@@ -256,7 +256,7 @@ print("WORST", worst)
 """
 
 
-@pytest.mark.parametrize("mode", ["always", "never"])
+@pytest.mark.parametrize("mode", ["always", "always512", "never"])
 def test_hgemm_pair_and_single_kernels_agree_with_float64(tl, mode, tmp_path):
     import subprocess
     script = tmp_path / "child.py"

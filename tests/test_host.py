@@ -126,9 +126,11 @@ def test_matmul_plan_picks_the_kernel_each_regime_is_built_for():
     assert tl.matmul_plan(32, 4096, 4096) == {"kernel": "skinny_cluster", "grid": 128, "tile_n": 32,
                                               "k_blocks_per_cta": 16, "cluster": 4}
     assert tl.matmul_plan(512, 4096, 4096)["kernel"] == "hgemm"
-    for N, K in ((4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)):   # prefill shapes: CTA pairs
+    # prefill shapes: CTA pairs, 512-row tiles where they fill the 74 pairs at least as well as 256-row ones
+    for N, K, kernel, grid in ((4096, 4096, "hgemm_pair512", 128), (11008, 4096, "hgemm_pair", 148),
+                               (4096, 11008, "hgemm_pair512", 128), (32000, 4096, "hgemm_pair512", 148)):
         p = tl.matmul_plan(2048, N, K)
-        assert p["kernel"] == "hgemm_pair" and p["grid"] == 148 and p["cluster"] == 2, (N, K, p)
+        assert p["kernel"] == kernel and p["grid"] == grid and p["cluster"] == 2, (N, K, p)
     assert tl.matmul_plan(3, 1000, 300)["kernel"] == "reference_order"          # K % 8 != 0: any-shape kernel
     with pytest.raises(tl.TLError):
         tl.matmul_plan(0, 8, 8)
