@@ -6,14 +6,17 @@
 //
 // One CTA per (head, 128 query rows); two CTAs per SM so that one CTA's softmax overlaps the
 // other's MMAs. Inside a CTA, per 64-column KV tile j:
-//   warp 0   TMA: Q once, K tiles (2 stages), V tiles (1 stage), 128-byte swizzle, zero fill
-//   warp 1   tcgen05.mma: S[j&1] = Q K_j^T (TMEM, 64 fp32 columns), then O += P_{j-1} V_{j-1}
-//            (TMEM, 128 columns); issuing S_j before the P.V of tile j-1 keeps the tensor core
-//            busy while the softmax warps work on tile j-1
-//   warps 2-5  one query row per thread: tcgen05.ld the S row, scale, mask, running max and sum
-//            (exp2 domain), P as fp16 into the swizzled shared tile the second MMA reads as its
-//            A operand. The accumulator is rescaled (tcgen05.ld/st) only when the running max
-//            grew by more than 2^8 since the last rescale; P stays below 2^8 in between.
+//   warp 0   TMA: Q once, K tiles (2 stages), V tiles (2 stages), 128-byte swizzle, zero fill
+//   warp 1   tcgen05.mma: S[j&1] = Q K_j^T (TMEM, 64 fp32 columns), up to two tiles ahead of the softmax
+//   warps 2-5  one query row per thread: tcgen05.ld the S row, mask, running max and sum (exp2
+//            domain, scale folded into the exponent's FFMA), P as fp16 back into the first 32 columns
+//            of the same S buffer (tcgen05.st). The accumulator is rescaled (tcgen05.ld/st) only
+//            when the running max grew by more than 2^8 since the last rescale; P stays below 2^8.
+//   warp 6   tcgen05.mma with the A operand in tensor memory: O += P_j V_j (TMEM, 128 columns); its
+//            completion frees the V stage and the S/P buffer
+// Two issuing threads because one thread's barrier waits, commits and fences per tile cost more
+// than the tile's MMAs take, and an MMA issue blocks while the tensor core's short queue is full
+// (measured: one issuer 49.5 us per 7B layer at T = 2048, two issuers 41.3 us).
 // V is read in place from the cache: (kv, head_dim) rows are the N x K operand of the second MMA in
 // MN-major form (head_dim contiguous), so no transposed copy exists.
 // Bound: tensor pipe / MUFU (exp2), not HBM: 4 * T * S * hd flops per head against
@@ -33,12 +36,11 @@ namespace {
 using namespace sm100;
 
 constexpr int BQ = 128, BKV = 64, HD = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 224;     // TMA, S issuer, 4 softmax warps, P.V issuer
 constexpr int Q_BYTES = BQ * HD * 2;          // two swizzle atoms of 64 columns
 constexpr int K_BYTES = BKV * HD * 2;         // two atoms, 64 rows each
 constexpr int V_BYTES = BKV * HD * 2;         // V tile as stored: 64 kv rows, two 64-column halves
-constexpr int P_BYTES = BQ * BKV * 2;         // one atom
-constexpr int K_STAGES = 2;
+constexpr int K_STAGES = 2, V_STAGES = 2;
 constexpr uint32_t TMEM_COLS = 256;           // S0 | S1 (64 each) | O (128)
 constexpr uint32_t S_COL = 0, O_COL = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;     // log2 units
@@ -65,12 +67,11 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     unsigned char* sQ = smem;
     unsigned char* sK = sQ + Q_BYTES;
     unsigned char* sV = sK + K_STAGES * K_BYTES;
-    unsigned char* sP = sV + V_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-    // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5 v_full | 6 v_empty(= pv_done) | 7,8 s_full | 9,10 s_empty | 11 p_full
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + V_STAGES * V_BYTES);
+    // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 pv_done | 9,10 s_full | 11,12 p_full
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,9 +85,9 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (threadIdx.x == 0) {
         mbar_init(BAR(0), 1);
         mbar_init(BAR(1), 1); mbar_init(BAR(2), 1); mbar_init(BAR(3), 1); mbar_init(BAR(4), 1);
-        mbar_init(BAR(5), 1); mbar_init(BAR(6), 1);
-        mbar_init(BAR(7), 1); mbar_init(BAR(8), 1); mbar_init(BAR(9), 4); mbar_init(BAR(10), 4);
-        mbar_init(BAR(11), 128);   // every softmax thread arrives after fencing its own P row
+        mbar_init(BAR(5), 1); mbar_init(BAR(6), 1); mbar_init(BAR(7), 1); mbar_init(BAR(8), 1);
+        mbar_init(BAR(9), 1); mbar_init(BAR(10), 1);
+        mbar_init(BAR(11), 128); mbar_init(BAR(12), 128);   // every softmax thread arrives after storing its own P row
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -124,39 +125,33 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < n_tiles && ok; j++) {
             // K runs one tile ahead of V: its stage frees as soon as the scores of tile j-1 exist
             if (j + 1 < n_tiles && !(ok = issue_k(j + 1))) break;
-            if (j >= 1 && !(ok = mbar_wait(BAR(6), (j - 1) & 1, abort_flag))) break;   // P.V of tile j-1 has read V
-            mbar_arrive_expect_tx(BAR(5), V_BYTES);
-            tma_load_3d(smem_u32(sV), &tmV, 0, j * BKV, head, BAR(5));
-            tma_load_3d(smem_u32(sV) + V_BYTES / 2, &tmV, 64, j * BKV, head, BAR(5));
+            const int vs = j & 1;
+            if (j >= V_STAGES && !(ok = mbar_wait(BAR(7 + vs), ((j >> 1) - 1) & 1, abort_flag))) break;   // P.V of tile j-2 has read this stage
+            const uint32_t dv = smem_u32(sV + vs * V_BYTES);
+            mbar_arrive_expect_tx(BAR(5 + vs), V_BYTES);
+            tma_load_3d(dv, &tmV, 0, j * BKV, head, BAR(5 + vs));
+            tma_load_3d(dv + V_BYTES / 2, &tmV, 64, j * BKV, head, BAR(5 + vs));
             v_issued++;
         }
         if (!ok) {  // let copies already in flight land before the CTA goes away
             for (uint32_t i = 0; i < (1u << 16); i++) if (mbar_try_wait(BAR(0), 0)) break;
             for (int j = max(0, k_issued - K_STAGES); j < k_issued; j++)
                 for (uint32_t i = 0; i < (1u << 16); i++) if (mbar_try_wait(BAR(1 + (j & 1)), (j >> 1) & 1)) break;
-            if (v_issued > 0)
-                for (uint32_t i = 0; i < (1u << 16); i++) if (mbar_try_wait(BAR(5), (v_issued - 1) & 1)) break;
+            for (int j = max(0, v_issued - V_STAGES); j < v_issued; j++)
+                for (uint32_t i = 0; i < (1u << 16); i++) if (mbar_try_wait(BAR(5 + (j & 1)), (j >> 1) & 1)) break;
         }
     } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer ------------------------------------------------------------
-        constexpr uint32_t idesc_s = make_idesc(BKV), idesc_o = make_idesc(HD) | IDESC_B_MN_MAJOR;
+        // ---------------- MMA issuer 1: S_j = Q K_j^T -----------------------------------------------
+        // Two issuing threads (this one and the P.V issuer below): the barrier waits, commits and
+        // fences of a tile cost one thread more time than its MMAs take to execute, and an MMA issue
+        // blocks while the tensor core's short queue is full.
+        constexpr uint32_t idesc_s = make_idesc(BKV);
         bool ok = mbar_wait(BAR(0), 0, abort_flag);
-        const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aV = smem_u32(sV);
-        auto issue_pv = [&](int t) -> bool {   // O += P_t V_t
-            if (!mbar_wait(BAR(11), t & 1, abort_flag)) return false;
-            if (!mbar_wait(BAR(5), t & 1, abort_flag)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < BKV / 16; k++)
-                umma(tmem_base + O_COL, make_desc(aP + k * 32), make_desc_mn(aV + k * 2048, V_BYTES / 2, 1024), idesc_o,
-                     (t > 0 || k > 0) ? 1u : 0u);
-            umma_commit(BAR(6));
-            return true;
-        };
+        const uint32_t aQ = smem_u32(sQ);
         for (int j = 0; j < n_tiles && ok; j++) {
             const int b = j & 1;
             if (!(ok = mbar_wait(BAR(1 + b), (j >> 1) & 1, abort_flag))) break;
-            if (j >= 2 && !(ok = mbar_wait(BAR(9 + b), ((j >> 1) - 1) & 1, abort_flag))) break;
+            if (j >= 2 && !(ok = mbar_wait(BAR(7 + b), ((j >> 1) - 1) & 1, abort_flag))) break;   // P.V of tile j-2 has read P from this buffer
             tc_fence_after();
             const uint32_t aK = smem_u32(sK + b * K_BYTES);
 #pragma unroll
@@ -164,12 +159,26 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 umma(tmem_base + S_COL + (uint32_t)(b * BKV),
                      make_desc(aQ + (k >> 2) * (Q_BYTES / 2) + (k & 3) * 32),
                      make_desc(aK + (k >> 2) * (K_BYTES / 2) + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
-            umma_commit(BAR(7 + b));   // scores ready
+            umma_commit(BAR(9 + b));   // scores ready
             umma_commit(BAR(3 + b));   // K stage reusable
-            if (j >= 1) ok = issue_pv(j - 1);
         }
-        if (ok) issue_pv(n_tiles - 1);
-    } else if (warp >= 2) {
+    } else if (warp == 6 && lane == 0) {
+        // ---------------- MMA issuer 2: O += P_t V_t, P_t read from the tensor-memory columns of S_t ----
+        constexpr uint32_t idesc_o = make_idesc(HD) | IDESC_B_MN_MAJOR;
+        bool ok = true;
+        for (int t = 0; t < n_tiles && ok; t++) {
+            const int tb = t & 1;
+            if (!(ok = mbar_wait(BAR(5 + tb), (t >> 1) & 1, abort_flag))) break;
+            if (!(ok = mbar_wait(BAR(11 + tb), (t >> 1) & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t aV = smem_u32(sV + tb * V_BYTES);
+#pragma unroll
+            for (int k = 0; k < BKV / 16; k++)
+                umma_ts(tmem_base + O_COL, tmem_base + S_COL + (uint32_t)(tb * BKV + k * 8),
+                        make_desc_mn(aV + k * 2048, V_BYTES / 2, 1024), idesc_o, (t > 0 || k > 0) ? 1u : 0u);
+            umma_commit(BAR(7 + tb));   // V stage and score/P buffer tb reusable, accumulator updated
+        }
+    } else if (warp >= 2 && warp < 6) {
         // ---------------- softmax: one query row per thread -------------------------------------
         const int q = warp & 3;                         // TMEM lane quarter this warp may access
         const int r = q * 32 + lane;
@@ -179,7 +188,7 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
             const int b = j & 1;
-            ok = mbar_wait(BAR(7 + b), (j >> 1) & 1, abort_flag);
+            ok = mbar_wait(BAR(9 + b), (j >> 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -187,47 +196,46 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_ld32(lane_addr + S_COL + (uint32_t)(b * BKV), s);
             tmem_ld32(lane_addr + S_COL + (uint32_t)(b * BKV + 32), s + 32);
             tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(9 + b));     // this score buffer may be overwritten
             const int c0 = j * BKV;
             const bool need_mask = c0 + BKV - 1 > p.pos0 + q0;
             // running maximum on the raw scores (the scale is positive); the scale is applied inside
             // the exponent's FFMA: p = 2^(s * scale - m)
-            float mraw = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < BKV; c++) {
+                for (int c = 0; c < BKV; c++)
                     if (c0 + c > rowpos) s[c] = 0xff800000u;   // -inf
-                    mraw = fmaxf(mraw, __uint_as_float(s[c]));
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < BKV; c++) mraw = fmaxf(mraw, __uint_as_float(s[c]));
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four independent chains
+#pragma unroll
+            for (int c = 0; c < BKV; c += 4) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) mx[i] = fmaxf(mx[i], __uint_as_float(s[c + i]));
+            }
+            const float mraw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             const float mloc = mraw * p.scale_log2;
             const bool grow = mloc > m_ref + RESCALE_THRESHOLD;   // always true for the first tile
             const float alpha = grow ? ex2(m_ref - mloc) : 1.0f;
             if (grow) m_ref = mloc;
             const float neg_m = -m_ref;
             uint32_t pk[BKV / 2];
-            float sum = 0.f;
+            float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
             for (int c = 0; c < BKV; c += 2) {
                 const float p0 = ex2(fmaf(__uint_as_float(s[c]), p.scale_log2, neg_m));
                 const float p1 = ex2(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, neg_m));
-                sum += p0 + p1;
+                sum0 += p0;
+                sum1 += p1;
                 __half2 h = __floats2half2_rn(p0, p1);
                 pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
             }
-            l = l * alpha + sum;
-            if (j > 0) {
-                // the previous P.V must have finished: it read the P tile and wrote the accumulator
-                ok = mbar_wait(BAR(6), (j - 1) & 1, abort_flag);
+            l = l * alpha + (sum0 + sum1);
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                // rescaling the accumulator: the previous P.V must have finished writing it
+                ok = mbar_wait(BAR(7 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
+                {
 #pragma unroll 1
                     for (int cc = 0; cc < HD; cc += 32) {
                         uint32_t o[32];
@@ -240,16 +248,15 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     tmem_st_wait();
                 }
             }
-            uint4* prow = reinterpret_cast<uint4*>(sP + r * 128);
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++)
-                prow[ch ^ (r & 7)] = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-            fence_proxy_async_smem();
+            // P_j as the A operand of the second MMA, in place of the first 32 columns of S_j: this
+            // thread's row, two fp16 per column
+            tmem_st32(lane_addr + S_COL + (uint32_t)(b * BKV), pk);
+            tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(BAR(11));
+            mbar_arrive(BAR(11 + b));
         }
         if (ok) {
-            ok = mbar_wait(BAR(6), (n_tiles - 1) & 1, abort_flag);
+            ok = mbar_wait(BAR(7 + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
@@ -287,7 +294,7 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
 
-constexpr size_t FA_SMEM = (size_t)Q_BYTES + K_STAGES * K_BYTES + V_BYTES + P_BYTES + 256 + 1024;
+constexpr size_t FA_SMEM = (size_t)Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + 256 + 1024;
 
 }  // namespace
 
