@@ -367,8 +367,16 @@ def prefill_2048(model, cfg, world, torch, dist, T: int = 2048):
     attn = 2.0 * T * (T + 1) * cfg.dim * cfg.n_layers                                 # causal pairs only: 4 hd flops each
     peak, src = tensor_peak()
     tf = (linear + attn) / sec / 1e12
+    out_sustained = {}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):      # the rate a seconds-long cuBLAS loop holds under the power cap, for context
+        with open(path) as f:
+            sustained = json.load(f).get("bf16_tflops_sustained")
+        if sustained:
+            out_sustained = {"frac_of_sustained_tensor_peak": tf / world / float(sustained)}
     return {"tokens": T, "ms": sec * 1e3, "tokens_per_s": T / sec, "algorithmic_tflop": (linear + attn) / 1e12,
             "tflops": tf, "tflops_per_gpu": tf / world, "frac_of_tensor_peak": tf / world / peak, "peak_source": src,
+            **out_sustained,
             "note": "algorithmic flops: all linear layers + causal attention (T (T+1) / 2 query-key pairs per head); "
                     "wall clock through tl_llama2_forward including the host round trip"}
 
