@@ -75,13 +75,17 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
         return TL_OK;
     }
     if (M > 8 && K % 8 == 0) {
-        int kind = 0, bn = 0;
-        hgemm_plan((int)M, (int)N, 1, sm_count, &kind, &bn);
+        int kind = 0, bn = 0, sk_per = 0;
+        hgemm_plan((int)M, (int)N, (int)K, 1, sm_count, &kind, &bn, &sk_per);
         *kernel = kind == 2 ? TL_PLAN_HGEMM_PAIR512 : (kind == 1 ? TL_PLAN_HGEMM_PAIR : TL_PLAN_HGEMM);
         *tile_n = bn; *cluster = kind >= 1 ? 2 : 0;
         const long long tile_m = kind == 2 ? 512 : (kind == 1 ? 256 : 128);
         const long long tiles = (long long)((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
         *grid = (int)std::min<long long>(tiles * (kind >= 1 ? 2 : 1), kind >= 1 ? (sm_count / 2) * 2 : sm_count);
+        if (sk_per > 0) {    // stream-K ranges of sk_per k-blocks per CTA pair
+            *k_blocks_per_cta = sk_per;
+            *grid = 2 * (int)((tiles * (long long)((K + 63) / 64) + sk_per - 1) / sk_per);
+        }
         return TL_OK;
     }
     *kernel = M <= 8 && K % 8 == 0 ? TL_PLAN_GEMV_SMALL : TL_PLAN_REFERENCE_ORDER;

@@ -24,6 +24,8 @@
 // leaves its loop, TMEM is freed and TL_ERR_TIMEOUT is recorded in the device status word.
 #include <cuda.h>
 
+#include <unordered_map>
+
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -56,6 +58,11 @@ struct GemmArgs {
     __half* kc; __half* vc; long long ld_kv;
     const __half* cos_t; const __half* sin_t;
     int head_dim;
+    // CTA-pair kernel, stream-K mode (sk_per > 0): the flattened (tile, k-block) space is cut into ranges
+    // of sk_per k-blocks, one per pair; partial tiles go through sk_ws, arrivals are counted in sk_counters
+    int sk_per;
+    float* sk_ws;
+    unsigned int* sk_counters;
 };
 
 // 32 consecutive columns of one output row: fp32 accumulators -> fp16 -> 64 bytes
@@ -307,6 +314,57 @@ template <int MSUB> struct PairCfg {
     static constexpr int THREADS = GEMM_THREADS + (MSUB - 1) * 128;     // four epilogue warps per sub-tile
 };
 
+// The work of one pair as a list of segments (tile, k-blocks [kb0, kb1)). Whole-tile mode: tiles pair,
+// pair + n_pairs, ... each with all its k-blocks. Stream-K mode: the contiguous range
+// [pair * per, (pair + 1) * per) of the flattened (tile, k-block) space, so a pair may start in the
+// middle of one tile and end in the middle of another. The partial pieces come FIRST (the one at the
+// start of the range, then the one at its end), the whole tiles after them: every tile's parts are
+// then finished early in the launch and the last arriver adds them up while its whole tiles run,
+// instead of at the very end. `first` marks the piece at the start of the range (workspace slot 0).
+struct PairSegments {
+    int mode_per, nkb, n_pairs, total_tiles;
+    int tile_next;                 // whole-tile mode cursor; stream-K: next whole tile
+    int stage;                     // stream-K: 0 start piece, 1 end piece, 2 whole tiles
+    int t_first, kb_first0, t_last, kb_last1, w_end;
+    bool empty;
+    __device__ PairSegments(int per, int nkb_, int pair, int n_pairs_, int total_tiles_)
+        : mode_per(per), nkb(nkb_), n_pairs(n_pairs_), total_tiles(total_tiles_), tile_next(pair), stage(0) {
+        if (per > 0) {
+            const long long total = (long long)total_tiles_ * nkb_;
+            const long long begin = min(total, (long long)pair * per), end = min(total, begin + per);
+            empty = begin >= end;
+            if (!empty) {
+                t_first = (int)(begin / nkb_); kb_first0 = (int)(begin - (long long)t_first * nkb_);
+                t_last = (int)((end - 1) / nkb_); kb_last1 = (int)(end - (long long)t_last * nkb_);
+                // whole tiles: t_first if it starts at k-block 0 (and is not cut at the end), ... , t_last if it ends at nkb
+                tile_next = (kb_first0 == 0 && (t_last > t_first || kb_last1 == nkb_)) ? t_first : t_first + 1;
+                w_end = (kb_last1 == nkb_) ? t_last + 1 : t_last;
+            }
+        }
+    }
+    __device__ bool next(int& tile, int& kb0, int& kb1, bool& first) {
+        if (mode_per > 0) {
+            if (empty) return false;
+            if (stage == 0) {      // the piece at the start of the range, if it is not a whole tile
+                stage = 1;
+                const int e = t_last == t_first ? kb_last1 : nkb;
+                if (kb_first0 > 0 || e < nkb) { tile = t_first; kb0 = kb_first0; kb1 = e; first = true; return true; }
+            }
+            if (stage == 1) {      // the piece at the end of the range, if it is a different, cut tile
+                stage = 2;
+                if (t_last > t_first && kb_last1 < nkb) { tile = t_last; kb0 = 0; kb1 = kb_last1; first = false; return true; }
+            }
+            if (tile_next >= w_end) return false;
+            tile = tile_next++; kb0 = 0; kb1 = nkb; first = false;
+            return true;
+        }
+        if (tile_next >= total_tiles) return false;
+        tile = tile_next; kb0 = 0; kb1 = nkb; first = false;
+        tile_next += n_pairs;
+        return true;
+    }
+};
+
 template <int EPI, int MSUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<MSUB>::THREADS, 1)
 k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -314,6 +372,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     constexpr int BN = PAIR_BN, STAGES = PairCfg<MSUB>::STAGES, STAGE_BYTES = PairCfg<MSUB>::STAGE_BYTES;
     constexpr uint32_t TMEM_COLS = 2 * BN;      // MSUB 1: two buffers of one accumulator; MSUB 2: one buffer of two
     constexpr int OUT_COLS = EPI == GEPI_SWIGLU ? BN / 2 : BN;
+    constexpr int EPI_THREADS = 128 * MSUB;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -321,6 +380,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();                              // 0: leader
@@ -357,14 +417,16 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         if (EPI == GEPI_QKV_ROPE) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB3) : "memory");
         int it = 0;
         bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        PairSegments segs(p.sk_per, nkb, pair, n_pairs, total_tiles);
+        int tile, kb0, kb1; bool first;
+        while (ok && segs.next(tile, kb0, kb1, first)) {
             const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
             const int mt = idx % mt_count, nt = idx / mt_count;
             const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
             const CUtensorMap* mb = EPI == GEPI_SWIGLU ? (rank == 0 ? &tmB : &tmB2)
                                                        : (which == 0 ? &tmB : (which == 1 ? &tmB2 : &tmB3));
             const int brow = EPI == GEPI_SWIGLU ? ntl * OUT_COLS : ntl * BN + (int)rank * (BN / 2);
-            for (int kb = 0; kb < nkb; kb++, it++) {
+            for (int kb = kb0; kb < kb1; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
                 if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
                 const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + MSUB * A_BYTES;
@@ -388,13 +450,15 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         constexpr uint32_t idesc = make_idesc_pair(BN);
         int it = 0, tcount = 0;
         bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tcount++) {
+        PairSegments segs(p.sk_per, nkb, pair, n_pairs, total_tiles);
+        int tile, kb0, kb1; bool first;
+        for (; ok && segs.next(tile, kb0, kb1, first); tcount++) {
             // MSUB 1: accumulator buffers alternate; MSUB 2: both accumulators form the single buffer 0
             const int buf = MSUB == 1 ? (tcount & 1) : 0, use = MSUB == 1 ? (tcount >> 1) : tcount;
             if (use > 0 && !(ok = mbar_wait(tempty0 + 8 * buf, (use - 1) & 1, abort_flag))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-            for (int kb = 0; kb < nkb; kb++, it++) {
+            for (int kb = kb0; kb < kb1; kb++, it++) {
                 const int s = it % STAGES, use_s = it / STAGES;
                 if (!(ok = mbar_wait(full0 + 8 * s, use_s & 1, abort_flag))) break;
                 tc_fence_after();
@@ -404,7 +468,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
                     for (int ms = 0; ms < MSUB; ms++)
                         umma_pair(d_tmem + (uint32_t)(ms * BN), make_desc(sa + ms * A_BYTES + k * 32), make_desc(sb + k * 32), idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
                 umma_commit_pair(empty0 + 8 * s);                   // my stage is reusable
                 umma_commit_pair(map_to_cta(empty0 + 8 * s, 1));    // and the peer's
             }
@@ -414,62 +478,164 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
         }
     } else if (warp >= 4) {
-        // ---------------- epilogue (both CTAs, own 128 rows) ----------------------------------------
+        // ---------------- epilogue (both CTAs, own 128 rows per sub-tile) ----------------------------
         const int q = warp & 3;
+        const int ms = (warp - 4) >> 2;            // warps 4..7 drain sub-tile 0, warps 8..11 sub-tile 1
+        const int rl = q * 32 + lane;              // row inside the sub-tile
         int tcount = 0;
         bool ok = true;
         const uint32_t leader_tempty0 = map_to_cta(tempty0, 0);
-        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tcount++) {
+        PairSegments segs(p.sk_per, nkb, pair, n_pairs, total_tiles);
+        int tile, kb0, kb1; bool first;
+        for (; ok && segs.next(tile, kb0, kb1, first); tcount++) {
             const int b = tile / tiles_per_batch, idx = tile - b * tiles_per_batch;
             const int mt = idx % mt_count, nt = idx / mt_count;
             const int which = EPI == GEPI_QKV_ROPE ? nt / nt_each : 0, ntl = nt - which * nt_each;
             const int buf = MSUB == 1 ? (tcount & 1) : 0, use = MSUB == 1 ? (tcount >> 1) : tcount;
             ok = mbar_wait(tfull0 + 8 * buf, use & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
+            if (p.sk_per > 0) {
+                // one decision for all epilogue warps of the CTA (they meet at named barrier 1 below); every
+                // epilogue thread reaches this reducing barrier because the wait above is bounded
+                uint32_t all_ok;
+                asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.and.pred p, 1, %2, q;\n selp.u32 %0, 1, 0, p;\n}\n"
+                             : "=r"(all_ok) : "r"((uint32_t)ok), "n"(EPI_THREADS) : "memory");
+                ok = all_ok != 0;
+            } else {
+                ok = __all_sync(0xffffffffu, ok);
+            }
             if (!ok) break;
             tc_fence_after();
-            {
-            const int ms = (warp - 4) >> 2;            // warps 4..7 drain sub-tile 0, warps 8..11 sub-tile 1
-            const int row = ((mt * 2 + (int)rank) * MSUB + ms) * BM + q * 32 + lane;
+            const int row = ((mt * 2 + (int)rank) * MSUB + ms) * BM + rl;
             const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf + ms) * BN);
             __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
-            if (EPI == GEPI_SWIGLU) {
-#pragma unroll 1
-                for (int c = 0; c < OUT_COLS; c += 32) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(tbase + (uint32_t)c, g);
-                    tmem_ld32(tbase + (uint32_t)(OUT_COLS + c), u);
-                    tmem_ld_wait();
-                    const int col0 = ntl * OUT_COLS + c;
-                    if (row < p.M && col0 < p.N) store32_swiglu(crow + col0, g, u);
+            // 32 finished accumulator columns of this thread's row -> the fused epilogue
+            auto emit = [&](int c, const uint32_t* r) {
+                const int col0 = ntl * BN + c;
+                if (row >= p.M || col0 >= p.N) return;
+                if (EPI == GEPI_RESIDUAL) {
+                    store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
+                } else if (EPI == GEPI_QKV_ROPE) {
+                    if (which == 2) {
+                        store32(p.vc + (long long)row * p.ld_kv + col0, r);
+                    } else {
+                        const int half_dim = p.head_dim >> 1, d2 = (col0 % p.head_dim) >> 1;
+                        __half* dst = which == 0 ? crow + col0 : p.kc + (long long)row * p.ld_kv + col0;
+                        store32_rope(dst, p.cos_t + (long long)row * half_dim + d2, p.sin_t + (long long)row * half_dim + d2, r);
+                    }
+                } else {
+                    store32(crow + col0, r);
                 }
-            } else {
+            };
+            auto emit_swiglu = [&](int c, const uint32_t* g, const uint32_t* u) {
+                const int col0 = ntl * OUT_COLS + c;
+                if (row < p.M && col0 < p.N) store32_swiglu(crow + col0, g, u);
+            };
+            if (kb0 == 0 && kb1 == nkb) {
+                if (EPI == GEPI_SWIGLU) {
+#pragma unroll 1
+                    for (int c = 0; c < OUT_COLS; c += 32) {
+                        uint32_t g[32], u[32];
+                        tmem_ld32(tbase + (uint32_t)c, g);
+                        tmem_ld32(tbase + (uint32_t)(OUT_COLS + c), u);
+                        tmem_ld_wait();
+                        emit_swiglu(c, g, u);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tbase + (uint32_t)c, r);
+                        tmem_ld_wait();
+                        emit(c, r);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * buf);
+                continue;
+            }
+            // ---- partial tile: fp32 partial to the workspace, last arriver of the tile half adds them up ----
+            // slot layout [pair][first segment of the range ? 0 : 1][rank][sub-tile][column / 4][row][4 floats]:
+            // a warp writes 512 contiguous bytes per instruction
+            constexpr long long PART = (long long)BM * BN;      // floats of one sub-tile partial
+            auto part_base = [&](int pr, int slot) { return p.sk_ws + ((((long long)pr * 2 + slot) * 2 + (long long)rank) * MSUB + ms) * PART; };
+            {
+                float4* dst = reinterpret_cast<float4*>(part_base(pair, first ? 0 : 1)) + rl;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
                     uint32_t r[32];
                     tmem_ld32(tbase + (uint32_t)c, r);
                     tmem_ld_wait();
-                    const int col0 = ntl * BN + c;
-                    if (row >= p.M || col0 >= p.N) continue;
-                    if (EPI == GEPI_RESIDUAL) {
-                        store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
-                    } else if (EPI == GEPI_QKV_ROPE) {
-                        if (which == 2) {
-                            store32(p.vc + (long long)row * p.ld_kv + col0, r);
-                        } else {
-                            const int half_dim = p.head_dim >> 1, d2 = (col0 % p.head_dim) >> 1;
-                            __half* dst = which == 0 ? crow + col0 : p.kc + (long long)row * p.ld_kv + col0;
-                            store32_rope(dst, p.cos_t + (long long)row * half_dim + d2, p.sin_t + (long long)row * half_dim + d2, r);
-                        }
-                    } else {
-                        store32(crow + col0, r);
-                    }
+#pragma unroll
+                    for (int v = 0; v < 8; v++)
+                        dst[(long long)(c / 4 + v) * BM] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                                        __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
                 }
-            }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * buf);
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            const int first_pair = (int)(((long long)tile * nkb) / p.sk_per);
+            const int last_pair = (int)((((long long)tile + 1) * nkb - 1) / p.sk_per);
+            if (warp == 4 && lane == 0) {
+                unsigned int* cnt = p.sk_counters + (long long)tile * 2 + rank;
+                const unsigned int old = atomicAdd(cnt, 1u);
+                const int is_last = old == (unsigned)(last_pair - first_pair) ? 1 : 0;
+                if (is_last) *cnt = 0;            // ready for the next launch
+                *last_flag = is_last;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            const bool is_last = *last_flag != 0;
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");   // flag read by all before the next segment rewrites it
+            if (!is_last) continue;
+            __threadfence();
+            // parts in k order (= pair order), each pair's slot by whether the tile holds the start of its range
+            auto slot_of = [&](int pr) { return ((long long)pr * p.sk_per) / nkb == tile ? 0 : 1; };
+            auto sum32 = [&](int c, uint32_t* r) {
+                float acc[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) acc[i] = 0.f;
+                // two parts per trip: 16 independent 16-byte loads in flight per thread; the order of the
+                // additions is the part order whatever the trip structure
+                for (int pr = first_pair; pr <= last_pair; pr += 2) {
+                    const bool two = pr + 1 <= last_pair;
+                    const float4* src0 = reinterpret_cast<const float4*>(part_base(pr, slot_of(pr))) + rl;
+                    const float4* src1 = two ? reinterpret_cast<const float4*>(part_base(pr + 1, slot_of(pr + 1))) + rl : src0;
+                    float4 v0[8], v1[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v0[j] = __ldcg(src0 + (long long)(c / 4 + j) * BM);
+                    if (two) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) v1[j] = __ldcg(src1 + (long long)(c / 4 + j) * BM);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; j++) { acc[4 * j] += v0[j].x; acc[4 * j + 1] += v0[j].y; acc[4 * j + 2] += v0[j].z; acc[4 * j + 3] += v0[j].w; }
+                    if (two) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) { acc[4 * j] += v1[j].x; acc[4 * j + 1] += v1[j].y; acc[4 * j + 2] += v1[j].z; acc[4 * j + 3] += v1[j].w; }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = __float_as_uint(acc[i]);
+            };
+            if (EPI == GEPI_SWIGLU) {
+#pragma unroll 1
+                for (int c = 0; c < OUT_COLS; c += 32) {
+                    uint32_t g[32], u[32];
+                    sum32(c, g);
+                    sum32(OUT_COLS + c, u);
+                    emit_swiglu(c, g, u);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t r[32];
+                    sum32(c, r);
+                    emit(c, r);
+                }
+            }
         }
     }
     // ---------------- teardown: nobody frees TMEM or leaves while the pair may still use it -----------
@@ -553,14 +719,54 @@ int launch_pair_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensor
     const int grid = 2 * std::max(1, std::min(pair_tiles, sm_count() / 2));
     return launch_pdl(k_hgemm_pair<EPI, MSUB>, dim3(grid), dim3(PairCfg<MSUB>::THREADS), PairCfg<MSUB>::SMEM, st, true, ma, mb, mb2, mb3, a);
 }
-// `n_tiles` = column tiles (per batch); rows come in 256- or 512-row tiles by what fills the pairs better
-int pair_msub(int M, long long n_tiles, int epi);
+// estimated plan of the CTA-pair kernel: tile height (msub x 256 rows), whole tiles (sk_per = 0) or stream-K
+// ranges of sk_per k-blocks per pair, and the estimated cycles of the launch
+struct PairPlan { int msub, sk_per; long long cost; };
+PairPlan pair_plan(int M, long long n_col_tiles, int nkb, int epi);
+
+// workspace of the stream-K mode per (device, stream): partial tiles of every pair (two per pair, fp32)
+// and the arrival counters (zero between launches: the last arriver of a tile resets its counter)
+struct SkWorkspace { float* ws; unsigned int* counters; };
+constexpr int SK_MAX_PAIRS = 128, SK_MAX_TILES = 1 << 16;
+std::mutex g_sk_mutex;
+std::unordered_map<unsigned long long, SkWorkspace> g_sk_ws;
+int sk_workspace_for(cudaStream_t st, SkWorkspace* out) {
+    int dev = 0;
+    TL_CUDA(cudaGetDevice(&dev));
+    const unsigned long long key = (unsigned long long)reinterpret_cast<uintptr_t>(st) * 64ull + (unsigned long long)dev;
+    std::lock_guard<std::mutex> lock(g_sk_mutex);
+    auto it = g_sk_ws.find(key);
+    if (it == g_sk_ws.end()) {
+        SkWorkspace w;
+        // [pair][2 slots][2 ranks][up to 2 sub-tiles][128 x 256] floats
+        TL_CUDA(cudaMalloc(&w.ws, (size_t)SK_MAX_PAIRS * 2 * 2 * 2 * BM * PAIR_BN * sizeof(float)));
+        TL_CUDA(cudaMalloc(&w.counters, (size_t)2 * SK_MAX_TILES * sizeof(unsigned int)));
+        TL_CUDA(cudaMemset(w.counters, 0, (size_t)2 * SK_MAX_TILES * sizeof(unsigned int)));
+        TL_CUDA(cudaDeviceSynchronize());
+        it = g_sk_ws.emplace(key, w).first;
+    }
+    *out = it->second;
+    return TL_OK;
+}
+
+// `n_col_tiles` = column tiles per batch
 template <int EPI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
-                const GemmArgs& a, int n_col_tiles, cudaStream_t st) {
+                const GemmArgs& a_in, int n_col_tiles, cudaStream_t st) {
+    GemmArgs a = a_in;
     const long long nt = (long long)n_col_tiles * a.batch;
-    if (pair_msub(a.M, nt, EPI) == 2) return launch_pair_cfg<EPI, 2>(ma, mb, mb2, mb3, a, (int)(((a.M + 511) / 512) * nt), st);
-    return launch_pair_cfg<EPI, 1>(ma, mb, mb2, mb3, a, (int)(((a.M + 255) / 256) * nt), st);
+    const int nkb = (a.K + BK - 1) / BK;
+    const PairPlan pl = pair_plan(a.M, nt, nkb, EPI);
+    const long long tiles = (long long)((a.M + 256 * pl.msub - 1) / (256 * pl.msub)) * nt;
+    int pair_ctas = (int)std::min<long long>(tiles, sm_count() / 2);
+    if (pl.sk_per > 0) {
+        SkWorkspace w;
+        TL_PROPAGATE(sk_workspace_for(st, &w));
+        a.sk_per = pl.sk_per; a.sk_ws = w.ws; a.sk_counters = w.counters;
+        pair_ctas = (int)((tiles * nkb + pl.sk_per - 1) / pl.sk_per);
+    }
+    if (pl.msub == 2) return launch_pair_cfg<EPI, 2>(ma, mb, mb2, mb3, a, pair_ctas, st);
+    return launch_pair_cfg<EPI, 1>(ma, mb, mb2, mb3, a, pair_ctas, st);
 }
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
@@ -568,43 +774,71 @@ inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) =
 int g_plan_sms = 0;   // when non-zero, the planning functions use it instead of the device's SM count
 int plan_sms() { return g_plan_sms > 0 ? g_plan_sms : sm_count(); }
 
-// Estimated cost (cycles per k-block x rounds of tiles over the sm/2 pairs) of the CTA-pair kernel in its
-// two shapes. Per k-block a 256 x 256 pair tile measures ~590 cycles (512 of MMA stretched by the
-// shared-memory fill running at its limit beside them), a 512 x 256 tile ~1090 (1024 of MMA, the fill
-// no longer the limit).
-// TL_HGEMM_PAIR=always|always512|never overrides the estimate (tests force every kernel onto small shapes)
-int pair_forced() {
-    static const int forced = [] {
-        const char* e = getenv("TL_HGEMM_PAIR");
-        return !e ? 0 : (!strcmp(e, "always") ? 1 : (!strcmp(e, "never") ? 2 : (!strcmp(e, "always512") ? 3 : 0)));
-    }();
-    return forced;
-}
-long long pair_cost_msub(int M, long long n_tiles, int msub) {
-    const long long tiles = (long long)((M + 256 * msub - 1) / (256 * msub)) * n_tiles;
-    const long long pairs = std::max(1, plan_sms() / 2);
-    return ((tiles + pairs - 1) / pairs) * (msub == 1 ? 590 : 1090);
-}
+// Estimated cycles of the CTA-pair kernel. Per k-block a 256 x 256 pair tile measures ~590 cycles (512 of
+// MMA stretched by the shared-memory fill running at its limit beside them), a 512 x 256 tile ~1090
+// (1024 of MMA, the fill no longer the limit). Whole tiles cost rounds-of-tiles-over-the-pairs x k-blocks
+// x that; stream-K ranges cost ceil(tiles x k-blocks / pairs) x that plus the exchange of the partial
+// tiles (~4000 cycles per part and 256 rows of tile height: a partial goes out to L2 and the last
+// arriver reads every part back).
 // The 512-row tile has no second accumulator buffer, so its epilogue is not hidden behind the next
 // tile's MMAs. The rotary epilogue (per-row factor loads, three destinations) is long enough that the
 // 256-row tile with its hidden epilogue wins for the fused QKV projection (2048 tokens of the 7B model:
 // 1.7 ms of 24.5 over 32 layers); the other epilogues gain from the larger tile.
-int pair_msub(int M, long long n_tiles, int epi) {
-    if (pair_forced() == 1) return 1;
-    if (pair_forced() == 3) return 2;
-    if (epi == GEPI_QKV_ROPE) return 1;
-    return pair_cost_msub(M, n_tiles, 2) < pair_cost_msub(M, n_tiles, 1) ? 2 : 1;
+// TL_HGEMM_PAIR=always|always512|streamk|streamk512|never overrides the estimate (tests force every
+// kernel onto small shapes)
+int pair_forced() {
+    static const int forced = [] {
+        const char* e = getenv("TL_HGEMM_PAIR");
+        if (!e) return 0;
+        if (!strcmp(e, "always")) return 1;
+        if (!strcmp(e, "never")) return 2;
+        if (!strcmp(e, "always512")) return 3;
+        if (!strcmp(e, "streamk")) return 4;
+        if (!strcmp(e, "streamk512")) return 5;
+        return 0;
+    }();
+    return forced;
 }
-long long pair_cost(int M, int n_tiles_256, int batch, int epi = GEPI_STORE) {
-    if (pair_forced() == 1 || pair_forced() == 3) return -1;
-    if (pair_forced() == 2) return (1ll << 60);
-    const long long nt = (long long)n_tiles_256 * batch;
-    return pair_cost_msub(M, nt, pair_msub(M, nt, epi));
+PairPlan pair_plan(int M, long long n_col_tiles, int nkb, int epi) {
+    const long long pairs = std::max(1, plan_sms() / 2);
+    const int forced = pair_forced();
+    PairPlan best{1, 0, -1};
+    for (int msub = 1; msub <= 2; msub++) {
+        if (forced == 1 || forced == 4) { if (msub != 1) continue; }
+        else if (forced == 3 || forced == 5) { if (msub != 2) continue; }
+        else if (epi == GEPI_QKV_ROPE && msub == 2) continue;
+        const long long tiles = (long long)((M + 256 * msub - 1) / (256 * msub)) * n_col_tiles;
+        const long long c = msub == 1 ? 590 : 1090;
+        if (forced != 4 && forced != 5) {
+            const long long cost = ((tiles + pairs - 1) / pairs) * nkb * c;
+            if (best.cost < 0 || cost < best.cost) best = PairPlan{msub, 0, cost};
+        }
+        if (tiles <= SK_MAX_TILES && pairs <= SK_MAX_PAIRS && forced != 1 && forced != 3) {
+            const long long per = (tiles * nkb + pairs - 1) / pairs;
+            const long long parts = (nkb + per - 1) / per + 1;
+            const long long cost = per * c + 4000 * msub * (parts + 1);
+            // Stream-K only where whole tiles leave most pairs idle for a long K loop (or where a test asks
+            // for it). On the Llama2-7B shapes it measured slower than whole tiles: the fp32 partial tiles
+            // (256 to 512 KB each) add ~150 MB of traffic to a 50 MB problem at M = 2048, 4096 x 4096
+            // (70 us against 52 us), and M = 512 came out between -10 % and +8 %.
+            const bool regime = 2 * tiles <= pairs && nkb >= 256 && best.cost >= 0 && cost * 100 < best.cost * 70;
+            if (forced == 4 || forced == 5 || regime) best = PairPlan{msub, (int)per, cost};
+        }
+    }
+    return best;
 }
-long long single_cost(int mt, int N, int batch, int bn) {
+// estimated cycles of the pair kernel for the choice between it and the single-CTA kernel
+long long pair_cost(int M, int n_tiles_256, int batch, int K, int epi = GEPI_STORE) {
+    const int forced = pair_forced();
+    if (forced == 2) return (1ll << 60);
+    if (forced != 0) return -1;
+    return pair_plan(M, (long long)n_tiles_256 * batch, (K + BK - 1) / BK, epi).cost;
+}
+// estimated cycles of the single-CTA kernel
+long long single_cost(int mt, int N, int batch, int bn, int K) {
     const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
     const long long waves = (tiles + plan_sms() - 1) / plan_sms();
-    return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
+    return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64) * ((K + BK - 1) / BK);
 }
 
 // N-tile width with the smallest estimated time: waves of tiles over the SMs times the cost of one
@@ -627,16 +861,19 @@ int pick_bn(int mt, int N, int batch) {
 
 }  // namespace
 
-void hgemm_plan(int M, int N, int batch, int sms, int* kind, int* bn) {
+void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int* sk_per) {
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     g_plan_sms = sms;
     const int mt = (M + BM - 1) / BM;
     *bn = pick_bn(mt, N, batch);
-    *kind = (M > BM && N % 32 == 0 && pair_cost(M, (N + 255) / 256, batch) < single_cost(mt, N, batch, *bn)) ? 1 : 0;
+    *sk_per = 0;
+    *kind = (M > BM && N % 32 == 0 && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, *bn, K)) ? 1 : 0;
     if (*kind == 1) {                     // 1: 256-row pair tiles, 2: 512-row pair tiles
+        const PairPlan pl = pair_plan(M, (long long)((N + 255) / 256) * batch, (K + BK - 1) / BK, GEPI_STORE);
         *bn = 256;
-        *kind = pair_msub(M, (long long)((N + 255) / 256) * batch, GEPI_STORE);
+        *kind = pl.msub;
+        *sk_per = pl.sk_per;
     }
     g_plan_sms = 0;
 }
@@ -661,7 +898,7 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
     const bool vec_c = ldc % 8 == 0 && sC % 8 == 0 && al16(C) && N % 32 == 0;   // the pair epilogue stores 64-byte chunks
-    if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch) < single_cost(mt, N, batch, bn)) {
+    if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, 128));
         return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, (N + 255) / 256, st);
     }
@@ -688,7 +925,7 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
     a.R = R; a.ldr = ldr;
-    if (M > BM && pair_cost(M, (N + 255) / 256, 1) < single_cost(mt, N, 1, bn)) {
+    if (M > BM && pair_cost(M, (N + 255) / 256, 1, K, GEPI_RESIDUAL) < single_cost(mt, N, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
         return launch_pair<GEPI_RESIDUAL>(ma, mb, mb, mb, a, (N + 255) / 256, st);
     }
@@ -708,7 +945,7 @@ int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __h
     TL_PROPAGATE(make_tensor_map_f16(&m3, W3, N, K, ldb, 0, 1, 128));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
-    if (M > BM && pair_cost(M, nt, 1) < single_cost(mt, N, 1, 128) * 768 / 512)   // single: 128 output columns per 256-wide tile
+    if (M > BM && pair_cost(M, nt, 1, K, GEPI_SWIGLU) < single_cost(mt, N, 1, 128, K) * 768 / 512)   // single: 128 output columns per 256-wide tile
         return launch_pair<GEPI_SWIGLU>(ma, m1, m3, m3, a, nt, st);
     return launch_k<256, GEPI_SWIGLU>(ma, m1, m3, m3, a, mt * nt, st);
 }
@@ -729,7 +966,7 @@ int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, c
     while (bn > 64 && (n_each % bn != 0 || (long long)mt * 3 * (n_each / bn) < sm_count())) bn >>= 1;
     CUtensorMap ma, mq, mk, mv;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
-    if (M > BM && n_each % 256 == 0 && pair_cost(M, 3 * (n_each / 256), 1, GEPI_QKV_ROPE) < single_cost(mt, 3 * n_each, 1, bn)) {
+    if (M > BM && n_each % 256 == 0 && pair_cost(M, 3 * (n_each / 256), 1, K, GEPI_QKV_ROPE) < single_cost(mt, 3 * n_each, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, 128));
         TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, 128));
         TL_PROPAGATE(make_tensor_map_f16(&mv, Wv, n_each, K, ldb, 0, 1, 128));

@@ -157,7 +157,7 @@ int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int
                   long long ldc, cudaStream_t st);
 
 // which tile the plain HGEMM would use on `sms` SMs: kind 0 = single-CTA tile of width *bn, 1 = CTA-pair 256x256
-void hgemm_plan(int M, int N, int batch, int sms, int* kind, int* bn);
+void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int* sk_per);
 
 // fused epilogues of the prefill HGEMM (N % 32 == 0, 16-byte aligned rows)
 bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,

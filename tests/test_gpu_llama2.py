@@ -216,6 +216,42 @@ def test_fast_fused_prefill_matches_oracle_at_head_dim_128(tl, oracle, T, tail):
     m.close()
 
 
+_FUSED_CHILD = r"""
+import sys, numpy as np
+sys.path.insert(0, sys.argv[1])
+import tensorlib_b200 as tl
+from tensorlib_b200 import synth
+tl.init(0)
+MID = synth.LlamaConfig(dim=512, hidden_dim=1408, n_layers=2, n_heads=4, vocab_size=1000, seq_len=384)
+m = tl.Llama2(MID, numerics=tl.FAST)
+m.load_payload(synth.llama2c_payload(MID, 777), shared_classifier=True)
+tokens = synth.token_ids(777, 5, 300, MID.vocab_size)
+out = [m.forward(tokens, 0, all_logits=True) for _ in range(2)]     # twice: counters of the stream-K mode reset
+assert tl.device_status() == 0
+assert np.array_equal(out[0], out[1])
+np.save(sys.argv[2], out[1])
+"""
+
+
+@pytest.mark.parametrize("mode", ["never", "always", "always512", "streamk", "streamk512"])
+def test_fused_prefill_epilogues_under_every_hgemm_kernel(tl, oracle, tmp_path, mode):
+    """The fused matmul epilogues of the prefill (RoPE + KV write, residual, SiLU*up) through the
+    single-CTA kernel, the CTA-pair kernel with 256- and 512-row tiles, and both with stream-K ranges
+    (partial tiles summed by the last arriver): all against the oracle's logits."""
+    import subprocess, sys as _sys
+    script, out = tmp_path / "child.py", tmp_path / "logits.npy"
+    script.write_text(_FUSED_CHILD)
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+    r = subprocess.run([_sys.executable, str(script), root, str(out)], capture_output=True, text=True,
+                       env=dict(os.environ, TL_HGEMM_PAIR=mode), timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    got = np.load(out).astype(np.float32)
+    tokens = synth.token_ids(777, 5, 300, MID.vocab_size)
+    want = oracle.llama2(MID, synth.llama2c_payload(MID, 777)).forward(tokens, 0, 1).astype(np.float32)
+    err = np.abs(got - want).max()
+    assert err <= 2e-2, f"{mode}: max abs logit error {err}"
+
+
 def test_multi_turn_generation_continues_over_the_kv_cache(tl, golden_tiny, tiny_payload):
     """Two turns (llama2.cpp keeps total_len across generate calls) equal one forward over the
     concatenated token stream, bit for bit in reference-order numerics."""
