@@ -106,7 +106,8 @@ TL_API int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C,
 /* Host-only introspection (no device needed): the kernel tl_matmul2d_f16 selects in fast numerics for
  * 16-byte aligned operands on a device with sm_count SMs, and how the work is cut: CTAs launched,
  * tile width along N (the padded batch for the skinny kernels), k-blocks of 64 per CTA (skinny
- * kernels), CTAs per cluster (0 = no clusters). */
+ * kernels) or per CTA pair (the pair kernel's stream-K mode; 0 = whole tiles), CTAs per cluster
+ * (0 = no clusters). */
 enum { TL_PLAN_REFERENCE_ORDER = 0, TL_PLAN_GEMV_RING = 1, TL_PLAN_GEMV_SMALL = 2, TL_PLAN_SKINNY_STREAMK = 3,
        TL_PLAN_SKINNY_CLUSTER = 4, TL_PLAN_HGEMM = 5, TL_PLAN_HGEMM_PAIR = 6 /* 256-row tiles per CTA pair */,
        TL_PLAN_HGEMM_PAIR512 = 7 /* 512-row tiles per CTA pair */ };

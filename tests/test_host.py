@@ -131,6 +131,11 @@ def test_matmul_plan_picks_the_kernel_each_regime_is_built_for():
                                (4096, 11008, "hgemm_pair512", 128), (32000, 4096, "hgemm_pair512", 148)):
         p = tl.matmul_plan(2048, N, K)
         assert p["kernel"] == kernel and p["grid"] == grid and p["cluster"] == 2, (N, K, p)
+    # long K with few tiles: stream-K ranges over all CTA pairs instead of 4 whole tiles on 4 pairs
+    p = tl.matmul_plan(512, 512, 32768)
+    assert p == {"kernel": "hgemm_pair", "grid": 148, "tile_n": 256, "k_blocks_per_cta": 28, "cluster": 2}, p
+    assert 74 * p["k_blocks_per_cta"] >= 4 * 512 > 73 * p["k_blocks_per_cta"]    # the ranges cover every k-block, none empty
+    assert tl.matmul_plan(2048, 4096, 4096)["k_blocks_per_cta"] == 0             # the Llama shapes keep whole tiles
     assert tl.matmul_plan(3, 1000, 300)["kernel"] == "reference_order"          # K % 8 != 0: any-shape kernel
     with pytest.raises(tl.TLError):
         tl.matmul_plan(0, 8, 8)
