@@ -77,26 +77,37 @@ __device__ __forceinline__ void store32(__half* dst, const uint32_t* r) {
         *reinterpret_cast<uint4*>(dst + v * 8) = o;
     }
 }
-__device__ __forceinline__ void store32_residual(__half* dst, const __half* res, const uint32_t* r) {
+// The operands of the fused epilogues are loaded first and all together: the destination may alias
+// them as far as the compiler knows (the residual add runs in place), so loads placed between the
+// stores would each wait for a full L2 round trip.
+__device__ __forceinline__ void store32_residual_pre(__half* dst, const uint4* rr, const uint32_t* r) {
 #pragma unroll
     for (int v = 0; v < 4; v++) {
-        uint4 o, rr = *reinterpret_cast<const uint4*>(res + v * 8);
+        uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
-        const __half2* rh = reinterpret_cast<const __half2*>(&rr);
+        const __half2* rh = reinterpret_cast<const __half2*>(&rr[v]);
 #pragma unroll
         for (int j = 0; j < 4; j++)   // the matmul result is rounded to fp16 first, then added in fp16
             oh[j] = __hadd2(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1])), rh[j]);
         *reinterpret_cast<uint4*>(dst + v * 8) = o;
     }
 }
+__device__ __forceinline__ void load32_residual(uint4* rr, const __half* res) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) rr[v] = *reinterpret_cast<const uint4*>(res + v * 8);
+}
+__device__ __forceinline__ void store32_residual(__half* dst, const __half* res, const uint32_t* r) {
+    uint4 rr[4];
+    load32_residual(rr, res);
+    store32_residual_pre(dst, rr, r);
+}
 // interleaved-pair rotation (x0, x1) -> (x0 c - x1 s, x0 s + x1 c), every product and sum rounded
 // to fp16 like the reference's apply_rotary_emb (tensorLib/src/device/CPU.cpp:427-461)
-__device__ __forceinline__ void store32_rope(__half* dst, const __half* cosr, const __half* sinr, const uint32_t* r) {
+__device__ __forceinline__ void store32_rope_pre(__half* dst, const uint2* cc, const uint2* ss, const uint32_t* r) {
 #pragma unroll
     for (int v = 0; v < 4; v++) {
-        uint2 cc = *reinterpret_cast<const uint2*>(cosr + v * 4), ss = *reinterpret_cast<const uint2*>(sinr + v * 4);
-        const __half* ch = reinterpret_cast<const __half*>(&cc);
-        const __half* sh = reinterpret_cast<const __half*>(&ss);
+        const __half* ch = reinterpret_cast<const __half*>(&cc[v]);
+        const __half* sh = reinterpret_cast<const __half*>(&ss[v]);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -108,6 +119,18 @@ __device__ __forceinline__ void store32_rope(__half* dst, const __half* cosr, co
         }
         *reinterpret_cast<uint4*>(dst + v * 8) = o;
     }
+}
+__device__ __forceinline__ void load32_rope(uint2* cc, uint2* ss, const __half* cosr, const __half* sinr) {
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        cc[v] = *reinterpret_cast<const uint2*>(cosr + v * 4);
+        ss[v] = *reinterpret_cast<const uint2*>(sinr + v * 4);
+    }
+}
+__device__ __forceinline__ void store32_rope(__half* dst, const __half* cosr, const __half* sinr, const uint32_t* r) {
+    uint2 cc[4], ss[4];
+    load32_rope(cc, ss, cosr, sinr);
+    store32_rope_pre(dst, cc, ss, r);
 }
 // silu(gate) * up with the gate through float: g / (1 + exp(-g)), rounded to fp16, then an fp16 product
 __device__ __forceinline__ void store32_swiglu(__half* dst, const uint32_t* g, const uint32_t* u) {
@@ -540,6 +563,39 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         tmem_ld_wait();
                         emit_swiglu(c, g, u);
                     }
+                } else if (EPI == GEPI_RESIDUAL || (EPI == GEPI_QKV_ROPE && which < 2)) {
+                    // the epilogue's own operands (residual row / rotary factors) of chunk c + 1 are fetched
+                    // while chunk c is converted and stored
+                    uint4 pre[4];                  // RESIDUAL: 64 bytes of the residual row; ROPE: 4 x (cos, sin) as uint2 pairs
+                    const int half_dim = p.head_dim >> 1;
+                    auto prefetch = [&](int c) {
+                        const int col0 = ntl * BN + c;
+                        if (row >= p.M || col0 >= p.N) return;
+                        if (EPI == GEPI_RESIDUAL) {
+                            load32_residual(pre, p.R + (long long)row * p.ldr + col0);
+                        } else {
+                            const int d2 = (col0 % p.head_dim) >> 1;
+                            load32_rope(reinterpret_cast<uint2*>(pre), reinterpret_cast<uint2*>(pre) + 4,
+                                        p.cos_t + (long long)row * half_dim + d2, p.sin_t + (long long)row * half_dim + d2);
+                        }
+                    };
+                    prefetch(0);
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tbase + (uint32_t)c, r);
+                        uint4 cur[4] = {pre[0], pre[1], pre[2], pre[3]};
+                        if (c + 32 < BN) prefetch(c + 32);
+                        tmem_ld_wait();
+                        const int col0 = ntl * BN + c;
+                        if (row >= p.M || col0 >= p.N) continue;
+                        if (EPI == GEPI_RESIDUAL) {
+                            store32_residual_pre(crow + col0, cur, r);
+                        } else {
+                            __half* dst = which == 0 ? crow + col0 : p.kc + (long long)row * p.ld_kv + col0;
+                            store32_rope_pre(dst, reinterpret_cast<const uint2*>(cur), reinterpret_cast<const uint2*>(cur) + 4, r);
+                        }
+                    }
                 } else {
 #pragma unroll 1
                     for (int c = 0; c < BN; c += 32) {
@@ -597,10 +653,11 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 float acc[32];
 #pragma unroll
                 for (int i = 0; i < 32; i++) acc[i] = 0.f;
-                // two parts per trip: 16 independent 16-byte loads in flight per thread; the order of the
-                // additions is the part order whatever the trip structure
-                for (int pr = first_pair; pr <= last_pair; pr += 2) {
-                    const bool two = pr + 1 <= last_pair;
+                // two parts per trip (one for SWIGLU, which holds two result chunks at once): 16 independent
+                // 16-byte loads in flight per thread; the additions follow the part order either way
+                constexpr int TRIP = EPI == GEPI_SWIGLU ? 1 : 2;
+                for (int pr = first_pair; pr <= last_pair; pr += TRIP) {
+                    const bool two = TRIP == 2 && pr + 1 <= last_pair;
                     const float4* src0 = reinterpret_cast<const float4*>(part_base(pr, slot_of(pr))) + rl;
                     const float4* src1 = two ? reinterpret_cast<const float4*>(part_base(pr + 1, slot_of(pr + 1))) + rl : src0;
                     float4 v0[8], v1[8];
