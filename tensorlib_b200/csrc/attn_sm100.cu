@@ -87,7 +87,7 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(BAR(1), 1); mbar_init(BAR(2), 1); mbar_init(BAR(3), 1); mbar_init(BAR(4), 1);
         mbar_init(BAR(5), 1); mbar_init(BAR(6), 1); mbar_init(BAR(7), 1); mbar_init(BAR(8), 1);
         mbar_init(BAR(9), 1); mbar_init(BAR(10), 1);
-        mbar_init(BAR(11), 128); mbar_init(BAR(12), 128);   // every softmax thread arrives after storing its own P row
+        mbar_init(BAR(11), 4); mbar_init(BAR(12), 4);       // one arrival per softmax warp, after all its lanes stored their P rows
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -253,7 +253,8 @@ k_flash_prefill(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_st32(lane_addr + S_COL + (uint32_t)(b * BKV), pk);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(BAR(11 + b));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(11 + b));
         }
         if (ok) {
             ok = mbar_wait(BAR(7 + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, abort_flag);
