@@ -10,17 +10,23 @@ device, norms = 1, token ids seeded: synthetic data of the benchmark's shape.
 
 The JSON line:
   value      tokens/s with everything resident on the device: one CUDA-graph replay per token,
-             the sampled id fed back in device memory; timed with CUDA events on the launching
-             stream, barrier + synchronize on both sides, max over ranks.
+             the sampled id fed back in device memory; K steps timed with CUDA events on the
+             launching stream, barrier + synchronize on both sides, max over ranks; repeated
+             REPEATS times over the same positions, `value` is the median (spread in `repeats`).
   e2e        the same metric through the reference-facing call tl_llama2_generate: every step
              moves the token id host->device and the sampled id device->host, like
              Llama2::generate does; wall clock like the reference measures it.
   roofline   the dominant kernel (RMSNorm + w1|w3 GEMV + SiLU*up, 43 % of the weight bytes of a
-             token), launched over all layers' weights (5.8 GB >> L2) and timed with CUDA events.
+             token), launched over all layers' weights (5.8 GB >> L2) and timed with CUDA events;
+             its output for layer 0 is checked against an fp32 recomputation first.
+             roofline.prefill_2048 is the compute-bound companion (one 2048-token prompt).
+  checks     device status word after every timed region (a timed-out wait fails the run); for
+             N > 1 the ids every rank sampled, compared across ranks and with the NCCL exchange.
   cpu_baseline / --impl reference
-             the reference's own OpenMP CPU code (oracle/_ref) on the host cores, on a bounded
-             sample: a ONE-layer 7B-shaped model with 1/32 of the classifier rows, one decode
-             step per sample; a full token is 32 such samples.
+             the reference's own OpenMP CPU code (oracle/_ref) on all host cores: whole tokens of
+             the full 32-layer model where host memory allows (about 30 GB), otherwise one decode
+             step of a ONE-layer model with 1/32 of the classifier rows, 32 of which make a token
+             (`extrapolation` says which).
 """
 from __future__ import annotations
 
@@ -68,7 +74,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -105,28 +111,61 @@ class ClockSampler:
 # -------------------------------------------------------------------------------------------------
 # CPU arm: the reference's own code on the host cores
 # -------------------------------------------------------------------------------------------------
-def cpu_reference_decode(steps: int, warmup: int, budget_s: float):
-    """Decode steps of a one-layer 7B-shaped model (vocab/32 classifier rows) on the reference's
-    CPU backend. Returns (tokens_per_s_extrapolated, ms_per_step, cores, kind, steps_done)."""
+def _cpu_lib():
     from oracle import ref_lib
     if ref_lib.have_ref():
         lib, kind = ref_lib.RefLib(), "reference"
     else:
         lib, kind = ref_lib.OracleLib(), "port"
-    layers_full = CFG.n_layers
-    cfg = synth.LlamaConfig(dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=1, n_heads=CFG.n_heads,
-                            vocab_size=CFG.vocab_size // layers_full, seq_len=CFG.seq_len, shared_classifier=True)
-    # values do not matter for timing: one seeded block tiled over the payload
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: ask for the host's cores explicitly
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib.set_threads(max(1, cores))
+    return lib, kind, lib.max_threads()
+
+
+def _tiled_payload(cfg) -> np.ndarray:
+    """Checkpoint payload for timing runs: values do not change the time of a dense pass, so one
+    seeded block is tiled over it (norm weights = 1)."""
     block = synth.normal_f16(SEED, 1, 1 << 22, 0.02)
     payload = np.resize(block, cfg.payload_elems())
     d, L, V = cfg.dim, cfg.n_layers, cfg.vocab_size
     payload[V * d: V * d + L * d] = 1.0                                   # attention_norm
     off = V * d + L * d + 4 * L * d * d
     payload[off: off + L * d] = 1.0                                       # ffn_norm
-    payload[-d:] = 1.0                                                    # final norm
+    off += L * d + 3 * L * d * cfg.hidden_dim
+    payload[off: off + d] = 1.0                                           # final norm
+    return payload
+
+
+def _host_memory_available() -> int:
+    try:
+        import psutil
+        return int(psutil.virtual_memory().available)
+    except Exception:
+        return 0
+
+
+def cpu_reference_decode(steps: int, warmup: int, budget_s: float, context: int):
+    """Greedy decode steps on the reference's CPU backend, all host cores. Whole tokens of the full
+    32-layer model when the host has the memory for it (payload + the reference's own copy of the
+    weights, about 30 GB), else decode steps of a one-layer model with vocab/32 classifier rows,
+    32 of which make a token. Returns a dict for the JSON line."""
+    lib, kind, cores = _cpu_lib()
+    full_bytes = 2 * CFG.payload_elems() * 2 + (4 << 30)
+    full = os.environ.get("TL_BENCH_CPU_FULL", "auto")
+    use_full = full == "1" or (full == "auto" and _host_memory_available() > full_bytes + (8 << 30))
+    if use_full:
+        cfg, factor = CFG, 1
+    else:
+        cfg = synth.LlamaConfig(dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=1, n_heads=CFG.n_heads,
+                                vocab_size=CFG.vocab_size // CFG.n_layers, seq_len=CFG.seq_len, shared_classifier=True)
+        factor = CFG.n_layers
+    payload = _tiled_payload(cfg)
     model = lib.llama2(cfg, payload)
+    del payload
     tok = np.array([1], dtype=np.int32)
-    pos = 0
+    # the KV cache below `context` is zero: attention over it costs what it costs over real keys
+    pos = min(context, cfg.seq_len - steps - warmup - 1)
     for _ in range(warmup):
         model.forward(tok, pos, 1); pos += 1
     t0 = time.perf_counter()
@@ -136,22 +175,76 @@ def cpu_reference_decode(steps: int, warmup: int, budget_s: float):
         if time.perf_counter() - t0 > budget_s and done >= 3:
             break
     dt = (time.perf_counter() - t0) / done
-    return 1.0 / (dt * layers_full), dt * 1e3, lib.max_threads(), kind, done
+    model.close()
+    if use_full:
+        sample = f"{done} whole tokens of the full 32-layer model at context {context}+ (no extrapolation)"
+    else:
+        sample = (f"{done} decode steps of a 1-layer 7B-shaped model with vocab/32 classifier rows at context "
+                  f"{context}+; a token is {factor} such steps (extrapolated x{factor})")
+    return {"tokens_per_s": 1.0 / (dt * factor), "ms_per_sample": dt * 1e3, "extrapolation": factor, "cores": cores,
+            "kind": kind, "samples": done, "sample": sample}
+
+
+def cpu_reference_matmul_and_prefill(budget_s: float = 25.0) -> dict:
+    """The other two CPU baselines of the benchmark plan: the reference's OpenMP matmul2d
+    (tensorLib/src/device/cpu/CPU.cpp:76-89) on the four sweep weight shapes, and the prefill of one
+    7B-shaped layer. Every output row of a matmul is an independent dot-product loop, so the time is
+    linear in M: M = 8 rows are timed and the rate is reported (a 2048-row point is that rate times 256).
+    The prefill is timed at T = 64 on a one-layer model and scaled to 32 layers x 2048 tokens by the
+    linear-layer flops (the attention part, quadratic in T, is 7 % of the flops at T = 2048)."""
+    lib, kind, cores = _cpu_lib()
+    out = {"cores": cores, "kind": kind, "matmul": []}
+    t_start = time.perf_counter()
+    for (K, N) in ((4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)):
+        W = np.resize(synth.normal_f16(SEED, 2, 1 << 20, 0.02), N * K).reshape(N, K)
+        x = synth.normal_f16(SEED, 3, 8 * K, 1.0).reshape(8, K)
+        lib.matmul2d(x[:1], W[:64])
+        t0 = time.perf_counter()
+        lib.matmul2d(x, W)
+        dt = time.perf_counter() - t0
+        out["matmul"].append({"K": K, "N": N, "M_timed": 8, "ms": dt * 1e3, "gflops": 2.0 * 8 * N * K / dt / 1e9})
+        if time.perf_counter() - t_start > budget_s:
+            break
+    T = 64
+    cfg = synth.LlamaConfig(dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=1, n_heads=CFG.n_heads,
+                            vocab_size=1000, seq_len=128, shared_classifier=True)
+    model = lib.llama2(cfg, _tiled_payload(cfg))
+    tokens = synth.token_ids(SEED, 9, T, cfg.vocab_size)
+    t0 = time.perf_counter()
+    model.forward(tokens, 0, 1)
+    dt = time.perf_counter() - t0
+    model.close()
+    per_layer = 4 * CFG.dim * CFG.dim + 3 * CFG.dim * CFG.hidden_dim
+    timed_flops = 2.0 * T * (per_layer + cfg.vocab_size * CFG.dim)
+    full_flops = 2.0 * 2048 * (CFG.n_layers * per_layer) + 2.0 * 2048 * CFG.vocab_size * CFG.dim   # the reference computes all-position logits
+    out["prefill_layer_T64_s"] = dt
+    out["prefill_2048_extrapolated_s"] = dt * full_flops / timed_flops
+    out["prefill_note"] = ("one 7B-shaped layer, 64 tokens, timed; scaled to 32 layers x 2048 tokens + all-position "
+                           "classifier by linear-layer flops (labelled extrapolation)")
+    return out
+
+
+def bench_config(n_gpus: int) -> dict:
+    """The workload description both arms print, key for key."""
+    return {"workload": workload_name(n_gpus), "parallelism": f"tp{n_gpus}",
+            "l2": "inputs larger than L2 (weights streamed per token >> 126 MB)"}
 
 
 def run_reference_arm(args, rank: int):
     if rank != 0:
         return
-    tps, ms, cores, kind, done = cpu_reference_decode(args.steps, max(args.warmup, 1), budget_s=150.0)
-    sample = ("one decode step of a 1-layer 7B-shaped model with vocab/32 classifier rows "
-              "(= 1/32 of a token) per step; tokens/s = 1 / (32 x step time)")
-    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": done, "warmup": max(args.warmup, 1), "ms_per_step": ms * CFG.n_layers,
+    context = 128 if args.gpus == 1 else 512
+    r = cpu_reference_decode(args.steps, max(args.warmup, 1), budget_s=120.0, context=context)
+    line = {"impl": "reference", "metric": METRIC, "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": r["samples"], "warmup": max(args.warmup, 1), "ms_per_step": r["ms_per_sample"],
+            "extrapolation": r["extrapolation"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic",
-            "config": {"workload": workload_name(args.gpus), "timing": "host wall clock, OpenMP on all host cores"},
-            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
-            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "data": "synthetic", "config": bench_config(args.gpus),
+            "timing": "host wall clock around Transformer::forward, OpenMP on all host cores; ms_per_step is the "
+                      "measured time of one sample, value = 1 / (extrapolation x that)",
+            "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
+                             "sample": r["sample"]},
+            "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -167,8 +260,27 @@ def workload_name(n_gpus: int) -> str:
 # -------------------------------------------------------------------------------------------------
 # GPU arm
 # -------------------------------------------------------------------------------------------------
+REPEATS = 5   # the K timed steps are repeated this often over the same positions; value = median
+
+
+class _DeviceArray:
+    """A raw device pointer dressed as a CUDA array so that torch can view it without a copy."""
+
+    def __init__(self, ptr: int, shape, typestr: str = "<f2"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+def require_clean_status(tl, where: str) -> None:
+    """A kernel that gave up on a bounded wait leaves a status word behind: such a run measured
+    wrong arithmetic, so it fails loudly instead of printing a number."""
+    st = tl.device_status()
+    if st != 0:
+        raise SystemExit(f"bench.py: device status {st} after {where}: a bounded device-side wait ran out")
+
+
 def roofline_gateup(tl, model, stream, torch, n_layers):
-    """Time the dominant kernel over all layers' w1|w3 (distinct weights every launch)."""
+    """Time the dominant kernel over all layers' w1|w3 (distinct weights every launch), after
+    checking what it computes for layer 0 against an fp32 recomputation."""
     lib = tl.load()
     dim, hid, L = CFG.dim, model.c.hidden_dim // model.c.tp_world, n_layers
     stream_ptr = stream.cuda_stream
@@ -187,6 +299,19 @@ def roofline_gateup(tl, model, stream, torch, n_layers):
         for nw, w1, w3 in ptrs:
             tl.check(lib.tl_rmsnorm_gateup_swiglu_f16(x.data_ptr(), nw, 1e-5, w1, w3, out.data_ptr(), hid, dim,
                                                       stream_ptr), "gateup")
+    # what the timed launch computes, layer 0: silu(w1 n) * (w3 n), n = x / rms(x) * norm weight
+    nw0, w1p, w3p = ptrs[0]
+    tl.check(lib.tl_rmsnorm_gateup_swiglu_f16(x.data_ptr(), nw0, 1e-5, w1p, w3p, out.data_ptr(), hid, dim, stream_ptr), "gateup")
+    torch.cuda.synchronize()
+    xf = x.float()
+    n32 = xf * torch.rsqrt((xf * xf).mean() + 1e-5) * torch.as_tensor(_DeviceArray(nw0, (dim,)), device="cuda").float()
+    g32 = torch.as_tensor(_DeviceArray(w1p, (hid, dim)), device="cuda").float() @ n32
+    u32 = torch.as_tensor(_DeviceArray(w3p, (hid, dim)), device="cuda").float() @ n32
+    want = torch.nn.functional.silu(g32) * u32
+    err = float(((out.float() - want).abs() / want.abs().clamp_min(float(want.pow(2).mean().sqrt()))).max())
+    if not err <= 2e-2:
+        raise SystemExit(f"bench.py: the timed gate/up kernel is off by {err} (relative) against an fp32 recomputation")
+    del g32, u32, want
     for _ in range(3):
         sweep()
     reps = 5
@@ -197,6 +322,7 @@ def roofline_gateup(tl, model, stream, torch, n_layers):
         sweep()
     e1.record(stream)
     torch.cuda.synchronize()
+    require_clean_status(tl, "the roofline launches")
     sec = e0.elapsed_time(e1) * 1e-3 / (reps * L)
     bytes_per_launch = 2 * hid * dim * 2 + 2 * dim * 2 + hid * 2   # w1+w3, x + norm weight, out
     peak, peak_src = measured_peaks()
@@ -205,6 +331,7 @@ def roofline_gateup(tl, model, stream, torch, n_layers):
     return {"bound": "hbm", "kernel": "k_gemv_ring<SWIGLU,NORM> (RMSNorm + w1|w3 GEMV + SiLU*up)",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
             "bytes_per_launch": bytes_per_launch, "us_per_launch": sec * 1e6, "traffic": traffic,
+            "output_check_max_rel_err": err,
             "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch "
                               "(profiles/gemv_ring_decode_llama2_7b.md)" + ("" if model.c.tp_world == 1 else
                                                                             f", divided by {model.c.tp_world} ranks")}
@@ -230,16 +357,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=args.layers, n_heads=CFG.n_heads,
         vocab_size=CFG.vocab_size, seq_len=CFG.seq_len, shared_classifier=False)
     model = tl.Llama2(cfg, numerics=tl.FAST, tp_rank=rank, tp_world=world)
+    fused = world > 1 and args.tp_exchange == "fused"
     if world > 1:
         from tensorlib_b200 import tp
         tp.attach(model, rank, world, dist)
-        if args.tp_exchange == "fused":
+        if fused:
             tp.open_fused_exchange(model, rank, world, dist)
     model.init_random(SEED, 0.02)
 
     n_ctx = 128 if world == 1 else 512
     K, W = args.steps, args.warmup
-    assert n_ctx + W + 2 * K + 2 <= CFG.seq_len, "steps + warmup exceed the 2048-token context"
+    assert n_ctx + W + K + 2 <= CFG.seq_len, "steps + warmup exceed the 2048-token context"
     prompt = synth.prompt_tokens(CFG, SEED, n_ctx)
 
     def barrier():
@@ -247,37 +375,66 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather_ids(ids):
+        """Every rank's copy of a sampled id sequence: (all ranks agree, rank 0's list)."""
+        if world == 1:
+            return True, [int(v) for v in ids]
+        got = [None] * world
+        dist.all_gather_object(got, [int(v) for v in ids])
+        return all(g == got[0] for g in got), got[0]
+
     # prefill (untimed): leaves the first sampled id in the device slot
+    checks = {}
     if args.skip_prefill:
         model.set_next_token(int(prompt[-1]))      # profiling runs: decode over a zero KV cache
+        first_token = int(prompt[-1])
     else:
-        model.forward(prompt, 0, all_logits=False)
+        first_token = int(model.forward(prompt, 0, all_logits=False)[0].astype(np.float32).argmax())
     stream = torch.cuda.Stream()
     sp = stream.cuda_stream
-    pos = n_ctx
+    pos0 = n_ctx
     with torch.cuda.stream(stream):
-        model.decode_device(pos, W, fetch=False, stream=sp)           # warm-up (captures the graph)
-        pos += W
+        # correctness before speed: eight steps from the prompt, ids fetched and compared across the ranks
+        barrier()
+        ids8 = model.decode_device(pos0, min(8, K), fetch=True, stream=sp)
+        require_clean_status(tl, "the first decode steps")
+        agree, ids8_list = gather_ids(ids8)
+        checks.update({"tp_ids_agree": agree, "first_ids": ids8_list, "exchange": args.tp_exchange if world > 1 else "none"})
+        if not agree:
+            raise SystemExit("bench.py: the ranks sampled different token ids")
+        model.decode_device(pos0, W, fetch=False, stream=sp)          # warm-up over the positions that are timed
         barrier()
         launches0 = model.kernel_launches()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record(stream)
-        model.decode_device(pos, K, fetch=False, stream=sp)
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
+        times = []
+        for _ in range(REPEATS):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record(stream)
+            model.decode_device(pos0, K, fetch=False, stream=sp)     # the same K positions every repeat
+            e1.record(stream)
+            barrier()
+            times.append(max_over_ranks(e0.elapsed_time(e1)))
         clocks = sampler.stop() if rank == 0 else None
-        launches = model.kernel_launches() - launches0
-        pos += K
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        launches = (model.kernel_launches() - launches0) // REPEATS
+        require_clean_status(tl, "the timed decode steps")
+        ids_timed = model.decode_device(pos0 + K, 1, fetch=True, stream=sp)   # the id that followed the last timed step
+        agree_timed, _ = gather_ids(ids_timed)
+        checks["tp_ids_agree_after_timed_region"] = agree_timed
+    ms = float(np.median(times))
     value = K / (ms * 1e-3)
+    repeats = {"n": REPEATS, "ms_per_step_median": ms / K, "ms_per_step_min": min(times) / K,
+               "ms_per_step_max": max(times) / K, "tokens_per_s_min": K / (max(times) * 1e-3),
+               "tokens_per_s_max": K / (min(times) * 1e-3)}
 
     # end to end through the reference-facing generate(): id host->device->host every step
     barrier()
@@ -287,47 +444,63 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         model.close()
         return
     ids, t_prefill, t_decode = model.generate(prompt, K + 1)
-    e2e_ms = t_decode * 1e3
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(t_decode * 1e3)
     e2e = (len(ids) - 1) / (e2e_ms * 1e-3)
+    agree_e2e, e2e_ids = gather_ids(ids[:8])
+    checks["e2e_ids_agree"] = agree_e2e
+    # generate() starts from the same prompt as the device-resident steps above: same kernels, same ids
+    checks["e2e_ids_equal_device_resident"] = (e2e_ids[0] == first_token and
+                                               e2e_ids[1:] == ids8_list[:len(e2e_ids) - 1])
+    require_clean_status(tl, "generate()")
 
     roof = roofline_gateup(tl, model, stream, torch, cfg.n_layers) if rank == 0 else None
     weight_bytes = model.weight_bytes()
+    # the compute-bound companion numbers: one 2048-token prefill (all ranks take part)
+    prefill = prefill_2048(model, cfg, world, torch, dist) if cfg.n_layers == CFG.n_layers else None
+    require_clean_status(tl, "the 2048-token prefill")
+    if fused:
+        # the same eight steps with the plain NCCL exchange: summation order differs (ring order against
+        # rank order), so equal ids are reported, not required
+        from tensorlib_b200 import tp
+        tp.close_fused_exchange(model, dist)
+        model.forward(prompt, 0, all_logits=False)
+        with torch.cuda.stream(stream):
+            ids_nccl = model.decode_device(pos0, min(8, K), fetch=True, stream=sp)
+        require_clean_status(tl, "the NCCL-exchange decode steps")
+        agree_nccl, ids_nccl_list = gather_ids(ids_nccl)
+        checks.update({"nccl_ids_agree_across_ranks": agree_nccl, "nccl_first_ids": ids_nccl_list,
+                       "fused_ids_equal_nccl_ids": ids_nccl_list == ids8_list})
+    model.close()
     if rank == 0:
         peak, _ = measured_peaks()
         emb_bytes = cfg.vocab_size * cfg.dim * 2            # the embedding table is gathered, not streamed
         step_bytes = weight_bytes - emb_bytes
+        if roof is not None and prefill is not None:
+            roof["prefill_2048"] = {"ms": prefill["ms"], "tflops_per_gpu": prefill["tflops_per_gpu"],
+                                    "frac_of_tensor_peak": prefill["frac_of_tensor_peak"], "bound": "tensor"}
         line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f16", "data": "synthetic",
-                "config": {"workload": workload_name(world) + ("" if cfg.n_layers == CFG.n_layers else f" [PROFILING ONLY: {cfg.n_layers} layers]"),
-                           "context_at_start": n_ctx + W,
-                           "parallelism": f"tp{world}",
-                           "tp_exchange": (args.tp_exchange if world > 1 else "none"), "numerics": "fp16 storage, fp32 accumulate",
-                           "l2": "inputs larger than L2 (weights streamed per token >> 126 MB)",
-                           "weight_bytes_per_token_per_gpu": step_bytes},
-                "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4,
-                        "prefill_s": t_prefill},
-                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
-                "step_hbm_frac": (step_bytes / (ms / K * 1e-3) / 1e9) / peak}
+                "dtype": "f16", "data": "synthetic"}
+        if world == 1 and cfg.n_layers == CFG.n_layers:
+            line["matmul_sweep"] = matmul_sweep(tl, torch, with_baselines=not args.no_cpu)   # long: printed before the headline keys
+        line.update({
+            "prefill_2048": prefill,
+            "config": bench_config(world) if cfg.n_layers == CFG.n_layers else
+            {**bench_config(world), "workload": workload_name(world) + f" [PROFILING ONLY: {cfg.n_layers} layers]"},
+            "details": {"context_at_start": n_ctx, "tp_exchange": (args.tp_exchange if world > 1 else "none"),
+                        "numerics": "fp16 storage, fp32 accumulate", "weight_bytes_per_token_per_gpu": step_bytes,
+                        "timed_region": f"{REPEATS} x {K} steps over positions [{pos0}, {pos0 + K}); value = K / median"},
+            "repeats": repeats, "checks": checks,
+            "gpu_launches": int(launches), "clocks": clocks,
+            "step_hbm_frac": (step_bytes / (ms / K * 1e-3) / 1e9) / peak})
         if world == 1 and not args.no_cpu:
-            tps, ms_cpu, cores, kind, done = cpu_reference_decode(64, 2, budget_s=20.0)
-            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind,
-                                    "sample": f"{done} decode steps of a 1-layer 7B-shaped model with vocab/32 "
-                                              "classifier rows (1/32 of a token each), extrapolated x32"}
-    # the compute-bound companion numbers: one 2048-token prefill (all ranks take part)
-    prefill = prefill_2048(model, cfg, world, torch, dist) if cfg.n_layers == CFG.n_layers else None
-    if world > 1 and args.tp_exchange == "fused":
-        from tensorlib_b200 import tp
-        tp.close_fused_exchange(model, dist)
-    model.close()
-    if rank == 0:
-        line["prefill_2048"] = prefill
-        if world == 1:
-            line["matmul_sweep"] = matmul_sweep(tl, torch)
+            r = cpu_reference_decode(16, 1, budget_s=20.0, context=n_ctx)
+            line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
+                                    "sample": r["sample"], "extrapolation": r["extrapolation"]}
+            line["cpu_baseline_other_configs"] = cpu_reference_matmul_and_prefill()
+        line["e2e"] = {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
+                       "prefill_s": t_prefill}
+        line["roofline"] = roof
         print(json.dumps(line), flush=True)
     if world > 1:
         from tensorlib_b200 import tp
@@ -382,17 +555,45 @@ def prefill_2048(model, cfg, world, torch, dist, T: int = 2048):
 
 
 def matmul_sweep(tl, torch, m_list=(1, 8, 32, 128, 512, 2048),
-                 kn_list=((4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000))):
+                 kn_list=((4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)), with_baselines: bool = True):
     """Config 1: y = x W^T, fp16 in / fp32 accumulate, device-resident, rotating over enough
-    weight copies (>= 512 MB) that no launch finds its weights in L2."""
+    weight copies (>= 512 MB) that no launch finds its weights in L2. 6 x 4 = 24 points, one row each
+    (see `columns`). Two same-GPU baselines are timed beside every point, neither on the product
+    path: cuBLAS through torch.matmul, and the reference's own CUDA route CUDA<half>::matmul2d
+    (gemv_v6 at M = 1, cublasHgemm with a handle created per call otherwise; compiled from the
+    reference sources into oracle/_ref) where that library is present."""
     lib = tl.load()
     hbm, _ = measured_peaks()
     tpk, _ = tensor_peak()
     sp = torch.cuda.current_stream().cuda_stream
-    out = []
+    ref = None
+    if with_baselines:
+        try:
+            from oracle import ref_lib
+            if ref_lib.have_ref():
+                ref = ref_lib.RefLib()
+                if ref.cuda_device_count() < 1:
+                    ref = None
+        except Exception:
+            ref = None
+    rows = []
+
+    def timed(fn, reps):
+        for i in range(5):
+            fn(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps
+
     for (K, N) in kn_list:
         copies = max(2, -(-512 * 2 ** 20 // (N * K * 2)))
         Ws = [torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02 for _ in range(copies)]
+        W_host = Ws[0].cpu().numpy() if ref is not None else None
         for M in m_list:
             x = torch.randn(M, K, device="cuda", dtype=torch.float16)
             y = torch.empty(M, N, device="cuda", dtype=torch.float16)
@@ -400,24 +601,30 @@ def matmul_sweep(tl, torch, m_list=(1, 8, 32, 128, 512, 2048),
             def run(i):
                 tl.check(lib.tl_matmul2d_f16(x.data_ptr(), Ws[i % copies].data_ptr(), y.data_ptr(), M, N, K,
                                              tl.FAST, sp), "tl_matmul2d_f16")
-            for i in range(5):
-                run(i)
-            reps = 50
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            e0.record()
-            for i in range(reps):
-                run(i)
-            e1.record()
-            torch.cuda.synchronize()
-            sec = e0.elapsed_time(e1) * 1e-3 / reps
+            sec = timed(run, 50)
+            want = x[:4].float() @ Ws[49 % copies].float().t()        # the last timed launch, four rows in fp32
+            err = float(((y[:4].float() - want).abs() / want.abs().clamp_min(float(want.pow(2).mean().sqrt()))).max())
+            if not err <= 1e-2:
+                raise SystemExit(f"bench.py: matmul sweep point M={M} K={K} N={N} is off by {err}")
+            cublas_us = ref_us = None
+            if with_baselines:
+                cublas_us = timed(lambda i: torch.matmul(x, Ws[i % copies].t(), out=y), 50) * 1e6
+            if ref is not None:
+                _, ref_us = ref.cuda_matmul2d(x.cpu().numpy(), W_host, reps=20, b_copies=copies)
             flops, nbytes = 2.0 * M * N * K, 2.0 * (N * K + M * K + M * N)
             t_roof = max(nbytes / (hbm * 1e9), flops / (tpk * 1e12))
-            out.append({"M": M, "K": K, "N": N, "us": sec * 1e6, "tflops": flops / sec / 1e12,
-                        "gbs": nbytes / sec / 1e9, "bound": "hbm" if nbytes / (hbm * 1e9) > flops / (tpk * 1e12) else "tensor",
-                        "frac_of_roofline": t_roof / sec})
+            bound = "hbm" if nbytes / (hbm * 1e9) > flops / (tpk * 1e12) else "tensor"
+            rows.append([M, K, N, round(sec * 1e6, 2), round(t_roof / sec, 4), bound,
+                         round(flops / sec / 1e12, 1) if bound == "tensor" else round(nbytes / sec / 1e9, 1),
+                         None if cublas_us is None else round(cublas_us, 2), None if ref_us is None else round(ref_us, 2)])
         del Ws
-    return out
+    st = tl.device_status()
+    if st != 0:
+        raise SystemExit(f"bench.py: device status {st} after the matmul sweep")
+    return {"columns": ["M", "K", "N", "us", "frac_of_roofline", "bound", "TFLOP/s or GB/s", "cublas_us (torch.matmul, baseline)",
+                        "ref_cuda_us (the reference's CUDA<half>::matmul2d on this GPU, baseline)"],
+            "rows": rows,
+            "roofline": "max(2(NK+MK+MN) bytes / measured copy bandwidth, 2MNK flops / measured bf16 burst peak)"}
 
 
 def main():
@@ -449,7 +656,7 @@ def main():
         torch.cuda.set_device(0)
         tl.init(0)
         M, K, N = (int(v) for v in args.sweep_only.split(","))
-        print(json.dumps({"profiling_only": True, "matmul_sweep": matmul_sweep(tl, torch, (M,), ((K, N),))}), flush=True)
+        print(json.dumps({"profiling_only": True, "matmul_sweep": matmul_sweep(tl, torch, (M,), ((K, N),), with_baselines=False)}), flush=True)
         return
     if args.prefill_only:
         import torch

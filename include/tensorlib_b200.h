@@ -88,9 +88,11 @@ TL_API int tl_free_host(void* hptr);
 /* ---- matmul: the drop-in boundary --------------------------------------------------------- */
 /* Device<half>::matmul2d (tensorLib/include/device/Device.hpp:22; CUDA implementation
  * tensorLib/src/device/cuda/gemm.cu:153-172): C[M,N] = A[M,K] * B[N,K]^T, all row-major
- * contiguous. Dispatches on M in fast numerics: M = 1 the streaming GEMV, 2..128 the skinny
- * tensor-core kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair
- * tiles); operands that are not 16-byte aligned or K % 8 != 0 take the any-shape kernel.
+ * contiguous. Dispatches on M in fast numerics: M = 1..8 the streaming GEMV ring (up to eight
+ * activation rows ride the eight columns of the MMA's B operand, so they cost the weight traffic
+ * of one; needs N even and K % 16 == 0), 9..128 (and other 2..8 shapes) the skinny tensor-core
+ * kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair tiles);
+ * operands that are not 16-byte aligned or K % 8 != 0 take the any-shape kernel.
  * All kernels are launched with programmatic stream serialization and wait on the device for the
  * previous kernel of `stream` before touching A, B or C, so back-to-back calls overlap their
  * set-up, never their data. The first skinny call on a given stream allocates a 34 MB workspace
@@ -125,7 +127,8 @@ TL_API int tl_rms_norm_f16(tl_half* out, const tl_half* in, const tl_half* weigh
 /* Device::apply_rotary_emb (Device.hpp:91-98, CPU.cpp:427-461): interleaved-pair rotation of a
  * contiguous (B,T,n_heads,head_dim) tensor; in == out allowed. cos/sin come from a table
  * computed on the host with the reference's float formula, so both numerics agree bit for bit.
- * The table grows (allocates, synchronises) when start_pos+T exceeds what earlier calls needed. */
+ * When start_pos+T exceeds what earlier calls needed, a larger table is allocated and filled (a
+ * blocking copy); tables handed out before, e.g. to a model, stay allocated and valid. */
 TL_API int tl_apply_rotary_emb_f16(const tl_half* in, tl_half* out, int start_pos, int B, int T,
                             int n_heads, int head_dim, tl_stream stream);
 /* Device::softmax over the last dimension (Device.hpp:77, cpu/softmax.cpp:10-31). */
@@ -169,7 +172,7 @@ TL_API int tl_attn_decode_f16(const tl_half* q, const tl_half* k_cache, const tl
  * The scratch and the counters live in a fixed array inside the library image (about 0.5 MB of
  * device memory per GPU that loads the library, held until exit), so the call performs no
  * cudaMalloc / cudaFree and needs no buffers beyond its inputs and output.
- * Limits: n_heads <= 128 and n_heads*splits*(head_dim+2) <= 131072; larger requests are rejected
+ * Limits: n_heads <= 128, head_dim <= 256, n_heads*splits*(head_dim+2) <= 131072; larger requests are rejected
  * with TL_ERR_INVALID_ARGUMENT (use tl_attn_decode_f16 with caller-owned scratch instead).
  * The first call on a device resolves the array's device address (cudaGetSymbolAddress); make
  * that first call before starting any stream capture. All calls share the one array: the entry
@@ -222,11 +225,13 @@ TL_API int tl_llama2_load_file(tl_llama2* m, const char* path);
 TL_API int tl_llama2_init_random(tl_llama2* m, uint64_t seed, float std);
 /* Transformer<half>::forward (Transformer.cpp:264-299): tokens_host[T] at start_pos.
  * logits_host (optional) receives (T, vocab) fp16 for all positions like the reference returns;
- * last_logits_host (optional) only the final position. Synchronises. */
+ * last_logits_host (optional) only the final position. Synchronises, and returns TL_ERR_TIMEOUT
+ * instead of results if a kernel of the pass gave up on a bounded wait (see tl_device_status). */
 TL_API int tl_llama2_forward(tl_llama2* m, const int* tokens_host, int T, int start_pos,
                       tl_half* logits_host, tl_half* last_logits_host);
 /* Llama2<half>::generate (model/llama2_7b/src/llama2.cpp:15-101): prefill the prompt, then greedy
- * decode. Every step moves the sampled id device->host and back like the reference does. Stops
+ * decode. Every step moves the sampled id device->host and back like the reference does (the device
+ * status word travels with it: a timed-out wait ends the call with TL_ERR_TIMEOUT). Stops
  * early on id 1 or 2 only if stop_on_eos != 0. Returns the number of ids written to out_tokens,
  * and wall-clock seconds of the two phases as the reference prints them. */
 TL_API int tl_llama2_generate(tl_llama2* m, const int* prompt_host, int n_prompt, int max_new,
@@ -241,7 +246,9 @@ TL_API int tl_llama2_generate_at(tl_llama2* m, int start_pos, const int* prompt_
 /* Device-resident greedy decode: `steps` tokens starting from the id in the model's device-side
  * token slot (left there by a previous forward/generate/decode call), one CUDA-graph replay per
  * token, no host round trip. out_tokens_host (optional) is filled after the last step. Runs on
- * `stream` and synchronises it only when out_tokens_host != NULL. */
+ * `stream` and synchronises it only when out_tokens_host != NULL; it then also reads the device
+ * status word and returns TL_ERR_TIMEOUT if a wait ran out (without out_tokens_host the caller
+ * checks tl_device_status itself after its own synchronisation). */
 TL_API int tl_llama2_decode_device(tl_llama2* m, int start_pos, int steps, int* out_tokens_host,
                             tl_stream stream);
 /* position bookkeeping and introspection */
@@ -278,10 +285,21 @@ TL_API int tl_tp_destroy(void);
  * validity needs no separate flag or fence. Needs an even vocabulary slice per rank. Set-up: every rank exports a 64-byte handle of its region, the
  * handles are gathered out of band (rank order, world*64 bytes), every rank opens them; all
  * ranks must pass a host barrier before the first decode step and before closing. Device-side
- * waits are bounded (TL_ERR_TIMEOUT in the device status word). Prefill keeps using NCCL. */
+ * waits are bounded: a consumer retries for roughly 0.1-0.3 s (2^18 polls of its slots), then records
+ * TL_ERR_TIMEOUT in the device status word and carries on with what it has; the model calls that
+ * synchronise (forward, generate, decode_device with out_tokens_host) turn that word into their
+ * return code. Ranks whose launches may drift apart by more than that (first-call graph
+ * instantiation, an allocation on one rank) should pass a host barrier first. */
 TL_API int tl_tp_exchange_export(tl_llama2* m, void* handle64, int nbytes);
 TL_API int tl_tp_exchange_open(tl_llama2* m, const void* handles, int world);
 TL_API int tl_tp_exchange_close(tl_llama2* m);
+/* Self-test of the bounded device-side wait (no counterpart in the reference, whose kernels never
+ * wait on anything): launches one consumer GEMV whose tensor-parallel input comes from a local
+ * two-rank receive region that nobody ever posts to, with the wait limited to max_polls polls
+ * (1 .. 2^20). The kernel must return by itself; the call synchronises `stream` and returns
+ * TL_OK, after which tl_device_status() reports TL_ERR_TIMEOUT once and the library stays usable.
+ * Nothing faults or traps. Allocates and frees its own few KB. */
+TL_API int tl_selftest_unposted_exchange(int max_polls, tl_stream stream);
 /* Host-only: the block of a [rows, cols] checkpoint tensor that rank `rank` of `world` keeps.
  * kind 0 = replicated, 1 = split by rows, 2 = split by columns. */
 TL_API int tl_tp_shard(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows,

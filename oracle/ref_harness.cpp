@@ -36,6 +36,8 @@
 #include <string>
 #include <vector>
 #include <omp.h>
+#include <cuda_runtime.h>
+#include "device/cuda/CUDA.cuh"
 
 namespace {
 
@@ -258,6 +260,8 @@ int ref_llama2_forward(void* h, const int* tokens, int T, int start_pos, int sil
         const ModelArgs& p = m->args;
         Transformer<half>& model = *m->model;
         const int dim = p.dim, H = p.n_heads;
+        if (silu_mode != 0 && silu_mode != 1)
+            throw std::invalid_argument("silu_mode must be 0 or 1: the reference's CPU code has one RMSNorm");
 
         Tensor<int> tok({1, T}, "cpu");
         for (int i = 0; i < T; i++) tok.setData({0, i}, tokens[i]);
@@ -302,6 +306,74 @@ int ref_llama2_forward(void* h, const int* tokens, int T, int start_pos, int sil
         Tensor<half> hn = model.norm.forward_plain(out);                   // :295
         Tensor<half> logits = model.output.forward(hn, buf.logical);       // :296
         copy_out(logits, logits_out);
+    });
+}
+
+// ---------------------------------------------------------------------------------------------
+// The reference's CUDA backend, driven through its own classes on "cuda" tensors. These entry
+// points need a GPU; they exist so that (a) the oracle's restatement of the CUDA RMSNorm can be
+// compared with the real kernel and (b) the reference's own matmul route (gemv_v6 / gemv_v4 /
+// hgemm_cublas behind CUDA<half>::matmul2d, tensorLib/src/device/cuda/gemm.cu:153-172) can be
+// timed on the same GPU as a baseline. Host arrays in, host arrays out.
+// ---------------------------------------------------------------------------------------------
+int ref_cuda_device_count() {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
+}
+
+// nn::RMSNorm<half>::forward on "cuda" tensors -> CUDA<half>::rms_norm -> rms_norm_kernel_v1
+// (tensorLib/src/nn/rmsNorm.cpp:62-106, tensorLib/src/device/cuda/rms_norm.cu:138-184).
+int ref_cuda_rms_norm_f16(const uint16_t* x, const uint16_t* w, uint16_t* y, int T, int dim, float eps) {
+    return guarded([&] {
+        nn::RMSNorm<half> norm(dim, eps, "cuda");
+        Tensor<half> xt({1, T, dim}, "cuda");
+        const size_t n = (size_t)T * dim;
+        if (cudaMemcpy(norm.weight.device->getDataPtr(), w, (size_t)dim * sizeof(half), cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(xt.device->getDataPtr(), x, n * sizeof(half), cudaMemcpyHostToDevice) != cudaSuccess)
+            throw std::runtime_error("cudaMemcpy to the device failed");
+        Tensor<half> out = norm.forward(xt);
+        if (cudaDeviceSynchronize() != cudaSuccess ||
+            cudaMemcpy(y, out.device->getDataPtr(), n * sizeof(half), cudaMemcpyDeviceToHost) != cudaSuccess)
+            throw std::runtime_error(std::string("reference rms_norm failed: ") + cudaGetErrorString(cudaGetLastError()));
+    });
+}
+
+// CUDA<half>::matmul2d (gemm.cu:153-172) on device copies of A[M,K], B[N,K]; `reps` timed calls
+// rotate over `b_copies` copies of B so that no call finds its weights in L2; the mean time per
+// call (CUDA events on the legacy stream, which is where the reference launches) goes to *us and
+// the result of the last call to C. reps == 0 runs it once untimed.
+int ref_cuda_matmul2d_f16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, int N, int K, int reps,
+                          int b_copies, double* us) {
+    return guarded([&] {
+        half *dA = nullptr, *dB = nullptr, *dC = nullptr;
+        const size_t na = (size_t)M * K, nb = (size_t)N * K, nc = (size_t)M * N;
+        if (b_copies < 1) b_copies = 1;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        auto cleanup = [&] {
+            cudaFree(dA); cudaFree(dB); cudaFree(dC);
+            if (e0) cudaEventDestroy(e0);
+            if (e1) cudaEventDestroy(e1);
+        };
+        if (cudaMalloc(&dA, na * 2) != cudaSuccess || cudaMalloc(&dB, nb * 2 * b_copies) != cudaSuccess ||
+            cudaMalloc(&dC, nc * 2) != cudaSuccess) { cleanup(); throw std::runtime_error("cudaMalloc failed"); }
+        cudaMemcpy(dA, A, na * 2, cudaMemcpyHostToDevice);
+        for (int c = 0; c < b_copies; c++) cudaMemcpy(dB + (size_t)c * nb, B, nb * 2, cudaMemcpyHostToDevice);
+        CUDA<half> dev;   // no storage of its own: matmul2d only uses its arguments
+        dev.matmul2d(dA, dB, dC, (size_t)M, (size_t)N, (size_t)K);
+        if (cudaDeviceSynchronize() != cudaSuccess) { cleanup(); throw std::runtime_error("reference matmul2d failed"); }
+        if (reps > 0) {
+            cudaEventCreate(&e0); cudaEventCreate(&e1);
+            for (int i = 0; i < 3; i++) dev.matmul2d(dA, dB + (size_t)(i % b_copies) * nb, dC, (size_t)M, (size_t)N, (size_t)K);
+            cudaEventRecord(e0, 0);
+            for (int i = 0; i < reps; i++) dev.matmul2d(dA, dB + (size_t)(i % b_copies) * nb, dC, (size_t)M, (size_t)N, (size_t)K);
+            cudaEventRecord(e1, 0);
+            if (cudaEventSynchronize(e1) != cudaSuccess) { cleanup(); throw std::runtime_error("reference matmul2d failed"); }
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (us) *us = (double)ms * 1e3 / reps;
+        }
+        cudaMemcpy(C, dC, nc * 2, cudaMemcpyDeviceToHost);
+        cleanup();
     });
 }
 

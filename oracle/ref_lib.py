@@ -72,6 +72,16 @@ class _Lib:
         self._maxthr.restype = C.c_int
         self._setthr = getattr(L, p + "omp_set_threads")
         self._setthr.argtypes = [C.c_int]
+        self._bind_extra()
+
+    def _bind_extra(self):
+        pass
+
+    def _bind(self, name, args):
+        f = getattr(self.lib, self.prefix + name)
+        f.argtypes = args
+        f.restype = C.c_int
+        self._fn[name] = f
 
     def _call(self, name, *args):
         rc = self._fn[name](*args)
@@ -171,6 +181,9 @@ class _Model:
         lib._call("llama2_load", self.h, _p16(payload), int(cfg.shared_classifier))
 
     def forward(self, tokens, start_pos: int, silu_mode: int = 1, want_hidden: bool = False):
+        """silu_mode 0 / 1: the SiLU route (CPU fp16 as shipped / through float). OracleLib only:
+        +2 computes RMSNorm as the reference's CUDA backend does (fp32 sum) instead of the CPU's
+        fp16 running sum, which loses 3-5 % at dim 4096."""
         tok = np.ascontiguousarray(tokens, dtype=np.int32)
         T = tok.size
         logits = np.empty((T, self.cfg.vocab_size), dtype=np.float16)
@@ -216,10 +229,48 @@ class RefLib(_Lib):
     prefix = "ref_"
     path = REF_SO
 
+    def _bind_extra(self):
+        self._bind("cuda_rms_norm_f16", [_u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_float])
+        self._bind("cuda_matmul2d_f16", [_u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.POINTER(C.c_double)])
+        self._cuda_count = self.lib.ref_cuda_device_count
+        self._cuda_count.restype = C.c_int
+
+    # -- the reference's CUDA backend (needs a GPU): a baseline and a cross-check, never an oracle ----
+    def cuda_device_count(self) -> int:
+        return int(self._cuda_count())
+
+    def cuda_rms_norm(self, x: np.ndarray, w: np.ndarray, eps: float = 1e-5) -> np.ndarray:
+        """nn::RMSNorm<half>::forward on "cuda" tensors (rms_norm_kernel_v1)."""
+        T, D = x.shape
+        y = np.empty_like(x)
+        self._call("cuda_rms_norm_f16", _p16(x), _p16(w), _p16(y), T, D, eps)
+        return y
+
+    def cuda_matmul2d(self, A: np.ndarray, B: np.ndarray, reps: int = 0, b_copies: int = 1):
+        """CUDA<half>::matmul2d (gemv_v6 / gemv_v4 / hgemm_cublas) on device copies; returns
+        (C, mean microseconds per call or None)."""
+        M, K = A.shape
+        N, _ = B.shape
+        Cm = np.empty((M, N), dtype=np.float16)
+        us = C.c_double(0.0)
+        self._call("cuda_matmul2d_f16", _p16(A), _p16(B), _p16(Cm), M, N, K, reps, b_copies, C.byref(us))
+        return Cm, (us.value if reps > 0 else None)
+
 
 class OracleLib(_Lib):
     prefix = "orc_"
     path = ORACLE_SO
+
+    def _bind_extra(self):
+        self._bind("rmsnorm_cuda_route_f16", [_u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_float])
+
+    def rmsnorm_cuda_route(self, x: np.ndarray, w: np.ndarray, eps: float = 1e-5) -> np.ndarray:
+        """RMSNorm as the reference's CUDA backend computes it (fp32 sum of squares)."""
+        T, D = x.shape
+        y = np.empty_like(x)
+        self._call("rmsnorm_cuda_route_f16", _p16(x), _p16(w), _p16(y), T, D, eps)
+        return y
 
 
 def have_ref() -> bool:

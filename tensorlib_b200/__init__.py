@@ -94,6 +94,7 @@ _SIGS = {
     "tl_tp_exchange_open": [_vp, _vp, _int],
     "tl_tp_exchange_close": [_vp],
     "tl_tp_shard": [_int] * 5 + [C.POINTER(_int)] * 4,
+    "tl_selftest_unposted_exchange": [_int, _vp],
 }
 _OTHER_RESTYPE = {"tl_strerror": (C.c_char_p, [_int]), "tl_last_error": (C.c_char_p, []),
                   "tl_version": (_int, [])}
@@ -312,6 +313,38 @@ def attn_prefill(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, start_
           "tl_attn_prefill_f16")
     synchronize()
     return out.to_numpy(np.float16, (T, width))
+
+
+def rmsnorm_qkv_rope(x, norm_w, wq, wk, wv, k_cache, v_cache, head_dim: int, pos: int, eps: float = 1e-5):
+    """tl_rmsnorm_qkv_rope_f16: x[dim] -> (q[n_q], k_cache', v_cache') with row `pos` of the caches
+    (max_seq, n_q) written in place on device copies, which are returned."""
+    n_q, dim = wq.shape
+    bufs = [DeviceBuffer.from_numpy(np.ascontiguousarray(a, dtype=np.float16))
+            for a in (x, norm_w, wq, wk, wv, k_cache, v_cache)]
+    dq = DeviceBuffer(n_q * 2)
+    check(load().tl_rmsnorm_qkv_rope_f16(bufs[0].ptr, bufs[1].ptr, eps, bufs[2].ptr, bufs[3].ptr, bufs[4].ptr, dq.ptr,
+                                         bufs[5].ptr, bufs[6].ptr, dim, n_q, head_dim, pos, None), "tl_rmsnorm_qkv_rope_f16")
+    return (dq.to_numpy(np.float16, (n_q,)), bufs[5].to_numpy(np.float16, k_cache.shape),
+            bufs[6].to_numpy(np.float16, v_cache.shape))
+
+
+def gemv_residual(x, W, residual):
+    """tl_gemv_residual_f16: residual[N] + W[N,K] x[K]."""
+    N, K = W.shape
+    dx, dW, dr = (DeviceBuffer.from_numpy(np.ascontiguousarray(a, dtype=np.float16)) for a in (x, W, residual))
+    dy = DeviceBuffer(N * 2)
+    check(load().tl_gemv_residual_f16(dx.ptr, dW.ptr, dr.ptr, dy.ptr, N, K, None), "tl_gemv_residual_f16")
+    return dy.to_numpy(np.float16, (N,))
+
+
+def rmsnorm_gateup_swiglu(x, norm_w, w1, w3, eps: float = 1e-5):
+    """tl_rmsnorm_gateup_swiglu_f16: silu(w1 n) * (w3 n) with n = rmsnorm(x) * norm_w."""
+    hidden, dim = w1.shape
+    dx, dn, d1, d3 = (DeviceBuffer.from_numpy(np.ascontiguousarray(a, dtype=np.float16)) for a in (x, norm_w, w1, w3))
+    dy = DeviceBuffer(hidden * 2)
+    check(load().tl_rmsnorm_gateup_swiglu_f16(dx.ptr, dn.ptr, eps, d1.ptr, d3.ptr, dy.ptr, hidden, dim, None),
+          "tl_rmsnorm_gateup_swiglu_f16")
+    return dy.to_numpy(np.float16, (hidden,))
 
 
 PLAN_NAMES = {0: "reference_order", 1: "gemv_ring", 2: "gemv_small", 3: "skinny_streamk", 4: "skinny_cluster",

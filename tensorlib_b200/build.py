@@ -18,7 +18,7 @@ LIB = os.path.join(PKG, "libtensorlib_b200.so")
 NVCC = os.environ.get("TL_NVCC", "/usr/local/cuda/bin/nvcc")
 
 SOURCES = ["runtime.cu", "ops_refmode.cu", "gemv.cu", "attn.cu", "attn_sm100.cu", "hgemm_sm100.cu", "skinny_sm100.cu", "decode_mega.cu", "engine.cu",
-           "api.cu", "host_mirror.cu", "tp.cu"]
+           "api.cu", "tp.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-Xptxas", "-v",
               "-ccbin", "g++"]
@@ -30,9 +30,6 @@ def _newer(a: str, b: str) -> bool:
 
 def _deps() -> list[str]:
     hdr = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".hpp", ".h"))]
-    host = os.path.join(PKG, "host")
-    if os.path.isdir(host):
-        hdr += [os.path.join(host, f) for f in os.listdir(host)]
     hdr.append(os.path.join(PKG, "..", "include", "tensorlib_b200.h"))
     return hdr
 

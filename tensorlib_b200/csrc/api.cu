@@ -17,6 +17,9 @@ namespace {
 inline const __half* H(const tl_half* p) { return reinterpret_cast<const __half*>(p); }
 inline __half* H(tl_half* p) { return reinterpret_cast<__half*>(p); }
 bool valid_numerics(int n) { return n == TL_NUMERICS_REFERENCE_ORDER || n == TL_NUMERICS_FAST; }
+// pinned word behind the token staging area: the device status word is copied here at every point
+// where a model call synchronises anyway, so a timed-out wait turns into an error return
+int* status_slot(tl_llama2* m) { return m->pinned + m->eng->cfg().max_seq_len + 4; }
 }  // namespace
 
 extern "C" {
@@ -32,9 +35,11 @@ int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t
     TL_REQUIRE(M < (1u << 31) && N < (1u << 31) && K < (1u << 31) && batch < (1u << 31), "dimension too large");
     cudaStream_t st = as_stream(stream);
     if (numerics == TL_NUMERICS_FAST && K > 0) {
+        if (batch == 1 && gemv_ring_rows_supported(A, B, M, N, K, ldb, lda))
+            return launch_gemv(H(A), H(B), H(C), (int)M, (int)N, (int)K, ldb, lda, ldc, st);
         if (batch == 1 && M >= 2 && M <= 128 && skinny_supported(A, B, M, N, K, lda, ldb))
             return launch_skinny(H(A), H(B), H(C), (int)M, (int)N, (int)K, lda, ldb, ldc, st);
-        if (M > 8 && hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc))
+        if (M > 8 && strideA % 8 == 0 && strideB % 8 == 0 && hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc))
             return launch_hgemm(H(A), H(B), H(C), (int)batch, (int)M, (int)N, (int)K, lda, ldb, ldc,
                                 strideA, strideB, strideC, st);
         if (gemv_supported(A, B, M < 8 ? M : 8, N, K, ldb) && lda % 8 == 0 && strideA % 8 == 0 && strideB % 8 == 0) {
@@ -68,6 +73,10 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
     TL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && sm_count >= 1 && M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "bad shape");
     *grid = *tile_n = *k_blocks_per_cta = *cluster = 0;
     if (M == 1 && N % 2 == 0 && K % 16 == 0 && K <= 12288) { *kernel = TL_PLAN_GEMV_RING; return TL_OK; }
+    if (M >= 2 && M <= 8 && N % 2 == 0 && K % 16 == 0) {   // the same ring with M columns in the MMA's B operand
+        *kernel = TL_PLAN_GEMV_RING; *grid = (int)std::min<size_t>((size_t)sm_count, (N / 2 + 7) / 8);
+        return TL_OK;
+    }
     if (M >= 2 && M <= 128 && K % 8 == 0) {
         const SkinnyPlan pl = skinny_plan((int)M, (int)N, (int)K, sm_count);
         *kernel = pl.cluster_splits >= 2 ? TL_PLAN_SKINNY_CLUSTER : TL_PLAN_SKINNY_STREAMK;
@@ -294,8 +303,10 @@ int tl_llama2_forward(tl_llama2* m, const int* tokens_host, int T, int start_pos
         TL_CUDA(cudaMemcpyAsync(logits_host, T == 1 ? e.last_logits() : e.logits(), (size_t)T * V * 2, cudaMemcpyDeviceToHost, nullptr));
     if (last_logits_host)
         TL_CUDA(cudaMemcpyAsync(last_logits_host, e.last_logits(), (size_t)V * 2, cudaMemcpyDeviceToHost, nullptr));
+    int* stat = status_slot(m);
+    TL_CUDA(cudaMemcpyAsync(stat, device_status_word(), sizeof(int), cudaMemcpyDeviceToHost, nullptr));
     TL_CUDA(cudaStreamSynchronize(nullptr));
-    return TL_OK;
+    return consume_device_status(*stat);
 }
 
 int tl_llama2_set_next_token(tl_llama2* m, int token) {
@@ -333,8 +344,11 @@ int tl_llama2_generate_at(tl_llama2* m, int start_pos, const int* prompt_host, i
     TL_PROPAGATE(e.set_tokens(tok, n_prompt, st));
     TL_PROPAGATE(e.forward(n_prompt, start_pos, false, st));
     TL_PROPAGATE(e.sample_last(n_prompt, st));
+    int* stat = status_slot(m);
     TL_CUDA(cudaMemcpyAsync(tok, e.d_next(), sizeof(int), cudaMemcpyDeviceToHost, st));
+    TL_CUDA(cudaMemcpyAsync(stat, device_status_word(), sizeof(int), cudaMemcpyDeviceToHost, st));
     TL_CUDA(cudaStreamSynchronize(st));
+    TL_PROPAGATE(consume_device_status(*stat));
     int next = tok[0];
     if (prefill_seconds) *prefill_seconds = std::chrono::duration<double>(clk::now() - t0).count();
     out_tokens_host[(*n_out)++] = next;
@@ -355,7 +369,9 @@ int tl_llama2_generate_at(tl_llama2* m, int start_pos, const int* prompt_host, i
             TL_PROPAGATE(e.sample_last(1, st));
         }
         TL_CUDA(cudaMemcpyAsync(tok, e.d_next(), sizeof(int), cudaMemcpyDeviceToHost, st));
+        TL_CUDA(cudaMemcpyAsync(stat, device_status_word(), sizeof(int), cudaMemcpyDeviceToHost, st));
         TL_CUDA(cudaStreamSynchronize(st));
+        TL_PROPAGATE(consume_device_status(*stat));
         next = tok[0];
         out_tokens_host[(*n_out)++] = next;
         pos++;
@@ -371,9 +387,12 @@ int tl_llama2_decode_device(tl_llama2* m, int start_pos, int steps, int* out_tok
     cudaStream_t st = as_stream(stream);
     TL_PROPAGATE(e.decode_steps(start_pos, steps, st));
     if (out_tokens_host && steps > 0) {
+        int* stat = status_slot(m);
         TL_CUDA(cudaMemcpyAsync(out_tokens_host, e.d_generated() + start_pos, (size_t)steps * sizeof(int),
                                 cudaMemcpyDeviceToHost, st));
+        TL_CUDA(cudaMemcpyAsync(stat, device_status_word(), sizeof(int), cudaMemcpyDeviceToHost, st));
         TL_CUDA(cudaStreamSynchronize(st));
+        return consume_device_status(*stat);
     }
     return TL_OK;
 }
@@ -457,6 +476,38 @@ int tl_rmsnorm_gateup_swiglu_f16(const tl_half* x, const tl_half* norm_w, float 
     a.W[0] = H(w1); a.W[1] = H(w3); a.n_mats = 2; a.N_each = hidden; a.K = dim;
     a.epilogue = EPI_SWIGLU; a.y = H(out); a.pdl = false;
     return launch_fused_gemv(a, as_stream(stream));
+}
+
+// Self-test of the bounded wait of the tensor-parallel exchange (see the header).
+int tl_selftest_unposted_exchange(int max_polls, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(max_polls >= 1 && max_polls <= (1 << 20), "max_polls must be in [1, 2^20]");
+    constexpr int K = 256, N = 64, WORLD = 2;
+    cudaStream_t st = as_stream(stream);
+    // [slots: WORLD x K words, all zero = epoch 0][step counter = 0][x, residual: K halfs each][W: N x K][y: N]
+    const size_t slot_bytes = (size_t)WORLD * K * sizeof(unsigned long long);
+    const size_t bytes = slot_bytes + 256 + (size_t)(2 * K + N * K + N) * sizeof(__half);
+    unsigned char* base = nullptr;
+    TL_CUDA(cudaMalloc(&base, bytes));
+    cudaError_t e = cudaMemsetAsync(base, 0, bytes, st);
+    int rc = e == cudaSuccess ? TL_OK : set_error(TL_ERR_CUDA, "memset failed: %s", cudaGetErrorString(e));
+    if (rc == TL_OK) {
+        __half* vec = reinterpret_cast<__half*>(base + slot_bytes + 256);
+        PeerExchange in{};
+        in.world = WORLD; in.rank = 0; in.n = K;
+        in.local_slots = reinterpret_cast<const unsigned long long*>(base);
+        in.step_ptr = reinterpret_cast<const unsigned int*>(base + slot_bytes);
+        in.phases_per_step = 1; in.phase_id = 0;          // expected epoch 1; the slots hold epoch 0 for ever
+        in.residual = vec + K; in.sum_out = nullptr;
+        FusedGemv f{};
+        f.x = vec; f.xin = &in; f.xin_tries = (unsigned)max_polls;
+        f.W[0] = vec + 2 * K; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = vec + 2 * K + N * K;
+        f.pdl = false;
+        rc = launch_fused_gemv(f, st);
+    }
+    cudaStreamSynchronize(st);      // the kernel must come back on its own; its only trace is the status word
+    cudaFree(base);
+    return rc;
 }
 
 int tl_llama2_decode_profile(tl_llama2* m, int start_pos, int cta, unsigned long long* stamps_host, int capacity,

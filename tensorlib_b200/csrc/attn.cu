@@ -513,10 +513,15 @@ extern "C" int tl_attn_decode_f16_noalloc(const tl_half* q, const tl_half* k_cac
     TL_REQUIRE((size_t)n_heads <= NOALLOC_MAX_HEADS,
                "tl_attn_decode_f16_noalloc: n_heads=%d exceeds the built-in scratch (max %zu heads); "
                "use tl_attn_decode_f16 with your own scratch", n_heads, NOALLOC_MAX_HEADS);
-    TL_REQUIRE((size_t)n_heads * splits * (head_dim + 2) <= NOALLOC_MAX_PARTIAL_FLOATS,
+    // bound every factor before forming the product, so that it cannot wrap below the limit
+    TL_REQUIRE(head_dim <= 256 && head_dim % 2 == 0 && splits <= 65535,
+               "tl_attn_decode_f16_noalloc: head_dim=%d (even, at most 256) or splits=%d (at most 65535) "
+               "exceeds the built-in scratch", head_dim, splits);
+    const size_t partial_floats = (size_t)n_heads * (size_t)splits * ((size_t)head_dim + 2);
+    TL_REQUIRE(partial_floats <= NOALLOC_MAX_PARTIAL_FLOATS,
                "tl_attn_decode_f16_noalloc: n_heads*splits*(head_dim+2)=%zu floats exceeds the built-in scratch "
                "(max %zu); use fewer splits or tl_attn_decode_f16 with your own scratch",
-               (size_t)n_heads * splits * (head_dim + 2), NOALLOC_MAX_PARTIAL_FLOATS);
+               partial_floats, NOALLOC_MAX_PARTIAL_FLOATS);
     int dev = -1;
     TL_CUDA(cudaGetDevice(&dev));
     TL_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "device index %d out of range", dev);

@@ -372,6 +372,10 @@ int Llama2Engine::linear(const __half* x, const __half* W, __half* y, int T, int
         launches_++;
         return launch_matmul_seq(p, st);
     }
+    if (gemv_ring_rows_supported(x, W, T, N, K, K, K)) {
+        launches_++;
+        return launch_gemv(x, W, y, T, N, K, K, K, N, st);
+    }
     if (T >= 2 && T <= 128 && skinny_supported(x, W, T, N, K, K, K)) {
         launches_++;
         return launch_skinny(x, W, y, T, N, K, K, K, N, st);

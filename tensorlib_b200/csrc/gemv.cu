@@ -8,10 +8,11 @@
 //  CTA's weight rows through a 3-stage shared-memory ring with TMA bulk copies
 //  (cp.async.bulk global -> shared, completion on an mbarrier): a stage holds 32 row-chunks of
 //  1024 halfs (64 KB), so ~190 KB per SM are in flight independent of what the consumers do.
-//  Sixteen consumer warps each own one "unit" of a stage (two weight rows), read it back with
-//  128-bit shared loads against the activation vector staged once in shared memory, accumulate
-//  in fp32, reduce with xor shuffles and apply the epilogue. HBM-bound; algorithmic bytes =
-//  2*(rows*K) + small vectors.
+//  Sixteen consumer warps multiply a stage on the tensor cores: the 32 weight rows are the M side
+//  of mma.sync.m16n8k16 (ldmatrix.x4 from the ring), the activation vector staged once in shared
+//  memory is column 0 of the B operand, and warp w owns the k16 steps [4w, 4w+4) of every chunk.
+//  The 16 per-warp partial sums of each row meet in shared memory at the end of a tile and warp 0
+//  applies the epilogue. HBM-bound; algorithmic bytes = 2*(rows*K) + small vectors.
 //  The neighbouring operators of the Llama2 block ride along: RMSNorm in the prologue (computed
 //  by the consumers while the producer is already streaming: weights never depend on the
 //  previous kernel, so the producer does not wait for it), RoPE + KV-cache write / residual add /
@@ -163,6 +164,8 @@ struct RingArgs {
     int wait_weights;             // the weight stream also waits for the previous kernel (generic entry point)
     int has_xin;                  // the activation vector is residual + sum of pushed partials
     PeerExchange xin, xout;
+    unsigned int xin_tries;       // polls of the slots before the tensor-parallel input wait gives up
+    int m_rows; long long ldx, ldy;   // k_gemv_ring_rows only: activation rows (2..8) and the pitches of x and y
 };
 
 // 16 bytes = two (payload, epoch) words, one volatile access (served by L2, where peer stores land)
@@ -196,6 +199,45 @@ __device__ __forceinline__ void unit_rows(const RingArgs& p, int unit, const __h
         ra = Wm + (long long)r * p.K;
         rb = ra + p.K;
     }
+}
+
+// The producer warp of both ring kernels: streams this CTA's weight rows, a stage (2*CW rows x one
+// 1024-half chunk) at a time, lane l copying row l of the stage with one bulk copy. Weights only:
+// in the model they never depend on the previous kernel; a caller of the plain matmul entry point
+// may have just written them (wait_weights).
+template <int EPI, int CW, int NST>
+__device__ __forceinline__ void ring_produce(const RingArgs& p, unsigned char* stages, uint32_t full0, uint32_t empty0,
+                                             int u_begin, int n_units, int nk, int n_iters, int lane) {
+    constexpr int CONSUMERS = CW, NSTAGES = NST, STAGE_BYTES = RingCfg<CW, NST>::STAGE_BYTES;
+    if (p.wait_weights) pdl_wait();
+    const uint64_t pol = policy_evict_first();
+    const __half* row_ptr = nullptr;
+    int cur_tile = -1, rows_in_tile = 0;
+    bool ok = true;
+    for (int it = 0; it < n_iters && ok; it++) {
+        const int s = it % NSTAGES, use = it / NSTAGES;
+        const int tile = it / nk, chunk = it - tile * nk;
+        if (tile != cur_tile) {
+            cur_tile = tile;
+            const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
+            rows_in_tile = units_here * 2;
+            if (lane < rows_in_tile) {
+                const __half *ra, *rb; int mat, r;
+                unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
+                row_ptr = (lane & 1) ? rb : ra;
+            }
+        }
+        if (use > 0) ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int kc = min(KC, p.K - chunk * KC);
+        if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
+        __syncwarp();
+        if (lane < rows_in_tile)
+            tma_load_1d(smem_u32(stages + (size_t)s * STAGE_BYTES + (size_t)lane * ROW_STRIDE),
+                        row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), full0 + 8 * s, pol);
+    }
+    if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
 
 template <int EPI, bool NORM, int CW, int NST>
@@ -233,37 +275,7 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
     pdl_launch_dependents();
 
     if (warp == CONSUMERS) {
-        // ---------------- producer: weights only; in the model they never depend on the previous
-        // kernel, a caller of the plain matmul entry point may have just written them ------------
-        if (p.wait_weights) pdl_wait();
-        const uint64_t pol = policy_evict_first();
-        const __half* row_ptr = nullptr;
-        int cur_tile = -1, rows_in_tile = 0;
-        bool ok = true;
-        for (int it = 0; it < n_iters && ok; it++) {
-            const int s = it % NSTAGES, use = it / NSTAGES;
-            const int tile = it / nk, chunk = it - tile * nk;
-            if (tile != cur_tile) {
-                cur_tile = tile;
-                const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
-                rows_in_tile = units_here * 2;
-                if (lane < rows_in_tile) {
-                    const __half *ra, *rb; int mat, r;
-                    unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
-                    row_ptr = (lane & 1) ? rb : ra;
-                }
-            }
-            if (use > 0) ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const int kc = min(KC, p.K - chunk * KC);
-            if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
-            __syncwarp();
-            if (lane < rows_in_tile)
-                tma_load_1d(smem_u32(stages + (size_t)s * STAGE_BYTES + (size_t)lane * ROW_STRIDE),
-                            row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), full0 + 8 * s, pol);
-        }
-        if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+        ring_produce<EPI, CW, NST>(p, stages, full0, empty0, u_begin, n_units, nk, n_iters, lane);
         return;
     }
 
@@ -282,7 +294,7 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
         const PeerExchange& e = p.xin;
         float s[8];
         bool all_here = false;
-        for (uint32_t tries = 0; tries < (WAIT_LIMIT >> 4) && !all_here; tries++) {
+        for (uint32_t tries = 0; tries < p.xin_tries && !all_here; tries++) {
             all_here = true;
 #pragma unroll
             for (int i = 0; i < 8; i++) s[i] = 0.f;
@@ -494,6 +506,130 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
 }
 
 // ---------------------------------------------------------------------------------------------
+// k_gemv_ring_rows: the same ring for 2..8 activation rows (tl_matmul2d_f16 with M = 2..8).
+// The B operand of mma.sync.m16n8k16 has eight columns; the M = 1 kernel fills column 0 only. Here
+// column m is activation row m, so up to eight rows cost the weight stream of one: the kernel
+// stays HBM-bound at 2*N*K bytes. The activation rows (up to 8 x K halfs) do not fit beside the
+// 3 x 64.5 KB ring, so they are not staged: every lane fetches its B fragments (row lane/4, two
+// 4-byte words per k16 step) for the coming chunk straight from global memory BEFORE it waits for
+// the chunk's weights, which hides the L1/L2 latency behind the HBM latency of the stage. Per-warp
+// partial sums [32 rows x 8 columns] meet in shared memory; warp w finishes the two rows of unit w.
+// ---------------------------------------------------------------------------------------------
+struct RowsCfg {
+    using Ring = RingCfg<16, 3>;
+    static constexpr int PART_FLOATS = 16 * Ring::STAGE_ROWS * 8;   // per buffer: [warp][row][column]
+    static size_t smem_bytes() {
+        return (size_t)3 * Ring::STAGE_BYTES + 2 * 3 * sizeof(uint64_t) + 16 + 2 * PART_FLOATS * sizeof(float);
+    }
+};
+
+__device__ __forceinline__ uint32_t ldg_u32(const __half* p) {
+    return __ldg(reinterpret_cast<const unsigned int*>(p));
+}
+
+__global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(RingArgs p) {
+    using Cfg = RingCfg<16, 3>;
+    constexpr int CONSUMERS = 16, NSTAGES = 3, STAGE_ROWS = Cfg::STAGE_ROWS, STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int STEPS_PER_WARP = Cfg::STEPS_PER_WARP;
+    extern __shared__ __align__(128) unsigned char smem[];
+    // layout: [3 stages][full barriers][empty barriers][pad][partials: 2 buffers]
+    unsigned char* stages = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGES * STAGE_BYTES);
+    float* partials = reinterpret_cast<float*>(smem + NSTAGES * STAGE_BYTES + 2 * NSTAGES * sizeof(uint64_t) + 16);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NSTAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int u_begin = (int)((long long)p.total_units * blockIdx.x / gridDim.x);
+    const int u_end = (int)((long long)p.total_units * (blockIdx.x + 1) / gridDim.x);
+    const int n_units = u_end - u_begin;
+    const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
+    const int nk = (p.K + KC - 1) / KC;
+    const int n_iters = n_tiles * nk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, CONSUMERS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == CONSUMERS) {
+        ring_produce<EPI_STORE, 16, 3>(p, stages, full0, empty0, u_begin, n_units, nk, n_iters, lane);
+        return;
+    }
+
+    pdl_wait();  // the activation rows may have been written by the previous kernel
+    const int g = lane >> 2, t = lane & 3;
+    const bool col_ok = g < p.m_rows;                         // column g of B = activation row g
+    const __half* xrow = p.x + (long long)(col_ok ? g : 0) * p.ldx + 2 * t;
+    const uint32_t lm_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + (lane >> 4) * 16);
+    bool ok = true;
+    int it = 0;
+    for (int tile = 0; tile < n_tiles && ok; tile++) {
+        const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int chunk = 0; chunk < nk; chunk++, it++) {
+            const int s = it % NSTAGES, use = it / NSTAGES;
+            const int steps = min(KC, p.K - chunk * KC) >> 4;
+            // this warp's B fragments of the chunk, in flight while the weights arrive
+            uint32_t b0[STEPS_PER_WARP], b1[STEPS_PER_WARP];
+#pragma unroll
+            for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
+                const int step = warp * STEPS_PER_WARP + kk;
+                b0[kk] = b1[kk] = 0u;
+                if (col_ok && step < steps) {
+                    const __half* xk = xrow + chunk * KC + step * 16;
+                    b0[kk] = ldg_u32(xk);
+                    b1[kk] = ldg_u32(xk + 8);
+                }
+            }
+            ok = mbar_wait(full0 + 8 * s, use & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t sbase = smem_u32(stages + (size_t)s * STAGE_BYTES) + lm_off;
+#pragma unroll
+            for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
+                const int step = warp * STEPS_PER_WARP + kk;
+                if (step < steps) {
+                    uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
+                    ldmatrix_x4(sbase + step * 32, a0, a1, a2, a3);
+                    mma_16816(acc0, a0, a1, a2, a3, b0[kk], b1[kk]);
+                    ldmatrix_x4(sbase + 16 * ROW_STRIDE + step * 32, c0, c1, c2, c3);
+                    mma_16816(acc1, c0, c1, c2, c3, b0[kk], b1[kk]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+        if (!ok) break;
+        // accumulator layout: d[0], d[1] = (row g, columns 2t, 2t+1); d[2], d[3] = (row g + 8, same columns)
+        float* part = partials + (tile & 1) * RowsCfg::PART_FLOATS + warp * (STAGE_ROWS * 8);
+        *reinterpret_cast<float2*>(part + g * 8 + 2 * t) = make_float2(acc0[0], acc0[1]);
+        *reinterpret_cast<float2*>(part + (g + 8) * 8 + 2 * t) = make_float2(acc0[2], acc0[3]);
+        *reinterpret_cast<float2*>(part + (g + 16) * 8 + 2 * t) = make_float2(acc1[0], acc1[1]);
+        *reinterpret_cast<float2*>(part + (g + 24) * 8 + 2 * t) = make_float2(acc1[2], acc1[3]);
+        consumer_bar_sync(CONSUMERS * 32);
+        // warp w finishes unit w of the tile: 2 rows x 8 columns = 16 sums of 16 partials; the two
+        // half-warps add eight partials each
+        const int o = lane & 15, hi = lane >> 4;
+        const float* src = partials + (tile & 1) * RowsCfg::PART_FLOATS + (2 * warp) * 8 + o;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) sum += src[(hi * 8 + w) * (STAGE_ROWS * 8)];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        const int col = o & 7;
+        if (hi == 0 && warp < units_here && col < p.m_rows) {
+            const int n = (u_begin + tile * CONSUMERS + warp) * 2 + (o >> 3);
+            p.y[(long long)col * p.ldy + n] = __float2half_rn(sum);
+        }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Plain GEMV for M rows of x (tl_matmul2d_f16 with M <= 8).
 // x is staged in K-tiles of KT halfs so that M*KT*2 bytes fit a 32 KB shared buffer.
 // ---------------------------------------------------------------------------------------------
@@ -606,6 +742,10 @@ bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, 
     return M >= 1 && M <= 8 && N >= 1 && K >= 8 && K % 8 == 0 && ldw % 8 == 0 && al16(x) && al16(W);
 }
 
+bool gemv_ring_rows_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw, size_t ldx) {
+    return M >= 2 && M <= 8 && gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0 && ldw == K && N % 2 == 0 && K % 16 == 0;
+}
+
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
                 long long ldx, long long ldy, cudaStream_t st) {
     TL_REQUIRE(gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0, "gemv: unsupported shape or alignment");
@@ -614,6 +754,17 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
         f.x = x; f.W[0] = W; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = y;
         f.pdl = true; f.weights_may_change = true;
         return launch_fused_gemv(f, st);
+    }
+    if (gemv_ring_rows_supported(x, W, M, N, K, ldw, ldx)) {   // up to eight rows at the weight traffic of one
+        static PerDeviceOnce once;
+        if (once.needed())
+            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
+        RingArgs a{};
+        a.x = x; a.W0 = W; a.N_each = N; a.K = K; a.total_units = N / 2; a.y = y;
+        a.status = device_status_word(); a.wait_weights = 1;
+        a.m_rows = M; a.ldx = ldx; a.ldy = ldy;
+        const int grid = std::max(1, std::min(sm_count(), (a.total_units + 7) / 8));
+        return launch_pdl(k_gemv_ring_rows, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
     }
     int KT = 16384 / M;                 // halfs per tile so that M*KT*2 <= 32 KB
     KT &= ~255;
@@ -652,6 +803,7 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
         TL_REQUIRE(q.xin->world >= 1 && q.xin->world <= TL_MAX_TP && q.xin->n == q.K && q.xin->residual,
                    "fused gemv: bad exchange input");
         a.xin = *q.xin;
+        a.xin_tries = q.xin_tries ? q.xin_tries : (WAIT_LIMIT >> 4);
     }
     if (q.epilogue == EPI_PUSH_F32 || q.epilogue == EPI_PUSH_F16) {
         TL_REQUIRE(q.xout && q.n_mats == 1 && q.xout->world >= 1 && q.xout->world <= TL_MAX_TP, "fused gemv: bad exchange output");

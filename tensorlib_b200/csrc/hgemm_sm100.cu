@@ -828,7 +828,9 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
-int g_plan_sms = 0;   // when non-zero, the planning functions use it instead of the device's SM count
+// when non-zero, the planning functions use it instead of the device's SM count; per thread, so a
+// host-only plan query on one thread cannot change what a launch on another thread decides
+thread_local int g_plan_sms = 0;
 int plan_sms() { return g_plan_sms > 0 ? g_plan_sms : sm_count(); }
 
 // Estimated cycles of the CTA-pair kernel. Per k-block a 256 x 256 pair tile measures ~590 cycles (512 of
@@ -919,8 +921,6 @@ int pick_bn(int mt, int N, int batch) {
 }  // namespace
 
 void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int* sk_per) {
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
     g_plan_sms = sms;
     const int mt = (M + BM - 1) / BM;
     *bn = pick_bn(mt, N, batch);

@@ -15,7 +15,10 @@ struct Tables {
 const Tables& tables();
 // int32 in device memory, 0 unless a kernel gave up on a bounded wait (then a tl_status code)
 int* device_status_word();
-// cos/sin tables [rows, head_dim/2] for positions [0, rows); grows on demand (sync + alloc).
+// turn a host copy of the status word (fetched at a sync point) into a return code; clears the word
+int consume_device_status(int value);
+// cos/sin tables [rows, head_dim/2] for positions [0, rows); grows on demand by allocating a larger
+// generation. Pointers handed out earlier stay valid for the life of the process.
 int rope_table(int head_dim, int min_rows, const __half** cos_t, const __half** sin_t);
 
 // ---- ops_refmode.cu: reference-order kernels (bit-identical to the reference CPU backend) ----
@@ -53,6 +56,8 @@ int launch_copy_rows(__half* dst, const __half* src, int rows, int dim, long lon
 bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw);
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
                 long long ldx, long long ldy, cudaStream_t st);
+// 2 <= M <= 8 on the weight-streaming ring (the activation rows are the columns of the MMA's B operand)
+bool gemv_ring_rows_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw, size_t ldx);
 
 enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGLU = 3, EPI_STORE_F32 = 4,
                     EPI_PUSH_F32 = 5, EPI_PUSH_F16 = 6 };
@@ -101,6 +106,7 @@ struct FusedGemv {
     bool pdl;                   // launch with programmatic stream serialization
     bool weights_may_change;    // the previous kernel of the stream may have written W: stream it after the wait
     const PeerExchange* xin;    // prologue: x = residual + sum over ranks of a pushed partial vector
+    unsigned int xin_tries;     // 0: the default bound on the polls of that wait (2^18, a few tenths of a second)
     const PeerExchange* xout;   // EPI_PUSH_F32 / EPI_PUSH_F16: where the results go on every rank
 };
 int launch_fused_gemv(const FusedGemv& p, cudaStream_t st);

@@ -25,6 +25,11 @@ struct RopeTable {
     __half* sin_t = nullptr;
 };
 std::vector<RopeTable> g_rope;
+// Tables that were replaced by a larger one. Their pointers may still be held by a model (and be
+// baked into its decode graph), so they stay allocated until the process exits; a generation is
+// rows * head_dim * 2 bytes, and the row count doubles, so all retired generations together are
+// smaller than the live one.
+std::vector<__half*> g_rope_retired;
 }  // namespace
 
 int set_error(int status, const char* fmt, ...) {
@@ -38,6 +43,17 @@ bool initialized() { return g_init; }
 int sm_count() { return g_sms; }
 const Tables& tables() { return g_tables; }
 int* device_status_word() { return g_status; }
+
+// `value` is a copy of the status word fetched at a synchronisation point. Non-zero: clear the
+// word on the device and report the failure to the caller instead of returning results computed
+// from partial or stale data.
+int consume_device_status(int value) {
+    if (value == 0) return TL_OK;
+    cudaMemset(g_status, 0, sizeof(int));
+    return set_error(value == TL_ERR_TIMEOUT ? TL_ERR_TIMEOUT : TL_ERR_CUDA,
+                     "a kernel gave up on a bounded device-side wait (status word %d): the results of this call are not valid",
+                     value);
+}
 
 // The three tables are functions half -> half, so 65536 entries each describe them completely.
 // They are evaluated with the same libm calls and the same conversions the reference's CPU
@@ -100,13 +116,17 @@ int rope_table(int head_dim, int min_rows, const __half** cos_t, const __half** 
         std::vector<__half> c((size_t)rows * half_dim), s((size_t)rows * half_dim);
         compute_rope_table(head_dim, rows, c.data(), s.data());
         __half *dc = nullptr, *ds = nullptr;
-        TL_CUDA(cudaDeviceSynchronize());  // earlier launches may still read the old table
         TL_CUDA(cudaMalloc(&dc, c.size() * 2));
-        TL_CUDA(cudaMalloc(&ds, s.size() * 2));
+        if (cudaMalloc(&ds, s.size() * 2) != cudaSuccess) {
+            cudaFree(dc);
+            return set_error(TL_ERR_OUT_OF_MEMORY, "rope table of %d rows", rows);
+        }
         TL_CUDA(cudaMemcpy(dc, c.data(), c.size() * 2, cudaMemcpyHostToDevice));
         TL_CUDA(cudaMemcpy(ds, s.data(), s.size() * 2, cudaMemcpyHostToDevice));
-        if (t->cos_t) cudaFree(t->cos_t);
-        if (t->sin_t) cudaFree(t->sin_t);
+        // a table that was handed out is never freed: earlier callers keep reading their generation
+        // (the first `rows` rows of every generation hold the same values)
+        if (t->cos_t) g_rope_retired.push_back(t->cos_t);
+        if (t->sin_t) g_rope_retired.push_back(t->sin_t);
         t->cos_t = dc;
         t->sin_t = ds;
         t->rows = rows;

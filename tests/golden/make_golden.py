@@ -13,7 +13,8 @@ unmodified reference sources, variable REF there) on seeded synthetic inputs and
   ops.npz           single operators on seeded inputs: matmul (several shapes incl. odd ones),
                     rms_norm, rotary embedding, softmax, silu, argmax.
   matmul_sweep.npz  the four (K, N) pairs of the sweep at M = 1 and 8: SHA-256 of the outputs and
-                    the first 64 values of each.
+                    the first 64 values of each; at M = 32, 128, 512 and 2048: three rows (first,
+                    one past the middle, last) x the first and last 32 columns.
 
 Only this script needs the reference checkout (through the built library); the tests read the .npz
 files. Usage:  make -C oracle ref && python tests/golden/make_golden.py
@@ -36,6 +37,12 @@ SEED = 20240229
 N_PROMPT, N_GEN = 16, 128
 KEEP_STEPS = (0, 1, 64, 127)
 SWEEP = ((4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000))
+SWEEP_LARGE_M = (32, 128, 512, 2048)
+
+
+def sweep_sample(M: int, N: int):
+    """Rows and columns of the large-M sweep points that the fixture pins."""
+    return np.array([0, M // 2 + 1, M - 1]), np.concatenate([np.arange(32), np.arange(N - 32, N)])
 
 
 def sha(a: np.ndarray) -> str:
@@ -67,6 +74,12 @@ def op_inputs():
 
 def main():
     ref = RefLib()
+    if "--only-sweep" not in sys.argv:
+        tiny_and_ops(ref)
+    sweep(ref)
+
+
+def tiny_and_ops(ref):
     # ---- tiny Llama2 ---------------------------------------------------------------------------
     cfg = synth.TINY
     payload = synth.llama2c_payload(cfg, SEED)
@@ -112,6 +125,9 @@ def main():
             ops[name] = ref.argmax(*args)
     np.savez_compressed(os.path.join(HERE, "ops.npz"), **ops)
 
+
+
+def sweep(ref):
     # ---- matmul sweep at CPU-affordable M -------------------------------------------------------
     sw = {}
     for (K, N) in SWEEP:
@@ -122,6 +138,10 @@ def main():
             sw[f"sha_K{K}_N{N}_M{M}"] = np.array(sha(y))
             sw[f"head_K{K}_N{N}_M{M}"] = y.reshape(-1)[:64].copy()
             print("sweep", K, N, M, sha(y)[:12])
+        for M in SWEEP_LARGE_M:       # every output element is an independent dot product: sample some
+            x = synth.normal_f16(SEED, synth.TID_SWEEP_X, M * K, 1.0).reshape(M, K)
+            rows, cols = sweep_sample(M, N)
+            sw[f"sample_K{K}_N{N}_M{M}"] = ref.matmul2d(np.ascontiguousarray(x[rows]), np.ascontiguousarray(W[cols]))
     np.savez_compressed(os.path.join(HERE, "matmul_sweep.npz"), **sw)
 
 

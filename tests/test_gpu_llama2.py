@@ -291,3 +291,46 @@ def test_long_context_decode_agrees_with_prefill_of_the_same_tokens(tl):
     with pytest.raises(tl.TLError):
         a.decode_device(2046, 3)              # would run past max_seq_len
     a.close(); b.close()
+
+
+def test_growing_the_shared_rope_table_leaves_a_models_table_valid(tl, golden_tiny, tiny_payload):
+    """A model keeps pointers into the cos/sin table of its head size (they are also baked into its
+    decode graph). A later call that needs more rows for the same head size allocates a larger
+    table; the model must go on reading valid memory and produce the same bits."""
+    m = make_model(tl, tiny_payload, tl.FAST)
+    prompt = golden_tiny["prompt"]
+    before = m.forward(prompt, 0, all_logits=False)
+    ids_before = m.decode_device(prompt.size, 12)
+    hd = synth.TINY.head_dim
+    x = synth.normal_f16(8, 1, 2 * 6 * hd, 1.0).reshape(2, 6, hd)
+    for pos in (300, 700, 3000):                          # beyond the 256 rows the model asked for: three regrowths
+        tl.apply_rotary_emb(x, pos)
+    junk = [tl.DeviceBuffer(256 * (hd // 2) * 2) for _ in range(64)]    # would reuse a freed table's memory
+    for j in junk:
+        tl.check(tl.load().tl_memset(j.ptr, 0xFF, j.nbytes, None), "memset")
+    tl.synchronize()
+    after = m.forward(prompt, 0, all_logits=False)
+    assert_bit_equal(after, before, "logits after the table grew")
+    assert np.array_equal(m.decode_device(prompt.size, 12), ids_before)
+    assert tl.device_status() == 0
+    m.close()
+
+
+def test_a_timed_out_device_wait_turns_into_an_error_return_of_the_model_call(tl, golden_tiny, tiny_payload):
+    """The model calls that synchronise read the device status word: after a kernel gave up on a
+    bounded wait they return TL_ERR_TIMEOUT instead of results, once, and then work again."""
+    m = make_model(tl, tiny_payload, tl.FAST)
+    prompt = golden_tiny["prompt"]
+    good = m.forward(prompt, 0, all_logits=False)
+    tl.check(tl.load().tl_selftest_unposted_exchange(256, None), "tl_selftest_unposted_exchange")
+    with pytest.raises(tl.TLError) as err:
+        m.forward(prompt, 0, all_logits=False)
+    assert err.value.status == 6 and "bounded" in str(err.value)
+    assert_bit_equal(m.forward(prompt, 0, all_logits=False), good, "next call")
+    tl.check(tl.load().tl_selftest_unposted_exchange(256, None), "tl_selftest_unposted_exchange")
+    with pytest.raises(tl.TLError) as err:
+        m.generate(prompt, 4)
+    assert err.value.status == 6
+    ids, _, _ = m.generate(prompt, 4)
+    assert ids.shape == (4,) and tl.device_status() == 0
+    m.close()

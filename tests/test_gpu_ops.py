@@ -279,3 +279,33 @@ def test_skinny_matmul_cluster_reduction_shapes(tl, oracle, M, N, K):
     got, want = tl.matmul2d(A, W, numerics=tl.FAST), oracle.matmul2d(A, W)
     assert tl.device_status() == 0
     assert max_rel_err(got, want) <= MATMUL_RTOL, (M, N, K)
+
+
+def test_bounded_wait_runs_out_and_the_library_stays_usable(tl, oracle):
+    """A consumer GEMV whose tensor-parallel input is never posted: the wait is limited to 1024
+    polls, the kernel returns by itself, the status word reads TL_ERR_TIMEOUT exactly once, and the
+    next ordinary call works. No trap, no fault, no unbounded spin."""
+    assert tl.device_status() == 0
+    tl.check(tl.load().tl_selftest_unposted_exchange(1024, None), "tl_selftest_unposted_exchange")
+    assert tl.device_status() == 6                        # TL_ERR_TIMEOUT
+    assert tl.device_status() == 0                        # reading it cleared it
+    A = synth.normal_f16(91, 1, 4096, 1.0).reshape(1, 4096)
+    W = synth.normal_f16(91, 2, 512 * 4096, 0.02).reshape(512, 4096)
+    assert max_rel_err(tl.matmul2d(A, W, numerics=tl.FAST), oracle.matmul2d(A, W)) <= MATMUL_RTOL
+    assert tl.device_status() == 0
+    assert tl.load().tl_selftest_unposted_exchange(0, None) == 1      # out-of-range limit is refused
+
+
+def test_batched_matmul_with_a_batch_stride_that_is_not_a_multiple_of_8(tl, oracle):
+    """Aligned pitches but an odd batch stride: the tensor-core kernels cannot take it, the call
+    must fall through to the any-shape kernel instead of failing."""
+    b, M, N, K = 3, 16, 24, 64
+    pad = 4                                               # batch stride M*K + 4 elements
+    A = synth.normal_f16(92, 1, b * (M * K + pad), 1.0)
+    Bt = synth.normal_f16(92, 2, b * N * K, 0.05).reshape(b, N, K)
+    dA, dB, dC = tl.DeviceBuffer.from_numpy(A), tl.DeviceBuffer.from_numpy(Bt), tl.DeviceBuffer(b * M * N * 2)
+    tl.check(tl.load().tl_matmul_batched_f16(dA.ptr, dB.ptr, dC.ptr, b, M, N, K, K, K, N, M * K + pad, N * K, M * N,
+                                             tl.FAST, None), "tl_matmul_batched_f16")
+    got = dC.to_numpy(np.float16, (b, M, N))
+    a3 = np.stack([A[i * (M * K + pad): i * (M * K + pad) + M * K].reshape(M, K) for i in range(b)])
+    assert max_rel_err(got, oracle.bmm_nt(np.ascontiguousarray(a3), Bt)) <= MATMUL_RTOL

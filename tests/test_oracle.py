@@ -124,3 +124,30 @@ def test_restatement_vs_reference_model(oracle, ref, tiny_payload):
         assert_bit_equal(ho, hr, "hidden states")
         assert_bit_equal(lo, lr, "prefill logits")
         assert_bit_equal(mo.forward(tok[:1], 12, mode), mr.forward(tok[:1], 12, mode), "decode logits")
+
+
+# ---- the RMSNorm of the reference at the 7B width --------------------------------------------------
+def test_cpu_rmsnorm_fp16_sum_loses_scale_at_dim_4096_and_the_cuda_route_does_not(oracle, ref):
+    """The reference's CPU RMSNorm adds the squares in fp16: once the running sum reaches 2048 an
+    addend below 1 is rounded away, so at dim 4096 the mean comes out too small and the result
+    3-5 % too large. The reference's CUDA kernel sums in fp32; the oracle restates both. This pins
+    the size of the effect (and that the restatement of the CPU form still equals the reference at
+    this width), which is why fast-numerics parity at dim 4096 is stated against the CUDA form."""
+    D = 4096
+    x = synth.normal_f16(41, 1, 3 * D, 1.0).reshape(3, D)
+    w = synth.normal_f16(41, 2, D, 1.0)
+    xf = x.astype(np.float64)
+    exact = xf / np.sqrt((xf * xf).mean(axis=1, keepdims=True) + 1e-5) * w.astype(np.float64)
+    cpu = oracle.rmsnorm(x, w)
+    assert_bit_equal(cpu, ref.rmsnorm(x, w), "CPU form at dim 4096")
+    big = np.abs(exact) > 0.5
+    ratio = cpu.astype(np.float64)[big] / exact[big]
+    assert 1.03 <= ratio.min() and ratio.max() <= 1.06, (ratio.min(), ratio.max())
+    cuda_form = oracle.rmsnorm_cuda_route(x, w).astype(np.float64)
+    # half(rms) carries 2^-11 relative error and the two fp16 roundings another 2^-11 each
+    assert np.abs(cuda_form - exact).max() <= 3 * 2.0 ** -11 * np.abs(exact).max()
+    # at the tiny model's width the two forms agree to fp16 rounding
+    xs = synth.normal_f16(41, 3, 2 * 288, 1.0).reshape(2, 288)
+    ws = np.ones(288, dtype=np.float16)
+    a, b = oracle.rmsnorm(xs, ws).astype(np.float64), oracle.rmsnorm_cuda_route(xs, ws).astype(np.float64)
+    assert np.abs(a - b).max() <= 4e-3 * np.abs(b).max()

@@ -61,8 +61,9 @@ def test_noalloc_attention_matches_the_allocating_entry_point_twice_in_a_row(tl)
 def test_noalloc_attention_rejects_requests_beyond_its_fixed_scratch(tl):
     lib = tl.load()
     d = tl.DeviceBuffer(1 << 16)
-    # 129 heads: over the head limit; 64 heads x 16 splits x 258: over the partial-result limit
-    for (h, hd, splits) in ((129, 16, 1), (64, 256, 16)):
+    # 129 heads: over the head limit; 64 heads x 16 splits x 258: over the partial-result limit;
+    # a head size and a split count whose product with the rest would wrap a 64-bit size
+    for (h, hd, splits) in ((129, 16, 1), (64, 256, 16), (2, 2 ** 31 - 2, 1), (128, 128, 2 ** 31 - 1)):
         rc = lib.tl_attn_decode_f16_noalloc(d.ptr, d.ptr, d.ptr, d.ptr, h, hd, 4, splits, None)
         assert rc == 1, "expected TL_ERR_INVALID_ARGUMENT"
         assert b"exceeds the built-in scratch" in lib.tl_last_error()
