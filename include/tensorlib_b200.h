@@ -105,6 +105,21 @@ TL_API int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_
 TL_API int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t batch, size_t M,
                           size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, size_t strideA,
                           size_t strideB, size_t strideC, int numerics, tl_stream stream);
+/* Device<half>::matmul, the strided batched form (tensorLib/include/device/Device.hpp:13-20; CUDA
+ * form tensorLib/src/device/cuda/gemm.cu:28-85, CPU form CPU.cpp:18-68): result is contiguous with
+ * shape result_shape[ndim] = (batch dims..., M, N); element (b..., m, k) of lhs sits at
+ * lhs[lhs_offset + sum_i b_i*lhs_stride[i] + m*lhs_stride[ndim-2] + k*lhs_stride[ndim-1]], element
+ * (b..., k, n) of rhs at rhs[rhs_offset + sum_i b_i*rhs_stride[i] + k*rhs_stride[ndim-2] +
+ * n*rhs_stride[ndim-1]] (a stride of 0 broadcasts). This is the call the legacy op
+ * ops::matmul::call makes (matmul.cpp:18-93). When the reduction dimension is contiguous in both
+ * operands (what Linear and the attention matmuls produce) fast numerics runs the same kernels as
+ * tl_matmul_batched_f16, one launch per innermost batch dimension; any other layout runs the
+ * any-stride kernel, which also is the reference-order path (sequential fp32 sum over k, one rounding,
+ * like the reference's CPU code; the reference's CUDA kernel accumulates in half). */
+TL_API int tl_matmul_strided_f16(const tl_half* lhs, const tl_half* rhs, tl_half* result, const int* lhs_stride_host,
+                                 const int* rhs_stride_host, size_t lhs_offset, size_t rhs_offset,
+                                 const int* result_shape_host, int ndim, size_t result_elements, size_t K, int numerics,
+                                 tl_stream stream);
 /* Host-only introspection (no device needed): the kernel tl_matmul2d_f16 selects in fast numerics for
  * 16-byte aligned operands on a device with sm_count SMs, and how the work is cut: CTAs launched,
  * tile width along N (the padded batch for the skinny kernels), k-blocks of 64 per CTA (skinny
@@ -149,6 +164,59 @@ TL_API int tl_argmax_f16(int* out_idx, const tl_half* in, size_t rows, size_t co
  * token ids read from device memory. */
 TL_API int tl_embedding_f16(tl_half* out, const tl_half* table, const int* tokens, int n_tokens, int dim,
                      int vocab, tl_stream stream);
+
+/* ---- the rest of the Device<half> surface (tensorLib/include/device/Device.hpp:30-78) -----------
+ * What an arbitrary Tensor<half> program needs from its device besides matmul. Arithmetic follows
+ * the reference's CPU backend bit for bit (tensorLib/src/device/cpu/CPU.cpp:127-402) except where
+ * noted; the kernels replace tensorLib/src/device/cuda/CUDA.cu:83-210, :440-464, binary.cuh:42-75
+ * and reduce.cuh:18-39. All are stream-ordered and return without synchronising. */
+/* Device::contiguous / setItemEwise / setItemScalar (Device.hpp:30-47): element i of the logical
+ * row-major order of `shape` lives at data[offset + sum_d idx_d * stride[d]] (convertIdx,
+ * CUDA.cuh:186-202). shape / stride: `ndim` <= 8 host ints (strides may be 0 for a broadcast view
+ * being read); n = product of shape < 2^32.
+ *   tl_contiguous_f16     result[i] = data[strided(i)]
+ *   tl_set_item_f16       data[strided(i)] = src[i]
+ *   tl_set_item_scalar_f16 data[strided(i)] = value */
+TL_API int tl_contiguous_f16(tl_half* result, const tl_half* data, const int* shape_host, const int* stride_host,
+                             int ndim, size_t offset, size_t n, tl_stream stream);
+TL_API int tl_set_item_f16(tl_half* data, const tl_half* src, const int* shape_host, const int* stride_host, int ndim,
+                           size_t offset, size_t n, tl_stream stream);
+TL_API int tl_set_item_scalar_f16(tl_half* data, tl_half value, const int* shape_host, const int* stride_host, int ndim,
+                                  size_t offset, size_t n, tl_stream stream);
+/* Device::neg .. rsqrt (Device.hpp:49-58, CPU.cpp:169-276): out[i] = f(in[i]), evaluated as the
+ * reference does (to float, libm function, one rounding). TL_UNARY_SILU is x*sigmoid(x) through
+ * float (the reference's CUDA kernel and CPU float route); TL_UNARY_SILU_CPU_HALF the CPU fp16
+ * route as shipped (see tl_silu_f16). sqrt / rsqrt of a value <= 0: the reference's CPU code throws
+ * std::domain_error (from inside an OpenMP region, which ends the process); like the reference's
+ * CUDA kernels this call cannot see the data without a synchronisation and returns the IEEE
+ * result instead (NaN, 0 or inf). */
+enum { TL_UNARY_NEG = 0, TL_UNARY_SIN = 1, TL_UNARY_COS = 2, TL_UNARY_EXP = 3, TL_UNARY_LOG = 4, TL_UNARY_ABS = 5,
+       TL_UNARY_TANH = 6, TL_UNARY_SILU = 7, TL_UNARY_SQRT = 8, TL_UNARY_RSQRT = 9, TL_UNARY_SILU_CPU_HALF = 10 };
+TL_API int tl_unary_f16(tl_half* out, const tl_half* in, size_t n, int op, tl_stream stream);
+/* Device::add / sub / mul / div with a tensor or a scalar, and pow with a scalar (Device.hpp:61-70,
+ * CPU.cpp:277-340): both operands to float, one operation, one rounding. A zero divisor: the
+ * reference's CPU code throws std::invalid_argument("Division by zero."); the scalar form does the
+ * same here (TL_ERR_INVALID_ARGUMENT), the tensor form returns the IEEE quotient like the
+ * reference's CUDA kernel. pow(0, negative) likewise gives inf instead of throwing. */
+enum { TL_BINARY_ADD = 0, TL_BINARY_SUB = 1, TL_BINARY_MUL = 2, TL_BINARY_DIV = 3, TL_BINARY_POW = 4 };
+TL_API int tl_binary_f16(tl_half* out, const tl_half* a, const tl_half* b, size_t n, int op, tl_stream stream);
+TL_API int tl_binary_scalar_f16(tl_half* out, const tl_half* a, tl_half scalar, size_t n, int op, tl_stream stream);
+/* Device::max / min / sum / mean over consecutive runs of reduce_size elements (Device.hpp:73-76,
+ * CPU.cpp:342-402): out[n / reduce_size]. TL_NUMERICS_REFERENCE_ORDER adds sequentially in fp16 like
+ * the reference (the mean divides by half(reduce_size)); TL_NUMERICS_FAST adds in fp32 and rounds
+ * once. max / min are exact in both (the first of several equal values wins). */
+enum { TL_REDUCE_MAX = 0, TL_REDUCE_MIN = 1, TL_REDUCE_SUM = 2, TL_REDUCE_MEAN = 3 };
+TL_API int tl_reduce_f16(tl_half* out, const tl_half* in, size_t reduce_size, size_t n, int op, int numerics,
+                         tl_stream stream);
+/* Device::argmax / argmin (Device.hpp:77-78, CPU.cpp:358-402): int32 index of the first extreme
+ * value of every run. want_min = 0: argmax (same result as tl_argmax_f16), 1: argmin. */
+TL_API int tl_argreduce_f16(int* out_idx, const tl_half* in, size_t reduce_size, size_t n, int want_min,
+                            tl_stream stream);
+/* type_cast (CPU.cpp:462-486, CUDA.cu:440-464): into half always through float with one rounding
+ * from float (an int32 beyond 2^24 is first rounded to float, as the reference does); half to int
+ * truncates toward zero. */
+enum { TL_CAST_F16_TO_F32 = 0, TL_CAST_F32_TO_F16 = 1, TL_CAST_F16_TO_I32 = 2, TL_CAST_I32_TO_F16 = 3 };
+TL_API int tl_cast(void* out, const void* in, size_t n, int kind, tl_stream stream);
 
 /* ---- fused decode stages (one token, fast numerics) ----------------------------------------
  * Each replaces a run of launches of the reference's decode step; the reference lines are the

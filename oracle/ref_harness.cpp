@@ -28,6 +28,7 @@
 #include "nn/linear.hpp"
 #include "nn/rmsNorm.hpp"
 #include "nn/embedding.hpp"
+#include "device/cpu/CPU.hpp"
 
 #include <cstdint>
 #include <cstring>
@@ -92,6 +93,18 @@ int ref_matmul2d_f16(const uint16_t* A, const uint16_t* B, uint16_t* C, int M, i
         CPU<half> dev;  // no storage of its own: matmul2d only uses its arguments
         dev.matmul2d(reinterpret_cast<const half*>(A), reinterpret_cast<const half*>(B),
                      reinterpret_cast<half*>(C), (size_t)M, (size_t)N, (size_t)K);
+    });
+}
+
+// Device<half>::matmul, the strided batched form (CPU.cpp:18-68), on the reference's CPU device object.
+int ref_matmul_strided_f16(const uint16_t* lhs, const uint16_t* rhs, uint16_t* result, const int* lhs_stride,
+                           const int* rhs_stride, size_t lhs_offset, size_t rhs_offset, const int* result_shape, int ndim,
+                           size_t result_elements, size_t K) {
+    return guarded([&] {
+        CPU<half> dev;
+        dev.matmul(reinterpret_cast<const half*>(lhs), reinterpret_cast<const half*>(rhs), reinterpret_cast<half*>(result),
+                   std::vector<int>(lhs_stride, lhs_stride + ndim), std::vector<int>(rhs_stride, rhs_stride + ndim), lhs_offset,
+                   rhs_offset, std::vector<int>(result_shape, result_shape + ndim), result_elements, K);
     });
 }
 
@@ -188,6 +201,136 @@ int ref_argmax_f16(const uint16_t* x, int* idx, int rows, int cols) {
         Tensor<half> xt = make_tensor({rows, cols}, x);
         Tensor<int> out = xt.argmax(-1, false);
         std::memcpy(idx, out.device->getDataPtr(), sizeof(int) * (size_t)rows);
+    });
+}
+
+// ---------------------------------------------------------------------------------------------
+// The rest of the Device<half> surface, straight on the reference's CPU<half> device object
+// (tensorLib/include/device/cpu/CPU.hpp): the virtuals a Tensor<half> program ends up calling.
+// ---------------------------------------------------------------------------------------------
+namespace {
+std::vector<int> ivec(const int* p, int n) { return std::vector<int>(p, p + n); }
+}
+
+int ref_contiguous_f16(uint16_t* result, const uint16_t* data, size_t data_elems, const int* shape, const int* stride,
+                       int ndim, size_t offset, size_t n) {
+    return guarded([&] {
+        CPU<half> dev(data_elems);
+        std::memcpy(dev.getDataPtr(), data, data_elems * sizeof(half));
+        dev.contiguous(reinterpret_cast<half*>(result), ivec(shape, ndim), ivec(stride, ndim), offset, n);
+    });
+}
+// value_or_src: a pointer to n source values (scalar == 0) or to one value (scalar != 0); `data` is updated in place
+int ref_set_item_f16(uint16_t* data, size_t data_elems, const uint16_t* value_or_src, int scalar, const int* shape,
+                     const int* stride, int ndim, size_t offset, size_t n) {
+    return guarded([&] {
+        CPU<half> dev(data_elems);
+        std::memcpy(dev.getDataPtr(), data, data_elems * sizeof(half));
+        if (scalar) {
+            half v;
+            std::memcpy(&v, value_or_src, sizeof v);
+            dev.setItemScalar(v, ivec(shape, ndim), ivec(stride, ndim), offset, n);
+        } else {
+            std::vector<half> src(n);
+            std::memcpy(src.data(), value_or_src, n * sizeof(half));
+            dev.setItemEwise(src.data(), ivec(shape, ndim), ivec(stride, ndim), offset, n);
+        }
+        std::memcpy(data, dev.getDataPtr(), data_elems * sizeof(half));
+    });
+}
+// op codes: TL_UNARY_* of include/tensorlib_b200.h. Inputs that make the reference throw inside its
+// OpenMP loop (sqrt / rsqrt of a value <= 0) must not be passed: that ends the process.
+int ref_unary_f16(const uint16_t* x, uint16_t* y, int n, int op) {
+    return guarded([&] {
+        if (op == 7) {                      // SiLU through the float route, as ref_silu_f16 does
+            Tensor<half> xt = make_tensor({n}, x);
+            Tensor<float> xf(xt);
+            Tensor<half> out(xf.silu());
+            copy_out(out, y);
+            return;
+        }
+        CPU<half> dev((size_t)n);
+        std::memcpy(dev.getDataPtr(), x, (size_t)n * sizeof(half));
+        half* r = reinterpret_cast<half*>(y);
+        switch (op) {
+            case 0: dev.neg(r, n); break;
+            case 1: dev.sin(r, n); break;
+            case 2: dev.cos(r, n); break;
+            case 3: dev.exp(r, n); break;
+            case 4: dev.log(r, n); break;
+            case 5: dev.abs(r, n); break;
+            case 6: dev.tanh(r, n); break;
+            case 8: dev.sqrt(r, n); break;
+            case 9: dev.rsqrt(r, n); break;
+            case 10: dev.silu(r, n); break;
+            default: throw std::invalid_argument("unknown unary op");
+        }
+    });
+}
+// 0 add, 1 sub, 2 mul, 3 div (no zero divisors: see above), 4 pow (scalar only)
+int ref_binary_f16(const uint16_t* a, const uint16_t* b, uint16_t* y, int n, int op) {
+    return guarded([&] {
+        CPU<half> dev((size_t)n);
+        std::memcpy(dev.getDataPtr(), a, (size_t)n * sizeof(half));
+        std::vector<half> other(n);
+        std::memcpy(other.data(), b, (size_t)n * sizeof(half));
+        half* r = reinterpret_cast<half*>(y);
+        switch (op) {
+            case 0: dev.add(r, other.data(), n); break;
+            case 1: dev.sub(r, other.data(), n); break;
+            case 2: dev.mul(r, other.data(), n); break;
+            case 3: dev.div(r, other.data(), n); break;
+            default: throw std::invalid_argument("unknown binary op");
+        }
+    });
+}
+int ref_binary_scalar_f16(const uint16_t* a, uint16_t s, uint16_t* y, int n, int op) {
+    return guarded([&] {
+        CPU<half> dev((size_t)n);
+        std::memcpy(dev.getDataPtr(), a, (size_t)n * sizeof(half));
+        half v;
+        std::memcpy(&v, &s, sizeof v);
+        half* r = reinterpret_cast<half*>(y);
+        switch (op) {
+            case 0: dev.add(r, v, n); break;
+            case 1: dev.sub(r, v, n); break;
+            case 2: dev.mul(r, v, n); break;
+            case 3: dev.div(r, v, n); break;
+            case 4: dev.pow(r, v, n); break;
+            default: throw std::invalid_argument("unknown binary op");
+        }
+    });
+}
+int ref_reduce_f16(const uint16_t* x, uint16_t* y, size_t reduce_size, size_t n, int op) {
+    return guarded([&] {
+        CPU<half> dev(n);
+        std::memcpy(dev.getDataPtr(), x, n * sizeof(half));
+        half* r = reinterpret_cast<half*>(y);
+        switch (op) {
+            case 0: dev.max(r, reduce_size, n); break;
+            case 1: dev.min(r, reduce_size, n); break;
+            case 2: dev.sum(r, reduce_size, n); break;
+            case 3: dev.mean(r, reduce_size, n); break;
+            default: throw std::invalid_argument("unknown reduce op");
+        }
+    });
+}
+int ref_argreduce_f16(const uint16_t* x, int* idx, size_t reduce_size, size_t n, int want_min) {
+    return guarded([&] {
+        CPU<half> dev(n);
+        std::memcpy(dev.getDataPtr(), x, n * sizeof(half));
+        if (want_min) dev.argmin(idx, reduce_size, n);
+        else dev.argmax(idx, reduce_size, n);
+    });
+}
+// 0 half->float, 1 float->half, 2 half->int, 3 int->half
+int ref_cast(const void* in, void* out, size_t n, int kind) {
+    return guarded([&] {
+        if (kind == 0) { CPU<float> d(0, nullptr); d.type_cast(static_cast<float*>(out), static_cast<const half*>(in), n); }
+        else if (kind == 1) { CPU<half> d(0, nullptr); d.type_cast(static_cast<half*>(out), static_cast<const float*>(in), n); }
+        else if (kind == 2) { CPU<int> d(0, nullptr); d.type_cast(static_cast<int*>(out), static_cast<const half*>(in), n); }
+        else if (kind == 3) { CPU<half> d(0, nullptr); d.type_cast(static_cast<half*>(out), static_cast<const int*>(in), n); }
+        else throw std::invalid_argument("unknown cast");
     });
 }
 

@@ -72,6 +72,17 @@ class _Lib:
         self._maxthr.restype = C.c_int
         self._setthr = getattr(L, p + "omp_set_threads")
         self._setthr.argtypes = [C.c_int]
+        ip, vp, sz = _i32p, C.c_void_p, C.c_size_t
+        for name, args in {
+            "unary_f16": [_u16p, _u16p, C.c_int, C.c_int],
+            "binary_f16": [_u16p, _u16p, _u16p, C.c_int, C.c_int],
+            "binary_scalar_f16": [_u16p, C.c_uint16, _u16p, C.c_int, C.c_int],
+            "reduce_f16": [_u16p, _u16p, sz, sz, C.c_int],
+            "argreduce_f16": [_u16p, ip, sz, sz, C.c_int],
+            "cast": [vp, vp, sz, C.c_int],
+            "matmul_strided_f16": [_u16p, _u16p, _u16p, ip, ip, sz, sz, ip, C.c_int, sz, sz],
+        }.items():
+            self._bind(name, args)
         self._bind_extra()
 
     def _bind_extra(self):
@@ -165,6 +176,58 @@ class _Lib:
         self._call("argmax_f16", _p16(x), _pi(idx), R, Cc)
         return idx
 
+    # -- the rest of the Device<half> surface (op names as in tensorlib_b200: UNARY_OPS, ...) -------
+    UNARY = {"neg": 0, "sin": 1, "cos": 2, "exp": 3, "log": 4, "abs": 5, "tanh": 6, "silu": 7, "sqrt": 8, "rsqrt": 9,
+             "silu_cpu_half": 10}
+    BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4}
+    REDUCE = {"max": 0, "min": 1, "sum": 2, "mean": 3}
+
+    def unary(self, x: np.ndarray, op: str) -> np.ndarray:
+        y = np.empty_like(x)
+        self._call("unary_f16", _p16(x), _p16(y), x.size, self.UNARY[op])
+        return y
+
+    def binary(self, a: np.ndarray, b, op: str) -> np.ndarray:
+        y = np.empty_like(a)
+        if np.ndim(b) == 0:
+            self._call("binary_scalar_f16", _p16(a), int(np.float16(b).view(np.uint16)), _p16(y), a.size, self.BINARY[op])
+        else:
+            self._call("binary_f16", _p16(a), _p16(np.ascontiguousarray(b)), _p16(y), a.size, self.BINARY[op])
+        return y
+
+    def reduce(self, x: np.ndarray, op: str) -> np.ndarray:
+        R, Cc = x.shape
+        y = np.empty(R, dtype=np.float16)
+        self._call("reduce_f16", _p16(x), _p16(y), Cc, x.size, self.REDUCE[op])
+        return y
+
+    def argreduce(self, x: np.ndarray, want_min: bool) -> np.ndarray:
+        R, Cc = x.shape
+        idx = np.empty(R, dtype=np.int32)
+        self._call("argreduce_f16", _p16(x), _pi(idx), Cc, x.size, int(want_min))
+        return idx
+
+    def cast(self, x: np.ndarray, to) -> np.ndarray:
+        kinds = {(np.float16, np.float32): 0, (np.float32, np.float16): 1, (np.float16, np.int32): 2, (np.int32, np.float16): 3}
+        x = np.ascontiguousarray(x)
+        y = np.empty(x.shape, dtype=to)
+        self._call("cast", x.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), x.size, kinds[(x.dtype.type, np.dtype(to).type)])
+        return y
+
+    def matmul_strided(self, lhs, rhs, lhs_stride, rhs_stride, lhs_offset, rhs_offset, result_shape, K) -> np.ndarray:
+        """Device::matmul with per-dimension strides over flat fp16 buffers."""
+        ls, rs, sh = (np.ascontiguousarray(v, dtype=np.int32) for v in (lhs_stride, rhs_stride, result_shape))
+        out = np.empty(tuple(result_shape), dtype=np.float16)
+        self._call("matmul_strided_f16", _p16(lhs), _p16(rhs), _p16(out), _pi(ls), _pi(rs), lhs_offset, rhs_offset, _pi(sh),
+                   sh.size, out.size, K)
+        return out
+
+    def contiguous(self, data: np.ndarray, shape, stride, offset: int = 0) -> np.ndarray:
+        raise NotImplementedError
+
+    def set_item(self, data: np.ndarray, src, shape, stride, offset: int = 0) -> np.ndarray:
+        raise NotImplementedError
+
     # -- model ---------------------------------------------------------------------------------
     def llama2(self, cfg, payload: np.ndarray) -> "_Model":
         return _Model(self, cfg, payload)
@@ -235,6 +298,24 @@ class RefLib(_Lib):
                                          C.POINTER(C.c_double)])
         self._cuda_count = self.lib.ref_cuda_device_count
         self._cuda_count.restype = C.c_int
+        self._bind("contiguous_f16", [_u16p, _u16p, C.c_size_t, _i32p, _i32p, C.c_int, C.c_size_t, C.c_size_t])
+        self._bind("set_item_f16", [_u16p, C.c_size_t, _u16p, C.c_int, _i32p, _i32p, C.c_int, C.c_size_t, C.c_size_t])
+
+    def contiguous(self, data, shape, stride, offset=0):
+        sh, sd = np.ascontiguousarray(shape, dtype=np.int32), np.ascontiguousarray(stride, dtype=np.int32)
+        n = int(np.prod(sh)) if sh.size else 1
+        out = np.empty(n, dtype=np.float16)
+        self._call("contiguous_f16", _p16(out), _p16(data), data.size, _pi(sh), _pi(sd), sh.size, offset, n)
+        return out.reshape(tuple(shape))
+
+    def set_item(self, data, src, shape, stride, offset=0):
+        sh, sd = np.ascontiguousarray(shape, dtype=np.int32), np.ascontiguousarray(stride, dtype=np.int32)
+        n = int(np.prod(sh)) if sh.size else 1
+        out = data.copy()
+        scalar = np.ndim(src) == 0
+        v = np.array([src], dtype=np.float16) if scalar else np.ascontiguousarray(src, dtype=np.float16).reshape(-1)
+        self._call("set_item_f16", _p16(out), out.size, _p16(v), int(scalar), _pi(sh), _pi(sd), sh.size, offset, n)
+        return out
 
     # -- the reference's CUDA backend (needs a GPU): a baseline and a cross-check, never an oracle ----
     def cuda_device_count(self) -> int:
@@ -264,6 +345,27 @@ class OracleLib(_Lib):
 
     def _bind_extra(self):
         self._bind("rmsnorm_cuda_route_f16", [_u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_float])
+        self._bind("contiguous_f16", [_u16p, _u16p, _i32p, _i32p, C.c_int, C.c_size_t, C.c_size_t])
+        self._bind("set_item_f16", [_u16p, _u16p, _i32p, _i32p, C.c_int, C.c_size_t, C.c_size_t])
+        self._bind("set_item_scalar_f16", [_u16p, C.c_uint16, _i32p, _i32p, C.c_int, C.c_size_t, C.c_size_t])
+
+    def contiguous(self, data, shape, stride, offset=0):
+        sh, sd = np.ascontiguousarray(shape, dtype=np.int32), np.ascontiguousarray(stride, dtype=np.int32)
+        n = int(np.prod(sh)) if sh.size else 1
+        out = np.empty(n, dtype=np.float16)
+        self._call("contiguous_f16", _p16(out), _p16(data), _pi(sh), _pi(sd), sh.size, offset, n)
+        return out.reshape(tuple(shape))
+
+    def set_item(self, data, src, shape, stride, offset=0):
+        sh, sd = np.ascontiguousarray(shape, dtype=np.int32), np.ascontiguousarray(stride, dtype=np.int32)
+        n = int(np.prod(sh)) if sh.size else 1
+        out = data.copy()
+        if np.ndim(src) == 0:
+            self._call("set_item_scalar_f16", _p16(out), int(np.float16(src).view(np.uint16)), _pi(sh), _pi(sd), sh.size, offset, n)
+        else:
+            self._call("set_item_f16", _p16(out), _p16(np.ascontiguousarray(src, dtype=np.float16).reshape(-1)), _pi(sh), _pi(sd),
+                       sh.size, offset, n)
+        return out
 
     def rmsnorm_cuda_route(self, x: np.ndarray, w: np.ndarray, eps: float = 1e-5) -> np.ndarray:
         """RMSNorm as the reference's CUDA backend computes it (fp32 sum of squares)."""

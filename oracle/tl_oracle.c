@@ -117,6 +117,29 @@ int orc_bmm_nt_f16(const h16* a, const h16* bt, h16* c, int B, int M, int N, int
     return 0;
 }
 
+/* Device::matmul, the strided batched form, CPU.cpp:18-68: one sequential fp32 dot product per
+ * result element, operands addressed through per-dimension strides. */
+int orc_matmul_strided_f16(const h16* lhs, const h16* rhs, h16* result, const int* lhs_stride, const int* rhs_stride,
+                           size_t lhs_offset, size_t rhs_offset, const int* result_shape, int ndim,
+                           size_t result_elements, size_t K) {
+    #pragma omp parallel for
+    for (size_t idx = 0; idx < result_elements; idx++) {
+        size_t lin = idx;
+        long long Aoff = (long long)lhs_offset, Boff = (long long)rhs_offset;
+        for (int i = ndim - 1; i >= 0; i--) {
+            int cur = (int)(lin % (size_t)result_shape[i]);
+            lin /= (size_t)result_shape[i];
+            if (i != ndim - 1) Aoff += (long long)cur * lhs_stride[i];
+            if (i != ndim - 2) Boff += (long long)cur * rhs_stride[i];
+        }
+        float sum = 0.0f;
+        const int t1 = lhs_stride[ndim - 1], t2 = rhs_stride[ndim - 2];
+        for (size_t k = 0; k < K; k++) sum += h2f(lhs[Aoff + (long long)k * t1]) * h2f(rhs[Boff + (long long)k * t2]);
+        result[idx] = f2h(sum);
+    }
+    return 0;
+}
+
 /* ---- nn::RMSNorm::forward_plain, rmsNorm.cpp:15-56 ------------------------------------------ */
 static int rmsnorm(const h16* x, const h16* w, h16* y, int T, int dim, float eps) {
     h16 heps = f2h(eps);                       /* float eps -> dtype scalar of operator+ */
@@ -238,6 +261,113 @@ static void argmax(const h16* x, int* idx, int rows, int cols) {
     }
 }
 int orc_argmax_f16(const h16* x, int* idx, int rows, int cols) { argmax(x, idx, rows, cols); return 0; }
+
+
+/* ==== the rest of the Device<half> surface (Device.hpp:30-78) ===================================== */
+/* convertIdx (CPU.cpp / CUDA.cuh:186-202): digits of i over shape, innermost last */
+static size_t convert_idx(size_t i, const int* shape, const int* stride, int ndim, size_t offset) {
+    long long off = 0;
+    for (int d = ndim - 1; d >= 0; d--) {
+        int cur = (int)(i % (size_t)shape[d]);
+        i /= (size_t)shape[d];
+        off += (long long)cur * stride[d];
+    }
+    return (size_t)(off + (long long)offset);
+}
+/* CPU::contiguous / setItemEwise / setItemScalar, CPU.cpp:127-167 */
+int orc_contiguous_f16(h16* result, const h16* data, const int* shape, const int* stride, int ndim, size_t offset, size_t n) {
+    for (size_t i = 0; i < n; i++) result[i] = data[convert_idx(i, shape, stride, ndim, offset)];
+    return 0;
+}
+int orc_set_item_f16(h16* data, const h16* src, const int* shape, const int* stride, int ndim, size_t offset, size_t n) {
+    for (size_t i = 0; i < n; i++) data[convert_idx(i, shape, stride, ndim, offset)] = src[i];
+    return 0;
+}
+int orc_set_item_scalar_f16(h16* data, h16 value, const int* shape, const int* stride, int ndim, size_t offset, size_t n) {
+    for (size_t i = 0; i < n; i++) data[convert_idx(i, shape, stride, ndim, offset)] = value;
+    return 0;
+}
+/* unary family, CPU.cpp:169-276. op codes as in include/tensorlib_b200.h (TL_UNARY_*). sqrt / rsqrt of
+ * a non-positive value make the reference throw; here they fail the call. */
+int orc_unary_f16(const h16* x, h16* y, int n, int op) {
+    for (int i = 0; i < n; i++) {
+        float f = h2f(x[i]);
+        switch (op) {
+            case 0: y[i] = f2h(-f); break;                       /* operator- of the host half: through float */
+            case 1: y[i] = f2h(sinf(f)); break;
+            case 2: y[i] = f2h(cosf(f)); break;
+            case 3: y[i] = f2h(expf(f)); break;
+            case 4: y[i] = f2h(logf(f)); break;
+            case 5: y[i] = f2h(fabsf(f)); break;
+            case 6: y[i] = f2h(tanhf(f)); break;
+            case 7: y[i] = silu_via_float(x[i]); break;
+            case 8: if (!(f > 0.0f)) return fail("Cannot take sqrt of non-positive values."); y[i] = f2h(sqrtf(f)); break;
+            case 9: if (!(f > 0.0f)) return fail("Cannot take sqrt of non-positive values."); y[i] = f2h(1 / sqrtf(f)); break;
+            case 10: y[i] = silu_half_as_is(x[i]); break;
+            default: return fail("unknown unary op");
+        }
+    }
+    return 0;
+}
+/* binary / scalar arithmetic, CPU.cpp:277-340: 0 add, 1 sub, 2 mul, 3 div, 4 pow */
+static int binop(h16 a, h16 b, int op, h16* out) {
+    switch (op) {
+        case 0: *out = hadd(a, b); return 0;
+        case 1: *out = hsub(a, b); return 0;
+        case 2: *out = hmul(a, b); return 0;
+        case 3: if (h2f(b) == 0) return fail("Division by zero."); *out = hdiv(a, b); return 0;
+        case 4: if (h2f(a) == 0 && h2f(b) < 0) return fail("Cannot take negative power of zero.");
+                *out = f2h(powf(h2f(a), h2f(b))); return 0;
+        default: return fail("unknown binary op");
+    }
+}
+int orc_binary_f16(const h16* a, const h16* b, h16* y, int n, int op) {
+    if (op == 4) return fail("pow takes a scalar exponent");
+    for (int i = 0; i < n; i++) if (binop(a[i], b[i], op, &y[i])) return 1;
+    return 0;
+}
+int orc_binary_scalar_f16(const h16* a, h16 s, h16* y, int n, int op) {
+    for (int i = 0; i < n; i++) if (binop(a[i], s, op, &y[i])) return 1;
+    return 0;
+}
+/* reductions over runs of reduce_size, CPU.cpp:342-402: 0 max, 1 min, 2 sum, 3 mean; sequential in fp16 */
+int orc_reduce_f16(const h16* x, h16* y, size_t reduce_size, size_t n, int op) {
+    h16 hsize = f2h((float)reduce_size);
+    for (size_t i = 0; i < n; i += reduce_size) {
+        h16 t = x[i];
+        for (size_t j = 1; j < reduce_size; j++) {
+            h16 v = x[i + j];
+            if (op == 0) t = (h2f(t) < h2f(v)) ? v : t;          /* std::max(a, b) */
+            else if (op == 1) t = (h2f(v) < h2f(t)) ? v : t;     /* std::min(a, b) */
+            else t = hadd(t, v);
+        }
+        if (op == 3) t = hdiv(t, hsize);
+        y[i / reduce_size] = t;
+    }
+    return 0;
+}
+int orc_argreduce_f16(const h16* x, int* idx, size_t reduce_size, size_t n, int want_min) {
+    for (size_t i = 0; i < n; i += reduce_size) {
+        h16 best = x[i]; int bi = 0;
+        for (size_t j = 1; j < reduce_size; j++) {
+            int better = want_min ? (h2f(x[i + j]) < h2f(best)) : (h2f(x[i + j]) > h2f(best));
+            if (better) { best = x[i + j]; bi = (int)j; }
+        }
+        idx[i / reduce_size] = bi;
+    }
+    return 0;
+}
+/* type_cast, CPU.cpp:462-486: 0 half->float, 1 float->half, 2 half->int (truncation), 3 int->half (through float) */
+int orc_cast(const void* in, void* out, size_t n, int kind) {
+    for (size_t i = 0; i < n; i++) {
+        if (kind == 0) ((float*)out)[i] = h2f(((const h16*)in)[i]);
+        else if (kind == 1) ((h16*)out)[i] = f2h(((const float*)in)[i]);
+        else if (kind == 2) ((int*)out)[i] = (int)h2f(((const h16*)in)[i]);
+        else if (kind == 3) ((h16*)out)[i] = f2h((float)((const int*)in)[i]);
+        else return fail("unknown cast");
+    }
+    return 0;
+}
 
 /* ---- Llama2 forward ---------------------------------------------------------------------------
  * Transformer::forward (Transformer.cpp:264-299) with TransformerBlock::forward (:162-178),

@@ -53,6 +53,7 @@ _SIGS = {
     "tl_matmul2d_f16": [_vp, _vp, _vp, _sz, _sz, _sz, _int, _vp],
     "tl_matmul_batched_f16": [_vp, _vp, _vp] + [_sz] * 10 + [_int, _vp],
     "tl_matmul2d_f16_host": [_vp, _vp, _vp, _sz, _sz, _sz, _int],
+    "tl_matmul_strided_f16": [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _vp, _int, _sz, _sz, _int, _vp],
     "tl_rms_norm_f16": [_vp, _vp, _vp, C.c_float, _int, _int, _int, _vp],
     "tl_apply_rotary_emb_f16": [_vp, _vp, _int, _int, _int, _int, _int, _vp],
     "tl_softmax_f16": [_vp, _vp, _sz, _sz, _int, _vp],
@@ -95,6 +96,15 @@ _SIGS = {
     "tl_tp_exchange_close": [_vp],
     "tl_tp_shard": [_int] * 5 + [C.POINTER(_int)] * 4,
     "tl_selftest_unposted_exchange": [_int, _vp],
+    "tl_contiguous_f16": [_vp, _vp, _vp, _vp, _int, _sz, _sz, _vp],
+    "tl_set_item_f16": [_vp, _vp, _vp, _vp, _int, _sz, _sz, _vp],
+    "tl_set_item_scalar_f16": [_vp, C.c_uint16, _vp, _vp, _int, _sz, _sz, _vp],
+    "tl_unary_f16": [_vp, _vp, _sz, _int, _vp],
+    "tl_binary_f16": [_vp, _vp, _vp, _sz, _int, _vp],
+    "tl_binary_scalar_f16": [_vp, _vp, C.c_uint16, _sz, _int, _vp],
+    "tl_reduce_f16": [_vp, _vp, _sz, _sz, _int, _int, _vp],
+    "tl_argreduce_f16": [_vp, _vp, _sz, _sz, _int, _vp],
+    "tl_cast": [_vp, _vp, _sz, _int, _vp],
 }
 _OTHER_RESTYPE = {"tl_strerror": (C.c_char_p, [_int]), "tl_last_error": (C.c_char_p, []),
                   "tl_version": (_int, [])}
@@ -239,6 +249,19 @@ def matmul_batched(A: np.ndarray, Bt: np.ndarray, numerics: int = FAST) -> np.nd
     return dC.to_numpy(np.float16, (b, M, N))
 
 
+def matmul_strided(lhs: np.ndarray, rhs: np.ndarray, lhs_stride, rhs_stride, lhs_offset: int, rhs_offset: int,
+                   result_shape, K: int, numerics: int = FAST) -> np.ndarray:
+    """Device::matmul on flat fp16 buffers with per-dimension strides (tl_matmul_strided_f16)."""
+    n = int(np.prod(result_shape))
+    ls, lsp = _ints(lhs_stride)
+    rs, rsp = _ints(rhs_stride)
+    sh, shp = _ints(result_shape)
+    dl, dr, dc = DeviceBuffer.from_numpy(lhs), DeviceBuffer.from_numpy(rhs), DeviceBuffer(max(n * 2, 2))
+    check(load().tl_matmul_strided_f16(dl.ptr, dr.ptr, dc.ptr, lsp, rsp, lhs_offset, rhs_offset, shp, len(result_shape), n, K,
+                                       numerics, None), "tl_matmul_strided_f16")
+    return dc.to_numpy(np.float16, tuple(result_shape))
+
+
 def _unary_like(fn_name, x: np.ndarray, *args):
     dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer(max(x.nbytes, 2))
     check(getattr(load(), fn_name)(dy.ptr, dx.ptr, *args), fn_name)
@@ -345,6 +368,83 @@ def rmsnorm_gateup_swiglu(x, norm_w, w1, w3, eps: float = 1e-5):
     check(load().tl_rmsnorm_gateup_swiglu_f16(dx.ptr, dn.ptr, eps, d1.ptr, d3.ptr, dy.ptr, hidden, dim, None),
           "tl_rmsnorm_gateup_swiglu_f16")
     return dy.to_numpy(np.float16, (hidden,))
+
+
+UNARY_OPS = {"neg": 0, "sin": 1, "cos": 2, "exp": 3, "log": 4, "abs": 5, "tanh": 6, "silu": 7, "sqrt": 8, "rsqrt": 9,
+             "silu_cpu_half": 10}
+BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4}
+REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3}
+
+
+def _ints(v):
+    a = np.ascontiguousarray(v, dtype=np.int32)
+    return a, a.ctypes.data_as(_vp)
+
+
+def contiguous(data: np.ndarray, shape, stride, offset: int = 0) -> np.ndarray:
+    """Device::contiguous of the view (shape, stride, offset) over the flat fp16 array `data`."""
+    n = int(np.prod(shape)) if len(shape) else 1
+    sh, shp = _ints(shape)
+    sd, sdp = _ints(stride)
+    dd, dr = DeviceBuffer.from_numpy(data), DeviceBuffer(max(n * 2, 2))
+    check(load().tl_contiguous_f16(dr.ptr, dd.ptr, shp, sdp, len(shape), offset, n, None), "tl_contiguous_f16")
+    return dr.to_numpy(np.float16, tuple(shape))
+
+
+def set_item(data: np.ndarray, src, shape, stride, offset: int = 0) -> np.ndarray:
+    """Device::setItemEwise (src an array of prod(shape) values) or setItemScalar (src a scalar)
+    into the view (shape, stride, offset) of `data`; returns the updated flat array."""
+    n = int(np.prod(shape)) if len(shape) else 1
+    sh, shp = _ints(shape)
+    sd, sdp = _ints(stride)
+    dd = DeviceBuffer.from_numpy(data)
+    if np.ndim(src) == 0:
+        bits = int(np.float16(src).view(np.uint16))
+        check(load().tl_set_item_scalar_f16(dd.ptr, bits, shp, sdp, len(shape), offset, n, None), "tl_set_item_scalar_f16")
+    else:
+        ds = DeviceBuffer.from_numpy(np.ascontiguousarray(src, dtype=np.float16))
+        check(load().tl_set_item_f16(dd.ptr, ds.ptr, shp, sdp, len(shape), offset, n, None), "tl_set_item_f16")
+    return dd.to_numpy(np.float16, data.shape)
+
+
+def unary(x: np.ndarray, op: str) -> np.ndarray:
+    return _unary_like("tl_unary_f16", x, x.size, UNARY_OPS[op], None)
+
+
+def binary(a: np.ndarray, b, op: str) -> np.ndarray:
+    """a (op) b with b an array of a's shape or a scalar."""
+    da, dy = DeviceBuffer.from_numpy(a), DeviceBuffer(max(a.nbytes, 2))
+    if np.ndim(b) == 0:
+        bits = int(np.float16(b).view(np.uint16))
+        check(load().tl_binary_scalar_f16(dy.ptr, da.ptr, bits, a.size, BINARY_OPS[op], None), "tl_binary_scalar_f16")
+    else:
+        db = DeviceBuffer.from_numpy(np.ascontiguousarray(b, dtype=np.float16))
+        check(load().tl_binary_f16(dy.ptr, da.ptr, db.ptr, a.size, BINARY_OPS[op], None), "tl_binary_f16")
+    return dy.to_numpy(np.float16, a.shape)
+
+
+def reduce(x: np.ndarray, op: str, numerics: int = FAST) -> np.ndarray:
+    """max / min / sum / mean over the last dimension of a 2-D array."""
+    R, Cc = x.shape
+    dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer(max(R * 2, 2))
+    check(load().tl_reduce_f16(dy.ptr, dx.ptr, Cc, x.size, REDUCE_OPS[op], numerics, None), "tl_reduce_f16")
+    return dy.to_numpy(np.float16, (R,))
+
+
+def argreduce(x: np.ndarray, want_min: bool) -> np.ndarray:
+    R, Cc = x.shape
+    dx, di = DeviceBuffer.from_numpy(x), DeviceBuffer(max(R * 4, 4))
+    check(load().tl_argreduce_f16(di.ptr, dx.ptr, Cc, x.size, int(want_min), None), "tl_argreduce_f16")
+    return di.to_numpy(np.int32, (R,))
+
+
+def cast(x: np.ndarray, to) -> np.ndarray:
+    """half <-> float32 / int32 through tl_cast."""
+    kinds = {(np.float16, np.float32): 0, (np.float32, np.float16): 1, (np.float16, np.int32): 2, (np.int32, np.float16): 3}
+    kind = kinds[(x.dtype.type, np.dtype(to).type)]
+    dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer(max(x.size * np.dtype(to).itemsize, 4))
+    check(load().tl_cast(dy.ptr, dx.ptr, x.size, kind, None), "tl_cast")
+    return dy.to_numpy(np.dtype(to), x.shape)
 
 
 PLAN_NAMES = {0: "reference_order", 1: "gemv_ring", 2: "gemv_small", 3: "skinny_streamk", 4: "skinny_cluster",

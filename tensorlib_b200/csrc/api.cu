@@ -101,6 +101,59 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
     return TL_OK;
 }
 
+// Device::matmul (Device.hpp:13-20): every batch dimension may have its own stride in either operand.
+// The innermost batch dimension becomes the batch of one launch; outer batch dimensions are walked
+// on the host. Operands whose reduction dimension is contiguous take the kernels tl_matmul_batched_f16
+// dispatches to; anything else takes the any-stride kernel.
+int tl_matmul_strided_f16(const tl_half* lhs, const tl_half* rhs, tl_half* result, const int* lhs_stride_host,
+                          const int* rhs_stride_host, size_t lhs_offset, size_t rhs_offset, const int* result_shape_host,
+                          int ndim, size_t result_elements, size_t K, int numerics, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(valid_numerics(numerics), "unknown numerics %d", numerics);
+    TL_REQUIRE(ndim >= 2 && ndim <= 8 && lhs_stride_host && rhs_stride_host && result_shape_host, "matmul: 2..8 dimensions");
+    size_t total = 1;
+    for (int i = 0; i < ndim; i++) {
+        TL_REQUIRE(result_shape_host[i] >= 0, "matmul: negative extent");
+        total *= (size_t)result_shape_host[i];
+    }
+    TL_REQUIRE(total == result_elements, "matmul: result_elements %zu is not the product of result_shape (%zu)", result_elements, total);
+    if (total == 0) return TL_OK;
+    TL_REQUIRE(lhs && rhs && result, "null matrix pointer");
+    const int* sh = result_shape_host;
+    const size_t M = (size_t)sh[ndim - 2], N = (size_t)sh[ndim - 1];
+    const long long a_m = lhs_stride_host[ndim - 2], a_k = lhs_stride_host[ndim - 1];
+    const long long b_k = rhs_stride_host[ndim - 2], b_n = rhs_stride_host[ndim - 1];
+    const int nb = ndim - 2;                                  // batch dimensions
+    const size_t inner = nb > 0 ? (size_t)sh[nb - 1] : 1;     // innermost batch dimension = one launch
+    const long long sA = nb > 0 ? lhs_stride_host[nb - 1] : 0, sB = nb > 0 ? rhs_stride_host[nb - 1] : 0;
+    size_t outer = 1;
+    for (int i = 0; i + 1 < nb; i++) outer *= (size_t)sh[i];
+    const bool k_contiguous = (K <= 1 || (a_k == 1 && b_k == 1)) && a_m >= (long long)K && b_n >= (long long)K && sA >= 0 && sB >= 0;
+    cudaStream_t st = as_stream(stream);
+    for (size_t o = 0; o < outer; o++) {
+        long long ao = (long long)lhs_offset, bo = (long long)rhs_offset;
+        size_t rem = o;
+        for (int i = nb - 2; i >= 0; i--) {                   // digits of o over the outer batch dimensions
+            const size_t d = rem % (size_t)sh[i];
+            rem /= (size_t)sh[i];
+            ao += (long long)d * lhs_stride_host[i];
+            bo += (long long)d * rhs_stride_host[i];
+        }
+        const tl_half* A = lhs + ao;
+        const tl_half* B = rhs + bo;
+        tl_half* C = result + o * inner * M * N;
+        if (k_contiguous && numerics == TL_NUMERICS_FAST) {
+            TL_PROPAGATE(tl_matmul_batched_f16(A, B, C, inner, M, N, K, (size_t)a_m, (size_t)b_n, N, (size_t)sA, (size_t)sB, M * N,
+                                               numerics, stream));
+        } else {
+            TL_REQUIRE(M < 65536, "matmul: more than 65535 rows with a strided reduction dimension");
+            SeqMatmul p{H(A), H(B), H(C), (int)inner, (int)M, (int)N, (int)K, a_m, a_k, b_n, b_k, (long long)N, sA, sB, (long long)(M * N)};
+            TL_PROPAGATE(launch_matmul_seq(p, st));
+        }
+    }
+    return TL_OK;
+}
+
 int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t M, size_t N, size_t K,
                     int numerics, tl_stream stream) {
     return tl_matmul_batched_f16(A, B, C, 1, M, N, K, K, K, N, 0, 0, 0, numerics, stream);
@@ -193,6 +246,64 @@ int tl_embedding_f16(tl_half* out, const tl_half* table, const int* tokens, int 
     TL_CHECK_INIT();
     TL_REQUIRE(out && table && tokens && dim > 0 && vocab > 0 && n_tokens >= 0, "embedding: bad arguments");
     return launch_embedding(H(out), H(table), tokens, n_tokens, dim, vocab, as_stream(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// The rest of the Device<half> surface (device_ops.cu)
+// ---------------------------------------------------------------------------------------------
+int tl_contiguous_f16(tl_half* result, const tl_half* data, const int* shape_host, const int* stride_host, int ndim,
+                      size_t offset, size_t n, tl_stream stream) {
+    TL_CHECK_INIT();
+    return launch_contiguous(H(result), H(data), shape_host, stride_host, ndim, offset, n, as_stream(stream));
+}
+int tl_set_item_f16(tl_half* data, const tl_half* src, const int* shape_host, const int* stride_host, int ndim,
+                    size_t offset, size_t n, tl_stream stream) {
+    TL_CHECK_INIT();
+    return launch_set_item(H(data), H(src), shape_host, stride_host, ndim, offset, n, as_stream(stream));
+}
+int tl_set_item_scalar_f16(tl_half* data, tl_half value, const int* shape_host, const int* stride_host, int ndim,
+                           size_t offset, size_t n, tl_stream stream) {
+    TL_CHECK_INIT();
+    __half_raw r;
+    r.x = value;
+    return launch_set_item_scalar(H(data), __half(r), shape_host, stride_host, ndim, offset, n, as_stream(stream));
+}
+int tl_unary_f16(tl_half* out, const tl_half* in, size_t n, int op, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(n == 0 || (out && in), "unary: null pointer");
+    return launch_unary(H(out), H(in), n, op, as_stream(stream));
+}
+int tl_binary_f16(tl_half* out, const tl_half* a, const tl_half* b, size_t n, int op, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(n == 0 || (out && a && b), "binary: null pointer");
+    TL_REQUIRE(op >= TL_BINARY_ADD && op <= TL_BINARY_DIV, "binary: op %d needs a scalar second operand or is unknown", op);
+    return launch_binary_op(H(out), H(a), H(b), n, op, as_stream(stream));
+}
+int tl_binary_scalar_f16(tl_half* out, const tl_half* a, tl_half scalar, size_t n, int op, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(n == 0 || (out && a), "binary: null pointer");
+    TL_REQUIRE(op >= TL_BINARY_ADD && op <= TL_BINARY_POW, "unknown binary op %d", op);
+    __half_raw r;
+    r.x = scalar;
+    const __half s(r);
+    if (op == TL_BINARY_DIV) TL_REQUIRE(__half2float(s) != 0.0f, "Division by zero.");   // divFunc, CPU.cpp:280-293
+    return launch_binary_scalar(H(out), H(a), s, n, op, as_stream(stream));
+}
+int tl_reduce_f16(tl_half* out, const tl_half* in, size_t reduce_size, size_t n, int op, int numerics, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(valid_numerics(numerics), "unknown numerics %d", numerics);
+    TL_REQUIRE(n == 0 || (out && in), "reduce: null pointer");
+    return launch_reduce(H(out), H(in), reduce_size, n, op, numerics, as_stream(stream));
+}
+int tl_argreduce_f16(int* out_idx, const tl_half* in, size_t reduce_size, size_t n, int want_min, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(n == 0 || (out_idx && in), "argreduce: null pointer");
+    return launch_argreduce(out_idx, H(in), reduce_size, n, want_min, as_stream(stream));
+}
+int tl_cast(void* out, const void* in, size_t n, int kind, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(n == 0 || (out && in), "cast: null pointer");
+    return launch_cast(out, in, n, kind, as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -51,6 +51,20 @@ int launch_residual_add_f32(__half* out, const __half* a, const float* sum32, si
 int launch_copy_rows(__half* dst, const __half* src, int rows, int dim, long long dst_pitch,
                      cudaStream_t st);
 
+// ---- device_ops.cu: the rest of the Device<half> surface ------------------------------------------
+int launch_contiguous(__half* result, const __half* data, const int* shape, const int* stride, int ndim, size_t offset,
+                      size_t n, cudaStream_t st);
+int launch_set_item(__half* data, const __half* src, const int* shape, const int* stride, int ndim, size_t offset,
+                    size_t n, cudaStream_t st);
+int launch_set_item_scalar(__half* data, __half value, const int* shape, const int* stride, int ndim, size_t offset,
+                           size_t n, cudaStream_t st);
+int launch_unary(__half* out, const __half* in, size_t n, int op, cudaStream_t st);
+int launch_binary_op(__half* out, const __half* a, const __half* b, size_t n, int op, cudaStream_t st);
+int launch_binary_scalar(__half* out, const __half* a, __half s, size_t n, int op, cudaStream_t st);
+int launch_reduce(__half* out, const __half* in, size_t reduce_size, size_t n, int op, int numerics, cudaStream_t st);
+int launch_argreduce(int* out_idx, const __half* in, size_t reduce_size, size_t n, int want_min, cudaStream_t st);
+int launch_cast(void* out, const void* in, size_t n, int kind, cudaStream_t st);
+
 // ---- gemv.cu: the decode path (M = 1..8), fast numerics ---------------------------------------
 // y[m, n] = sum_k x[m, k] W[n, k]; requires K % 8 == 0 and 16-byte aligned rows.
 bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw);

@@ -1,0 +1,210 @@
+// Drop-in check of include/tensorlib_b200_device.hpp: the same Device<half> virtual called on the
+// reference's own CUDA<half> object and on a B200 object, on the same device data, must agree
+// (exactly for data movement and index results, within one fp16 step for arithmetic that the two
+// evaluate with different float libraries, within the matmul tolerance for matmuls and sums).
+//
+// Built against the reference's headers and objects by `make -C oracle ref_shim`; `--link-only`
+// returns before anything touches CUDA, so building and linking it is itself a test on a host
+// without a GPU. Prints one line per operator and "SHIM OK" at the end.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "tensorlib_b200_device.hpp"
+
+namespace {
+
+int g_failures = 0;
+
+float h2f(half h) { return __half2float(h); }
+int ulp_key(half h) {
+    unsigned short u;
+    std::memcpy(&u, &h, 2);
+    return (u & 0x8000) ? -(int)(u & 0x7FFF) : (int)u;
+}
+std::vector<half> randoms(size_t n, float scale, unsigned seed, bool positive = false) {
+    std::vector<half> v(n);
+    unsigned long long s = seed * 0x9E3779B97F4A7C15ull + 12345;
+    for (size_t i = 0; i < n; i++) {
+        s = s * 6364136223846793005ull + 1442695040888963407ull;
+        float u = (float)((s >> 40) & 0xFFFFFF) / 16777216.0f;     // [0,1)
+        float x = positive ? (0.05f + u) * scale : (2.0f * u - 1.0f) * scale;
+        v[i] = __float2half(x);
+    }
+    return v;
+}
+void upload(half* dst, const std::vector<half>& v) { cudaMemcpy(dst, v.data(), v.size() * sizeof(half), cudaMemcpyHostToDevice); }
+template <typename T>
+std::vector<T> download(const T* src, size_t n) {
+    std::vector<T> v(n);
+    cudaDeviceSynchronize();
+    cudaMemcpy(v.data(), src, n * sizeof(T), cudaMemcpyDeviceToHost);
+    return v;
+}
+struct DevBuf {
+    half* p = nullptr;
+    explicit DevBuf(size_t n) { cudaMalloc(&p, (n ? n : 1) * sizeof(half)); cudaMemset(p, 0, (n ? n : 1) * sizeof(half)); }
+    ~DevBuf() { cudaFree(p); }
+};
+
+// mode 0: bit-exact; 1: at most `tol` fp16 steps apart; 2: |a-b| <= tol * max(|b|, rms(b))
+void compare(const std::string& what, const std::vector<half>& a, const std::vector<half>& b, int mode, double tol) {
+    double worst = 0, rms = 0;
+    for (half x : b) rms += (double)h2f(x) * h2f(x);
+    rms = std::sqrt(rms / (b.empty() ? 1 : b.size())) + 1e-30;
+    size_t bad = 0;
+    for (size_t i = 0; i < a.size(); i++) {
+        const float fa = h2f(a[i]), fb = h2f(b[i]);
+        if (std::isnan(fa) && std::isnan(fb)) continue;
+        double d;
+        if (mode == 2) d = std::fabs((double)fa - fb) / std::max((double)std::fabs(fb), rms);
+        else d = std::abs(ulp_key(a[i]) - ulp_key(b[i]));
+        worst = std::max(worst, d);
+        if (d > tol) bad++;
+    }
+    std::printf("%-34s %s  (worst %s %.4g)\n", what.c_str(), bad ? "MISMATCH" : "ok", mode == 2 ? "rel" : "steps", worst);
+    if (bad) g_failures++;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+    if (argc > 1 && std::string(argv[1]) == "--link-only") {
+        std::printf("linked: B200 overrides %zu-byte vtable of Device<half>\n", sizeof(B200));
+        return 0;
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { std::printf("no GPU\n"); return 2; }
+    tlb200::check(tl_init(0));
+
+    const size_t n = 1 << 16;
+    auto x = randoms(n, 4.0f, 1), y = randoms(n, 3.0f, 2), pos = randoms(n, 8.0f, 3, true);
+    // one object of each kind per input, sharing nothing
+    auto pair = [&](const std::vector<half>& data) {
+        auto r = std::make_shared<CUDA<half>>(data.size());
+        auto o = std::make_shared<B200>(data.size());
+        upload(r->getDataPtr(), data);
+        upload(o->getDataPtr(), data);
+        return std::make_pair(std::static_pointer_cast<Device<half>>(r), std::static_pointer_cast<Device<half>>(o));
+    };
+    DevBuf out_r(n), out_o(n), other(n);
+    upload(other.p, y);
+
+    // ---- unary family ------------------------------------------------------------------------------------
+    using Unary = void (Device<half>::*)(half*, size_t);
+    struct U { const char* name; Unary fn; bool positive; int steps; };
+    const U unaries[] = {{"neg", &Device<half>::neg, false, 0}, {"sin", &Device<half>::sin, false, 1}, {"cos", &Device<half>::cos, false, 1},
+                         {"exp", &Device<half>::exp, false, 1}, {"log", &Device<half>::log, true, 1}, {"abs", &Device<half>::abs, false, 0},
+                         {"tanh", &Device<half>::tanh, false, 1}, {"silu", &Device<half>::silu, false, 1},
+                         {"sqrt", &Device<half>::sqrt, true, 1}, {"rsqrt", &Device<half>::rsqrt, true, 1}};
+    for (const U& u : unaries) {
+        auto p = pair(u.positive ? pos : x);
+        (p.first.get()->*u.fn)(out_r.p, n);
+        (p.second.get()->*u.fn)(out_o.p, n);
+        compare(u.name, download(out_o.p, n), download(out_r.p, n), u.steps ? 1 : 0, u.steps);
+    }
+    // ---- binary with a tensor and with a scalar ---------------------------------------------------------------
+    {
+        auto p = pair(x);
+        const Device<half>&r = *p.first, &o = *p.second;
+        upload(other.p, pos);                                  // no zero divisors
+        r.add(out_r.p, other.p, n); o.add(out_o.p, other.p, n); compare("add", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        r.sub(out_r.p, other.p, n); o.sub(out_o.p, other.p, n); compare("sub", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        r.mul(out_r.p, other.p, n); o.mul(out_o.p, other.p, n); compare("mul", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        r.div(out_r.p, other.p, n); o.div(out_o.p, other.p, n); compare("div", download(out_o.p, n), download(out_r.p, n), 1, 1);
+        const half s = __float2half(1.75f);
+        r.add(out_r.p, s, n); o.add(out_o.p, s, n); compare("add scalar", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        r.sub(out_r.p, s, n); o.sub(out_o.p, s, n); compare("sub scalar", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        r.mul(out_r.p, s, n); o.mul(out_o.p, s, n); compare("mul scalar", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        r.div(out_r.p, s, n); o.div(out_o.p, s, n); compare("div scalar", download(out_o.p, n), download(out_r.p, n), 1, 1);
+        auto pp = pair(pos);
+        pp.first->pow(out_r.p, __float2half(2.0f), n); pp.second->pow(out_o.p, __float2half(2.0f), n);
+        compare("pow 2", download(out_o.p, n), download(out_r.p, n), 1, 1);
+    }
+    // ---- reductions over rows of 256 ------------------------------------------------------------------------
+    {
+        auto p = pair(x);
+        const Device<half>&r = *p.first, &o = *p.second;
+        const size_t rs = 256, rows = n / rs;
+        r.max(out_r.p, rs, n); o.max(out_o.p, rs, n); compare("max", download(out_o.p, rows), download(out_r.p, rows), 0, 0);
+        r.min(out_r.p, rs, n); o.min(out_o.p, rs, n); compare("min", download(out_o.p, rows), download(out_r.p, rows), 0, 0);
+        r.sum(out_r.p, rs, n); o.sum(out_o.p, rs, n); compare("sum", download(out_o.p, rows), download(out_r.p, rows), 2, 2e-2);
+        r.mean(out_r.p, rs, n); o.mean(out_o.p, rs, n); compare("mean", download(out_o.p, rows), download(out_r.p, rows), 2, 2e-2);
+        int *ir = nullptr, *io = nullptr;
+        cudaMalloc(&ir, rows * sizeof(int)); cudaMalloc(&io, rows * sizeof(int));
+        // the reference's CUDA argmax leaves ties unspecified; 24-bit random inputs rounded to fp16 do tie, so compare the VALUES picked
+        r.argmax(ir, rs, n); o.argmax(io, rs, n);
+        auto ar = download(ir, rows), ao = download(io, rows);
+        size_t bad = 0;
+        for (size_t i = 0; i < rows; i++) bad += h2f(x[i * rs + ar[i]]) != h2f(x[i * rs + ao[i]]);
+        std::printf("%-34s %s\n", "argmax (value picked)", bad ? "MISMATCH" : "ok"); g_failures += bad != 0;
+        r.argmin(ir, rs, n); o.argmin(io, rs, n);
+        ar = download(ir, rows); ao = download(io, rows);
+        bad = 0;
+        for (size_t i = 0; i < rows; i++) bad += h2f(x[i * rs + ar[i]]) != h2f(x[i * rs + ao[i]]);
+        std::printf("%-34s %s\n", "argmin (value picked)", bad ? "MISMATCH" : "ok"); g_failures += bad != 0;
+        cudaFree(ir); cudaFree(io);
+        r.softmax(out_r.p, rows, rs); o.softmax(out_o.p, rows, rs);
+        compare("softmax", download(out_o.p, n), download(out_r.p, n), 2, 2e-2);
+    }
+    // ---- strided copies: a (64, 32, 32) buffer read as its (32, 64, 32) transpose, written back through the same view
+    {
+        auto p = pair(x);
+        const std::vector<int> shape{32, 64, 32}, stride{32, 32 * 32, 1};
+        p.first->contiguous(out_r.p, shape, stride, 0, n); p.second->contiguous(out_o.p, shape, stride, 0, n);
+        compare("contiguous", download(out_o.p, n), download(out_r.p, n), 0, 0);
+        p.first->setItemEwise(other.p, shape, stride, 0, n); p.second->setItemEwise(other.p, shape, stride, 0, n);
+        compare("setItemEwise", download(p.second->getDataPtr(), n), download(p.first->getDataPtr(), n), 0, 0);
+        const std::vector<int> sub{8, 16}, sst{64, 2};
+        p.first->setItemScalar(__float2half(-3.5f), sub, sst, 5, 128); p.second->setItemScalar(__float2half(-3.5f), sub, sst, 5, 128);
+        compare("setItemScalar", download(p.second->getDataPtr(), n), download(p.first->getDataPtr(), n), 0, 0);
+    }
+    // ---- matmul2d: GEMV (K = 4096 takes the reference's gemv_v6), M = 16 and M = 300 (cuBLAS there) -----------------
+    for (int M : {1, 16, 300}) {
+        const size_t K = 4096, N = 512;
+        auto a = randoms(M * K, 1.0f, 10 + M), w = randoms(N * K, 0.05f, 20 + M);
+        DevBuf dA(M * K), dW(N * K), cr(M * N), co(M * N);
+        upload(dA.p, a); upload(dW.p, w);
+        CUDA<half> r; B200 o;
+        r.matmul2d(dA.p, dW.p, cr.p, M, N, K); o.matmul2d(dA.p, dW.p, co.p, M, N, K);
+        compare("matmul2d M=" + std::to_string(M), download(co.p, M * N), download(cr.p, M * N), 2, 1e-2);
+    }
+    // ---- batched strided matmul: (3, 8, 32) x (3, 32, 16), rhs given as its (3, 16, 32) storage; the reference's kernel
+    //      accumulates in half, hence the loose tolerance
+    {
+        const int Bn = 3, M = 8, K = 32, N = 16;
+        auto a = randoms(Bn * M * K, 1.0f, 31), w = randoms(Bn * N * K, 0.2f, 32);
+        DevBuf dA(a.size()), dW(w.size()), cr(Bn * M * N), co(Bn * M * N);
+        upload(dA.p, a); upload(dW.p, w);
+        CUDA<half> r; B200 o;
+        const std::vector<int> ls{M * K, K, 1}, rs{N * K, 1, K}, shape{Bn, M, N};
+        r.matmul(dA.p, dW.p, cr.p, ls, rs, 0, 0, shape, Bn * M * N, K);
+        o.matmul(dA.p, dW.p, co.p, ls, rs, 0, 0, shape, Bn * M * N, K);
+        compare("matmul (strided, batched)", download(co.p, Bn * M * N), download(cr.p, Bn * M * N), 2, 3e-2);
+    }
+    // ---- rotary embedding and RMSNorm ------------------------------------------------------------------------------
+    {
+        const int T = 4, H = 8, hd = 128;
+        auto v = randoms(T * H * hd, 1.0f, 41);
+        DevBuf in(v.size()), rr(v.size()), ro(v.size());
+        upload(in.p, v);
+        CUDA<half> r; B200 o;
+        r.apply_rotary_emb(in.p, rr.p, 37, 1, T, H, hd); o.apply_rotary_emb(in.p, ro.p, 37, 1, T, H, hd);
+        compare("apply_rotary_emb", download(ro.p, v.size()), download(rr.p, v.size()), 2, 1e-2);
+        const int hidden = 4096, tokens = 3;
+        auto xin = randoms(hidden * tokens, 2.0f, 42), wn = randoms(hidden, 1.0f, 43);
+        DevBuf dx(xin.size()), dw(hidden), nr(xin.size()), no(xin.size());
+        upload(dx.p, xin); upload(dw.p, wn);
+        r.rms_norm(nr.p, dx.p, dw.p, 1e-5f, hidden, tokens); o.rms_norm(no.p, dx.p, dw.p, 1e-5f, hidden, tokens);
+        compare("rms_norm", download(no.p, xin.size()), download(nr.p, xin.size()), 2, 1e-2);
+    }
+    int status = 0;
+    tlb200::check(tl_device_status(&status));
+    if (status != 0) { std::printf("device status %d\n", status); g_failures++; }
+    std::printf(g_failures ? "SHIM FAILED (%d)\n" : "SHIM OK\n", g_failures);
+    return g_failures ? 1 : 0;
+}

@@ -28,7 +28,11 @@ from tensorlib_b200 import synth  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 MATMUL_RTOL = 1e-2
-LOGIT_ATOL = 2e-2            # logits are O(1); same rule as the dim-512 model tests
+# Logits of a whole layer pass: |got - want| <= 2e-2 * max(|want|, rms of the row), i.e. the matmul
+# metric with twice its tolerance. (At this width the oracle itself sits 1.5e-2 away from float64
+# arithmetic in absolute terms, with logits of rms 1.3 and magnitude up to 6; the float64 check below
+# holds the fast path to the same distance from exact arithmetic as the reference's own.)
+LOGIT_RTOL = 2e-2
 LAYER = synth.LlamaConfig(dim=4096, hidden_dim=11008, n_layers=1, n_heads=32, vocab_size=2000, seq_len=256)
 
 
@@ -77,13 +81,49 @@ def layer_tensors(payload):
 
 def check_logits(got, want, what):
     got, want = got.astype(np.float32), want.astype(np.float32)
-    err = float(np.abs(got - want).max())
-    print(f"{what}: max abs logit error {err:.4f} over {got.shape[0]} positions")
-    assert err <= LOGIT_ATOL, f"{what}: max abs logit error {err}"
+    err, rel = float(np.abs(got - want).max()), max_rel_err(got, want)
+    print(f"{what}: max abs logit error {err:.4f}, relative (row-rms floor) {rel:.4f}, over {got.shape[0]} positions")
+    assert rel <= LOGIT_RTOL, f"{what}: max relative logit error {rel} (abs {err})"
     s = np.sort(want, axis=1)
     clear = (s[:, -1] - s[:, -2]) > 2 * err
     assert np.array_equal(got.argmax(1)[clear], want.argmax(1)[clear]), what
     return err
+
+
+def layer_forward_f64(payload, tokens):
+    """The same layer in float64 on the fp16 weights: exact arithmetic up to 1e-15."""
+    w, c = layer_tensors(payload), LAYER
+    f = lambda a: a.astype(np.float64)
+    emb = f(payload[:c.vocab_size * c.dim].reshape(c.vocab_size, c.dim))
+    T, H, hd = len(tokens), c.n_heads, c.head_dim
+
+    def norm(v, g):
+        return v / np.sqrt((v * v).mean(-1, keepdims=True) + 1e-5) * f(g)
+
+    def rope(v):
+        v = v.reshape(T, H, hd // 2, 2)
+        th = np.arange(T)[:, None] / (10000.0 ** (np.arange(0, hd, 2) / hd))[None, :]
+        cs, sn = np.cos(th)[:, None, :], np.sin(th)[:, None, :]
+        out = np.empty_like(v)
+        out[..., 0] = v[..., 0] * cs - v[..., 1] * sn
+        out[..., 1] = v[..., 0] * sn + v[..., 1] * cs
+        return out.reshape(T, H * hd)
+
+    x = emb[tokens]
+    xn = norm(x, w["attention_norm"])
+    q, k, v = rope(xn @ f(w["wq"]).T), rope(xn @ f(w["wk"]).T), xn @ f(w["wv"]).T
+    att = np.empty_like(q)
+    for h in range(H):
+        sl = slice(h * hd, (h + 1) * hd)
+        s = q[:, sl] @ k[:, sl].T / np.sqrt(float(hd))
+        s[np.triu_indices(T, 1)] = -np.inf
+        pr = np.exp(s - s.max(1, keepdims=True))
+        att[:, sl] = (pr / pr.sum(1, keepdims=True)) @ v[:, sl]
+    hres = x + att @ f(w["wo"]).T
+    xn = norm(hres, w["ffn_norm"])
+    g, u = xn @ f(w["w1"]).T, xn @ f(w["w3"]).T
+    x2 = hres + ((g / (1 + np.exp(-g))) * u) @ f(w["w2"]).T
+    return norm(x2, payload[-c.dim:]) @ emb.T
 
 
 def test_fast_numerics_7b_layer_prefill_continuation_and_decode(tl, oracle, layer):
@@ -93,7 +133,12 @@ def test_fast_numerics_7b_layer_prefill_continuation_and_decode(tl, oracle, laye
     mo = oracle.llama2(LAYER, layer)
     CUDA_NORM = 3                                    # SiLU through float + RMSNorm with an fp32 sum
     # fused prefill (tcgen05 HGEMMs with the RoPE / residual / SiLU*up epilogues, flash attention)
-    check_logits(m.forward(tokens[:200], 0, all_logits=True), mo.forward(tokens[:200], 0, CUDA_NORM), "prefill T=200")
+    got200, want200 = m.forward(tokens[:200], 0, all_logits=True), mo.forward(tokens[:200], 0, CUDA_NORM)
+    check_logits(got200, want200, "prefill T=200")
+    exact = layer_forward_f64(layer, tokens[:200])
+    e_fast, e_oracle = np.abs(got200.astype(np.float64) - exact).max(), np.abs(want200.astype(np.float64) - exact).max()
+    print(f"against float64: fast path {e_fast:.4f}, oracle {e_oracle:.4f}")
+    assert e_fast <= 1.25 * e_oracle + 2e-3, (e_fast, e_oracle)
     # chunked continuations over the same cache: 12 rows (skinny kernel), then 3 rows (GEMV ring, 3 columns)
     check_logits(m.forward(tokens[200:212], 200, all_logits=True), mo.forward(tokens[200:212], 200, CUDA_NORM), "chunk T=12")
     check_logits(m.forward(tokens[212:215], 212, all_logits=True), mo.forward(tokens[212:215], 212, CUDA_NORM), "chunk T=3")

@@ -151,3 +151,62 @@ def test_cpu_rmsnorm_fp16_sum_loses_scale_at_dim_4096_and_the_cuda_route_does_no
     ws = np.ones(288, dtype=np.float16)
     a, b = oracle.rmsnorm(xs, ws).astype(np.float64), oracle.rmsnorm_cuda_route(xs, ws).astype(np.float64)
     assert np.abs(a - b).max() <= 4e-3 * np.abs(b).max()
+
+
+# ---- the rest of the Device<half> surface: restatement against the reference's CPU<half> ------------
+def test_restatement_vs_reference_unary_binary_reduce_cast(oracle, ref):
+    import device_cases as dc
+    fin, pos = dc.finite_halfs(), dc.positive_halfs()
+    for op in dc.UNARY_ON_ALL:
+        assert_bit_equal(oracle.unary(fin, op), ref.unary(fin, op), op)
+    for op in dc.UNARY_ON_POSITIVE:
+        assert_bit_equal(oracle.unary(pos, op), ref.unary(pos, op), op)
+    rolled = np.ascontiguousarray(np.roll(fin, 777))
+    for op in ("add", "sub", "mul"):
+        assert_bit_equal(oracle.binary(fin, rolled, op), ref.binary(fin, rolled, op), op)
+    nz = np.ascontiguousarray(np.roll(pos, 4321)[:fin.size - 30000])
+    a = np.ascontiguousarray(fin[:nz.size])
+    assert_bit_equal(oracle.binary(a, nz, "div"), ref.binary(a, nz, "div"), "div")
+    for s in dc.SCALARS:
+        for op in ("add", "sub", "mul", "div"):
+            assert_bit_equal(oracle.binary(fin, s, op), ref.binary(fin, s, op), f"{op} {s}")
+        assert_bit_equal(oracle.binary(pos, s, "pow"), ref.binary(pos, s, "pow"), f"pow {s}")
+    x = synth.normal_f16(19, 1, 37 * 301, 2.0).reshape(37, 301)
+    x[3, 5] = x[3, 200] = x[3].max()                       # ties: the first one wins
+    x[4, :] = 0.0
+    x[4, 17] = -0.0
+    for op in ("max", "min", "sum", "mean"):
+        assert_bit_equal(oracle.reduce(x, op), ref.reduce(x, op), op)
+    assert np.array_equal(oracle.argreduce(x, False), ref.argreduce(x, False))
+    assert np.array_equal(oracle.argreduce(x, True), ref.argreduce(x, True))
+    wide = synth.normal_f16(19, 2, 3 * 5000, 1.0).reshape(3, 5000)   # long rows: the fp16 running sum drifts
+    assert_bit_equal(oracle.reduce(wide, "sum"), ref.reduce(wide, "sum"), "sum of 5000")
+    assert_bit_equal(oracle.reduce(wide, "mean"), ref.reduce(wide, "mean"), "mean of 5000")
+    assert np.array_equal(oracle.cast(fin, np.float32), ref.cast(fin, np.float32))
+    f32 = (np.random.default_rng(5).standard_normal(20000) * 300).astype(np.float32)
+    assert_bit_equal(oracle.cast(f32, np.float16), ref.cast(f32, np.float16), "float -> half")
+    small = np.ascontiguousarray(fin[np.abs(fin.astype(np.float32)) < 30000])
+    assert np.array_equal(oracle.cast(small, np.int32), ref.cast(small, np.int32))
+    i32 = np.random.default_rng(6).integers(-70000, 70000, 20000).astype(np.int32)
+    assert_bit_equal(oracle.cast(i32, np.float16), ref.cast(i32, np.float16), "int -> half")
+
+
+def test_restatement_vs_reference_strided_copies(oracle, ref):
+    import device_cases as dc
+    for view in dc.STRIDED_VIEWS:
+        name, _, shape, stride, offset = view
+        buf = dc.buffer_for(view)
+        want = ref.contiguous(buf, shape, stride, offset)
+        assert_bit_equal(oracle.contiguous(buf, shape, stride, offset), want, name)
+        if 0 in stride:
+            continue                                       # writing through a broadcast view is a race in the reference
+        src = synth.normal_f16(18, 3, int(np.prod(shape)), 1.0)
+        assert_bit_equal(oracle.set_item(buf, src, shape, stride, offset), ref.set_item(buf, src, shape, stride, offset), name)
+        assert_bit_equal(oracle.set_item(buf, 2.5, shape, stride, offset), ref.set_item(buf, 2.5, shape, stride, offset), name)
+
+
+def test_restatement_vs_reference_strided_batched_matmul(oracle, ref):
+    import device_cases as dc
+    for name, lhs, rhs, ls, rs, lo, ro, shape, K in dc.strided_matmul_cases():
+        assert_bit_equal(oracle.matmul_strided(lhs, rhs, ls, rs, lo, ro, shape, K),
+                         ref.matmul_strided(lhs, rhs, ls, rs, lo, ro, shape, K), name)
