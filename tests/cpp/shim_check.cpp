@@ -171,7 +171,8 @@ int main(int argc, char** argv) {
         upload(dA.p, a); upload(dW.p, w);
         CUDA<half> r; B200 o;
         r.matmul2d(dA.p, dW.p, cr.p, M, N, K); o.matmul2d(dA.p, dW.p, co.p, M, N, K);
-        compare("matmul2d M=" + std::to_string(M), download(co.p, M * N), download(cr.p, M * N), 2, 1e-2);
+        // M > 1 is cublasHgemm on the reference side, which also accumulates in half: K = 4096 costs it ~1e-2
+        compare("matmul2d M=" + std::to_string(M), download(co.p, M * N), download(cr.p, M * N), 2, M == 1 ? 1e-2 : 3e-2);
     }
     // ---- batched strided matmul: (3, 8, 32) x (3, 32, 16), rhs given as its (3, 16, 32) storage; the reference's kernel
     //      accumulates in half, hence the loose tolerance
