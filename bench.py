@@ -436,6 +436,22 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                "ms_per_step_max": max(times) / K, "tokens_per_s_min": K / (max(times) * 1e-3),
                "tokens_per_s_max": K / (min(times) * 1e-3)}
 
+    if args.profile_step:
+        barrier()
+        stamps = np.stack([model.decode_profile(pos0 + K, 0).astype(np.float64) for _ in range(3)])[-1]
+        if rank == 0:
+            L = cfg.n_layers
+            per = stamps[1:1 + 4 * L].reshape(L, 4, 3) if world > 1 and fused else stamps[:4 * L].reshape(L, 4, 3)
+            names = ["wo", "gate/up", "w2", "qkv(next)"] if world > 1 and fused else ["qkv", "wo", "gate/up", "w2"]
+            rep = {}
+            for i, nm in enumerate(names):
+                rep[nm] = {"wait_us": float(np.median(per[:, i, 1] - per[:, i, 0]) / 1e3),
+                           "work_us": float(np.median(per[:, i, 2] - per[:, i, 1]) / 1e3)}
+                if i + 1 < len(names):
+                    rep[nm]["gap_to_next_us"] = float(np.median(per[:, i + 1, 0] - per[:, i, 2]) / 1e3)
+            rep["layer_us"] = float(np.median(np.diff(per[:, 0, 0])) / 1e3)
+            rep["step_us"] = float((stamps[-1, 2] - stamps[0, 0]) / 1e3)
+            print(json.dumps({"profiling_only": True, "n_gpus": world, "decode_step_phases": rep}), flush=True)
     # end to end through the reference-facing generate(): id host->device->host every step
     barrier()
     if args.skip_prefill:
@@ -640,6 +656,9 @@ def main():
     ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1 decode: partial sums exchanged by peer stores inside the GEMV kernels (default) "
                          "or by ncclAllReduce between them")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="profiling only: after the timed region run one decode step with device timestamps and "
+                         "print the per-phase microseconds of rank 0 (median over layers)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="profiling only: just the 2048-token prefill (combine with --layers for a small capture)")
     args = ap.parse_args()

@@ -325,9 +325,13 @@ TL_API int tl_llama2_kernel_launches(tl_llama2* m, long long* launches); /* kern
 TL_API int tl_llama2_weight_bytes(tl_llama2* m, long long* bytes);       /* on this rank */
 /* Tracing aid (the reference only has wall-clock prints, llama2.cpp:35-99): run ONE decode step
  * at start_pos (token = the id in the device slot) and return device timestamps (ns, %globaltimer)
- * taken by CTA `cta` for every phase of the one-kernel step: stamps_host[phase][3] = {phase work
- * starts (grid barrier passed), activation vector staged, phase work done}. Phases per layer:
- * qkv, attention, wo, gate/up, w2; then the classifier. capacity = entries available. */
+ * per GEMV phase: stamps_host[phase][3] = {the phase's first instruction, activation vector staged
+ * (under tensor parallelism: the exchanged partial sums have arrived and are added), phase done}.
+ * Default decode path (graph of kernels): the step runs as plain launches, CTA 0 of every kernel
+ * stamps; phases in launch order are qkv, wo, gate/up, w2 per layer, then the classifier
+ * (4 * n_layers + 1; attention is the gap between a qkv and the following wo). one_kernel_decode:
+ * CTA `cta` stamps qkv, attention, wo, gate/up, w2 per layer, then the classifier. Every rank of a
+ * tensor-parallel group must call it together. capacity = entries available. */
 TL_API int tl_llama2_decode_profile(tl_llama2* m, int start_pos, int cta, unsigned long long* stamps_host,
                                     int capacity, int* n_phases);
 /* Device pointer and local shape of a weight tensor: name in {"tok_embeddings", "attention_norm",

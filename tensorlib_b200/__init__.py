@@ -530,6 +530,17 @@ class Llama2:
               "tl_llama2_decode_device")
         return out
 
+    def decode_profile(self, start_pos: int, cta: int = 0) -> np.ndarray:
+        """One decode step with device timestamps (ns, %globaltimer): array [phases, 3] = (start,
+        activation vector staged, done) per GEMV phase in launch order (tl_llama2_decode_profile).
+        Under tensor parallelism every rank must call it together."""
+        cap = 3 * (5 * self.cfg.n_layers + 2)
+        buf = np.zeros(cap, dtype=np.uint64)
+        n = _int(0)
+        check(load().tl_llama2_decode_profile(self.h, start_pos, cta, buf.ctypes.data_as(_vp), cap, C.byref(n)),
+              "tl_llama2_decode_profile")
+        return buf[:3 * n.value].reshape(n.value, 3)
+
     def kernel_launches(self) -> int:
         v = C.c_longlong(0)
         check(load().tl_llama2_kernel_launches(self.h, C.byref(v)), "tl_llama2_kernel_launches")

@@ -595,19 +595,22 @@ int tl_selftest_unposted_exchange(int max_polls, tl_stream stream) {
     TL_REQUIRE(max_polls >= 1 && max_polls <= (1 << 20), "max_polls must be in [1, 2^20]");
     constexpr int K = 256, N = 64, WORLD = 2;
     cudaStream_t st = as_stream(stream);
-    // [slots: WORLD x K words, all zero = epoch 0][step counter = 0][x, residual: K halfs each][W: N x K][y: N]
+    // [slots: WORLD x K words, all zero = epoch 0][step counter = 0][published vector: K/2 words]
+    // [x, residual: K halfs each][W: N x K][y: N]
     const size_t slot_bytes = (size_t)WORLD * K * sizeof(unsigned long long);
-    const size_t bytes = slot_bytes + 256 + (size_t)(2 * K + N * K + N) * sizeof(__half);
+    const size_t pub_bytes = (size_t)K / 2 * sizeof(unsigned long long);
+    const size_t bytes = slot_bytes + 256 + pub_bytes + (size_t)(2 * K + N * K + N) * sizeof(__half);
     unsigned char* base = nullptr;
     TL_CUDA(cudaMalloc(&base, bytes));
     cudaError_t e = cudaMemsetAsync(base, 0, bytes, st);
     int rc = e == cudaSuccess ? TL_OK : set_error(TL_ERR_CUDA, "memset failed: %s", cudaGetErrorString(e));
     if (rc == TL_OK) {
-        __half* vec = reinterpret_cast<__half*>(base + slot_bytes + 256);
+        __half* vec = reinterpret_cast<__half*>(base + slot_bytes + 256 + pub_bytes);
         PeerExchange in{};
         in.world = WORLD; in.rank = 0; in.n = K;
         in.local_slots = reinterpret_cast<const unsigned long long*>(base);
         in.step_ptr = reinterpret_cast<const unsigned int*>(base + slot_bytes);
+        in.local_pub = reinterpret_cast<unsigned long long*>(base + slot_bytes + 256);
         in.phases_per_step = 1; in.phase_id = 0;          // expected epoch 1; the slots hold epoch 0 for ever
         in.residual = vec + K; in.sum_out = nullptr;
         FusedGemv f{};

@@ -624,6 +624,9 @@ int Llama2Engine::xch_export(cudaIpcMemHandle_t* out) {
         xch_off_part_[0] = take(W * dim * sizeof(unsigned long long));
         xch_off_part_[1] = take(W * dim * sizeof(unsigned long long));
         xch_off_logits_ = take(((size_t)cfg_.vocab_size / 2 + 1) * sizeof(unsigned long long));
+        // local only: the reduced vector of each exchange, published once per GPU as (two halfs, epoch) words
+        xch_off_pub_[0] = take(dim / 2 * sizeof(unsigned long long));
+        xch_off_pub_[1] = take(dim / 2 * sizeof(unsigned long long));
         xch_off_step_ = take(sizeof(unsigned int));
         xch_bytes_ = off;
         void* d = nullptr;
@@ -669,6 +672,7 @@ PeerExchange Llama2Engine::make_exchange(int buf, int phase_id) const {
     const size_t base_off = buf < 2 ? xch_off_part_[buf] : xch_off_logits_;
     e.n = buf < 2 ? cfg_.dim : vocab_local_;
     e.local_slots = reinterpret_cast<const unsigned long long*>(xch_base_ + base_off);
+    e.local_pub = buf < 2 ? reinterpret_cast<unsigned long long*>(xch_base_ + xch_off_pub_[buf]) : nullptr;
     for (int d = 0; d < e.world; d++)
         e.peer_slot[d] = reinterpret_cast<unsigned long long*>(xch_peer_[d] + base_off) + (size_t)e.rank * slot_words;
     e.step_ptr = reinterpret_cast<const unsigned int*>(xch_base_ + xch_off_step_);
@@ -684,55 +688,65 @@ PeerExchange Llama2Engine::make_exchange(int buf, int phase_id) const {
 int Llama2Engine::decode_step_tp_fused(cudaStream_t st, bool pdl) {
     const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_, L = cfg_.n_layers;
     long long n = 0;
-    TL_PROPAGATE(launch_embedding(x_, emb_, d_next_, 1, dim, cfg_.vocab_size, st)); n++;
-    for (int l = 0; l < L; l++) {
+    // Three launches per layer: [attention] [wo -> exchange -> norm + w1|w3 + SiLU*up] [w2 -> exchange ->
+    // norm + next layer's wq|wk|wv + RoPE + KV write]; the last pair ends in the classifier instead.
+    // prof_ (tl_llama2_decode_profile): three %globaltimer stamps per GEMV phase, in launch order.
+    unsigned long long* prof = prof_;
+    auto next_prof = [&]() { unsigned long long* p = prof; if (prof) prof += 3; return p; };
+    auto qkv_phase = [&](int l, FusedGemv& a, PeerExchange& in) {
         const LayerWeights& w = layers_[l];
-        PeerExchange in_w2{};
-        FusedGemv a{};
         a.x = x_; a.norm_w = w.attn_norm; a.eps = 1e-5f;
         a.W[0] = w.wq; a.W[1] = w.wk; a.W[2] = w.wv; a.n_mats = 3; a.N_each = dl; a.K = dim;
         a.epilogue = EPI_QKV_ROPE; a.y = q_; a.k_out = w.cache_k; a.v_out = w.cache_v;
         a.cos_row = cos_t_; a.sin_row = sin_t_; a.head_dim = hd_; a.pos_ptr = d_pos_; a.kv_pitch = dl;
         a.pdl = pdl;
         if (l > 0) {  // x = h + sum of the previous layer's w2 partials
-            in_w2 = make_exchange(1, 2 * (l - 1) + 1);
-            in_w2.residual = h_; in_w2.sum_out = x_;
-            a.xin = &in_w2;
+            in = make_exchange(1, 2 * (l - 1) + 1);
+            in.residual = h_; in.sum_out = x_;
+            a.xin = &in;
         }
+    };
+    TL_PROPAGATE(launch_embedding(x_, emb_, d_next_, 1, dim, cfg_.vocab_size, st)); n++;
+    {
+        FusedGemv a{}; PeerExchange in{};
+        qkv_phase(0, a, in);
+        a.prof = next_prof();
         TL_PROPAGATE(launch_fused_gemv(a, st)); n++;
-
+    }
+    for (int l = 0; l < L; l++) {
+        const LayerWeights& w = layers_[l];
         DecodeAttn at{q_, w.cache_k, w.cache_v, att_, attn_scratch_, attn_counters_, H_local_, hd_, 0,
                       attn_splits_, d_pos_, dl, pdl};
         TL_PROPAGATE(launch_decode_attn_cluster(at, st)); n++;
 
-        PeerExchange out_wo = make_exchange(0, 2 * l);
-        FusedGemv o{};
-        o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
-        o.epilogue = EPI_PUSH_F32; o.xout = &out_wo;
-        TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
-
-        PeerExchange in_wo = make_exchange(0, 2 * l);
+        PeerExchange out_wo = make_exchange(0, 2 * l), in_wo = make_exchange(0, 2 * l);
         in_wo.residual = x_; in_wo.sum_out = h_;
-        FusedGemv f{};
+        FusedGemv o{}, f{};
+        o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
+        o.epilogue = EPI_PUSH_F32; o.xout = &out_wo; o.prof = next_prof();
         f.x = x_; f.norm_w = w.ffn_norm; f.eps = 1e-5f; f.xin = &in_wo;
         f.W[0] = w.w1; f.W[1] = w.w3; f.n_mats = 2; f.N_each = hl; f.K = dim;
-        f.epilogue = EPI_SWIGLU; f.y = g_; f.pdl = pdl;
-        TL_PROPAGATE(launch_fused_gemv(f, st)); n++;
+        f.epilogue = EPI_SWIGLU; f.y = g_; f.pdl = pdl; f.prof = next_prof();
+        TL_PROPAGATE(launch_fused_gemv_pair(o, f, st)); n++;
 
-        PeerExchange out_w2 = make_exchange(1, 2 * l + 1);
-        FusedGemv d{};
+        PeerExchange out_w2 = make_exchange(1, 2 * l + 1), in_next{}, out_cls{};
+        FusedGemv d{}, c{};
         d.x = g_; d.W[0] = w.w2; d.n_mats = 1; d.N_each = dim; d.K = hl; d.pdl = pdl;
-        d.epilogue = EPI_PUSH_F32; d.xout = &out_w2;
-        TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
+        d.epilogue = EPI_PUSH_F32; d.xout = &out_w2; d.prof = next_prof();
+        if (l + 1 < L) {
+            qkv_phase(l + 1, c, in_next);
+        } else {
+            in_next = make_exchange(1, 2 * (L - 1) + 1);
+            in_next.residual = h_; in_next.sum_out = x_;
+            out_cls = make_exchange(2, 2 * L);
+            c.x = x_; c.norm_w = final_norm_; c.eps = 1e-5f; c.xin = &in_next;
+            c.W[0] = wcls_; c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_PUSH_F16; c.xout = &out_cls;
+            c.pdl = pdl;
+        }
+        c.prof = next_prof();
+        TL_PROPAGATE(launch_fused_gemv_pair(d, c, st)); n++;
     }
-    PeerExchange in_last = make_exchange(1, 2 * (L - 1) + 1);
-    in_last.residual = h_; in_last.sum_out = x_;
-    PeerExchange out_cls = make_exchange(2, 2 * L);
-    FusedGemv c{};
-    c.x = x_; c.norm_w = final_norm_; c.eps = 1e-5f; c.xin = &in_last;
-    c.W[0] = wcls_; c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_PUSH_F16; c.xout = &out_cls;
-    c.pdl = pdl;
-    TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
+    const PeerExchange out_cls = make_exchange(2, 2 * L);
     k_argmax_after_exchange<<<1, 1024, 0, st>>>(d_next_, out_cls.local_slots, logits_, cfg_.vocab_size, out_cls.step_ptr,
                                                 out_cls.phases_per_step, out_cls.phase_id, device_status_word()); n++;
     TL_LAUNCH_CHECK();
@@ -750,6 +764,8 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
     const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_;
     long long n = 0;
     last_logits_ = logits_;
+    unsigned long long* prof = prof_;
+    auto next_prof = [&]() { unsigned long long* p = prof; if (prof) prof += 3; return p; };
     TL_PROPAGATE(launch_embedding(x_, emb_, d_next_, 1, dim, cfg_.vocab_size, st)); n++;
     for (int l = 0; l < cfg_.n_layers; l++) {
         const LayerWeights& w = layers_[l];
@@ -758,7 +774,7 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
         a.W[0] = w.wq; a.W[1] = w.wk; a.W[2] = w.wv; a.n_mats = 3; a.N_each = dl; a.K = dim;
         a.epilogue = EPI_QKV_ROPE; a.y = q_; a.k_out = w.cache_k; a.v_out = w.cache_v;
         a.cos_row = cos_t_; a.sin_row = sin_t_; a.head_dim = hd_; a.pos_ptr = d_pos_; a.kv_pitch = dl;
-        a.pdl = pdl;
+        a.pdl = pdl; a.prof = next_prof();
         TL_PROPAGATE(launch_fused_gemv(a, st)); n++;
 
         DecodeAttn at{q_, w.cache_k, w.cache_v, att_, attn_scratch_, attn_counters_, H_local_, hd_, 0,
@@ -766,7 +782,7 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
         TL_PROPAGATE(launch_decode_attn_cluster(at, st)); n++;
 
         FusedGemv o{};
-        o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl;
+        o.x = att_; o.W[0] = w.wo; o.n_mats = 1; o.N_each = dim; o.K = dl; o.pdl = pdl; o.prof = next_prof();
         if (coll_) {
             o.epilogue = EPI_STORE_F32; o.y32 = ao32_;
             TL_PROPAGATE(launch_fused_gemv(o, st)); n++;
@@ -780,11 +796,11 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
         FusedGemv f{};
         f.x = h_; f.norm_w = w.ffn_norm; f.eps = 1e-5f;
         f.W[0] = w.w1; f.W[1] = w.w3; f.n_mats = 2; f.N_each = hl; f.K = dim;
-        f.epilogue = EPI_SWIGLU; f.y = g_; f.pdl = pdl;
+        f.epilogue = EPI_SWIGLU; f.y = g_; f.pdl = pdl; f.prof = next_prof();
         TL_PROPAGATE(launch_fused_gemv(f, st)); n++;
 
         FusedGemv d{};
-        d.x = g_; d.W[0] = w.w2; d.n_mats = 1; d.N_each = dim; d.K = hl; d.pdl = pdl;
+        d.x = g_; d.W[0] = w.w2; d.n_mats = 1; d.N_each = dim; d.K = hl; d.pdl = pdl; d.prof = next_prof();
         if (coll_) {
             d.epilogue = EPI_STORE_F32; d.y32 = ao32_;
             TL_PROPAGATE(launch_fused_gemv(d, st)); n++;
@@ -798,7 +814,7 @@ int Llama2Engine::decode_step_fast(cudaStream_t st, bool pdl) {
     FusedGemv c{};
     c.x = x_; c.norm_w = final_norm_; c.eps = 1e-5f;
     c.W[0] = (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_;
-    c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_STORE; c.pdl = pdl;
+    c.n_mats = 1; c.N_each = vocab_local_; c.K = dim; c.epilogue = EPI_STORE; c.pdl = pdl; c.prof = next_prof();
     if (coll_) {
         c.y = cls_local_;
         TL_PROPAGATE(launch_fused_gemv(c, st)); n++;
@@ -912,9 +928,29 @@ int Llama2Engine::ensure_mega() {
 }
 
 int Llama2Engine::decode_profile(int start_pos, int cta, unsigned long long* out_host, int capacity, int* n_phases) {
-    TL_REQUIRE(use_mega(), "phase timestamps exist for the one-kernel decode step only (one_kernel_decode = 1)");
+    TL_REQUIRE(out_host && n_phases, "null argument");
+    if (!use_mega()) {
+        // the step as plain launches (programmatic dependent launch, no graph), CTA 0 of every GEMV phase stamping
+        // %globaltimer at its first instruction, when its activation vector is staged and when it is done
+        TL_REQUIRE(cfg_.numerics == TL_NUMERICS_FAST, "phase timestamps exist for fast numerics only");
+        const int phases = 4 * cfg_.n_layers + 1;   // GEMV phases in launch order: qkv, wo, gate/up, w2 per layer, then the classifier (attention is not stamped)
+        TL_REQUIRE(capacity >= 3 * phases, "timestamp buffer needs %d entries", 3 * phases);
+        TL_PROPAGATE(ensure_activations(1, 0));
+        unsigned long long* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, (size_t)3 * phases * sizeof(unsigned long long)));
+        TL_CUDA(cudaMemset(d, 0, (size_t)3 * phases * sizeof(unsigned long long)));
+        TL_CUDA(cudaMemcpy(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice));
+        prof_ = d;
+        int rc = decode_step_fast(nullptr, true);
+        prof_ = nullptr;
+        if (rc == TL_OK && cudaMemcpy(out_host, d, (size_t)3 * phases * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+            rc = set_error(TL_ERR_CUDA, "timestamp copy failed");
+        cudaFree(d);
+        *n_phases = phases;
+        return rc;
+    }
     TL_PROPAGATE(ensure_mega());
-    TL_REQUIRE(out_host && n_phases && capacity >= 3 * mega_n_phases_, "timestamp buffer needs %d entries", 3 * mega_n_phases_);
+    TL_REQUIRE(capacity >= 3 * mega_n_phases_, "timestamp buffer needs %d entries", 3 * mega_n_phases_);
     unsigned long long* d = nullptr;
     TL_CUDA(cudaMalloc(&d, (size_t)3 * mega_n_phases_ * sizeof(unsigned long long)));
     TL_CUDA(cudaMemcpy(d_pos_, &start_pos, sizeof(int), cudaMemcpyHostToDevice));

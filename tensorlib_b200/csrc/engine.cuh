@@ -117,7 +117,8 @@ private:
     PeerExchange make_exchange(int buf, int phase_id) const;
     unsigned char* xch_base_ = nullptr;
     unsigned char* xch_peer_[TL_MAX_TP] = {};
-    size_t xch_off_part_[2] = {0, 0}, xch_off_logits_ = 0, xch_off_step_ = 0, xch_bytes_ = 0;
+    size_t xch_off_part_[2] = {0, 0}, xch_off_pub_[2] = {0, 0}, xch_off_logits_ = 0, xch_off_step_ = 0, xch_bytes_ = 0;
+    unsigned long long* prof_ = nullptr;   // device buffer for %globaltimer stamps while decode_profile runs a step
     bool xch_ready_ = false;
     const __half* last_logits_ = nullptr;
 };

@@ -165,6 +165,7 @@ struct RingArgs {
     int has_xin;                  // the activation vector is residual + sum of pushed partials
     PeerExchange xin, xout;
     unsigned int xin_tries;       // polls of the slots before the tensor-parallel input wait gives up
+    unsigned long long* prof;     // optional: CTA 0 stamps %globaltimer at [0] start, [1] vector staged, [2] done
     int m_rows; long long ldx, ldy;   // k_gemv_ring_rows only: activation rows (2..8) and the pitches of x and y
 };
 
@@ -201,97 +202,74 @@ __device__ __forceinline__ void unit_rows(const RingArgs& p, int unit, const __h
     }
 }
 
-// The producer warp of both ring kernels: streams this CTA's weight rows, a stage (2*CW rows x one
-// 1024-half chunk) at a time, lane l copying row l of the stage with one bulk copy. Weights only:
-// in the model they never depend on the previous kernel; a caller of the plain matmul entry point
-// may have just written them (wait_weights).
-template <int EPI, int CW, int NST>
-__device__ __forceinline__ void ring_produce(const RingArgs& p, unsigned char* stages, uint32_t full0, uint32_t empty0,
-                                             int u_begin, int n_units, int nk, int n_iters, int lane) {
-    constexpr int CONSUMERS = CW, NSTAGES = NST, STAGE_BYTES = RingCfg<CW, NST>::STAGE_BYTES;
-    if (p.wait_weights) pdl_wait();
-    const uint64_t pol = policy_evict_first();
-    const __half* row_ptr = nullptr;
-    int cur_tile = -1, rows_in_tile = 0;
-    bool ok = true;
-    for (int it = 0; it < n_iters && ok; it++) {
-        const int s = it % NSTAGES, use = it / NSTAGES;
-        const int tile = it / nk, chunk = it - tile * nk;
-        if (tile != cur_tile) {
-            cur_tile = tile;
-            const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
-            rows_in_tile = units_here * 2;
-            if (lane < rows_in_tile) {
-                const __half *ra, *rb; int mat, r;
-                unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
-                row_ptr = (lane & 1) ? rb : ra;
-            }
-        }
-        if (use > 0) ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const int kc = min(KC, p.K - chunk * KC);
-        if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
-        __syncwarp();
-        if (lane < rows_in_tile)
-            tma_load_1d(smem_u32(stages + (size_t)s * STAGE_BYTES + (size_t)lane * ROW_STRIDE),
-                        row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), full0 + 8 * s, pol);
-    }
-    if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
-template <int EPI, bool NORM, int CW, int NST>
-__global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::CTAS_PER_SM) k_gemv_ring(RingArgs p) {
-    using Cfg = RingCfg<CW, NST>;
-    constexpr int CONSUMERS = CW, NSTAGES = NST, STAGE_ROWS = Cfg::STAGE_ROWS, STAGE_BYTES = Cfg::STAGE_BYTES;
-    constexpr int STEPS_PER_WARP = Cfg::STEPS_PER_WARP;
-    extern __shared__ __align__(128) unsigned char smem[];
-    // layout: [NSTAGES stages][x: K halfs][full barriers][empty barriers][reduction scratch]
-    unsigned char* stages = smem;
-    uint4* xs = reinterpret_cast<uint4*>(smem + NSTAGES * STAGE_BYTES);
-    const int K8 = p.K >> 3;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGES * STAGE_BYTES + (((size_t)p.K * 2 + 127) & ~(size_t)127));
-    float* red = reinterpret_cast<float*>(bars + 2 * NSTAGES);
-    float* partials = red + CONSUMERS;  // [2][CONSUMERS][STAGE_ROWS] per-warp partial row sums, double buffered
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NSTAGES);
+// Shared-memory view of a ring kernel and the ring position of the calling role. A kernel may run
+// several GEMV phases back to back through the same ring (k_gemv_ring2): `it` keeps counting, so
+// the producer streams the next phase's weights while the consumers still finish the previous one.
+struct RingSmem {
+    unsigned char* stages; uint4* xs; float* red; float* partials; uint32_t full0, empty0;
+};
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // this CTA's contiguous share of the units, balanced to +-1
+// The producer warp of the ring kernels: streams this CTA's weight rows, a stage (2*CW rows x one
+// 1024-half chunk) at a time, lane l copying row l of the stage with one bulk copy. Weights only:
+// in the model they never depend on the previous kernel; a caller of the plain matmul entry point
+// may have just written them (wait_weights). Returns false after a timed-out wait.
+template <int EPI, int CW, int NST>
+__device__ __forceinline__ bool ring_produce(const RingArgs& p, const RingSmem& sm, int& it, int lane, uint64_t pol) {
+    constexpr int CONSUMERS = CW, NSTAGES = NST, STAGE_BYTES = RingCfg<CW, NST>::STAGE_BYTES;
     const int u_begin = (int)((long long)p.total_units * blockIdx.x / gridDim.x);
     const int u_end = (int)((long long)p.total_units * (blockIdx.x + 1) / gridDim.x);
     const int n_units = u_end - u_begin;
     const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
     const int nk = (p.K + KC - 1) / KC;
-    const int n_iters = n_tiles * nk;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < NSTAGES; s++) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, CONSUMERS);
+    bool ok = true;
+    for (int tile = 0; tile < n_tiles && ok; tile++) {
+        const int rows_in_tile = min(CONSUMERS, n_units - tile * CONSUMERS) * 2;
+        const __half* row_ptr = nullptr;
+        if (lane < rows_in_tile) {
+            const __half *ra, *rb; int mat, r;
+            unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
+            row_ptr = (lane & 1) ? rb : ra;
         }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int chunk = 0; chunk < nk; chunk++, it++) {
+            const int s = it % NSTAGES, use = it / NSTAGES;
+            if (use > 0) ok = mbar_wait(sm.empty0 + 8 * s, (use - 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const int kc = min(KC, p.K - chunk * KC);
+            if (lane == 0) mbar_arrive_expect_tx(sm.full0 + 8 * s, (uint32_t)(rows_in_tile * kc * 2));
+            __syncwarp();
+            if (lane < rows_in_tile)
+                tma_load_1d(smem_u32(sm.stages + (size_t)s * STAGE_BYTES + (size_t)lane * ROW_STRIDE),
+                            row_ptr + (size_t)chunk * KC, (uint32_t)(kc * 2), sm.full0 + 8 * s, pol);
+        }
     }
-    __syncthreads();
-    pdl_launch_dependents();
+    if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+    return ok;
+}
 
-    if (warp == CONSUMERS) {
-        ring_produce<EPI, CW, NST>(p, stages, full0, empty0, u_begin, n_units, nk, n_iters, lane);
-        return;
-    }
-
-    // ---------------- consumers -------------------------------------------------------------------
-    pdl_wait();  // activations written by the previous kernel are visible from here on
-    const int ctid = threadIdx.x;  // 0..255
-    const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
-    float rinv = 1.0f;
-    // Tensor-parallel input (has_xin): x = residual + sum over ranks of the partial vectors the ranks
-    // pushed into the local slots; a word counts once its epoch is this step's (bounded retries).
-    const unsigned int xin_epoch = p.has_xin ? exchange_epoch(p.xin) : 0u;
-    const unsigned int xout_epoch = (EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16) ? exchange_epoch(p.xout) : 0u;
-    // one 16-byte group of the activation vector (plain, or reduced over the ranks)
-    auto load_x = [&](int c) -> uint4 {
-        if (!p.has_xin) return x4[c];
-        const PeerExchange& e = p.xin;
+// Tensor-parallel input of a GEMV: x = residual + sum over ranks of the partial vectors the ranks
+// pushed into this GPU's slots. The sum is formed ONCE per GPU, not once per CTA: CTA c waits for
+// (bounded) and adds the slots of its own slice of the vector only (K / gridDim elements: a few
+// 16-byte groups), adds the residual, and publishes the fp16 result as (two halfs, epoch) words in a
+// local buffer; then every CTA gathers the whole published vector (K/2 words) from L2, retrying
+// words whose epoch is not this step's yet. A CTA therefore reads world * K / grid * 8 + K * 4 bytes
+// instead of world * K * 8. The CTAs of the grid wait on one another here; that is safe because the
+// grid has at most one CTA per SM and the next kernel of the stream cannot start before every CTA
+// of this one has been scheduled (it is released by their launch_dependents).
+// Returns the 16-byte group c of the vector; all consumer threads must have called
+// exchange_reduce_slice first.
+template <int CW>
+__device__ __forceinline__ void exchange_reduce_slice(const RingArgs& p, unsigned int epoch, int ctid) {
+    const PeerExchange& e = p.xin;
+    const int K8 = p.K >> 3;
+    const int g_begin = (int)((long long)K8 * blockIdx.x / gridDim.x), g_end = (int)((long long)K8 * (blockIdx.x + 1) / gridDim.x);
+    for (int c = g_begin + ctid; c < g_end; c += CW * 32) {
         float s[8];
         bool all_here = false;
         for (uint32_t tries = 0; tries < p.xin_tries && !all_here; tries++) {
@@ -305,7 +283,7 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
                     const uint4 w = ld_words2(src + 2 * q);
                     s[2 * q] += __uint_as_float(w.x);
                     s[2 * q + 1] += __uint_as_float(w.z);
-                    all_here &= (w.y == xin_epoch) & (w.w == xin_epoch);
+                    all_here &= (w.y == epoch) & (w.w == epoch);
                 }
             }
         }
@@ -315,9 +293,52 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
         __half* oh = reinterpret_cast<__half*>(&out);
 #pragma unroll
         for (int i = 0; i < 8; i++) oh[i] = hadd_ref(rh[i], __float2half_rn(s[i]));
-        if (blockIdx.x == 0 && e.sum_out) reinterpret_cast<uint4*>(e.sum_out)[c] = out;
-        return out;
-    };
+        if (e.sum_out) reinterpret_cast<uint4*>(e.sum_out)[c] = out;
+        st_words2(e.local_pub + 4 * c, out.x, out.y, epoch);        // four (half2, epoch) words = one group
+        st_words2(e.local_pub + 4 * c + 2, out.z, out.w, epoch);
+    }
+}
+__device__ __forceinline__ uint4 exchange_gather_group(const RingArgs& p, unsigned int epoch, int c) {
+    const unsigned long long* src = p.xin.local_pub + 4 * c;
+    uint4 lo, hi;
+    bool here = false;
+    for (uint32_t tries = 0; tries < p.xin_tries && !here; tries++) {
+        lo = ld_words2(src);
+        hi = ld_words2(src + 2);
+        here = (lo.y == epoch) & (lo.w == epoch) & (hi.y == epoch) & (hi.w == epoch);
+    }
+    if (!here) atomicExch(p.status, TL_ERR_TIMEOUT);
+    return make_uint4(lo.x, lo.z, hi.x, hi.z);
+}
+
+// The consumer warps' share of one GEMV phase: stage the activation vector (optionally reduced over
+// the ranks, optionally RMS-normalised), multiply the stages as they arrive, apply the epilogue.
+template <int EPI, bool NORM, int CW, int NST>
+__device__ __forceinline__ bool ring_consume(const RingArgs& p, const RingSmem& sm, int& it, int& tile_parity) {
+    using Cfg = RingCfg<CW, NST>;
+    constexpr int CONSUMERS = CW, NSTAGES = NST, STAGE_ROWS = Cfg::STAGE_ROWS, STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int STEPS_PER_WARP = Cfg::STEPS_PER_WARP;
+    unsigned char* stages = sm.stages;
+    uint4* xs = sm.xs;
+    float* red = sm.red;
+    float* partials = sm.partials;
+    const uint32_t full0 = sm.full0, empty0 = sm.empty0;
+    const int K8 = p.K >> 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // this CTA's contiguous share of the units, balanced to +-1
+    const int u_begin = (int)((long long)p.total_units * blockIdx.x / gridDim.x);
+    const int u_end = (int)((long long)p.total_units * (blockIdx.x + 1) / gridDim.x);
+    const int n_units = u_end - u_begin;
+    const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
+    const int nk = (p.K + KC - 1) / KC;
+    const int ctid = threadIdx.x;  // 0 .. 32 * CW - 1
+    const uint4* x4 = reinterpret_cast<const uint4*>(p.x);
+    float rinv = 1.0f;
+    const unsigned int xin_epoch = p.has_xin ? exchange_epoch(p.xin) : 0u;
+    const unsigned int xout_epoch = (EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16) ? exchange_epoch(p.xout) : 0u;
+    if (p.has_xin) exchange_reduce_slice<CW>(p, xin_epoch, ctid);
+    // one 16-byte group of the activation vector (plain, or reduced over the ranks)
+    auto load_x = [&](int c) -> uint4 { return p.has_xin ? exchange_gather_group(p, xin_epoch, c) : x4[c]; };
     if (NORM) {
         // RMSNorm in one pass: the staged vector is x * w (fp16); the scalar 1/rms multiplies the
         // finished dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk), so
@@ -347,6 +368,7 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
         for (int c = ctid; c < K8; c += CONSUMERS * 32) xs[c] = load_x(c);
         consumer_bar_sync(CONSUMERS * 32);
     }
+    if (p.prof && blockIdx.x == 0 && ctid == 0) p.prof[1] = globaltimer_ns();
 
     // Main loop. A stage is a 32-row x 1024-k slab of weights. The dot products run on the tensor
     // cores (mma.sync m16n8k16, fp32 accumulate): the slab's rows are the M dimension (two m16
@@ -390,7 +412,6 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
         }
     }
     bool ok = true;
-    int it = 0;
     const int g = lane >> 2, t = lane & 3;
     // ldmatrix row addresses: lanes 0-7 rows 0-7 (k 0-7), 8-15 rows 8-15, 16-23 rows 0-7 (k 8-15), 24-31 rows 8-15
     const uint32_t lm_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + (lane >> 4) * 16);
@@ -427,7 +448,8 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
         }
         if (!ok) break;
         // column 0 of the accumulators lives in the lanes with t == 0: rows g and g+8 of each m16 tile
-        float* part = partials + (tile & 1) * (CONSUMERS * STAGE_ROWS);
+        float* part = partials + (tile_parity & 1) * (CONSUMERS * STAGE_ROWS);
+        tile_parity ^= 1;
         if (t == 0) {
             part[warp * STAGE_ROWS + g] = acc0[0];
             part[warp * STAGE_ROWS + g + 8] = acc0[2];
@@ -503,6 +525,80 @@ __global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::C
         }
     }
     if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
+    return ok;
+}
+
+template <int CW, int NST>
+__device__ __forceinline__ RingSmem ring_smem_init(unsigned char* smem, int max_k) {
+    using Cfg = RingCfg<CW, NST>;
+    // layout: [NST stages][x: max_k halfs][full barriers][empty barriers][reduction scratch]
+    RingSmem sm;
+    sm.stages = smem;
+    sm.xs = reinterpret_cast<uint4*>(smem + NST * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NST * Cfg::STAGE_BYTES + (((size_t)max_k * 2 + 127) & ~(size_t)127));
+    sm.red = reinterpret_cast<float*>(bars + 2 * NST);
+    sm.partials = sm.red + CW;  // [2][CW][STAGE_ROWS] per-warp partial row sums, double buffered
+    sm.full0 = smem_u32(bars);
+    sm.empty0 = smem_u32(bars + NST);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; s++) {
+            mbar_init(sm.full0 + 8 * s, 1);
+            mbar_init(sm.empty0 + 8 * s, CW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    return sm;
+}
+
+template <int EPI, bool NORM, int CW, int NST>
+__global__ void __launch_bounds__(RingCfg<CW, NST>::THREADS, RingCfg<CW, NST>::CTAS_PER_SM) k_gemv_ring(RingArgs p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const bool stamp = p.prof && blockIdx.x == 0 && threadIdx.x == 0;
+    if (stamp) p.prof[0] = globaltimer_ns();
+    const RingSmem sm = ring_smem_init<CW, NST>(smem, p.K);
+    pdl_launch_dependents();
+    int it = 0;
+    if ((threadIdx.x >> 5) == CW) {
+        if (p.wait_weights) pdl_wait();
+        ring_produce<EPI, CW, NST>(p, sm, it, threadIdx.x & 31, policy_evict_first());
+        return;
+    }
+    pdl_wait();  // activations written by the previous kernel are visible from here on
+    int tile_parity = 0;
+    ring_consume<EPI, NORM, CW, NST>(p, sm, it, tile_parity);
+    if (stamp) p.prof[2] = globaltimer_ns();
+}
+
+// Two GEMV phases of the tensor-parallel decode step in one launch, through one ring:
+//   phase A  a K-split matmul (wo or w2) whose fp32 partial sums are pushed to every rank, then
+//   phase B  the matmul that consumes the exchanged sum: RMSNorm + w1|w3 + SiLU*up after wo,
+//            RMSNorm + wq|wk|wv + RoPE + KV write (next layer) or RMSNorm + classifier after w2.
+// Between the two the consumers only wait for what phase B needs anyway, the partial sums of all
+// ranks; the producer warp does not wait at all and fills the ring with phase B's weights while the
+// partial sums travel. This takes one launch and one kernel boundary out of every exchange.
+template <int EPI_B>
+__global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring2(RingArgs pa, RingArgs pb) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const bool stamp = pa.prof && blockIdx.x == 0 && threadIdx.x == 0;
+    if (stamp) pa.prof[0] = globaltimer_ns();
+    const RingSmem sm = ring_smem_init<16, 3>(smem, max(pa.K, pb.K));
+    pdl_launch_dependents();
+    int it = 0;
+    if ((threadIdx.x >> 5) == 16) {
+        const uint64_t pol = policy_evict_first();
+        if (ring_produce<EPI_PUSH_F32, 16, 3>(pa, sm, it, threadIdx.x & 31, pol))
+            ring_produce<EPI_B, 16, 3>(pb, sm, it, threadIdx.x & 31, pol);
+        return;
+    }
+    pdl_wait();
+    int tile_parity = 0;
+    if (!ring_consume<EPI_PUSH_F32, false, 16, 3>(pa, sm, it, tile_parity)) return;
+    if (stamp) pa.prof[2] = globaltimer_ns();
+    consumer_bar_sync(16 * 32);        // every warp is done with phase A's activation vector
+    if (stamp) pb.prof[0] = globaltimer_ns();
+    ring_consume<EPI_B, true, 16, 3>(pb, sm, it, tile_parity);
+    if (stamp) pb.prof[2] = globaltimer_ns();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -557,7 +653,10 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(R
     pdl_launch_dependents();
 
     if (warp == CONSUMERS) {
-        ring_produce<EPI_STORE, 16, 3>(p, stages, full0, empty0, u_begin, n_units, nk, n_iters, lane);
+        if (p.wait_weights) pdl_wait();
+        const RingSmem sm{stages, nullptr, nullptr, nullptr, full0, empty0};
+        int pit = 0;
+        ring_produce<EPI_STORE, 16, 3>(p, sm, pit, lane, policy_evict_first());
         return;
     }
 
@@ -782,7 +881,8 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
     return TL_OK;
 }
 
-int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
+namespace {
+int build_ring_args(const FusedGemv& q, RingArgs* out) {
     auto al16 = [](const void* v) { return (reinterpret_cast<uintptr_t>(v) & 15) == 0; };
     TL_REQUIRE(q.K >= 16 && q.K % 16 == 0 && q.K <= 12288, "fused gemv: K=%d must be a multiple of 16, <= 12288", q.K);
     TL_REQUIRE(q.N_each > 0 && q.N_each % 2 == 0, "fused gemv: N must be even");
@@ -799,9 +899,10 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
     a.status = device_status_word();
     a.wait_weights = q.weights_may_change ? 1 : 0;
     a.has_xin = q.xin != nullptr;
+    a.prof = q.prof;
     if (q.xin) {
-        TL_REQUIRE(q.xin->world >= 1 && q.xin->world <= TL_MAX_TP && q.xin->n == q.K && q.xin->residual,
-                   "fused gemv: bad exchange input");
+        TL_REQUIRE(q.xin->world >= 1 && q.xin->world <= TL_MAX_TP && q.xin->n == q.K && q.xin->residual && q.xin->local_pub &&
+                   q.K % 8 == 0, "fused gemv: bad exchange input");
         a.xin = *q.xin;
         a.xin_tries = q.xin_tries ? q.xin_tries : (WAIT_LIMIT >> 4);
     }
@@ -818,6 +919,25 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
         if (q.epilogue == EPI_RESIDUAL) TL_REQUIRE(q.n_mats == 1 && q.residual, "residual epilogue: one matrix and a residual");
         a.total_units = q.n_mats * q.N_each / 2;
     }
+    *out = a;
+    return TL_OK;
+}
+
+template <int EPI_B>
+int launch_ring2(const RingArgs& a, const RingArgs& b, cudaStream_t st, bool pdl) {
+    using Cfg = RingCfg<16, 3>;
+    static PerDeviceOnce once;
+    if (once.needed())
+        TL_CUDA(cudaFuncSetAttribute(k_gemv_ring2<EPI_B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    const int units = std::max(a.total_units, b.total_units);
+    const int grid = std::max(1, std::min(sm_count(), (units + 7) / 8));
+    return launch_pdl(k_gemv_ring2<EPI_B>, dim3(grid), dim3(Cfg::THREADS), Cfg::smem_bytes(std::max(a.K, b.K)), st, pdl, a, b);
+}
+}  // namespace
+
+int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
+    RingArgs a{};
+    TL_PROPAGATE(build_ring_args(q, &a));
     const bool norm = q.norm_w != nullptr;
 #define TL_FUSED(E) (norm ? launch_ring<E, true>(a, st, q.pdl) : launch_ring<E, false>(a, st, q.pdl))
     switch (q.epilogue) {
@@ -831,6 +951,23 @@ int launch_fused_gemv(const FusedGemv& q, cudaStream_t st) {
         default: return set_error(TL_ERR_INVALID_ARGUMENT, "fused gemv: unknown epilogue %d", q.epilogue);
     }
 #undef TL_FUSED
+}
+
+// Phase A: a K-split matmul pushing fp32 partial sums (EPI_PUSH_F32, no norm); phase B: the matmul
+// fed by that exchange (xin set, RMSNorm prologue) with one of the three epilogues that follow an
+// exchange in the decode step.
+int launch_fused_gemv_pair(const FusedGemv& qa, const FusedGemv& qb, cudaStream_t st) {
+    TL_REQUIRE(qa.epilogue == EPI_PUSH_F32 && !qa.norm_w && !qa.xin && qb.xin && qb.norm_w,
+               "fused gemv pair: phase A pushes partial sums, phase B consumes an exchange behind an RMSNorm");
+    RingArgs a{}, b{};
+    TL_PROPAGATE(build_ring_args(qa, &a));
+    TL_PROPAGATE(build_ring_args(qb, &b));
+    switch (qb.epilogue) {
+        case EPI_SWIGLU: return launch_ring2<EPI_SWIGLU>(a, b, st, qa.pdl);
+        case EPI_QKV_ROPE: return launch_ring2<EPI_QKV_ROPE>(a, b, st, qa.pdl);
+        case EPI_PUSH_F16: return launch_ring2<EPI_PUSH_F16>(a, b, st, qa.pdl);
+        default: return set_error(TL_ERR_INVALID_ARGUMENT, "fused gemv pair: phase B epilogue %d is not one that follows an exchange", qb.epilogue);
+    }
 }
 
 }  // namespace tlb

@@ -94,6 +94,7 @@ struct PeerExchange {
     int world, rank;
     int n;                                       // payload elements per rank slot (fp32 sums or fp16 logits)
     const unsigned long long* local_slots;       // consumer view: [world][words per slot]
+    unsigned long long* local_pub;               // consumer side: [n / 2] (two halfs, epoch) words, the reduced vector published once per GPU
     unsigned long long* peer_slot[TL_MAX_TP];    // producer view: slot [my rank] in rank d's memory
     const unsigned int* step_ptr;                // local: decode step counter (same value on every rank)
     int phases_per_step, phase_id;               // epoch = *step_ptr * phases_per_step + phase_id + 1
@@ -120,10 +121,13 @@ struct FusedGemv {
     bool pdl;                   // launch with programmatic stream serialization
     bool weights_may_change;    // the previous kernel of the stream may have written W: stream it after the wait
     const PeerExchange* xin;    // prologue: x = residual + sum over ranks of a pushed partial vector
+    unsigned long long* prof;   // optional device buffer for three %globaltimer stamps of CTA 0 (start, vector staged, done)
     unsigned int xin_tries;     // 0: the default bound on the polls of that wait (2^18, a few tenths of a second)
     const PeerExchange* xout;   // EPI_PUSH_F32 / EPI_PUSH_F16: where the results go on every rank
 };
 int launch_fused_gemv(const FusedGemv& p, cudaStream_t st);
+// two phases in one launch: a K-split matmul that pushes its partial sums, then the matmul that consumes the exchanged sum
+int launch_fused_gemv_pair(const FusedGemv& a, const FusedGemv& b, cudaStream_t st);
 
 // ---- attn.cu: attention, fast numerics -----------------------------------------------------------
 struct DecodeAttn {
