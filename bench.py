@@ -427,6 +427,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         clocks = sampler.stop() if rank == 0 else None
         launches = (model.kernel_launches() - launches0) // REPEATS
         require_clean_status(tl, "the timed decode steps")
+        barrier()      # rank 0 just spent host time stopping the clock sampler: the ranks must launch together
         ids_timed = model.decode_device(pos0 + K, 1, fetch=True, stream=sp)   # the id that followed the last timed step
         agree_timed, _ = gather_ids(ids_timed)
         checks["tp_ids_agree_after_timed_region"] = agree_timed

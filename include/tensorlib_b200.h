@@ -357,7 +357,7 @@ TL_API int tl_tp_destroy(void);
  * validity needs no separate flag or fence. Needs an even vocabulary slice per rank. Set-up: every rank exports a 64-byte handle of its region, the
  * handles are gathered out of band (rank order, world*64 bytes), every rank opens them; all
  * ranks must pass a host barrier before the first decode step and before closing. Device-side
- * waits are bounded: a consumer retries for roughly 0.1-0.3 s (2^18 polls of its slots), then records
+ * waits are bounded: a consumer retries for roughly two seconds (2^21 polls of its slots), then records
  * TL_ERR_TIMEOUT in the device status word and carries on with what it has; the model calls that
  * synchronise (forward, generate, decode_device with out_tokens_host) turn that word into their
  * return code. Ranks whose launches may drift apart by more than that (first-call graph

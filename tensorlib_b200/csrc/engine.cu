@@ -579,7 +579,7 @@ __global__ void k_argmax_after_exchange(int* out_idx, const unsigned long long* 
     for (int j = threadIdx.x; 2 * j < cols; j += blockDim.x) {
         unsigned int data = 0, flag = 0;
         bool here = false;
-        for (unsigned i = 0; i < (1u << 18) && !here; i++) {
+        for (unsigned i = 0; i < 2 * TL_EXCHANGE_TRIES && !here; i++) {
             asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(data), "=r"(flag) : "l"(words + j) : "memory");
             here = flag == epoch;
         }

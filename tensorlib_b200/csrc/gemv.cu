@@ -904,7 +904,7 @@ int build_ring_args(const FusedGemv& q, RingArgs* out) {
         TL_REQUIRE(q.xin->world >= 1 && q.xin->world <= TL_MAX_TP && q.xin->n == q.K && q.xin->residual && q.xin->local_pub &&
                    q.K % 8 == 0, "fused gemv: bad exchange input");
         a.xin = *q.xin;
-        a.xin_tries = q.xin_tries ? q.xin_tries : (WAIT_LIMIT >> 4);
+        a.xin_tries = q.xin_tries ? q.xin_tries : TL_EXCHANGE_TRIES;
     }
     if (q.epilogue == EPI_PUSH_F32 || q.epilogue == EPI_PUSH_F16) {
         TL_REQUIRE(q.xout && q.n_mats == 1 && q.xout->world >= 1 && q.xout->world <= TL_MAX_TP, "fused gemv: bad exchange output");

@@ -90,6 +90,10 @@ enum GemvEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV_ROPE = 2, EPI_SWIGL
 // Slots are reused every step without a second handshake: a rank can only reach the next writer
 // of a slot after consuming data its peers produce after their reads of that slot.
 constexpr int TL_MAX_TP = 8;
+// Polls a consumer spends on words that have not arrived before it gives up (each poll is a round of
+// L2 reads, 0.5-1 us): about two seconds, long enough for a rank that was held up on the host by an
+// allocation or a graph instantiation, short enough that a lost rank surfaces as TL_ERR_TIMEOUT.
+constexpr unsigned int TL_EXCHANGE_TRIES = 1u << 21;
 struct PeerExchange {
     int world, rank;
     int n;                                       // payload elements per rank slot (fp32 sums or fp16 logits)
@@ -122,7 +126,7 @@ struct FusedGemv {
     bool weights_may_change;    // the previous kernel of the stream may have written W: stream it after the wait
     const PeerExchange* xin;    // prologue: x = residual + sum over ranks of a pushed partial vector
     unsigned long long* prof;   // optional device buffer for three %globaltimer stamps of CTA 0 (start, vector staged, done)
-    unsigned int xin_tries;     // 0: the default bound on the polls of that wait (2^18, a few tenths of a second)
+    unsigned int xin_tries;     // 0: the default bound on the polls of that wait (TL_EXCHANGE_TRIES)
     const PeerExchange* xout;   // EPI_PUSH_F32 / EPI_PUSH_F16: where the results go on every rank
 };
 int launch_fused_gemv(const FusedGemv& p, cudaStream_t st);
