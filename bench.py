@@ -356,7 +356,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     cfg = CFG if args.layers == CFG.n_layers else synth.LlamaConfig(
         dim=CFG.dim, hidden_dim=CFG.hidden_dim, n_layers=args.layers, n_heads=CFG.n_heads,
         vocab_size=CFG.vocab_size, seq_len=CFG.seq_len, shared_classifier=False)
-    model = tl.Llama2(cfg, numerics=tl.FAST, tp_rank=rank, tp_world=world)
+    one_kernel = args.decode_path == "kernel" and (world == 1 or args.tp_exchange == "fused")
+    model = tl.Llama2(cfg, numerics=tl.FAST, tp_rank=rank, tp_world=world, one_kernel_decode=one_kernel)
     fused = world > 1 and args.tp_exchange == "fused"
     if world > 1:
         from tensorlib_b200 import tp
@@ -442,8 +443,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         stamps = np.stack([model.decode_profile(pos0 + K, 0).astype(np.float64) for _ in range(3)])[-1]
         if rank == 0:
             L = cfg.n_layers
-            per = stamps[1:1 + 4 * L].reshape(L, 4, 3) if world > 1 and fused else stamps[:4 * L].reshape(L, 4, 3)
-            names = ["wo", "gate/up", "w2", "qkv(next)"] if world > 1 and fused else ["qkv", "wo", "gate/up", "w2"]
+            if one_kernel:
+                per, names = stamps[:5 * L].reshape(L, 5, 3), ["qkv", "attention", "wo", "gate/up", "w2"]
+            elif world > 1 and fused:
+                per, names = stamps[1:1 + 4 * L].reshape(L, 4, 3), ["wo", "gate/up", "w2", "qkv(next)"]
+            else:
+                per, names = stamps[:4 * L].reshape(L, 4, 3), ["qkv", "wo", "gate/up", "w2"]
             rep = {}
             for i, nm in enumerate(names):
                 rep[nm] = {"wait_us": float(np.median(per[:, i, 1] - per[:, i, 0]) / 1e3),
@@ -452,7 +457,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     rep[nm]["gap_to_next_us"] = float(np.median(per[:, i + 1, 0] - per[:, i, 2]) / 1e3)
             rep["layer_us"] = float(np.median(np.diff(per[:, 0, 0])) / 1e3)
             rep["step_us"] = float((stamps[-1, 2] - stamps[0, 0]) / 1e3)
-            print(json.dumps({"profiling_only": True, "n_gpus": world, "decode_step_phases": rep}), flush=True)
+            print(json.dumps({"profiling_only": True, "n_gpus": world, "decode_path": args.decode_path,
+                              "decode_step_phases": rep}), flush=True)
     # end to end through the reference-facing generate(): id host->device->host every step
     barrier()
     if args.skip_prefill:
@@ -505,6 +511,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "config": bench_config(world) if cfg.n_layers == CFG.n_layers else
             {**bench_config(world), "workload": workload_name(world) + f" [PROFILING ONLY: {cfg.n_layers} layers]"},
             "details": {"context_at_start": n_ctx, "tp_exchange": (args.tp_exchange if world > 1 else "none"),
+                        "decode_path": "one persistent dataflow kernel per token" if one_kernel else "CUDA graph of fused kernels",
                         "numerics": "fp16 storage, fp32 accumulate", "weight_bytes_per_token_per_gpu": step_bytes,
                         "timed_region": f"{REPEATS} x {K} steps over positions [{pos0}, {pos0 + K}); value = K / median"},
             "repeats": repeats, "checks": checks,
@@ -657,6 +664,8 @@ def main():
     ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1 decode: partial sums exchanged by peer stores inside the GEMV kernels (default) "
                          "or by ncclAllReduce between them")
+    ap.add_argument("--decode-path", default="kernel", choices=["kernel", "graph"],
+                    help="decode step as one persistent dataflow kernel (default) or as a CUDA graph of fused kernels")
     ap.add_argument("--profile-step", action="store_true",
                     help="profiling only: after the timed region run one decode step with device timestamps and "
                          "print the per-phase microseconds of rank 0 (median over layers)")

@@ -324,8 +324,7 @@ int tl_llama2_create(const tl_llama2_config* cfg, tl_llama2** out) {
     TL_REQUIRE(c.n_heads % c.tp_world == 0 && c.hidden_dim % c.tp_world == 0 && c.vocab_size % c.tp_world == 0,
                "heads, hidden_dim and vocab_size must divide by tp_world");
     TL_REQUIRE(c.tp_world == 1 || c.numerics == TL_NUMERICS_FAST, "tensor parallelism needs fast numerics");
-    TL_REQUIRE(!c.one_kernel_decode || (c.tp_world == 1 && c.numerics == TL_NUMERICS_FAST),
-               "one_kernel_decode needs a single GPU and fast numerics");
+    TL_REQUIRE(!c.one_kernel_decode || c.numerics == TL_NUMERICS_FAST, "one_kernel_decode needs fast numerics");
     if (c.numerics == TL_NUMERICS_FAST) {
         TL_REQUIRE(c.dim % 16 == 0 && (c.hidden_dim / c.tp_world) % 16 == 0 && ((c.dim / c.n_heads) * (c.n_heads / c.tp_world)) % 16 == 0,
                    "fast numerics needs dim, local hidden_dim and local attention width to be multiples of 16");

@@ -1,23 +1,35 @@
-// One decode step of the Llama2 forward as ONE persistent kernel (fast numerics, batch 1).
+// One decode step of the Llama2 forward as ONE persistent kernel (fast numerics, batch 1), with
+// DATAFLOW synchronisation between its phases.
 //
 // Replaces, per token, the reference's ~2.8 k launches (model/llama2_7b/src/Transformer.cpp:264-299
-// and everything it calls) and this library's own 164-launch graph. One CTA per SM stays resident
-// for the whole token and walks a list of phases:
+// and everything it calls) and this library's own graph of ~130 kernels. One CTA per SM stays
+// resident for the whole token and walks the phases
 //     per layer:  [RMSNorm + wq|wk|wv GEMV + RoPE + KV write] | [attention] | [wo GEMV + residual] |
 //                 [RMSNorm + w1|w3 GEMV + SiLU*up] | [w2 GEMV + residual]
-//     then        [RMSNorm + classifier GEMV] | argmax + position bookkeeping (CTA 0)
-// separated by grid-wide barriers. The point of fusing the phases is the weight stream: the
-// producer warp of every CTA pushes the weight rows of ALL phases, in order, through the
-// shared-memory ring with TMA bulk copies and never waits for a barrier (weights do not depend on
-// activations); it only waits for ring slots. While the consumers sit in a barrier or compute
-// attention, the ring (190 KB per SM, 28 MB per GPU) fills with the next phase's weights, so HBM
-// does not idle at phase boundaries the way it does at kernel boundaries.
+//     then        [RMSNorm + classifier GEMV + greedy sampling]
+// Two things keep HBM busy across phase boundaries:
+//   * the weight stream: the producer warp of every CTA pushes the weight rows of ALL phases, in
+//     order, through the shared-memory ring with TMA bulk copies and never waits for a phase to end
+//     (weights do not depend on activations); it only waits for ring slots. The ring holds 190 KB
+//     per SM (28 MB per GPU, ~4 us of HBM time);
+//   * no barriers: the activation vector a phase produces travels through L2 as 32-bit words that
+//     carry their fp16 value AND the low 16 bits of the producing phase's epoch (a counter that
+//     advances with every phase of every step), written with one store per word (or pair). A
+//     consumer polls the words it needs until their epoch is the one it expects, so a hand-over costs
+//     one L2 round trip after the LAST producer finished instead of a grid-wide barrier or a kernel
+//     boundary (measured ~5 us each), and words never need resetting: the value a word held before
+//     is one step (5 L + 1 epochs) older, which no 16-bit comparison confuses with the current one.
+// Under tensor parallelism the partial sums of wo and w2 are pushed into every rank's memory as
+// (fp32, epoch) words like in the multi-kernel step; each CTA adds the ranks' partials for its own
+// slice of the vector, adds the residual, and publishes the slice as ordinary words, so the sum is
+// formed once per GPU and the consumers are the same code as on one GPU.
 //
-// Consumers: 16 warps. In a GEMV phase each owns one unit (two weight rows) of a stage; in the
-// attention phase they form 4 groups of 4 warps, each group working on one (head, split) item.
-// Activations exchanged between CTAs are read with ld.global.cg (L2) because L1 is not coherent
-// across SMs within a kernel. Every wait (mbarrier, grid barrier) is bounded and reports
-// TL_ERR_TIMEOUT through the device status word instead of hanging.
+// Consumers: 16 warps. In a GEMV phase warp w multiplies the k16 steps [4w, 4w+4) of every 1024-wide
+// chunk for the 32 rows of a stage on the tensor cores (mma.sync, the activation vector in column
+// 0 of B); in the attention phase they form 4 groups of 4 warps, each working on one (head, split)
+// item. Every wait (mbarrier, word poll, peer slot poll) is bounded and reports TL_ERR_TIMEOUT
+// through the device status word instead of hanging. The CTAs wait on one another, so the launch
+// is cooperative (all CTAs co-resident).
 #include <cuda.h>
 
 #include <vector>
@@ -131,21 +143,103 @@ constexpr int ATT_GROUPS = 4, ATT_WARPS = 4;          // 4 groups x 4 warps
 constexpr int MAX_HD = 256, HD_ITERS = MAX_HD / 64;
 constexpr int ATT_SMEM_PER_GROUP = (2 * ATT_WARPS + ATT_WARPS * MAX_HD + 4) * 4;
 
-enum { PH_GEMV = 0, PH_ATTN = 1 };
-
 }  // namespace
 
 namespace {
 
-template <int EPI>
-__device__ __forceinline__ void unit_rows(const MegaPhase& p, int unit, const __half*& ra, const __half*& rb,
-                                          int& mat, int& r) {
-    if (EPI == EPI_SWIGLU) {
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---- words: (fp16 value, 16-bit epoch) in 32 bits -----------------------------------------------------
+constexpr uint32_t POLL_LIMIT = 1u << 22;     // L2 polls (~0.5 us each) before a consumer gives up
+__device__ __forceinline__ uint32_t make_word(__half v, uint32_t e16) { return (uint32_t)__half_as_ushort(v) | (e16 << 16); }
+__device__ __forceinline__ void st_word1(uint32_t* p, uint32_t w) {
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(w) : "memory");
+}
+__device__ __forceinline__ void st_word_pair(uint32_t* p, uint32_t w0, uint32_t w1) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(w0), "r"(w1) : "memory");
+}
+__device__ __forceinline__ uint4 ld_word4(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ld_word2(const uint32_t* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool epochs_ok(const uint4& w, uint32_t e16) {
+    return ((w.x >> 16) == e16) & ((w.y >> 16) == e16) & ((w.z >> 16) == e16) & ((w.w >> 16) == e16);
+}
+// eight consecutive values of a word vector as eight packed halfs, waiting (bounded) for their epoch
+__device__ __forceinline__ uint4 gather8(const uint32_t* words, uint32_t e16, int* status) {
+    uint4 a, b;
+    bool here = false;
+    for (uint32_t i = 0; i < POLL_LIMIT && !here; i++) {
+        a = ld_word4(words);
+        b = ld_word4(words + 4);
+        here = epochs_ok(a, e16) & epochs_ok(b, e16);
+    }
+    if (!here) atomicExch(status, TL_ERR_TIMEOUT);
+    return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16),
+                      (b.z & 0xffffu) | (b.w << 16));
+}
+// two consecutive values as one packed half2
+__device__ __forceinline__ uint32_t gather2(const uint32_t* words, uint32_t e16, int* status) {
+    uint2 w;
+    bool here = false;
+    for (uint32_t i = 0; i < POLL_LIMIT && !here; i++) {
+        w = ld_word2(words);
+        here = ((w.x >> 16) == e16) & ((w.y >> 16) == e16);
+    }
+    if (!here) atomicExch(status, TL_ERR_TIMEOUT);
+    return (w.x & 0xffffu) | (w.y << 16);
+}
+// (payload, epoch) 8-byte words of the cross-GPU exchange (see PeerExchange in kernels.cuh)
+__device__ __forceinline__ uint4 ld_xwords2(const unsigned long long* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_xwords2(unsigned long long* p, unsigned int d0, unsigned int d1, unsigned int epoch) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(epoch), "r"(d1), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ void st_xword(unsigned long long* p, unsigned int d, unsigned int epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(d), "r"(epoch) : "memory");
+}
+
+// ---- phases -----------------------------------------------------------------------------------------------
+enum { PH_QKV = 0, PH_ATTN = 1, PH_WO = 2, PH_GATEUP = 3, PH_W2 = 4, PH_CLS = 5 };
+
+struct GemvDesc {
+    const __half *W0, *W1, *W2;
+    int N_each, K, total_units;
+    bool swiglu;
+};
+// the weight side of phase `kind` of layer l: what the producer streams and the consumers multiply
+__device__ __forceinline__ GemvDesc gemv_desc(const FlowArgs& a, int kind, int l) {
+    GemvDesc d{};
+    if (kind == PH_CLS) { d.W0 = a.wcls; d.N_each = a.vocab_local; d.K = a.dim; d.total_units = a.vocab_local / 2; return d; }
+    const FlowLayer& w = a.layers[l];
+    if (kind == PH_QKV) { d.W0 = w.wq; d.W1 = w.wk; d.W2 = w.wv; d.N_each = a.dl; d.K = a.dim; d.total_units = 3 * a.dl / 2; }
+    else if (kind == PH_WO) { d.W0 = w.wo; d.N_each = a.dim; d.K = a.dl; d.total_units = a.dim / 2; }
+    else if (kind == PH_GATEUP) { d.W0 = w.w1; d.W1 = w.w3; d.N_each = a.hl; d.K = a.dim; d.total_units = a.hl; d.swiglu = true; }
+    else { d.W0 = w.w2; d.N_each = a.dim; d.K = a.hl; d.total_units = a.dim / 2; }
+    return d;
+}
+// unit u of a phase = the two weight rows one lane pair finishes: rows (2u, 2u+1) of one of up to three
+// matrices, or row u of w1 and of w3
+__device__ __forceinline__ void unit_rows(const GemvDesc& p, int unit, const __half*& ra, const __half*& rb, int& mat, int& r) {
+    if (p.swiglu) {
         mat = 0; r = unit;
         ra = p.W0 + (long long)unit * p.K;
         rb = p.W1 + (long long)unit * p.K;
     } else {
-        int row = unit * 2;
+        const int row = unit * 2;
         mat = row / p.N_each;
         r = row - mat * p.N_each;
         const __half* Wm = mat == 0 ? p.W0 : (mat == 1 ? p.W1 : p.W2);
@@ -153,53 +247,32 @@ __device__ __forceinline__ void unit_rows(const MegaPhase& p, int unit, const __
         rb = ra + p.K;
     }
 }
-__device__ __forceinline__ void unit_rows_rt(const MegaPhase& p, int unit, const __half*& ra, const __half*& rb) {
-    int mat, r;
-    if (p.epilogue == EPI_SWIGLU) unit_rows<EPI_SWIGLU>(p, unit, ra, rb, mat, r);
-    else unit_rows<EPI_STORE>(p, unit, ra, rb, mat, r);
-}
 
 struct Ctx {
     unsigned char* stages; uint4* xs; float* red; float* partials; uint32_t full0, empty0;
     int warp, lane, ctid, tile_parity;
     int tok, pos;
+    unsigned int epoch0;   // step * phases: epoch of phase p of this step is epoch0 + p + 1
     float rinv;            // 1/rms of the current phase's input (1 when the phase has no RMSNorm)
     int it;                // ring iteration counter of this role
-    unsigned int bar_target;
     bool ok;
+    float best_v; int best_i;   // classifier: this lane's best logit so far
 };
+__device__ __forceinline__ uint32_t e16_of(const Ctx& c, int phase) { return (c.epoch0 + (unsigned)phase + 1u) & 0xffffu; }
+__device__ __forceinline__ uint32_t e32_of(const Ctx& c, int phase) { return c.epoch0 + (unsigned)phase + 1u; }
 
-// Grid-wide barrier among the consumer warps of all CTAs (the producers never join it).
-__device__ __forceinline__ void grid_barrier(const MegaArgs& a, Ctx& c) {
-    // bar.sync orders every consumer thread's stores before thread 0's release-add (cumulative at
-    // gpu scope); the acquire-load that sees the last arrival orders the other CTAs' stores before
-    // everything after the second bar.sync. No return value is needed from the add, so it is a
-    // fire-and-forget reduction rather than an atomic round trip.
-    named_bar_sync(1, CONSUMER_THREADS);
-    if (c.ctid == 0) {
-        c.bar_target += gridDim.x;
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.grid_bar) : "memory");
-        bool done = false;
-        for (uint32_t i = 0; i < (1u << 24); i++)
-            if (ld_acquire_u32(a.grid_bar) >= c.bar_target) { done = true; break; }
-        if (!done) atomicExch(a.status, TL_ERR_TIMEOUT);
-    }
-    named_bar_sync(1, CONSUMER_THREADS);
-}
-
-// stage the activation vector of a GEMV phase in shared memory (optionally RMS-normalised)
-__device__ __forceinline__ void stage_x(const MegaArgs& a, const MegaPhase& p, Ctx& c) {
-    const int K8 = p.K >> 3;
-    const __half* xsrc = p.x ? p.x : a.emb + (long long)c.tok * a.dim;
-    const uint4* x4 = reinterpret_cast<const uint4*>(xsrc);
-    if (p.norm_w) {
-        // RMSNorm in one pass: the vector staged is x * w (fp16); the scalar 1/rms is applied to
-        // the finished dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk),
-        // so no second pass over x has to wait for the reduction.
+// ---- staging the activation vector of a GEMV phase ------------------------------------------------------------
+// RMSNorm in one pass: the vector staged is x * w (fp16); the scalar 1/rms is applied to the finished
+// dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk), so no second pass over
+// x has to wait for the reduction.
+template <typename Load>
+__device__ __forceinline__ void stage_vector(const FlowArgs& a, Ctx& c, int K, const __half* norm_w, Load load8) {
+    const int K8 = K >> 3;
+    if (norm_w) {
         float ss = 0.f;
-        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
+        const uint4* nw4 = reinterpret_cast<const uint4*>(norm_w);
         for (int i = c.ctid; i < K8; i += CONSUMER_THREADS) {
-            uint4 v = __ldcg(x4 + i), g = nw4[i];
+            uint4 v = load8(i), g = nw4[i];
             ss += sumsq8(v);
             __half2* vh = reinterpret_cast<__half2*>(&v);
             const __half2* gh = reinterpret_cast<const __half2*>(&g);
@@ -216,41 +289,77 @@ __device__ __forceinline__ void stage_x(const MegaArgs& a, const MegaPhase& p, C
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < CONSUMERS; w++) tot += c.red[w];
-        c.rinv = rsqrtf(tot / (float)p.K + a.eps);
+        c.rinv = rsqrtf(tot / (float)K + a.eps);
     } else {
-        for (int i = c.ctid; i < K8; i += CONSUMER_THREADS) c.xs[i] = __ldcg(x4 + i);
+        for (int i = c.ctid; i < K8; i += CONSUMER_THREADS) c.xs[i] = load8(i);
         c.rinv = 1.0f;
         named_bar_sync(1, CONSUMER_THREADS);
     }
 }
 
-template <int EPI>
-__device__ __forceinline__ void gemv_consume(const MegaArgs& a, const MegaPhase& p, Ctx& c) {
+// Tensor parallelism: this CTA's slice of (residual + sum over ranks of the pushed partial sums),
+// published as words with the epoch of the phase that produced the partials. buf 0: wo, 1: w2.
+__device__ __forceinline__ void reduce_slice_and_publish(const FlowArgs& a, Ctx& c, int buf, int src_phase,
+                                                         const uint32_t* residual_words, uint32_t* out_words) {
+    const int K8 = a.dim >> 3;
+    const int g_begin = (int)((long long)K8 * blockIdx.x / gridDim.x), g_end = (int)((long long)K8 * (blockIdx.x + 1) / gridDim.x);
+    const unsigned int epoch = e32_of(c, src_phase);
+    const uint32_t e16 = e16_of(c, src_phase);
+    for (int g = g_begin + c.ctid; g < g_end; g += CONSUMER_THREADS) {
+        // the residual of these eight elements: the embedding row in layer 0, else words this CTA verified when it staged them
+        __half res[8];
+        if (residual_words) {
+            const uint4 r0 = ld_word4(residual_words + 8 * g), r1 = ld_word4(residual_words + 8 * g + 4);
+            res[0] = __ushort_as_half(r0.x & 0xffff); res[1] = __ushort_as_half(r0.y & 0xffff);
+            res[2] = __ushort_as_half(r0.z & 0xffff); res[3] = __ushort_as_half(r0.w & 0xffff);
+            res[4] = __ushort_as_half(r1.x & 0xffff); res[5] = __ushort_as_half(r1.y & 0xffff);
+            res[6] = __ushort_as_half(r1.z & 0xffff); res[7] = __ushort_as_half(r1.w & 0xffff);
+        } else {
+            const uint4 r = __ldg(reinterpret_cast<const uint4*>(a.emb + (long long)c.tok * a.dim) + g);
+            *reinterpret_cast<uint4*>(res) = r;
+        }
+        float s[8];
+        bool all_here = false;
+        for (uint32_t tries = 0; tries < a.exchange_tries && !all_here; tries++) {
+            all_here = true;
+#pragma unroll
+            for (int i = 0; i < 8; i++) s[i] = 0.f;
+            for (int r = 0; r < a.world; r++) {   // rank order: every rank adds the same values in the same order
+                const unsigned long long* src = a.local_part[buf] + (size_t)r * a.dim + 8 * g;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint4 w = ld_xwords2(src + 2 * q);
+                    s[2 * q] += __uint_as_float(w.x);
+                    s[2 * q + 1] += __uint_as_float(w.z);
+                    all_here &= (w.y == epoch) & (w.w == epoch);
+                }
+            }
+        }
+        if (!all_here) atomicExch(a.status, TL_ERR_TIMEOUT);
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) w[i] = make_word(hadd_ref(res[i], __float2half_rn(s[i])), e16);
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(out_words + 8 * g), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(out_words + 8 * g + 4), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+    }
+}
+
+// ---- one GEMV phase: multiply the stages as they arrive, hand each finished row pair to `epi` ---------------------
+// epi(mat, r, sa, sb, unit): called by the even lanes of warp 0 for their unit: rows (r, r+1) of matrix `mat`
+// (or row r of w1 and w3 for SiLU*up), sa / sb the two fp32 dot products already scaled by 1/rms.
+template <typename Epi>
+__device__ __forceinline__ void gemv_consume(const FlowArgs& a, const GemvDesc& p, Ctx& c, Epi epi) {
     const int u_begin = (int)((long long)p.total_units * blockIdx.x / gridDim.x);
     const int u_end = (int)((long long)p.total_units * (blockIdx.x + 1) / gridDim.x);
     const int n_units = u_end - u_begin;
     const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
     const int nk = (p.K + KC - 1) / KC;
-    // Tensor-core dot products (mma.sync m16n8k16, fp32 accumulate): the 32 rows of a stage are two
-    // m16 tiles, the activation vector is column 0 of B; warp w multiplies k16 steps
-    // [w*STEPS_PER_WARP, +STEPS_PER_WARP) of every chunk for all rows; the per-warp partial row
-    // sums meet in shared memory at the end of a tile and warp 0 finishes the rows.
     const int lane = c.lane, g = lane >> 2, t = lane & 3;
     const uint32_t lm_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + (lane >> 4) * 16);
     const __half* xh = reinterpret_cast<const __half*>(c.xs);
     for (int tile = 0; tile < n_tiles && c.ok; tile++) {
         const int units_here = min(CONSUMERS, n_units - tile * CONSUMERS);
         float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-        // warp 0 finishes the rows of this tile: fetch what its epilogue needs from L2 now, so the
-        // latency overlaps the multiply instead of following it
-        __half res_a = __float2half_rn(0.f), res_b = res_a;
-        if (EPI == EPI_RESIDUAL && c.warp == 0 && !(lane & 1) && (lane >> 1) < units_here) {
-            const __half *ra, *rb; int mat, r;
-            unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
-            const __half* res = p.residual ? p.residual : a.emb + (long long)c.tok * a.dim;
-            res_a = ldcg_half(res + r);
-            res_b = ldcg_half(res + r + 1);
-        }
         for (int chunk = 0; chunk < nk; chunk++, c.it++) {
             const int s = c.it % NSTAGES, use = c.it / NSTAGES;
             c.ok = mbar_wait(c.full0 + 8 * s, use & 1);
@@ -291,44 +400,18 @@ __device__ __forceinline__ void gemv_consume(const MegaArgs& a, const MegaPhase&
         for (int w = 0; w < CONSUMERS; w++) rowsum += part[w * STAGE_ROWS + lane];
         const float other = __shfl_xor_sync(0xffffffffu, rowsum, 1);
         if ((lane & 1) || (lane >> 1) >= units_here) continue;
-        const float sa = rowsum * c.rinv, sb = other * c.rinv;
-        const __half ha = __float2half_rn(sa), hb = __float2half_rn(sb);
         const __half *ra, *rb; int mat, r;
-        unit_rows<EPI>(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
-        if (EPI == EPI_STORE) {
-            p.y[(long long)mat * p.N_each + r] = ha;
-            p.y[(long long)mat * p.N_each + r + 1] = hb;
-        } else if (EPI == EPI_STORE_F32) {
-            p.y32[(long long)mat * p.N_each + r] = sa;
-            p.y32[(long long)mat * p.N_each + r + 1] = sb;
-        } else if (EPI == EPI_RESIDUAL) {
-            p.y[r] = hadd_ref(res_a, ha);
-            p.y[r + 1] = hadd_ref(res_b, hb);
-        } else if (EPI == EPI_QKV_ROPE) {
-            if (mat == 2) {
-                __half* vo = p.v_cache + (long long)c.pos * a.kv_pitch;
-                vo[r] = ha; vo[r + 1] = hb;
-            } else {
-                const int half_dim = a.hd >> 1;
-                const int d2 = (r % a.hd) >> 1;
-                const __half cs = a.cos_t[(long long)c.pos * half_dim + d2];
-                const __half sn = a.sin_t[(long long)c.pos * half_dim + d2];
-                const __half o0 = hsub_ref(hmul_ref(ha, cs), hmul_ref(hb, sn));
-                const __half o1 = hadd_ref(hmul_ref(ha, sn), hmul_ref(hb, cs));
-                __half* dst = mat == 0 ? p.y : p.k_cache + (long long)c.pos * a.kv_pitch;
-                dst[r] = o0; dst[r + 1] = o1;
-            }
-        } else {  // EPI_SWIGLU
-            const __half g = a.silu_tab[__half_as_ushort(ha)];
-            p.y[r] = hmul_ref(g, hb);
-        }
+        unit_rows(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
+        epi(mat, r, rowsum * c.rinv, other * c.rinv);
     }
 }
 
-// Attention of the new token over positions [0, pos] of the caches, read in place. Work items are
-// (head, split) pairs; a group of 4 warps takes one item at a time; partial (max, sum, acc) go to
-// a scratch slot; the last group to finish a head merges its splits.
-__device__ __forceinline__ void attn_phase(const MegaArgs& a, const MegaPhase& p, Ctx& c) {
+// Attention of the new token over positions [0, pos] of the caches, read in place; the newest row
+// (position pos) and the query come from this step's words. Work items are (head, split) pairs; a
+// group of 4 warps takes one item at a time; partial (max, sum, acc) go to a scratch slot; the last
+// group to finish a head merges its splits and publishes the head's output words.
+__device__ __forceinline__ void attn_phase(const FlowArgs& a, Ctx& c, int l, int phase) {
+    const FlowLayer& lw = a.layers[l];
     const int g = c.warp / ATT_WARPS, gw = c.warp % ATT_WARPS, lane = c.lane;
     float* gs = reinterpret_cast<float*>(c.xs) + (size_t)g * (ATT_SMEM_PER_GROUP / 4);
     float* sm_m = gs; float* sm_l = gs + ATT_WARPS; float* sm_acc = gs + 2 * ATT_WARPS;
@@ -338,83 +421,91 @@ __device__ __forceinline__ void attn_phase(const MegaArgs& a, const MegaPhase& p
     const float scale = rsqrtf((float)hd);
     const int n_items = a.H * a.splits;
     const int gtid = gw * 32 + lane;
+    const uint32_t e_qkv = e16_of(c, phase - 1), e_out = e16_of(c, phase);
     for (int item = blockIdx.x * ATT_GROUPS + g; item < n_items; item += gridDim.x * ATT_GROUPS) {
         const int h = item / a.splits, split = item - h * a.splits;
         const int s_begin = split * per, s_end = min(S, s_begin + per);
-        float2 qf[HD_ITERS];
-#pragma unroll
-        for (int i = 0; i < HD_ITERS; i++) {
-            int d = 2 * lane + 64 * i;
-            if (d < hd) {
-                unsigned int raw = __ldcg(reinterpret_cast<const unsigned int*>(p.x + (size_t)h * hd + d));
-                qf[i] = __half22float2(*reinterpret_cast<__half2*>(&raw));
-            } else qf[i] = make_float2(0.f, 0.f);
-        }
-        float m = -INFINITY, l = 0.f;
+        float m = -INFINITY, l_sum = 0.f;
         float2 acc[HD_ITERS];
 #pragma unroll
         for (int i = 0; i < HD_ITERS; i++) acc[i] = make_float2(0.f, 0.f);
-        constexpr int U = 4;
-        for (int s0 = s_begin + gw * U; s0 < s_end; s0 += ATT_WARPS * U) {
-            unsigned int kv[U][HD_ITERS], vv[U][HD_ITERS];
+        if (s_begin < s_end) {      // (an empty split only reports -inf)
+            float2 qf[HD_ITERS];
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int s = s0 + u;
-                const size_t base = (size_t)s * a.kv_pitch + (size_t)h * hd;
-#pragma unroll
-                for (int i = 0; i < HD_ITERS; i++) {
-                    int d = 2 * lane + 64 * i;
-                    bool okk = s < s_end && d < hd;
-                    kv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(p.k_cache + base + d)) : 0u;
-                    vv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(p.v_cache + base + d)) : 0u;
-                }
+            for (int i = 0; i < HD_ITERS; i++) {
+                const int d = 2 * lane + 64 * i;
+                if (d < hd) {
+                    uint32_t raw = gather2(a.w.q + (size_t)h * hd + d, e_qkv, a.status);
+                    qf[i] = __half22float2(*reinterpret_cast<__half2*>(&raw));
+                } else qf[i] = make_float2(0.f, 0.f);
             }
-            float sc[U];
+            constexpr int U = 4;
+            for (int s0 = s_begin + gw * U; s0 < s_end; s0 += ATT_WARPS * U) {
+                unsigned int kv[U][HD_ITERS], vv[U][HD_ITERS];
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                float d = 0.f;
-#pragma unroll
-                for (int i = 0; i < HD_ITERS; i++) {
-                    float2 kf = __half22float2(*reinterpret_cast<__half2*>(&kv[u][i]));
-                    d = fmaf(qf[i].x, kf.x, d);
-                    d = fmaf(qf[i].y, kf.y, d);
-                }
-                sc[u] = d;
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-                for (int u = 0; u < U; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                if (s0 + u < s_end) {
-                    const float x = sc[u] * scale;
-                    const float mn = fmaxf(m, x);
-                    const float corr = __expf(m - mn), pe = __expf(x - mn);
-                    l = l * corr + pe;
+                for (int u = 0; u < U; u++) {
+                    const int s = s0 + u;
+                    const size_t base = (size_t)s * a.dl + (size_t)h * hd;
 #pragma unroll
                     for (int i = 0; i < HD_ITERS; i++) {
-                        float2 vf = __half22float2(*reinterpret_cast<__half2*>(&vv[u][i]));
-                        acc[i].x = fmaf(pe, vf.x, acc[i].x * corr);
-                        acc[i].y = fmaf(pe, vf.y, acc[i].y * corr);
+                        const int d = 2 * lane + 64 * i;
+                        const bool okk = s < s_end && d < hd;
+                        if (okk && s == c.pos) {      // this step's row: still on its way through L2
+                            kv[u][i] = gather2(a.w.k + (size_t)h * hd + d, e_qkv, a.status);
+                            vv[u][i] = gather2(a.w.v + (size_t)h * hd + d, e_qkv, a.status);
+                        } else {
+                            kv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(lw.cache_k + base + d)) : 0u;
+                            vv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(lw.cache_v + base + d)) : 0u;
+                        }
                     }
-                    m = mn;
+                }
+                float sc[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    float d = 0.f;
+#pragma unroll
+                    for (int i = 0; i < HD_ITERS; i++) {
+                        float2 kf = __half22float2(*reinterpret_cast<__half2*>(&kv[u][i]));
+                        d = fmaf(qf[i].x, kf.x, d);
+                        d = fmaf(qf[i].y, kf.y, d);
+                    }
+                    sc[u] = d;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                    for (int u = 0; u < U; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    if (s0 + u < s_end) {
+                        const float x = sc[u] * scale;
+                        const float mn = fmaxf(m, x);
+                        const float corr = __expf(m - mn), pe = __expf(x - mn);
+                        l_sum = l_sum * corr + pe;
+#pragma unroll
+                        for (int i = 0; i < HD_ITERS; i++) {
+                            float2 vf = __half22float2(*reinterpret_cast<__half2*>(&vv[u][i]));
+                            acc[i].x = fmaf(pe, vf.x, acc[i].x * corr);
+                            acc[i].y = fmaf(pe, vf.y, acc[i].y * corr);
+                        }
+                        m = mn;
+                    }
                 }
             }
         }
-        if (lane == 0) { sm_m[gw] = m; sm_l[gw] = l; }
+        if (lane == 0) { sm_m[gw] = m; sm_l[gw] = l_sum; }
 #pragma unroll
         for (int i = 0; i < HD_ITERS; i++) {
-            int d = 2 * lane + 64 * i;
+            const int d = 2 * lane + 64 * i;
             if (d < hd) { sm_acc[gw * MAX_HD + d] = acc[i].x; sm_acc[gw * MAX_HD + d + 1] = acc[i].y; }
         }
         named_bar_sync(2 + g, ATT_WARPS * 32);
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sm_m[w]);
-        float L = 0.f;
+        float Lsum = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) L += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * __expf(sm_m[w] - M);
+        for (int w = 0; w < ATT_WARPS; w++) Lsum += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * __expf(sm_m[w] - M);
         float* slot = a.attn_scratch + ((size_t)h * a.splits + split) * (hd + 2);
         for (int d = gtid; d < hd; d += ATT_WARPS * 32) {
             float v = 0.f;
@@ -423,7 +514,7 @@ __device__ __forceinline__ void attn_phase(const MegaArgs& a, const MegaPhase& p
                 v += sm_m[w] == -INFINITY ? 0.f : sm_acc[w * MAX_HD + d] * __expf(sm_m[w] - M);
             slot[2 + d] = v;
         }
-        if (gtid == 0) { slot[0] = M; slot[1] = L; }
+        if (gtid == 0) { slot[0] = M; slot[1] = Lsum; }
         __threadfence();
         named_bar_sync(2 + g, ATT_WARPS * 32);
         if (gtid == 0) {
@@ -448,14 +539,14 @@ __device__ __forceinline__ void attn_phase(const MegaArgs& a, const MegaPhase& p
                     float ms = __ldcg(base + (size_t)sp * (hd + 2));
                     if (ms != -INFINITY) v += __ldcg(base + (size_t)sp * (hd + 2) + 2 + d) * __expf(ms - GM);
                 }
-                p.y[(size_t)h * hd + d] = __float2half_rn(v / GL);
+                st_word1(a.w.att + (size_t)h * hd + d, make_word(__float2half_rn(v / GL), e_out));
             }
         }
         named_bar_sync(2 + g, ATT_WARPS * 32);  // the group's shared scratch is reused by its next item
     }
 }
 
-__global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
+__global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_flow(FlowArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     Ctx c;
     c.stages = smem;
@@ -467,7 +558,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
     c.full0 = smem_u32(bars);
     c.empty0 = smem_u32(bars + NSTAGES);
     c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31; c.ctid = threadIdx.x;
-    c.it = 0; c.bar_target = 0; c.ok = true;
+    c.it = 0; c.ok = true;
+    c.best_v = -INFINITY; c.best_i = 0x7fffffff;
+    const int L = a.n_layers, n_phases = 5 * L + 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGES; s++) {
@@ -484,11 +577,10 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
         const int lane = c.lane;
         bool ok = true;
         int it = 0;
-        // (An L2 prefetch running ahead of the ring with cp.async.bulk.prefetch.L2 was measured and
-        // dropped: phase times grew by ~50 %, the extra bulk requests compete with the ring's own.)
-        for (int ph = 0; ph < a.n_phases && ok; ph++) {
-            const MegaPhase& p = a.phases[ph];
-            if (p.kind != PH_GEMV) continue;
+        for (int ph = 0; ph < n_phases && ok; ph++) {
+            const int kind = ph == 5 * L ? PH_CLS : ph % 5;
+            if (kind == PH_ATTN) continue;
+            const GemvDesc p = gemv_desc(a, kind, ph / 5);
             const int u_begin = (int)((long long)p.total_units * blockIdx.x / gridDim.x);
             const int u_end = (int)((long long)p.total_units * (blockIdx.x + 1) / gridDim.x);
             const int n_units = u_end - u_begin;
@@ -498,8 +590,8 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
                 const int rows_in_tile = min(CONSUMERS, n_units - tile * CONSUMERS) * 2;
                 const __half* row_ptr = nullptr;
                 if (lane < rows_in_tile) {
-                    const __half *ra, *rb;
-                    unit_rows_rt(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb);
+                    const __half *ra, *rb; int mat, r;
+                    unit_rows(p, u_begin + tile * CONSUMERS + (lane >> 1), ra, rb, mat, r);
                     row_ptr = (lane & 1) ? rb : ra;
                 }
                 for (int chunk = 0; chunk < nk; chunk++, it++) {
@@ -523,58 +615,217 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_mega(MegaArgs a) {
     // ---------------- consumers ----------------------------------------------------------------------
     c.tok = __ldcg(a.d_next);
     c.pos = __ldcg(a.d_pos);
+    c.epoch0 = __ldcg(a.step) * (unsigned)n_phases;
     if (c.tok < 0 || c.tok >= a.vocab) c.tok = 0;
-    // optional per-phase timestamps (ns) of one CTA: [phase][0] work start (barrier passed),
-    // [1] activation vector staged, [2] phase work done
+    const bool tp = a.world > 1;
+    const __half* emb_row = a.emb + (long long)c.tok * a.dim;
+    const int half_dim = a.hd >> 1;
+    // optional per-phase timestamps (ns) of one CTA: [phase][0] phase start, [1] activation vector staged,
+    // [2] phase work done
     const bool prof = a.prof != nullptr && blockIdx.x == a.prof_cta && c.ctid == 0;
-    auto now = []() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-    for (int ph = 0; ph < a.n_phases; ph++) {
-        const MegaPhase& p = a.phases[ph];
-        if (ph > 0) grid_barrier(a, c);
-        if (prof) a.prof[3 * ph] = now();
-        if (p.kind == PH_ATTN) {
-            attn_phase(a, p, c);
-            if (prof) a.prof[3 * ph + 1] = a.prof[3 * ph + 2] = now();
-            continue;
+    for (int l = 0; l < L; l++) {
+        const FlowLayer& lw = a.layers[l];
+        const int p0 = 5 * l;
+        // ---- [RMSNorm + wq|wk|wv + RoPE + KV write] ------------------------------------------------------
+        if (prof) a.prof[3 * p0] = globaltimer_ns();
+        if (l == 0) {
+            stage_vector(a, c, a.dim, lw.attn_norm, [&](int i) { return __ldg(reinterpret_cast<const uint4*>(emb_row) + i); });
+        } else {
+            if (tp) reduce_slice_and_publish(a, c, 1, p0 - 1, a.w.h, a.w.x);     // x = h + sum of the w2 partials
+            const uint32_t e = e16_of(c, p0 - 1);
+            stage_vector(a, c, a.dim, lw.attn_norm, [&](int i) { return gather8(a.w.x + 8 * i, e, a.status); });
         }
-        stage_x(a, p, c);
-        if (prof) a.prof[3 * ph + 1] = now();
-        switch (p.epilogue) {
-            case EPI_STORE: gemv_consume<EPI_STORE>(a, p, c); break;
-            case EPI_STORE_F32: gemv_consume<EPI_STORE_F32>(a, p, c); break;
-            case EPI_RESIDUAL: gemv_consume<EPI_RESIDUAL>(a, p, c); break;
-            case EPI_QKV_ROPE: gemv_consume<EPI_QKV_ROPE>(a, p, c); break;
-            default: gemv_consume<EPI_SWIGLU>(a, p, c); break;
+        if (prof) a.prof[3 * p0 + 1] = globaltimer_ns();
+        {
+            const uint32_t e = e16_of(c, p0);
+            const __half* cs_row = a.cos_t + (long long)c.pos * half_dim;
+            const __half* sn_row = a.sin_t + (long long)c.pos * half_dim;
+            __half* krow = lw.cache_k + (long long)c.pos * a.dl;
+            __half* vrow = lw.cache_v + (long long)c.pos * a.dl;
+            gemv_consume(a, gemv_desc(a, PH_QKV, l), c, [&](int mat, int r, float sa, float sb) {
+                const __half ha = __float2half_rn(sa), hb = __float2half_rn(sb);
+                if (mat == 2) {                       // v: the cache row for later steps, words for this one
+                    *reinterpret_cast<__half2*>(vrow + r) = __halves2half2(ha, hb);
+                    st_word_pair(a.w.v + r, make_word(ha, e), make_word(hb, e));
+                } else {                              // q, k: interleaved-pair rotation, fp16 rounding per op
+                    const int d2 = (r % a.hd) >> 1;
+                    const __half cs = cs_row[d2], sn = sn_row[d2];
+                    const __half o0 = hsub_ref(hmul_ref(ha, cs), hmul_ref(hb, sn));
+                    const __half o1 = hadd_ref(hmul_ref(ha, sn), hmul_ref(hb, cs));
+                    if (mat == 1) *reinterpret_cast<__half2*>(krow + r) = __halves2half2(o0, o1);
+                    st_word_pair((mat == 0 ? a.w.q : a.w.k) + r, make_word(o0, e), make_word(o1, e));
+                }
+            });
         }
-        if (prof) a.prof[3 * ph + 2] = now();
+        if (prof) a.prof[3 * p0 + 2] = globaltimer_ns();
+        // ---- [attention] ----------------------------------------------------------------------------------
+        named_bar_sync(1, CONSUMER_THREADS);      // the attention scratch shares the activation vector's shared memory
+        if (prof) a.prof[3 * (p0 + 1)] = a.prof[3 * (p0 + 1) + 1] = globaltimer_ns();
+        attn_phase(a, c, l, p0 + 1);
+        named_bar_sync(1, CONSUMER_THREADS);
+        if (prof) a.prof[3 * (p0 + 1) + 2] = globaltimer_ns();
+        // ---- [wo + residual] ------------------------------------------------------------------------------
+        if (prof) a.prof[3 * (p0 + 2)] = globaltimer_ns();
+        {
+            const uint32_t e_in = e16_of(c, p0 + 1);
+            stage_vector(a, c, a.dl, nullptr, [&](int i) { return gather8(a.w.att + 8 * i, e_in, a.status); });
+        }
+        if (prof) a.prof[3 * (p0 + 2) + 1] = globaltimer_ns();
+        {
+            const uint32_t e = e16_of(c, p0 + 2);
+            const unsigned int e32 = e32_of(c, p0 + 2);
+            gemv_consume(a, gemv_desc(a, PH_WO, l), c, [&](int mat, int r, float sa, float sb) {
+                if (tp) {                              // K-split: fp32 partial sums into slot [rank] on every rank
+#pragma unroll 1
+                    for (int d = 0; d < a.world; d++) st_xwords2(a.peer_part[0][d] + r, __float_as_uint(sa), __float_as_uint(sb), e32);
+                    return;
+                }
+                __half r0, r1;                         // h = x + wo(att), fp16 add like Tensor::EwiseAdd
+                if (l == 0) { const __half2 rr = *reinterpret_cast<const __half2*>(emb_row + r); r0 = __low2half(rr); r1 = __high2half(rr); }
+                else { const uint2 rw = ld_word2(a.w.x + r); r0 = __ushort_as_half(rw.x & 0xffff); r1 = __ushort_as_half(rw.y & 0xffff); }
+                st_word_pair(a.w.h + r, make_word(hadd_ref(r0, __float2half_rn(sa)), e), make_word(hadd_ref(r1, __float2half_rn(sb)), e));
+            });
+        }
+        if (prof) a.prof[3 * (p0 + 2) + 2] = globaltimer_ns();
+        // ---- [RMSNorm + w1|w3 + SiLU*up] -------------------------------------------------------------------
+        named_bar_sync(1, CONSUMER_THREADS);
+        if (prof) a.prof[3 * (p0 + 3)] = globaltimer_ns();
+        {
+            if (tp) reduce_slice_and_publish(a, c, 0, p0 + 2, l == 0 ? nullptr : a.w.x, a.w.h);
+            const uint32_t e_in = e16_of(c, p0 + 2);
+            stage_vector(a, c, a.dim, lw.ffn_norm, [&](int i) { return gather8(a.w.h + 8 * i, e_in, a.status); });
+        }
+        if (prof) a.prof[3 * (p0 + 3) + 1] = globaltimer_ns();
+        {
+            const uint32_t e = e16_of(c, p0 + 3);
+            gemv_consume(a, gemv_desc(a, PH_GATEUP, l), c, [&](int mat, int r, float sa, float sb) {
+                const __half gate = a.silu_tab[__half_as_ushort(__float2half_rn(sa))];
+                st_word1(a.w.g + r, make_word(hmul_ref(gate, __float2half_rn(sb)), e));
+            });
+        }
+        if (prof) a.prof[3 * (p0 + 3) + 2] = globaltimer_ns();
+        // ---- [w2 + residual] ------------------------------------------------------------------------------
+        named_bar_sync(1, CONSUMER_THREADS);
+        if (prof) a.prof[3 * (p0 + 4)] = globaltimer_ns();
+        {
+            const uint32_t e_in = e16_of(c, p0 + 3);
+            stage_vector(a, c, a.hl, nullptr, [&](int i) { return gather8(a.w.g + 8 * i, e_in, a.status); });
+        }
+        if (prof) a.prof[3 * (p0 + 4) + 1] = globaltimer_ns();
+        {
+            const uint32_t e = e16_of(c, p0 + 4);
+            const unsigned int e32 = e32_of(c, p0 + 4);
+            gemv_consume(a, gemv_desc(a, PH_W2, l), c, [&](int mat, int r, float sa, float sb) {
+                if (tp) {
+#pragma unroll 1
+                    for (int d = 0; d < a.world; d++) st_xwords2(a.peer_part[1][d] + r, __float_as_uint(sa), __float_as_uint(sb), e32);
+                    return;
+                }
+                const uint2 rw = ld_word2(a.w.h + r);
+                const __half r0 = __ushort_as_half(rw.x & 0xffff), r1 = __ushort_as_half(rw.y & 0xffff);
+                st_word_pair(a.w.x + r, make_word(hadd_ref(r0, __float2half_rn(sa)), e), make_word(hadd_ref(r1, __float2half_rn(sb)), e));
+            });
+        }
+        if (prof) a.prof[3 * (p0 + 4) + 2] = globaltimer_ns();
+        named_bar_sync(1, CONSUMER_THREADS);
     }
+    // ---- [RMSNorm + classifier] + greedy sampling -------------------------------------------------------------
+    const int pc = 5 * L;
+    if (prof) a.prof[3 * pc] = globaltimer_ns();
+    {
+        if (tp) reduce_slice_and_publish(a, c, 1, pc - 1, a.w.h, a.w.x);
+        const uint32_t e_in = e16_of(c, pc - 1);
+        stage_vector(a, c, a.dim, a.final_norm, [&](int i) { return gather8(a.w.x + 8 * i, e_in, a.status); });
+    }
+    if (prof) a.prof[3 * pc + 1] = globaltimer_ns();
+    {
+        const unsigned int e32 = e32_of(c, pc);
+        gemv_consume(a, gemv_desc(a, PH_CLS, 0), c, [&](int mat, int r, float sa, float sb) {
+            const __half ha = __float2half_rn(sa), hb = __float2half_rn(sb);
+            if (tp) {                                  // this rank's slice of the logits onto every rank
+                const __half2 pair = __halves2half2(ha, hb);
+#pragma unroll 1
+                for (int d = 0; d < a.world; d++) st_xword(a.peer_logits[d] + (r >> 1), *reinterpret_cast<const unsigned int*>(&pair), e32);
+                return;
+            }
+            *reinterpret_cast<__half2*>(a.logits + r) = __halves2half2(ha, hb);
+            const float va = __half2float(ha), vb = __half2float(hb);      // rows ascend within a lane: '>' keeps the lowest index
+            if (va > c.best_v || c.best_i == 0x7fffffff) { c.best_v = va; c.best_i = r; }
+            if (vb > c.best_v) { c.best_v = vb; c.best_i = r + 1; }
+        });
+    }
+    if (prof) a.prof[3 * pc + 2] = globaltimer_ns();
     if (!c.ok && c.lane == 0) atomicExch(a.status, TL_ERR_TIMEOUT);
-    grid_barrier(a, c);
-    if (blockIdx.x != 0) return;
-    // greedy sampling (lowest index wins ties, CPU.cpp:358-372) and position bookkeeping by CTA 0
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int j = c.ctid; j < a.vocab; j += CONSUMER_THREADS) {
-        float v = __half2float(ldcg_half(a.logits + j));
-        if (bi == 0x7fffffff || v > bv) { bv = v; bi = j; }
+
+    // Greedy sampling (lowest index wins ties, CPU.cpp:358-372) and the bookkeeping of the step.
+    int chosen = -1;
+    if (tp) {
+        // every rank holds all slices once the words of this step have arrived; CTA 0 unpacks and scans them
+        if (blockIdx.x != 0) return;
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        const unsigned int e32 = e32_of(c, pc);
+        for (int j = c.ctid; 2 * j < a.vocab; j += CONSUMER_THREADS) {
+            unsigned int data = 0, flag = 0;
+            bool here = false;
+            for (unsigned i = 0; i < 2 * a.exchange_tries && !here; i++) {
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(data), "=r"(flag) : "l"(a.local_logits + j) : "memory");
+                here = flag == e32;
+            }
+            if (!here) atomicExch(a.status, TL_ERR_TIMEOUT);
+            *reinterpret_cast<unsigned int*>(a.logits + 2 * j) = data;
+            const __half2 hh = *reinterpret_cast<const __half2*>(&data);
+            const float v0 = __low2float(hh), v1 = __high2float(hh);
+            if (bi == 0x7fffffff || v0 > bv) { bv = v0; bi = 2 * j; }
+            if (v1 > bv) { bv = v1; bi = 2 * j + 1; }
+        }
+        c.best_v = bv; c.best_i = bi;
+    } else if (c.warp != 0) {
+        return;                                        // only warp 0 finished rows; the other warps are done
     }
+    // reduce (value, index) over the lanes (and, under tensor parallelism, over the warps of CTA 0)
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        const float ov = __shfl_xor_sync(0xffffffffu, c.best_v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, c.best_i, o);
+        if (ov > c.best_v || (ov == c.best_v && oi < c.best_i)) { c.best_v = ov; c.best_i = oi; }
     }
-    float* sv = c.red;
-    int* si = reinterpret_cast<int*>(c.xs);
-    if (c.lane == 0) { sv[c.warp] = bv; si[c.warp] = bi; }
-    named_bar_sync(1, CONSUMER_THREADS);
-    if (c.ctid == 0) {
-        for (int w = 1; w < CONSUMERS; w++)
-            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-        if (bi == 0x7fffffff) bi = 0;
-        *a.d_next = bi;
-        if (c.pos >= 0 && c.pos < a.max_seq) a.d_generated[c.pos] = bi;
+    if (tp) {
+        float* sv = c.red;
+        int* si = reinterpret_cast<int*>(c.xs);
+        named_bar_sync(1, CONSUMER_THREADS);           // everyone is done with the staged vector
+        if (c.lane == 0) { sv[c.warp] = c.best_v; si[c.warp] = c.best_i; }
+        named_bar_sync(1, CONSUMER_THREADS);
+        if (c.ctid == 0) {
+            float bv = sv[0]; int bi = si[0];
+            for (int w = 1; w < CONSUMERS; w++)
+                if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+            chosen = bi == 0x7fffffff ? 0 : bi;
+        }
+    } else if (c.lane == 0) {
+        // one candidate per CTA; the last CTA to arrive picks among them
+        const unsigned long long cand = ((unsigned long long)__float_as_uint(c.best_v) << 32) | (unsigned int)c.best_i;
+        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(a.cand + blockIdx.x), "l"(cand) : "memory");
+        __threadfence();
+        const unsigned int prev = atomicAdd(a.cand_counter, 1u);
+        if (prev == gridDim.x - 1) {
+            __threadfence();
+            *a.cand_counter = 0;
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (unsigned b = 0; b < gridDim.x; b++) {
+                const unsigned long long v = __ldcg(a.cand + b);
+                const float fv = __uint_as_float((unsigned int)(v >> 32));
+                const int iv = (int)(unsigned int)(v & 0xffffffffu);
+                if (iv != 0x7fffffff && (fv > bv || (fv == bv && iv < bi) || bi == 0x7fffffff)) { bv = fv; bi = iv; }
+            }
+            chosen = bi == 0x7fffffff ? 0 : bi;
+        }
+    }
+    if (chosen >= 0) {
+        *a.d_next = chosen;
+        if (c.pos >= 0 && c.pos < a.max_seq) a.d_generated[c.pos] = chosen;
         *a.d_pos = c.pos + 1;
+        *a.step = __ldcg(a.step) + 1u;
     }
 }
 
@@ -589,12 +840,11 @@ int mega_smem_bytes(int max_k) {
     return NSTAGES * STAGE_BYTES + x_bytes + 2 * NSTAGES * 8 + CONSUMERS * 4 + 2 * CONSUMERS * STAGE_ROWS * 4 + 64;
 }
 
-int launch_decode_mega(const MegaArgs& args, int grid, int smem, cudaStream_t st) {
+int launch_decode_flow(const FlowArgs& args, int grid, int smem, cudaStream_t st) {
     static PerDeviceOnce once;
     if (once.needed()) {
-        TL_CUDA(cudaFuncSetAttribute(k_decode_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        TL_CUDA(cudaFuncSetAttribute(k_decode_flow, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     }
-    TL_CUDA(cudaMemsetAsync(args.grid_bar, 0, sizeof(unsigned int), st));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(MEGA_THREADS);
@@ -605,7 +855,7 @@ int launch_decode_mega(const MegaArgs& args, int grid, int smem, cudaStream_t st
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    TL_CUDA(cudaLaunchKernelEx(&cfg, k_decode_mega, args));
+    TL_CUDA(cudaLaunchKernelEx(&cfg, k_decode_flow, args));
     return TL_OK;
 }
 

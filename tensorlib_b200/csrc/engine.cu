@@ -864,55 +864,39 @@ int Llama2Engine::ensure_decode_graph(cudaStream_t st) {
     return TL_OK;
 }
 
-// Phase list of the one-kernel decode step: the same stages as decode_step_fast, as data.
+// Set-up of the one-kernel decode step: the per-layer weight table, the word vectors the phases hand
+// to one another, the sampling scratch. Under tensor parallelism the exchange region must be open.
 int Llama2Engine::ensure_mega() {
     if (mega_ready_) return TL_OK;
     TL_PROPAGATE(ensure_activations(1, 0));
+    TL_REQUIRE(vocab_local_ % 2 == 0 && cfg_.dim % 16 == 0 && dim_local_ % 16 == 0 && hidden_local_ % 16 == 0,
+               "one-kernel decode needs an even vocabulary slice and widths that are multiples of 16");
+    TL_REQUIRE(cfg_.tp_world == 1 || xch_ready_, "one-kernel decode under tensor parallelism needs the fused exchange (tl_tp_exchange_open)");
     const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_;
-    std::vector<MegaPhase> ph;
-    auto gemv = [&](int epi, const __half* x, const __half* nw, const __half* W0, const __half* W1, const __half* W2,
-                    int n_mats, int N_each, int K) {
-        MegaPhase p{};
-        p.kind = 0; p.epilogue = epi; p.x = x; p.norm_w = nw; p.W0 = W0; p.W1 = W1; p.W2 = W2;
-        p.N_each = N_each; p.K = K;
-        p.total_units = epi == EPI_SWIGLU ? N_each : n_mats * N_each / 2;
-        return p;
-    };
+    std::vector<FlowLayer> lay(cfg_.n_layers);
     for (int l = 0; l < cfg_.n_layers; l++) {
         const LayerWeights& w = layers_[l];
-        const __half* xin = l == 0 ? nullptr : x_;   // layer 0 reads the embedding row of the token
-        MegaPhase qkv = gemv(EPI_QKV_ROPE, xin, w.attn_norm, w.wq, w.wk, w.wv, 3, dl, dim);
-        qkv.y = q_; qkv.k_cache = w.cache_k; qkv.v_cache = w.cache_v;
-        ph.push_back(qkv);
-        MegaPhase at{};
-        at.kind = 1; at.x = q_; at.k_cache = w.cache_k; at.v_cache = w.cache_v; at.y = att_;
-        ph.push_back(at);
-        MegaPhase wo = gemv(EPI_RESIDUAL, att_, nullptr, w.wo, nullptr, nullptr, 1, dim, dl);
-        wo.y = h_; wo.residual = xin;
-        ph.push_back(wo);
-        MegaPhase gu = gemv(EPI_SWIGLU, h_, w.ffn_norm, w.w1, w.w3, nullptr, 2, hl, dim);
-        gu.y = g_;
-        ph.push_back(gu);
-        MegaPhase dn = gemv(EPI_RESIDUAL, g_, nullptr, w.w2, nullptr, nullptr, 1, dim, hl);
-        dn.y = x_; dn.residual = h_;
-        ph.push_back(dn);
+        lay[l] = FlowLayer{w.attn_norm, w.wq, w.wk, w.wv, w.wo, w.ffn_norm, w.w1, w.w3, w.w2, w.cache_k, w.cache_v};
     }
-    MegaPhase cls = gemv(EPI_STORE, x_, final_norm_, (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_,
-                         nullptr, nullptr, 1, vocab_local_, dim);
-    cls.y = logits_;
-    ph.push_back(cls);
-    mega_n_phases_ = (int)ph.size();
-    if (!mega_phases_) {
-        TL_CUDA(cudaMalloc(&mega_phases_, ph.size() * sizeof(MegaPhase)));
-        allocs_.push_back(mega_phases_);
-        void* d = nullptr;
-        TL_CUDA(cudaMalloc(&d, 256));
-        allocs_.push_back(d);
-        grid_bar_ = static_cast<unsigned int*>(d);
-    }
-    TL_CUDA(cudaMemcpy(mega_phases_, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice));
-    const int max_k = std::max(std::max(dim, dl), hl);
     mega_grid_ = sm_count();
+    if (!mega_phases_) {
+        TL_CUDA(cudaMalloc(&mega_phases_, lay.size() * sizeof(FlowLayer)));
+        allocs_.push_back(mega_phases_);
+        // words: x, h [dim]; q, k, v, att [dl]; g [hl]; then the sampling candidates, their counter and the step counter
+        const size_t n_words = 2 * (size_t)dim + 4 * (size_t)dl + (size_t)hl;
+        const size_t bytes = n_words * sizeof(unsigned int) + 256 + (size_t)mega_grid_ * sizeof(unsigned long long) + 256;
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, bytes));
+        TL_CUDA(cudaMemset(d, 0, bytes));
+        allocs_.push_back(d);
+        flow_words_ = static_cast<unsigned int*>(d);
+        unsigned char* tail = reinterpret_cast<unsigned char*>(flow_words_ + n_words);
+        tail = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tail) + 255) & ~(uintptr_t)255);
+        flow_cand_ = reinterpret_cast<unsigned long long*>(tail);
+        flow_counters_ = reinterpret_cast<unsigned int*>(tail + (size_t)mega_grid_ * sizeof(unsigned long long));
+    }
+    TL_CUDA(cudaMemcpy(mega_phases_, lay.data(), lay.size() * sizeof(FlowLayer), cudaMemcpyHostToDevice));
+    const int max_k = std::max(std::max(dim, dl), hl);
     mega_smem_ = mega_smem_bytes(max_k);
     mega_x_bytes_ = mega_x_bytes(max_k);
     TL_REQUIRE(mega_smem_ <= 227 * 1024, "decode step kernel needs %d bytes of shared memory", mega_smem_);
@@ -923,6 +907,7 @@ int Llama2Engine::ensure_mega() {
         allocs_.push_back(d);
         mega_attn_scratch_ = static_cast<float*>(d);
     }
+    mega_n_phases_ = flow_phases(cfg_.n_layers);
     mega_ready_ = true;
     return TL_OK;
 }
@@ -963,18 +948,41 @@ int Llama2Engine::decode_profile(int start_pos, int cta, unsigned long long* out
 }
 
 int Llama2Engine::decode_step_mega(cudaStream_t st, unsigned long long* prof, int prof_cta) {
-    MegaArgs a{};
+    FlowArgs a{};
     a.prof = prof; a.prof_cta = prof_cta;
     last_logits_ = logits_;
-    a.phases = static_cast<const MegaPhase*>(mega_phases_); a.n_phases = mega_n_phases_;
-    a.emb = emb_; a.dim = cfg_.dim; a.vocab = cfg_.vocab_size;
-    a.H = H_local_; a.hd = hd_; a.splits = mega_splits_; a.max_seq = cfg_.max_seq_len; a.kv_pitch = dim_local_;
+    const int dim = cfg_.dim, dl = dim_local_, hl = hidden_local_;
+    a.layers = static_cast<const FlowLayer*>(mega_phases_); a.n_layers = cfg_.n_layers;
+    a.emb = emb_; a.final_norm = final_norm_;
+    a.wcls = (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_;
+    a.dim = dim; a.dl = dl; a.hl = hl; a.vocab = cfg_.vocab_size; a.vocab_local = vocab_local_;
+    a.H = H_local_; a.hd = hd_; a.splits = mega_splits_; a.max_seq = cfg_.max_seq_len;
+    unsigned int* w = flow_words_;
+    a.w.x = w; w += dim; a.w.h = w; w += dim;
+    a.w.q = w; w += dl; a.w.k = w; w += dl; a.w.v = w; w += dl; a.w.att = w; w += dl;
+    a.w.g = w;
     a.attn_scratch = mega_attn_scratch_; a.attn_counters = attn_counters_;
     a.cos_t = cos_t_; a.sin_t = sin_t_; a.silu_tab = tables().silu_float_tab;
-    a.logits = logits_; a.d_next = d_next_; a.d_pos = d_pos_; a.d_generated = d_generated_;
-    a.grid_bar = grid_bar_; a.status = device_status_word(); a.eps = 1e-5f; a.x_bytes = mega_x_bytes_;
+    a.logits = logits_; a.cand = flow_cand_; a.cand_counter = flow_counters_;
+    a.d_next = d_next_; a.d_pos = d_pos_; a.d_generated = d_generated_;
+    a.step = flow_counters_ + 1;
+    a.status = device_status_word(); a.eps = 1e-5f; a.x_bytes = mega_x_bytes_;
+    a.world = cfg_.tp_world; a.rank = cfg_.tp_rank;
+    a.exchange_tries = TL_EXCHANGE_TRIES;
+    if (cfg_.tp_world > 1) {
+        TL_REQUIRE(xch_ready_, "one-kernel decode under tensor parallelism needs the fused exchange");
+        a.step = reinterpret_cast<unsigned int*>(xch_base_ + xch_off_step_);     // the counter every rank advances in step
+        for (int buf = 0; buf < 2; buf++) {
+            a.local_part[buf] = reinterpret_cast<const unsigned long long*>(xch_base_ + xch_off_part_[buf]);
+            for (int d = 0; d < cfg_.tp_world; d++)
+                a.peer_part[buf][d] = reinterpret_cast<unsigned long long*>(xch_peer_[d] + xch_off_part_[buf]) + (size_t)cfg_.tp_rank * dim;
+        }
+        a.local_logits = reinterpret_cast<const unsigned long long*>(xch_base_ + xch_off_logits_);
+        for (int d = 0; d < cfg_.tp_world; d++)
+            a.peer_logits[d] = reinterpret_cast<unsigned long long*>(xch_peer_[d] + xch_off_logits_) + (size_t)cfg_.tp_rank * (vocab_local_ / 2);
+    }
     launches_ += 1;
-    return launch_decode_mega(a, mega_grid_, mega_smem_, st);
+    return launch_decode_flow(a, mega_grid_, mega_smem_, st);
 }
 
 int Llama2Engine::decode_steps(int start_pos, int steps, cudaStream_t st) {

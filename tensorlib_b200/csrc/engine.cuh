@@ -98,11 +98,14 @@ private:
     const __half *cos_t_ = nullptr, *sin_t_ = nullptr;
 
     // one-kernel decode step (single GPU, fast numerics): phase list in device memory
-    bool use_mega() const { return cfg_.one_kernel_decode != 0 && coll_ == nullptr && cfg_.numerics == TL_NUMERICS_FAST; }
+    // the persistent step kernel: single GPU, or tensor parallel once the fused exchange is open
+    bool use_mega() const { return cfg_.one_kernel_decode != 0 && (coll_ == nullptr || xch_ready_) && cfg_.numerics == TL_NUMERICS_FAST; }
     int ensure_mega();
     int decode_step_mega(cudaStream_t st, unsigned long long* prof = nullptr, int prof_cta = 0);
     void* mega_phases_ = nullptr;
-    unsigned int* grid_bar_ = nullptr;
+    unsigned int* flow_words_ = nullptr;          // the vectors the phases hand over, as (value, epoch) words
+    unsigned long long* flow_cand_ = nullptr;     // [grid] per-CTA sampling candidates
+    unsigned int* flow_counters_ = nullptr;       // [0] candidate arrivals, [1] decode steps done (epoch base)
     int mega_n_phases_ = 0, mega_grid_ = 0, mega_smem_ = 0, mega_splits_ = 1, mega_x_bytes_ = 0;
     float* mega_attn_scratch_ = nullptr;
     bool mega_ready_ = false;
