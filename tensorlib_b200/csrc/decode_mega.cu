@@ -407,142 +407,163 @@ __device__ __forceinline__ void gemv_consume(const FlowArgs& a, const GemvDesc& 
 }
 
 // Attention of the new token over positions [0, pos] of the caches, read in place; the newest row
-// (position pos) and the query come from this step's words. Work items are (head, split) pairs; a
-// group of 4 warps takes one item at a time; partial (max, sum, acc) go to a scratch slot; the last
-// group to finish a head merges its splits and publishes the head's output words.
-__device__ __forceinline__ void attn_phase(const FlowArgs& a, Ctx& c, int l, int phase) {
+// (position pos) and the query come from this step's words. A work item is (head, split) and is taken
+// by a whole CTA: 16 warps x ATT_U positions each = 128 positions per pass, all loads of a pass in
+// flight together, so an item of up to 128 positions costs one memory latency. The number of splits
+// follows the context (ceil(S / 128), at most ATT_MAX_SPLITS): with one split the warps' partial
+// (max, sum, acc) meet in shared memory and the head's output words are published at once; with
+// several, partials go to a scratch slot and the last CTA to finish a head merges them.
+constexpr int ATT_U = 8;                        // positions per warp and pass
+constexpr int ATT_MAX_SPLITS = 16;
+__device__ __forceinline__ int attn_splits_for(int S) { return min(ATT_MAX_SPLITS, max(1, (S + 16 * ATT_U - 1) / (16 * ATT_U))); }
+
+// L2 prefetch of the cache rows this CTA will read in the attention phase of layer l (they do not depend
+// on this step, so the request can go out a whole phase early)
+__device__ __forceinline__ void attn_prefetch(const FlowArgs& a, const Ctx& c, int l) {
     const FlowLayer& lw = a.layers[l];
-    const int g = c.warp / ATT_WARPS, gw = c.warp % ATT_WARPS, lane = c.lane;
-    float* gs = reinterpret_cast<float*>(c.xs) + (size_t)g * (ATT_SMEM_PER_GROUP / 4);
-    float* sm_m = gs; float* sm_l = gs + ATT_WARPS; float* sm_acc = gs + 2 * ATT_WARPS;
-    int* is_last = reinterpret_cast<int*>(gs + 2 * ATT_WARPS + ATT_WARPS * MAX_HD);
+    const int hd = a.hd, S = c.pos + 1, splits = attn_splits_for(S), per = (S + splits - 1) / splits;
+    const int lines = (hd * 2 + 127) / 128;     // 128-byte lines per row
+    for (int item = blockIdx.x; item < a.H * splits; item += gridDim.x) {
+        const int h = item / splits, split = item - h * splits;
+        const int s_begin = split * per, s_end = min(c.pos, s_begin + per);      // rows below pos only
+        for (int i = c.ctid; i < (s_end - s_begin) * lines * 2; i += CONSUMER_THREADS) {
+            const int row = i / (2 * lines), rem = i - row * 2 * lines;
+            const __half* base = (rem < lines ? lw.cache_k : lw.cache_v) + (size_t)(s_begin + row) * a.dl + (size_t)h * hd;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(base) + (rem % lines) * 128));
+        }
+    }
+}
+
+template <int HDI>      // head_dim <= 64 * HDI
+__device__ __forceinline__ void attn_phase(const FlowArgs& a, Ctx& c, int l, int phase) {
+    constexpr int U = HDI <= 2 ? ATT_U : ATT_U / 2;         // fewer rows in flight for wide heads: registers
+    const FlowLayer& lw = a.layers[l];
+    const int lane = c.lane, warp = c.warp;
+    float* sm_m = reinterpret_cast<float*>(c.xs);          // [16]
+    float* sm_l = sm_m + CONSUMERS;                          // [16]
+    float* sm_acc = sm_l + CONSUMERS;                        // [16][MAX_HD]
+    int* is_last = reinterpret_cast<int*>(sm_acc + CONSUMERS * MAX_HD);
     const int hd = a.hd, S = c.pos + 1;
-    const int per = (S + a.splits - 1) / a.splits;
+    const int splits = attn_splits_for(S), per = (S + splits - 1) / splits;
     const float scale = rsqrtf((float)hd);
-    const int n_items = a.H * a.splits;
-    const int gtid = gw * 32 + lane;
     const uint32_t e_qkv = e16_of(c, phase - 1), e_out = e16_of(c, phase);
-    for (int item = blockIdx.x * ATT_GROUPS + g; item < n_items; item += gridDim.x * ATT_GROUPS) {
-        const int h = item / a.splits, split = item - h * a.splits;
+    for (int item = blockIdx.x; item < a.H * splits; item += gridDim.x) {
+        const int h = item / splits, split = item - h * splits;
         const int s_begin = split * per, s_end = min(S, s_begin + per);
         float m = -INFINITY, l_sum = 0.f;
-        float2 acc[HD_ITERS];
+        float2 acc[HDI], qf[HDI];
 #pragma unroll
-        for (int i = 0; i < HD_ITERS; i++) acc[i] = make_float2(0.f, 0.f);
-        if (s_begin < s_end) {      // (an empty split only reports -inf)
-            float2 qf[HD_ITERS];
-#pragma unroll
-            for (int i = 0; i < HD_ITERS; i++) {
-                const int d = 2 * lane + 64 * i;
-                if (d < hd) {
-                    uint32_t raw = gather2(a.w.q + (size_t)h * hd + d, e_qkv, a.status);
-                    qf[i] = __half22float2(*reinterpret_cast<__half2*>(&raw));
-                } else qf[i] = make_float2(0.f, 0.f);
-            }
-            constexpr int U = 4;
-            for (int s0 = s_begin + gw * U; s0 < s_end; s0 += ATT_WARPS * U) {
-                unsigned int kv[U][HD_ITERS], vv[U][HD_ITERS];
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    const int s = s0 + u;
-                    const size_t base = (size_t)s * a.dl + (size_t)h * hd;
-#pragma unroll
-                    for (int i = 0; i < HD_ITERS; i++) {
-                        const int d = 2 * lane + 64 * i;
-                        const bool okk = s < s_end && d < hd;
-                        if (okk && s == c.pos) {      // this step's row: still on its way through L2
-                            kv[u][i] = gather2(a.w.k + (size_t)h * hd + d, e_qkv, a.status);
-                            vv[u][i] = gather2(a.w.v + (size_t)h * hd + d, e_qkv, a.status);
-                        } else {
-                            kv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(lw.cache_k + base + d)) : 0u;
-                            vv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(lw.cache_v + base + d)) : 0u;
-                        }
-                    }
-                }
-                float sc[U];
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    float d = 0.f;
-#pragma unroll
-                    for (int i = 0; i < HD_ITERS; i++) {
-                        float2 kf = __half22float2(*reinterpret_cast<__half2*>(&kv[u][i]));
-                        d = fmaf(qf[i].x, kf.x, d);
-                        d = fmaf(qf[i].y, kf.y, d);
-                    }
-                    sc[u] = d;
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-                    for (int u = 0; u < U; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    if (s0 + u < s_end) {
-                        const float x = sc[u] * scale;
-                        const float mn = fmaxf(m, x);
-                        const float corr = __expf(m - mn), pe = __expf(x - mn);
-                        l_sum = l_sum * corr + pe;
-#pragma unroll
-                        for (int i = 0; i < HD_ITERS; i++) {
-                            float2 vf = __half22float2(*reinterpret_cast<__half2*>(&vv[u][i]));
-                            acc[i].x = fmaf(pe, vf.x, acc[i].x * corr);
-                            acc[i].y = fmaf(pe, vf.y, acc[i].y * corr);
-                        }
-                        m = mn;
-                    }
-                }
-            }
-        }
-        if (lane == 0) { sm_m[gw] = m; sm_l[gw] = l_sum; }
-#pragma unroll
-        for (int i = 0; i < HD_ITERS; i++) {
+        for (int i = 0; i < HDI; i++) {
+            acc[i] = make_float2(0.f, 0.f);
             const int d = 2 * lane + 64 * i;
-            if (d < hd) { sm_acc[gw * MAX_HD + d] = acc[i].x; sm_acc[gw * MAX_HD + d + 1] = acc[i].y; }
+            if (d < hd) {
+                uint32_t raw = gather2(a.w.q + (size_t)h * hd + d, e_qkv, a.status);
+                qf[i] = __half22float2(*reinterpret_cast<__half2*>(&raw));
+            } else qf[i] = make_float2(0.f, 0.f);
         }
-        named_bar_sync(2 + g, ATT_WARPS * 32);
+        for (int s0 = s_begin + warp * U; s0 < s_end; s0 += CONSUMERS * U) {
+            unsigned int kv[U][HDI], vv[U][HDI];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int s = s0 + u;
+                const size_t base = (size_t)s * a.dl + (size_t)h * hd;
+#pragma unroll
+                for (int i = 0; i < HDI; i++) {
+                    const int d = 2 * lane + 64 * i;
+                    const bool okk = s < s_end && d < hd;
+                    if (okk && s == c.pos) {      // this step's row: still on its way through L2
+                        kv[u][i] = gather2(a.w.k + (size_t)h * hd + d, e_qkv, a.status);
+                        vv[u][i] = gather2(a.w.v + (size_t)h * hd + d, e_qkv, a.status);
+                    } else {
+                        kv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(lw.cache_k + base + d)) : 0u;
+                        vv[u][i] = okk ? __ldcg(reinterpret_cast<const unsigned int*>(lw.cache_v + base + d)) : 0u;
+                    }
+                }
+            }
+            float sc[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < HDI; i++) {
+                    float2 kf = __half22float2(*reinterpret_cast<__half2*>(&kv[u][i]));
+                    d = fmaf(qf[i].x, kf.x, d);
+                    d = fmaf(qf[i].y, kf.y, d);
+                }
+                sc[u] = d;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int u = 0; u < U; u++) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (s0 + u < s_end) {
+                    const float x = sc[u] * scale;
+                    const float mn = fmaxf(m, x);
+                    const float corr = __expf(m - mn), pe = __expf(x - mn);
+                    l_sum = l_sum * corr + pe;
+#pragma unroll
+                    for (int i = 0; i < HDI; i++) {
+                        float2 vf = __half22float2(*reinterpret_cast<__half2*>(&vv[u][i]));
+                        acc[i].x = fmaf(pe, vf.x, acc[i].x * corr);
+                        acc[i].y = fmaf(pe, vf.y, acc[i].y * corr);
+                    }
+                    m = mn;
+                }
+            }
+        }
+        if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l_sum; }
+#pragma unroll
+        for (int i = 0; i < HDI; i++) {
+            const int d = 2 * lane + 64 * i;
+            if (d < hd) { sm_acc[warp * MAX_HD + d] = acc[i].x; sm_acc[warp * MAX_HD + d + 1] = acc[i].y; }
+        }
+        named_bar_sync(1, CONSUMER_THREADS);
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sm_m[w]);
+        for (int w = 0; w < CONSUMERS; w++) M = fmaxf(M, sm_m[w]);
         float Lsum = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) Lsum += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * __expf(sm_m[w] - M);
-        float* slot = a.attn_scratch + ((size_t)h * a.splits + split) * (hd + 2);
-        for (int d = gtid; d < hd; d += ATT_WARPS * 32) {
-            float v = 0.f;
+        for (int w = 0; w < CONSUMERS; w++) Lsum += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * __expf(sm_m[w] - M);
+        float v = 0.f;
+        if (c.ctid < hd) {
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; w++)
-                v += sm_m[w] == -INFINITY ? 0.f : sm_acc[w * MAX_HD + d] * __expf(sm_m[w] - M);
-            slot[2 + d] = v;
+            for (int w = 0; w < CONSUMERS; w++)
+                v += sm_m[w] == -INFINITY ? 0.f : sm_acc[w * MAX_HD + c.ctid] * __expf(sm_m[w] - M);
         }
-        if (gtid == 0) { slot[0] = M; slot[1] = Lsum; }
-        __threadfence();
-        named_bar_sync(2 + g, ATT_WARPS * 32);
-        if (gtid == 0) {
-            unsigned int prev = atomicAdd(&a.attn_counters[h], 1u);
-            *is_last = prev == (unsigned)a.splits - 1;
-            if (*is_last) a.attn_counters[h] = 0;
-        }
-        named_bar_sync(2 + g, ATT_WARPS * 32);
-        if (*is_last) {
+        if (splits == 1) {
+            if (c.ctid < hd) st_word1(a.w.att + (size_t)h * hd + c.ctid, make_word(__float2half_rn(v / Lsum), e_out));
+        } else {
+            float* slot = a.attn_scratch + ((size_t)h * ATT_MAX_SPLITS + split) * (hd + 2);
+            if (c.ctid < hd) slot[2 + c.ctid] = v;
+            if (c.ctid == 0) { slot[0] = M; slot[1] = Lsum; }
             __threadfence();
-            const float* base = a.attn_scratch + (size_t)h * a.splits * (hd + 2);
-            float GM = -INFINITY;
-            for (int sp = 0; sp < a.splits; sp++) GM = fmaxf(GM, __ldcg(base + (size_t)sp * (hd + 2)));
-            float GL = 0.f;
-            for (int sp = 0; sp < a.splits; sp++) {
-                float ms = __ldcg(base + (size_t)sp * (hd + 2));
-                if (ms != -INFINITY) GL += __ldcg(base + (size_t)sp * (hd + 2) + 1) * __expf(ms - GM);
+            named_bar_sync(1, CONSUMER_THREADS);
+            if (c.ctid == 0) {
+                const unsigned int prev = atomicAdd(&a.attn_counters[h], 1u);
+                *is_last = prev == (unsigned)splits - 1;
+                if (*is_last) a.attn_counters[h] = 0;
             }
-            for (int d = gtid; d < hd; d += ATT_WARPS * 32) {
-                float v = 0.f;
-                for (int sp = 0; sp < a.splits; sp++) {
-                    float ms = __ldcg(base + (size_t)sp * (hd + 2));
-                    if (ms != -INFINITY) v += __ldcg(base + (size_t)sp * (hd + 2) + 2 + d) * __expf(ms - GM);
+            named_bar_sync(1, CONSUMER_THREADS);
+            if (*is_last && c.ctid < hd) {
+                __threadfence();
+                const float* base = a.attn_scratch + (size_t)h * ATT_MAX_SPLITS * (hd + 2);
+                float GM = -INFINITY;
+                for (int sp = 0; sp < splits; sp++) GM = fmaxf(GM, __ldcg(base + (size_t)sp * (hd + 2)));
+                float GL = 0.f, out = 0.f;
+                for (int sp = 0; sp < splits; sp++) {
+                    const float ms = __ldcg(base + (size_t)sp * (hd + 2));
+                    if (ms != -INFINITY) {
+                        const float w = __expf(ms - GM);
+                        GL += __ldcg(base + (size_t)sp * (hd + 2) + 1) * w;
+                        out += __ldcg(base + (size_t)sp * (hd + 2) + 2 + c.ctid) * w;
+                    }
                 }
-                st_word1(a.w.att + (size_t)h * hd + d, make_word(__float2half_rn(v / GL), e_out));
+                st_word1(a.w.att + (size_t)h * hd + c.ctid, make_word(__float2half_rn(out / GL), e_out));
             }
         }
-        named_bar_sync(2 + g, ATT_WARPS * 32);  // the group's shared scratch is reused by its next item
+        named_bar_sync(1, CONSUMER_THREADS);  // the shared scratch is reused by the CTA's next item
     }
 }
 
@@ -628,6 +649,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_flow(FlowArgs a) {
         const int p0 = 5 * l;
         // ---- [RMSNorm + wq|wk|wv + RoPE + KV write] ------------------------------------------------------
         if (prof) a.prof[3 * p0] = globaltimer_ns();
+        attn_prefetch(a, c, l);
         if (l == 0) {
             stage_vector(a, c, a.dim, lw.attn_norm, [&](int i) { return __ldg(reinterpret_cast<const uint4*>(emb_row) + i); });
         } else {
@@ -661,7 +683,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_decode_flow(FlowArgs a) {
         // ---- [attention] ----------------------------------------------------------------------------------
         named_bar_sync(1, CONSUMER_THREADS);      // the attention scratch shares the activation vector's shared memory
         if (prof) a.prof[3 * (p0 + 1)] = a.prof[3 * (p0 + 1) + 1] = globaltimer_ns();
-        attn_phase(a, c, l, p0 + 1);
+        if (a.hd <= 64) attn_phase<1>(a, c, l, p0 + 1);
+        else if (a.hd <= 128) attn_phase<2>(a, c, l, p0 + 1);
+        else attn_phase<4>(a, c, l, p0 + 1);
         named_bar_sync(1, CONSUMER_THREADS);
         if (prof) a.prof[3 * (p0 + 1) + 2] = globaltimer_ns();
         // ---- [wo + residual] ------------------------------------------------------------------------------

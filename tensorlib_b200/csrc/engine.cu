@@ -900,7 +900,7 @@ int Llama2Engine::ensure_mega() {
     mega_smem_ = mega_smem_bytes(max_k);
     mega_x_bytes_ = mega_x_bytes(max_k);
     TL_REQUIRE(mega_smem_ <= 227 * 1024, "decode step kernel needs %d bytes of shared memory", mega_smem_);
-    mega_splits_ = mega_attn_splits(H_local_, mega_grid_);
+    mega_splits_ = 16;    // scratch slots per head: the kernel picks ceil(context / 128) splits, at most 16
     if (!mega_attn_scratch_) {
         void* d = nullptr;
         TL_CUDA(cudaMalloc(&d, (size_t)H_local_ * 16 * (hd_ + 2) * sizeof(float)));
