@@ -580,8 +580,9 @@ def prefill_2048(model, cfg, world, torch, dist, T: int = 2048):
 
 def matmul_sweep(tl, torch, m_list=(1, 8, 32, 128, 512, 2048),
                  kn_list=((4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)), with_baselines: bool = True):
-    """Config 1: y = x W^T, fp16 in / fp32 accumulate, device-resident, rotating over enough
-    weight copies (>= 512 MB) that no launch finds its weights in L2. 6 x 4 = 24 points, one row each
+    """Config 1: y = x W^T, fp16 in / fp32 accumulate, device-resident, through tl_linear_f16 (the weights are
+    parameters), rotating over enough weight copies (>= 512 MB) that no launch finds its weights in L2.
+    6 x 4 = 24 points, one row each
     (see `columns`). Two same-GPU baselines are timed beside every point, neither on the product
     path: cuBLAS through torch.matmul, and the reference's own CUDA route CUDA<half>::matmul2d
     (gemv_v6 at M = 1, cublasHgemm with a handle created per call otherwise; compiled from the
@@ -622,9 +623,8 @@ def matmul_sweep(tl, torch, m_list=(1, 8, 32, 128, 512, 2048),
             x = torch.randn(M, K, device="cuda", dtype=torch.float16)
             y = torch.empty(M, N, device="cuda", dtype=torch.float16)
 
-            def run(i):
-                tl.check(lib.tl_matmul2d_f16(x.data_ptr(), Ws[i % copies].data_ptr(), y.data_ptr(), M, N, K,
-                                             tl.FAST, sp), "tl_matmul2d_f16")
+            def run(i):      # y = x W^T with W a constant parameter: the nn::Linear form of the sweep
+                tl.check(lib.tl_linear_f16(x.data_ptr(), Ws[i % copies].data_ptr(), y.data_ptr(), M, K, N, sp), "tl_linear_f16")
             sec = timed(run, 50)
             want = x[:4].float() @ Ws[49 % copies].float().t()        # the last timed launch, four rows in fp32
             err = float(((y[:4].float() - want).abs() / want.abs().clamp_min(float(want.pow(2).mean().sqrt()))).max())
@@ -664,8 +664,8 @@ def main():
     ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
                     help="N>1 decode: partial sums exchanged by peer stores inside the GEMV kernels (default) "
                          "or by ncclAllReduce between them")
-    ap.add_argument("--decode-path", default="kernel", choices=["kernel", "graph"],
-                    help="decode step as one persistent dataflow kernel (default) or as a CUDA graph of fused kernels")
+    ap.add_argument("--decode-path", default="graph", choices=["graph", "kernel"],
+                    help="decode step as a CUDA graph of fused kernels (default, the faster one) or as one persistent dataflow kernel")
     ap.add_argument("--profile-step", action="store_true",
                     help="profiling only: after the timed region run one decode step with device timestamps and "
                          "print the per-phase microseconds of rank 0 (median over layers)")

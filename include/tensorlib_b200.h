@@ -88,10 +88,10 @@ TL_API int tl_free_host(void* hptr);
 /* ---- matmul: the drop-in boundary --------------------------------------------------------- */
 /* Device<half>::matmul2d (tensorLib/include/device/Device.hpp:22; CUDA implementation
  * tensorLib/src/device/cuda/gemm.cu:153-172): C[M,N] = A[M,K] * B[N,K]^T, all row-major
- * contiguous. Dispatches on M in fast numerics: M = 1..8 the streaming GEMV ring (up to eight
- * activation rows ride the eight columns of the MMA's B operand, so they cost the weight traffic
- * of one; needs N even and K % 16 == 0), 9..128 (and other 2..8 shapes) the skinny tensor-core
- * kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair tiles);
+ * contiguous. Dispatches on M in fast numerics: M = 1..32 the streaming GEMV ring (the activation
+ * rows ride the columns of the MMA's B operand, eight per warp column group, so they cost the
+ * weight traffic of one; needs N even and K % 16 == 0), 33..128 (and other 2..32 shapes) the skinny
+ * tensor-core kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair tiles);
  * operands that are not 16-byte aligned or K % 8 != 0 take the any-shape kernel.
  * All kernels are launched with programmatic stream serialization and wait on the device for the
  * previous kernel of `stream` before touching A, B or C, so back-to-back calls overlap their
@@ -99,6 +99,14 @@ TL_API int tl_free_host(void* hptr);
  * for that stream (kept until exit): make it before starting a stream capture. */
 TL_API int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t M, size_t N, size_t K,
                     int numerics, tl_stream stream);
+/* nn::Linear<half>::forward (tensorLib/src/nn/linear.cpp:43-49; weight [out, in] as linear.cpp:10-14
+ * stores it): y[T, out] = x[T, in] * W[out, in]^T in fast numerics. Same kernels as tl_matmul2d_f16
+ * with one more promise from the caller: W is a parameter, i.e. no kernel in flight on `stream`
+ * writes it. For T <= 8 the weight stream then starts before the previous kernel of the stream has
+ * finished (only x and y are ordered behind it), which takes the ring's fill latency off a chain of
+ * Linear layers. */
+TL_API int tl_linear_f16(const tl_half* x, const tl_half* W, tl_half* y, size_t T, size_t in_features,
+                         size_t out_features, tl_stream stream);
 /* The per-batch loop of ops::matmul::call2 (tensorLib/src/ops/matmul.cpp:297-321) as one call:
  * for b in [0,batch): C_b[M,N] = A_b[M,K] * B_b[N,K]^T with row pitches lda/ldb/ldc and batch
  * strides (all in elements; a batch stride of 0 broadcasts, as call2's stride-0 views do). */

@@ -53,6 +53,7 @@ _SIGS = {
     "tl_matmul2d_f16": [_vp, _vp, _vp, _sz, _sz, _sz, _int, _vp],
     "tl_matmul_batched_f16": [_vp, _vp, _vp] + [_sz] * 10 + [_int, _vp],
     "tl_matmul2d_f16_host": [_vp, _vp, _vp, _sz, _sz, _sz, _int],
+    "tl_linear_f16": [_vp, _vp, _vp, _sz, _sz, _sz, _vp],
     "tl_matmul_strided_f16": [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _vp, _int, _sz, _sz, _int, _vp],
     "tl_rms_norm_f16": [_vp, _vp, _vp, C.c_float, _int, _int, _int, _vp],
     "tl_apply_rotary_emb_f16": [_vp, _vp, _int, _int, _int, _int, _int, _vp],
@@ -227,6 +228,15 @@ def matmul2d(A: np.ndarray, B: np.ndarray, numerics: int = FAST) -> np.ndarray:
     dA, dB, dC = DeviceBuffer.from_numpy(A), DeviceBuffer.from_numpy(B), DeviceBuffer(max(M * N * 2, 2))
     check(load().tl_matmul2d_f16(dA.ptr, dB.ptr, dC.ptr, M, N, K, numerics, None), "tl_matmul2d_f16")
     return dC.to_numpy(np.float16, (M, N))
+
+
+def linear(x: np.ndarray, W: np.ndarray) -> np.ndarray:
+    """nn::Linear::forward: x[T, in] @ W[out, in]^T through tl_linear_f16."""
+    T, K = x.shape
+    N, _ = W.shape
+    dx, dW, dy = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(W), DeviceBuffer(max(T * N * 2, 2))
+    check(load().tl_linear_f16(dx.ptr, dW.ptr, dy.ptr, T, K, N, None), "tl_linear_f16")
+    return dy.to_numpy(np.float16, (T, N))
 
 
 def matmul2d_host(A: np.ndarray, B: np.ndarray, numerics: int = FAST) -> np.ndarray:

@@ -73,7 +73,7 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
     TL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && sm_count >= 1 && M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "bad shape");
     *grid = *tile_n = *k_blocks_per_cta = *cluster = 0;
     if (M == 1 && N % 2 == 0 && K % 16 == 0 && K <= 12288) { *kernel = TL_PLAN_GEMV_RING; return TL_OK; }
-    if (M >= 2 && M <= 8 && N % 2 == 0 && K % 16 == 0) {   // the same ring with M columns in the MMA's B operand
+    if (M >= 2 && M <= 32 && N % 2 == 0 && K % 16 == 0) {   // the same ring with the M rows as columns of the MMA's B operand
         *kernel = TL_PLAN_GEMV_RING; *grid = (int)std::min<size_t>((size_t)sm_count, (N / 2 + 7) / 8);
         return TL_OK;
     }
@@ -157,6 +157,23 @@ int tl_matmul_strided_f16(const tl_half* lhs, const tl_half* rhs, tl_half* resul
 int tl_matmul2d_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t M, size_t N, size_t K,
                     int numerics, tl_stream stream) {
     return tl_matmul_batched_f16(A, B, C, 1, M, N, K, K, K, N, 0, 0, 0, numerics, stream);
+}
+
+// nn::Linear<half>::forward (tensorLib/src/nn/linear.cpp:43-49): y[T, out] = x[T, in] * W[out, in]^T.
+int tl_linear_f16(const tl_half* x, const tl_half* W, tl_half* y, size_t T, size_t in_features, size_t out_features,
+                  tl_stream stream) {
+    TL_CHECK_INIT();
+    if (T == 0 || out_features == 0) return TL_OK;
+    TL_REQUIRE(x && W && y, "null pointer");
+    TL_REQUIRE(T < (1u << 31) && in_features < (1u << 31) && out_features < (1u << 31), "dimension too large");
+    const size_t K = in_features, N = out_features;
+    cudaStream_t st = as_stream(stream);
+    // 1..8 rows ride the weight-streaming ring, whose producer may run ahead of the previous kernel: W is a parameter
+    if (T == 1 && gemv_supported(x, W, 1, N, K, K) && N % 2 == 0 && K % 16 == 0 && K <= 12288)
+        return launch_gemv(H(x), H(W), H(y), 1, (int)N, (int)K, K, K, N, st, true);
+    if (gemv_ring_rows_supported(x, W, T, N, K, K, K))
+        return launch_gemv(H(x), H(W), H(y), (int)T, (int)N, (int)K, K, K, N, st, true);
+    return tl_matmul2d_f16(x, W, y, T, N, K, TL_NUMERICS_FAST, stream);
 }
 
 int tl_matmul2d_f16_host(const tl_half* A_host, const tl_half* B_host, tl_half* C_host, size_t M,

@@ -602,18 +602,22 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring2(RingA
 }
 
 // ---------------------------------------------------------------------------------------------
-// k_gemv_ring_rows: the same ring for 2..8 activation rows (tl_matmul2d_f16 with M = 2..8).
+// k_gemv_ring_rows<G>: the same ring for 2..32 activation rows (tl_matmul2d_f16 with M = 2..32).
 // The B operand of mma.sync.m16n8k16 has eight columns; the M = 1 kernel fills column 0 only. Here
-// column m is activation row m, so up to eight rows cost the weight stream of one: the kernel
-// stays HBM-bound at 2*N*K bytes. The activation rows (up to 8 x K halfs) do not fit beside the
-// 3 x 64.5 KB ring, so they are not staged: every lane fetches its B fragments (row lane/4, two
-// 4-byte words per k16 step) for the coming chunk straight from global memory BEFORE it waits for
-// the chunk's weights, which hides the L1/L2 latency behind the HBM latency of the stage. Per-warp
-// partial sums [32 rows x 8 columns] meet in shared memory; warp w finishes the two rows of unit w.
+// column m of column group j is activation row 8 j + m, so up to 8 G rows cost the weight stream of
+// one: the kernel stays HBM-bound at 2*N*K bytes. The 16 consumer warps form a (16 / G) x G grid:
+// warp (kq, cg) multiplies the k16 steps [kq * 4 G, (kq + 1) * 4 G) of every chunk against column
+// group cg for all 32 rows of a stage, so a stage is read from shared memory G times (G = 4:
+// 256 KB per 64 KB stage, ~1 us at 128 B/clk against the ~1.5 us a stage takes to arrive from HBM).
+// The activation rows (up to 32 x K halfs) do not fit beside the 3 x 64.5 KB ring, so they are not
+// staged: every lane fetches its B fragments (row 8 cg + lane/4, two 4-byte words per k16 step) for
+// the coming chunk straight from global memory BEFORE it waits for the chunk's weights, which hides
+// the L1/L2 latency behind the HBM latency of the stage. Per-warp partial sums [32 rows x 8 columns]
+// meet in shared memory (16 KB whatever G is); warp w finishes the two rows of unit w.
 // ---------------------------------------------------------------------------------------------
 struct RowsCfg {
     using Ring = RingCfg<16, 3>;
-    static constexpr int PART_FLOATS = 16 * Ring::STAGE_ROWS * 8;   // per buffer: [warp][row][column]
+    static constexpr int PART_FLOATS = 16 * Ring::STAGE_ROWS * 8;   // per buffer: [kq][row][8 G columns] = 16 warps x 32 rows x 8
     static size_t smem_bytes() {
         return (size_t)3 * Ring::STAGE_BYTES + 2 * 3 * sizeof(uint64_t) + 16 + 2 * PART_FLOATS * sizeof(float);
     }
@@ -623,10 +627,13 @@ __device__ __forceinline__ uint32_t ldg_u32(const __half* p) {
     return __ldg(reinterpret_cast<const unsigned int*>(p));
 }
 
+template <int G>
 __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(RingArgs p) {
     using Cfg = RingCfg<16, 3>;
     constexpr int CONSUMERS = 16, NSTAGES = 3, STAGE_ROWS = Cfg::STAGE_ROWS, STAGE_BYTES = Cfg::STAGE_BYTES;
-    constexpr int STEPS_PER_WARP = Cfg::STEPS_PER_WARP;
+    constexpr int KQ = CONSUMERS / G;            // ways the k16 steps of a chunk are split
+    constexpr int STEPS = (KC / 16) / KQ;        // steps per warp and chunk
+    constexpr int COLS = 8 * G;
     extern __shared__ __align__(128) unsigned char smem[];
     // layout: [3 stages][full barriers][empty barriers][pad][partials: 2 buffers]
     unsigned char* stages = smem;
@@ -640,7 +647,6 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(R
     const int n_units = u_end - u_begin;
     const int n_tiles = (n_units + CONSUMERS - 1) / CONSUMERS;
     const int nk = (p.K + KC - 1) / KC;
-    const int n_iters = n_tiles * nk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGES; s++) {
@@ -661,9 +667,11 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(R
     }
 
     pdl_wait();  // the activation rows may have been written by the previous kernel
+    const int kq = warp / G, cg = warp % G;
     const int g = lane >> 2, t = lane & 3;
-    const bool col_ok = g < p.m_rows;                         // column g of B = activation row g
-    const __half* xrow = p.x + (long long)(col_ok ? g : 0) * p.ldx + 2 * t;
+    const int xrow_idx = 8 * cg + g;                           // column g of this warp's B = activation row 8 cg + g
+    const bool col_ok = xrow_idx < p.m_rows;
+    const __half* xrow = p.x + (long long)(col_ok ? xrow_idx : 0) * p.ldx + 2 * t;
     const uint32_t lm_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + (lane >> 4) * 16);
     bool ok = true;
     int it = 0;
@@ -674,10 +682,10 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(R
             const int s = it % NSTAGES, use = it / NSTAGES;
             const int steps = min(KC, p.K - chunk * KC) >> 4;
             // this warp's B fragments of the chunk, in flight while the weights arrive
-            uint32_t b0[STEPS_PER_WARP], b1[STEPS_PER_WARP];
+            uint32_t b0[STEPS], b1[STEPS];
 #pragma unroll
-            for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
-                const int step = warp * STEPS_PER_WARP + kk;
+            for (int kk = 0; kk < STEPS; kk++) {
+                const int step = kq * STEPS + kk;
                 b0[kk] = b1[kk] = 0u;
                 if (col_ok && step < steps) {
                     const __half* xk = xrow + chunk * KC + step * 16;
@@ -690,8 +698,8 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(R
             if (!ok) break;
             const uint32_t sbase = smem_u32(stages + (size_t)s * STAGE_BYTES) + lm_off;
 #pragma unroll
-            for (int kk = 0; kk < STEPS_PER_WARP; kk++) {
-                const int step = warp * STEPS_PER_WARP + kk;
+            for (int kk = 0; kk < STEPS; kk++) {
+                const int step = kq * STEPS + kk;
                 if (step < steps) {
                     uint32_t a0, a1, a2, a3, c0, c1, c2, c3;
                     ldmatrix_x4(sbase + step * 32, a0, a1, a2, a3);
@@ -704,25 +712,26 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring_rows(R
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
         if (!ok) break;
-        // accumulator layout: d[0], d[1] = (row g, columns 2t, 2t+1); d[2], d[3] = (row g + 8, same columns)
-        float* part = partials + (tile & 1) * RowsCfg::PART_FLOATS + warp * (STAGE_ROWS * 8);
-        *reinterpret_cast<float2*>(part + g * 8 + 2 * t) = make_float2(acc0[0], acc0[1]);
-        *reinterpret_cast<float2*>(part + (g + 8) * 8 + 2 * t) = make_float2(acc0[2], acc0[3]);
-        *reinterpret_cast<float2*>(part + (g + 16) * 8 + 2 * t) = make_float2(acc1[0], acc1[1]);
-        *reinterpret_cast<float2*>(part + (g + 24) * 8 + 2 * t) = make_float2(acc1[2], acc1[3]);
+        // accumulator layout: d[0], d[1] = (row g, columns 2t, 2t+1); d[2], d[3] = (row g + 8, same columns).
+        // partials[kq][row][8 cg + column]
+        float* part = partials + (tile & 1) * RowsCfg::PART_FLOATS + kq * (STAGE_ROWS * COLS) + 8 * cg;
+        *reinterpret_cast<float2*>(part + g * COLS + 2 * t) = make_float2(acc0[0], acc0[1]);
+        *reinterpret_cast<float2*>(part + (g + 8) * COLS + 2 * t) = make_float2(acc0[2], acc0[3]);
+        *reinterpret_cast<float2*>(part + (g + 16) * COLS + 2 * t) = make_float2(acc1[0], acc1[1]);
+        *reinterpret_cast<float2*>(part + (g + 24) * COLS + 2 * t) = make_float2(acc1[2], acc1[3]);
         consumer_bar_sync(CONSUMERS * 32);
-        // warp w finishes unit w of the tile: 2 rows x 8 columns = 16 sums of 16 partials; the two
-        // half-warps add eight partials each
-        const int o = lane & 15, hi = lane >> 4;
-        const float* src = partials + (tile & 1) * RowsCfg::PART_FLOATS + (2 * warp) * 8 + o;
-        float sum = 0.f;
+        // warp w finishes unit w of the tile: 2 rows x 8 G columns, each the sum of KQ partials
+        const float* src = partials + (tile & 1) * RowsCfg::PART_FLOATS + (2 * warp) * COLS;
 #pragma unroll
-        for (int w = 0; w < 8; w++) sum += src[(hi * 8 + w) * (STAGE_ROWS * 8)];
-        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-        const int col = o & 7;
-        if (hi == 0 && warp < units_here && col < p.m_rows) {
-            const int n = (u_begin + tile * CONSUMERS + warp) * 2 + (o >> 3);
-            p.y[(long long)col * p.ldy + n] = __float2half_rn(sum);
+        for (int o = lane; o < 2 * COLS; o += 32) {
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < KQ; q++) sum += src[q * (STAGE_ROWS * COLS) + o];
+            const int col = o % COLS;
+            if (warp < units_here && col < p.m_rows) {
+                const int n = (u_begin + tile * CONSUMERS + warp) * 2 + o / COLS;
+                p.y[(long long)col * p.ldy + n] = __float2half_rn(sum);
+            }
         }
     }
     if (!ok && lane == 0) atomicExch(p.status, TL_ERR_TIMEOUT);
@@ -842,28 +851,35 @@ bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, 
 }
 
 bool gemv_ring_rows_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw, size_t ldx) {
-    return M >= 2 && M <= 8 && gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0 && ldw == K && N % 2 == 0 && K % 16 == 0;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    return M >= 2 && M <= 32 && N >= 2 && K >= 16 && al16(x) && al16(W) && ldx % 8 == 0 && ldw == K && N % 2 == 0 && K % 16 == 0;
 }
 
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
-                long long ldx, long long ldy, cudaStream_t st) {
-    TL_REQUIRE(gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0, "gemv: unsupported shape or alignment");
+                long long ldx, long long ldy, cudaStream_t st, bool weights_constant) {
+    TL_REQUIRE((gemv_supported(x, W, M, N, K, ldw) && ldx % 8 == 0) || gemv_ring_rows_supported(x, W, M, N, K, ldw, ldx),
+               "gemv: unsupported shape or alignment");
     if (M == 1 && ldw == K && N % 2 == 0 && K % 16 == 0 && K <= 12288) {  // the decode kernel, plain store epilogue
         FusedGemv f{};
         f.x = x; f.W[0] = W; f.n_mats = 1; f.N_each = N; f.K = K; f.epilogue = EPI_STORE; f.y = y;
-        f.pdl = true; f.weights_may_change = true;
+        f.pdl = true; f.weights_may_change = !weights_constant;
         return launch_fused_gemv(f, st);
     }
     if (gemv_ring_rows_supported(x, W, M, N, K, ldw, ldx)) {   // up to eight rows at the weight traffic of one
         static PerDeviceOnce once;
-        if (once.needed())
-            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
+        if (once.needed()) {
+            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
+            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
+            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
+        }
         RingArgs a{};
         a.x = x; a.W0 = W; a.N_each = N; a.K = K; a.total_units = N / 2; a.y = y;
-        a.status = device_status_word(); a.wait_weights = 1;
+        a.status = device_status_word(); a.wait_weights = weights_constant ? 0 : 1;
         a.m_rows = M; a.ldx = ldx; a.ldy = ldy;
         const int grid = std::max(1, std::min(sm_count(), (a.total_units + 7) / 8));
-        return launch_pdl(k_gemv_ring_rows, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
+        if (M <= 8) return launch_pdl(k_gemv_ring_rows<1>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
+        if (M <= 16) return launch_pdl(k_gemv_ring_rows<2>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
+        return launch_pdl(k_gemv_ring_rows<4>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
     }
     int KT = 16384 / M;                 // halfs per tile so that M*KT*2 <= 32 KB
     KT &= ~255;

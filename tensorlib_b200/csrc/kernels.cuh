@@ -68,8 +68,10 @@ int launch_cast(void* out, const void* in, size_t n, int kind, cudaStream_t st);
 // ---- gemv.cu: the decode path (M = 1..8), fast numerics ---------------------------------------
 // y[m, n] = sum_k x[m, k] W[n, k]; requires K % 8 == 0 and 16-byte aligned rows.
 bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw);
+// weights_constant: no kernel in flight on `st` writes W, so its stream may start before the previous
+// kernel of the stream has finished (nn::Linear's parameter; a generic matmul operand may not promise that)
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
-                long long ldx, long long ldy, cudaStream_t st);
+                long long ldx, long long ldy, cudaStream_t st, bool weights_constant = false);
 // 2 <= M <= 8 on the weight-streaming ring (the activation rows are the columns of the MMA's B operand)
 bool gemv_ring_rows_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw, size_t ldx);
 

@@ -117,7 +117,7 @@ def test_empty_and_invalid_arguments(tl):
 
 
 # ---- fast numerics: tolerance ------------------------------------------------------------------------
-@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 7, 8])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 7, 8, 9, 16, 17, 25, 32])
 def test_fast_gemv_small_m(tl, oracle, M):
     for (N, K) in ((288, 288), (768, 288), (288, 768), (1000, 4096), (513, 1032), (64, 11008)):
         A = synth.normal_f16(31, M, M * K, 1.0).reshape(M, K)
@@ -309,3 +309,15 @@ def test_batched_matmul_with_a_batch_stride_that_is_not_a_multiple_of_8(tl, orac
     got = dC.to_numpy(np.float16, (b, M, N))
     a3 = np.stack([A[i * (M * K + pad): i * (M * K + pad) + M * K].reshape(M, K) for i in range(b)])
     assert max_rel_err(got, oracle.bmm_nt(np.ascontiguousarray(a3), Bt)) <= MATMUL_RTOL
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 20])
+def test_linear_entry_point_matches_the_oracle(tl, oracle, T):
+    """tl_linear_f16 (nn::Linear::forward with a constant weight): same results as the matmul entry point."""
+    for (N, K) in ((768, 288), (1000, 4096), (4096, 11008)):
+        x = synth.normal_f16(93, T, T * K, 1.0).reshape(T, K)
+        W = synth.normal_f16(93, 2, N * K, 0.02).reshape(N, K)
+        got = tl.linear(x, W)
+        assert max_rel_err(got, oracle.matmul2d(x, W)) <= MATMUL_RTOL, (T, N, K)
+        assert_bit_equal(got, tl.matmul2d(x, W, numerics=tl.FAST), "linear vs matmul2d")
+    assert tl.device_status() == 0
