@@ -88,10 +88,10 @@ TL_API int tl_free_host(void* hptr);
 /* ---- matmul: the drop-in boundary --------------------------------------------------------- */
 /* Device<half>::matmul2d (tensorLib/include/device/Device.hpp:22; CUDA implementation
  * tensorLib/src/device/cuda/gemm.cu:153-172): C[M,N] = A[M,K] * B[N,K]^T, all row-major
- * contiguous. Dispatches on M in fast numerics: M = 1..32 the streaming GEMV ring (the activation
- * rows ride the columns of the MMA's B operand, eight per warp column group, so they cost the
- * weight traffic of one; needs N even and K % 16 == 0), 33..128 (and other 2..32 shapes) the skinny
- * tensor-core kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair tiles);
+ * contiguous. Dispatches on M in fast numerics: M = 1..8 the streaming GEMV ring (up to eight
+ * activation rows ride the eight columns of the MMA's B operand, so they cost the weight traffic
+ * of one; needs N even and K % 16 == 0), 9..128 (and other 2..8 shapes) the skinny tensor-core
+ * kernel (weights streamed once), larger M the tcgen05 HGEMM (single-CTA or CTA-pair tiles);
  * operands that are not 16-byte aligned or K % 8 != 0 take the any-shape kernel.
  * All kernels are launched with programmatic stream serialization and wait on the device for the
  * previous kernel of `stream` before touching A, B or C, so back-to-back calls overlap their

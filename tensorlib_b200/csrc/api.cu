@@ -73,7 +73,7 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
     TL_REQUIRE(M >= 1 && N >= 1 && K >= 8 && sm_count >= 1 && M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "bad shape");
     *grid = *tile_n = *k_blocks_per_cta = *cluster = 0;
     if (M == 1 && N % 2 == 0 && K % 16 == 0 && K <= 12288) { *kernel = TL_PLAN_GEMV_RING; return TL_OK; }
-    if (M >= 2 && M <= 32 && N % 2 == 0 && K % 16 == 0) {   // the same ring with the M rows as columns of the MMA's B operand
+    if (M >= 2 && M <= 8 && N % 2 == 0 && K % 16 == 0) {   // the same ring with the M rows as columns of the MMA's B operand
         *kernel = TL_PLAN_GEMV_RING; *grid = (int)std::min<size_t>((size_t)sm_count, (N / 2 + 7) / 8);
         return TL_OK;
     }

@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(RingCfg<16, 3>::THREADS, 1) k_gemv_ring2(RingA
 }
 
 // ---------------------------------------------------------------------------------------------
-// k_gemv_ring_rows<G>: the same ring for 2..32 activation rows (tl_matmul2d_f16 with M = 2..32).
+// k_gemv_ring_rows<G>: the same ring for 2..8 G activation rows (used with G = 1: tl_matmul2d_f16 with M = 2..8).
 // The B operand of mma.sync.m16n8k16 has eight columns; the M = 1 kernel fills column 0 only. Here
 // column m of column group j is activation row 8 j + m, so up to 8 G rows cost the weight stream of
 // one: the kernel stays HBM-bound at 2*N*K bytes. The 16 consumer warps form a (16 / G) x G grid:
@@ -852,7 +852,10 @@ bool gemv_supported(const void* x, const void* W, size_t M, size_t N, size_t K, 
 
 bool gemv_ring_rows_supported(const void* x, const void* W, size_t M, size_t N, size_t K, size_t ldw, size_t ldx) {
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    return M >= 2 && M <= 32 && N >= 2 && K >= 16 && al16(x) && al16(W) && ldx % 8 == 0 && ldw == K && N % 2 == 0 && K % 16 == 0;
+    // More than eight rows (G = 2, 4 column groups) measured slower than the skinny tensor-core kernel: 16 or 32
+    // activation rows no longer fit the ~28 KB of L1 left beside the ring, so the B fragments come from L2 at two to
+    // four times the bytes of the weight stream (M = 16: 27.3 us against 22.7 us at 4096 x 11008; M = 32: 51.8 against 23.8).
+    return M >= 2 && M <= 8 && N >= 2 && K >= 16 && al16(x) && al16(W) && ldx % 8 == 0 && ldw == K && N % 2 == 0 && K % 16 == 0;
 }
 
 int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K, long long ldw,
@@ -867,19 +870,14 @@ int launch_gemv(const __half* x, const __half* W, __half* y, int M, int N, int K
     }
     if (gemv_ring_rows_supported(x, W, M, N, K, ldw, ldx)) {   // up to eight rows at the weight traffic of one
         static PerDeviceOnce once;
-        if (once.needed()) {
+        if (once.needed())
             TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
-            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
-            TL_CUDA(cudaFuncSetAttribute(k_gemv_ring_rows<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RowsCfg::smem_bytes()));
-        }
         RingArgs a{};
         a.x = x; a.W0 = W; a.N_each = N; a.K = K; a.total_units = N / 2; a.y = y;
         a.status = device_status_word(); a.wait_weights = weights_constant ? 0 : 1;
         a.m_rows = M; a.ldx = ldx; a.ldy = ldy;
         const int grid = std::max(1, std::min(sm_count(), (a.total_units + 7) / 8));
-        if (M <= 8) return launch_pdl(k_gemv_ring_rows<1>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
-        if (M <= 16) return launch_pdl(k_gemv_ring_rows<2>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
-        return launch_pdl(k_gemv_ring_rows<4>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
+        return launch_pdl(k_gemv_ring_rows<1>, dim3(grid), dim3(RingCfg<16, 3>::THREADS), RowsCfg::smem_bytes(), st, true, a);
     }
     int KT = 16384 / M;                 // halfs per tile so that M*KT*2 <= 32 KB
     KT &= ~255;
