@@ -173,6 +173,8 @@ int tl_linear_f16(const tl_half* x, const tl_half* W, tl_half* y, size_t T, size
         return launch_gemv(H(x), H(W), H(y), 1, (int)N, (int)K, K, K, N, st, true);
     if (gemv_ring_rows_supported(x, W, T, N, K, K, K))
         return launch_gemv(H(x), H(W), H(y), (int)T, (int)N, (int)K, K, K, N, st, true);
+    if (T >= 2 && T <= 128 && skinny_supported(x, W, T, N, K, K, K))
+        return launch_skinny(H(x), H(W), H(y), (int)T, (int)N, (int)K, K, K, N, st, true);
     return tl_matmul2d_f16(x, W, y, T, N, K, TL_NUMERICS_FAST, stream);
 }
 

@@ -374,11 +374,11 @@ int Llama2Engine::linear(const __half* x, const __half* W, __half* y, int T, int
     }
     if (gemv_ring_rows_supported(x, W, T, N, K, K, K)) {
         launches_++;
-        return launch_gemv(x, W, y, T, N, K, K, K, N, st);
+        return launch_gemv(x, W, y, T, N, K, K, K, N, st, true);
     }
     if (T >= 2 && T <= 128 && skinny_supported(x, W, T, N, K, K, K)) {
         launches_++;
-        return launch_skinny(x, W, y, T, N, K, K, K, N, st);
+        return launch_skinny(x, W, y, T, N, K, K, K, N, st, true);     // model weights are constants
     }
     if (T > 8 && hgemm_supported(x, W, y, T, N, K, K, K, N)) {
         launches_++;

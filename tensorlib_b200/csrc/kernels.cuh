@@ -184,7 +184,7 @@ bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K
 struct SkinnyPlan { int nb, tiles, nkb, per, grid, cluster_splits; };
 SkinnyPlan skinny_plan(int M, int N, int K, int sms);
 int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int K, long long lda, long long ldw,
-                  long long ldc, cudaStream_t st);
+                  long long ldc, cudaStream_t st, bool weights_constant = false);
 
 // which tile the plain HGEMM would use on `sms` SMs: kind 0 = single-CTA tile of width *bn, 1 = CTA-pair 256x256
 void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int* sk_per);

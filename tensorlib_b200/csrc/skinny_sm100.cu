@@ -45,6 +45,7 @@ struct SkinnyArgs {
     float* ws;                  // [2 * grid][NB][TW] fp32 partial tiles
     unsigned int* counters;     // [tiles], zero between launches
     int* status;
+    int w_const;                // W is a parameter nobody in flight writes: its copies may start before the previous kernel ends
 };
 
 template <int NB> struct SkinnyCfg {
@@ -87,9 +88,20 @@ k_skinny(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
     // set-up done (barriers, TMEM): let the next kernel of the stream start its own set-up, then wait
     // for the previous one before any operand is read or any result written
     pdl_launch_dependents();
+    const bool producer = warp == 0 && lane == 0;
+    int w_ahead = 0;       // stages whose weight half is already on its way (constant weights only)
+    if (producer && p.w_const) {
+        // the weight halves of the first ring-full of stages do not depend on the previous kernel
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+        for (long long g = g_begin; g < g_end && w_ahead < STAGES; g++, w_ahead++) {
+            const int t = (int)(g / p.nkb), kb = (int)(g - (long long)t * p.nkb);
+            mbar_arrive_expect_tx(full0 + 8 * w_ahead, STAGE_BYTES);
+            tma_load_3d(smem_u32(smem + w_ahead * STAGE_BYTES), &tmW, kb * BK, t * TW, 0, full0 + 8 * w_ahead);
+        }
+    }
     pdl_wait();
 
-    if (warp == 0 && lane == 0) {
+    if (producer) {
         // ---------------- TMA producer ---------------------------------------------------------
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
@@ -100,8 +112,10 @@ k_skinny(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtens
             const int s = it % STAGES, use = it / STAGES;
             if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
             const uint32_t sw = smem_u32(smem + s * STAGE_BYTES), sx = sw + W_BYTES;
-            mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_3d(sw, &tmW, kb * BK, t * TW, 0, full0 + 8 * s);
+            if (it >= w_ahead) {
+                mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_3d(sw, &tmW, kb * BK, t * TW, 0, full0 + 8 * s);
+            }
             tma_load_3d(sx, &tmX, kb * BK, 0, 0, full0 + 8 * s);
         }
         if (!ok) {  // let copies already in flight land before the CTA goes away
@@ -282,9 +296,18 @@ k_skinny_cluster(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    const bool producer = warp == 0 && lane == 0;
+    int w_ahead = 0;       // stages whose weight half is already on its way (constant weights only)
+    if (producer && p.w_const) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+        for (int kb = kb0; kb < kb1 && w_ahead < STAGES; kb++, w_ahead++) {
+            mbar_arrive_expect_tx(full0 + 8 * w_ahead, STAGE_BYTES);
+            tma_load_3d(smem_u32(smem + w_ahead * STAGE_BYTES), &tmW, kb * BK, t * TW, 0, full0 + 8 * w_ahead);
+        }
+    }
     pdl_wait();
 
-    if (warp == 0 && lane == 0) {
+    if (producer) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
         bool ok = true;
@@ -293,8 +316,10 @@ k_skinny_cluster(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             const int s = it % STAGES, use = it / STAGES;
             if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
             const uint32_t sw = smem_u32(smem + s * STAGE_BYTES), sx = sw + W_BYTES;
-            mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_3d(sw, &tmW, kb * BK, t * TW, 0, full0 + 8 * s);
+            if (it >= w_ahead) {
+                mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_3d(sw, &tmW, kb * BK, t * TW, 0, full0 + 8 * s);
+            }
             tma_load_3d(sx, &tmX, kb * BK, 0, 0, full0 + 8 * s);
         }
         if (!ok) {
@@ -479,7 +504,7 @@ SkinnyPlan skinny_plan(int M, int N, int K, int sms) {
 }
 
 int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int K, long long lda, long long ldw,
-                  long long ldc, cudaStream_t st) {
+                  long long ldc, cudaStream_t st, bool weights_constant) {
     TL_REQUIRE(skinny_supported(A, W, M, N, K, lda, ldw), "skinny matmul: unsupported shape or alignment");
     const SkinnyPlan pl = skinny_plan(M, N, K, sm_count());
     const int nb = pl.nb, tiles = pl.tiles, nkb = pl.nkb, per = pl.per, cluster_splits = pl.cluster_splits, grid = pl.grid;
@@ -488,7 +513,7 @@ int launch_skinny(const __half* A, const __half* W, __half* C, int M, int N, int
     CUtensorMap mw, mx;
     TL_PROPAGATE(make_tensor_map_f16(&mw, W, N, K, ldw, 0, 1, TW));
     TL_PROPAGATE(make_tensor_map_f16(&mx, A, M, K, lda, 0, 1, nb));
-    SkinnyArgs a{C, ldc, M, N, K, tiles, nkb, per, cluster_splits, w.ws, w.counters, device_status_word()};
+    SkinnyArgs a{C, ldc, M, N, K, tiles, nkb, per, cluster_splits, w.ws, w.counters, device_status_word(), weights_constant ? 1 : 0};
     if (cluster_splits >= 2) {
         if (nb == 32) return launch_cluster<32>(mw, mx, a, tiles * cluster_splits, cluster_splits, st);
         if (nb == 64) return launch_cluster<64>(mw, mx, a, tiles * cluster_splits, cluster_splits, st);
