@@ -17,7 +17,7 @@ OUT = os.path.join(PKG, "_build")
 LIB = os.path.join(PKG, "libtensorlib_b200.so")
 NVCC = os.environ.get("TL_NVCC", "/usr/local/cuda/bin/nvcc")
 
-SOURCES = ["runtime.cu", "ops_refmode.cu", "device_ops.cu", "gemv.cu", "attn.cu", "attn_sm100.cu", "hgemm_sm100.cu", "skinny_sm100.cu", "decode_mega.cu", "engine.cu",
+SOURCES = ["runtime.cu", "ops_refmode.cu", "device_ops.cu", "gemv.cu", "attn.cu", "attn_sm100.cu", "hgemm_sm100.cu", "skinny_sm100.cu", "decode_mega.cu", "tp_prefill.cu", "engine.cu",
            "api.cu", "tp.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-Xptxas", "-v",

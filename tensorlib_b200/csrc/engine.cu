@@ -473,22 +473,57 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
     const bool fused = T > 128 && tensor_map_encode_available() && hd_ % 32 == 0 && dl % 64 == 0 && hl % 32 == 0 &&
                        dim % 32 == 0;
     const bool fused_residual = fused && coll_ == nullptr;
+    // Tensor parallel with the exchange region open: the K-split matmuls push their partial rows to the ranks
+    // that own them and the owner's add + RMSNorm kernel hands the normalised rows to every rank
+    // (tp_prefill.cu); no collective library call in the layer loop. TL_TP_PREFILL=nccl keeps the allreduce form.
+    const int world = cfg_.tp_world;
+    static const bool force_nccl = [] { const char* e = getenv("TL_TP_PREFILL"); return e && !strcmp(e, "nccl"); }();
+    const bool tp_fused = fused && coll_ != nullptr && xch_ready_ && !force_nccl && T % (128 * world) == 0 && dim <= 8192 &&
+                          T / world <= pf_rpo_max_;
+    const int rpo = tp_fused ? T / world : 0, row0 = cfg_.tp_rank * rpo;
+    __half* xn = tp_fused ? reinterpret_cast<__half*>(xch_base_ + pf_off_xn_) : xn_;
+    auto exchange = [&](const __half* A, const __half* Wk, int K, const __half* resid, __half* resid_out, const __half* norm_w) -> int {
+        // one fused compute + collective: push GEMM, owner-side reduce + norm + gather, wait for every owner's rows
+        HgemmPush push{};
+        push.world = world; push.rows_per_owner = rpo; push.epoch = ++pf_epoch_;
+        const size_t slot = (size_t)pf_rpo_max_ * dim, fslot = (size_t)(pf_rpo_max_ / 128) * 64;
+        for (int d = 0; d < world; d++) {
+            push.base[d] = reinterpret_cast<__half*>(xch_peer_[d] + pf_off_recv_) + (size_t)cfg_.tp_rank * slot;
+            push.flags[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + pf_off_aflags_) + (size_t)cfg_.tp_rank * fslot;
+        }
+        int col_tiles = 0;
+        launches_ += 3;
+        TL_PROPAGATE(launch_hgemm_push(A, Wk, T, dim, K, K, K, push, &col_tiles, st));
+        TpReduceNorm rn{};
+        rn.world = world; rn.rows = rpo; rn.row0 = row0; rn.dim = dim; rn.col_tiles = col_tiles; rn.epoch = push.epoch;
+        rn.recv = reinterpret_cast<const __half*>(xch_base_ + pf_off_recv_); rn.recv_slot_stride = (long long)slot;
+        rn.arrive_flags = reinterpret_cast<const unsigned int*>(xch_base_ + pf_off_aflags_); rn.flags_slot_stride = (int)fslot;
+        rn.residual = resid + (size_t)row0 * dim; rn.residual_out = resid_out + (size_t)row0 * dim;
+        rn.norm_w = norm_w; rn.eps = 1e-5f;
+        for (int d = 0; d < world; d++) {
+            rn.xn_dst[d] = reinterpret_cast<__half*>(xch_peer_[d] + pf_off_xn_);
+            rn.gather_flags[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + pf_off_gflags_);
+        }
+        TL_PROPAGATE(launch_tp_reduce_norm(rn, st));
+        return launch_tp_wait_rows(reinterpret_cast<const unsigned int*>(xch_base_ + pf_off_gflags_), T, push.epoch, st);
+    };
     launches_++;
     TL_PROPAGATE(launch_embedding(x_, emb_, d_tokens_, T, dim, cfg_.vocab_size, st));
     for (int l = 0; l < cfg_.n_layers; l++) {
         const LayerWeights& w = layers_[l];
-        TL_PROPAGATE(launch_rmsnorm_fast(xn_, x_, w.attn_norm, 1e-5f, dim, T, st));
+        // (under the fused exchange the norm of layers > 0 was applied by the owner of each row at the end of the previous layer)
+        if (!tp_fused || l == 0) TL_PROPAGATE(launch_rmsnorm_fast(xn, x_, w.attn_norm, 1e-5f, dim, T, st));
         if (fused) {
             launches_ += 2;
             const size_t half_hd = (size_t)hd_ / 2;
-            TL_PROPAGATE(launch_hgemm_qkv_rope(xn_, w.wq, w.wk, w.wv, q_, w.cache_k + (size_t)pos * dl,
+            TL_PROPAGATE(launch_hgemm_qkv_rope(xn, w.wq, w.wk, w.wv, q_, w.cache_k + (size_t)pos * dl,
                                                w.cache_v + (size_t)pos * dl, T, dl, dim, dim, dim, dl, dl,
                                                cos_t_ + (size_t)pos * half_hd, sin_t_ + (size_t)pos * half_hd, hd_, st));
         } else {
             launches_ += 5;   // linear() counts its own launches
-            TL_PROPAGATE(linear(xn_, w.wq, q_, T, dl, dim, st));
-            TL_PROPAGATE(linear(xn_, w.wk, k_, T, dl, dim, st));
-            TL_PROPAGATE(linear(xn_, w.wv, v_, T, dl, dim, st));
+            TL_PROPAGATE(linear(xn, w.wq, q_, T, dl, dim, st));
+            TL_PROPAGATE(linear(xn, w.wk, k_, T, dl, dim, st));
+            TL_PROPAGATE(linear(xn, w.wv, v_, T, dl, dim, st));
             TL_PROPAGATE(launch_rope(q_, q_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
             TL_PROPAGATE(launch_rope(k_, k_, pos, T, T, H, hd_, cos_t_, sin_t_, st));
             TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dl, k_, T, dl, dl, st));
@@ -514,7 +549,9 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             SeqMatmul pv{scores_, w.cache_v, att_, H, T, hd_, S, S, 1, 1, dl, dl, (long long)T * S, hd_, hd_};
             TL_PROPAGATE(launch_matmul_seq(pv, st));
         }
-        if (fused_residual) {
+        if (tp_fused) {
+            TL_PROPAGATE(exchange(att_, w.wo, dl, x_, h_, w.ffn_norm));          // h = x + wo(att); xn = norm(h) * ffn_norm
+        } else if (fused_residual) {
             launches_++;
             TL_PROPAGATE(launch_hgemm_residual(att_, w.wo, x_, h_, T, dim, dl, dl, dl, dim, dim, st));
         } else {
@@ -523,18 +560,23 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
             TL_PROPAGATE(launch_binary(h_, x_, ao_, (size_t)T * dim, 0, st));
         }
-        launches_++;
-        TL_PROPAGATE(launch_rmsnorm_fast(xn_, h_, w.ffn_norm, 1e-5f, dim, T, st));
+        if (!tp_fused) {
+            launches_++;
+            TL_PROPAGATE(launch_rmsnorm_fast(xn, h_, w.ffn_norm, 1e-5f, dim, T, st));
+        }
         if (fused) {
             launches_++;
-            TL_PROPAGATE(launch_hgemm_swiglu(xn_, w.w1, w.w3, g_, T, hl, dim, dim, dim, hl, st));
+            TL_PROPAGATE(launch_hgemm_swiglu(xn, w.w1, w.w3, g_, T, hl, dim, dim, dim, hl, st));
         } else {
             launches_++;
-            TL_PROPAGATE(linear(xn_, w.w1, g_, T, hl, dim, st));
-            TL_PROPAGATE(linear(xn_, w.w3, u_, T, hl, dim, st));
+            TL_PROPAGATE(linear(xn, w.w1, g_, T, hl, dim, st));
+            TL_PROPAGATE(linear(xn, w.w3, u_, T, hl, dim, st));
             TL_PROPAGATE(launch_swiglu_fast(g_, g_, u_, (size_t)T * hl, st));
         }
-        if (fused_residual) {
+        if (tp_fused) {
+            const __half* next_norm = l + 1 < cfg_.n_layers ? layers_[l + 1].attn_norm : final_norm_;
+            TL_PROPAGATE(exchange(g_, w.w2, hl, h_, x_, next_norm));             // x = h + w2(g); xn = norm(x) * next norm
+        } else if (fused_residual) {
             launches_++;
             TL_PROPAGATE(launch_hgemm_residual(g_, w.w2, h_, x_, T, dim, hl, hl, hl, dim, dim, st));
         } else {
@@ -546,13 +588,14 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
     }
     launches_ += 1;
     const int t0 = all_logits ? 0 : T - 1, tn = all_logits ? T : 1;
-    TL_PROPAGATE(launch_rmsnorm_fast(xn_ + (size_t)t0 * dim, x_ + (size_t)t0 * dim, final_norm_, 1e-5f, dim, tn, st));
+    // (fused exchange: the last layer's owner-side kernel already applied the final norm to every row)
+    if (!tp_fused) TL_PROPAGATE(launch_rmsnorm_fast(xn + (size_t)t0 * dim, x_ + (size_t)t0 * dim, final_norm_, 1e-5f, dim, tn, st));
     const __half* cls = (shared_classifier_ && cfg_.tp_world == 1) ? emb_ : wcls_;
     if (cfg_.tp_world == 1)
-        return linear(xn_ + (size_t)t0 * dim, cls, logits_ + (size_t)t0 * cfg_.vocab_size, tn, cfg_.vocab_size, dim, st);
+        return linear(xn + (size_t)t0 * dim, cls, logits_ + (size_t)t0 * cfg_.vocab_size, tn, cfg_.vocab_size, dim, st);
     // vocabulary-split classifier: local slice, then gather the slices of every rank
     for (int t = t0; t < t0 + tn; t++) {
-        TL_PROPAGATE(linear(xn_ + (size_t)t * dim, cls, cls_local_, 1, vocab_local_, dim, st));
+        TL_PROPAGATE(linear(xn + (size_t)t * dim, cls, cls_local_, 1, vocab_local_, dim, st));
         TL_PROPAGATE(coll_->allgather_f16(cls_local_, logits_ + (size_t)t * cfg_.vocab_size, vocab_local_, st));
     }
     return TL_OK;
@@ -628,6 +671,14 @@ int Llama2Engine::xch_export(cudaIpcMemHandle_t* out) {
         xch_off_pub_[0] = take(dim / 2 * sizeof(unsigned long long));
         xch_off_pub_[1] = take(dim / 2 * sizeof(unsigned long long));
         xch_off_step_ = take(sizeof(unsigned int));
+        // prefill: receive buffer of the pushed partial rows [source][rows per owner][dim], the gathered normalised
+        // rows [max_seq][dim], arrival flags [source][row block][64 column tiles], gather flags [max_seq]
+        const size_t S = cfg_.max_seq_len;
+        pf_rpo_max_ = (int)(((S + W - 1) / W + 127) / 128 * 128);
+        pf_off_recv_ = take(W * (size_t)pf_rpo_max_ * dim * sizeof(__half));
+        pf_off_xn_ = take(S * dim * sizeof(__half));
+        pf_off_aflags_ = take(W * (size_t)(pf_rpo_max_ / 128) * 64 * sizeof(unsigned int));
+        pf_off_gflags_ = take(S * sizeof(unsigned int));
         xch_bytes_ = off;
         void* d = nullptr;
         TL_CUDA(cudaMalloc(&d, xch_bytes_));

@@ -123,6 +123,10 @@ private:
     size_t xch_off_part_[2] = {0, 0}, xch_off_pub_[2] = {0, 0}, xch_off_logits_ = 0, xch_off_step_ = 0, xch_bytes_ = 0;
     unsigned long long* prof_ = nullptr;   // device buffer for %globaltimer stamps while decode_profile runs a step
     bool xch_ready_ = false;
+    // prefill part of the exchange region (tp_prefill.cu) and the exchange counter every rank advances in step
+    size_t pf_off_recv_ = 0, pf_off_xn_ = 0, pf_off_aflags_ = 0, pf_off_gflags_ = 0;
+    int pf_rpo_max_ = 0;
+    unsigned int pf_epoch_ = 0;
     const __half* last_logits_ = nullptr;
 };
 

@@ -63,7 +63,32 @@ struct GemmArgs {
     int sk_per;
     float* sk_ws;
     unsigned int* sk_counters;
+    // Tensor-parallel push (STORE epilogue of a K-split matmul): row m of the partial result is owned by rank
+    // m / push_rows and is stored at push_base[owner] + (m % push_rows) * ldc in that rank's memory (plain
+    // peer stores); when the 128 rows x BN columns a CTA finished are stored, flag word
+    // push_flags[owner][(m0 % push_rows) / 128 * PUSH_MAX_COL_TILES + column tile] is set to push_epoch.
+    // push_rows = 0: an ordinary store to C.
+    __half* push_base[8];
+    unsigned int* push_flags[8];
+    int push_rows;
+    unsigned int push_epoch;
 };
+constexpr int PUSH_MAX_COL_TILES = 64;
+
+// after the epilogue threads of one 128-row sub-tile have stored their rows to the owner's memory: make the
+// stores visible system-wide, meet, and let one thread raise the flag of (row block, column tile)
+__device__ __forceinline__ void push_signal(const GemmArgs& p, int row0, int col_tile, int bar_id, bool writer) {
+    __threadfence_system();
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    if (writer && row0 < p.M) {
+        const int owner = row0 / p.push_rows, rb = (row0 - owner * p.push_rows) >> 7;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flags[owner] + rb * PUSH_MAX_COL_TILES + col_tile), "r"(p.push_epoch) : "memory");
+    }
+}
+__device__ __forceinline__ __half* push_row_ptr(const GemmArgs& p, int row) {
+    const int owner = min(row / p.push_rows, 7);
+    return p.push_base[owner] + (long long)(row - owner * p.push_rows) * p.ldc;
+}
 
 // 32 consecutive columns of one output row: fp32 accumulators -> fp16 -> 64 bytes
 __device__ __forceinline__ void store32(__half* dst, const uint32_t* r) {
@@ -261,7 +286,8 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
             tc_fence_after();
             const int row = mt * BM + q * 32 + lane;
             const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
+            __half* crow = (EPI == GEPI_STORE && p.push_rows > 0) ? push_row_ptr(p, row)
+                                                                   : p.C + (long long)b * p.sC + (long long)row * p.ldc;
             if (EPI == GEPI_SWIGLU) {
 #pragma unroll 1
                 for (int c = 0; c < OUT_COLS; c += 32) {
@@ -301,6 +327,7 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            if (EPI == GEPI_STORE && p.push_rows > 0) push_signal(p, mt * BM, ntl, 2, warp == 4 && lane == 0);
         }
     }
     // ---------------- teardown ---------------------------------------------------------------------
@@ -530,7 +557,8 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             tc_fence_after();
             const int row = ((mt * 2 + (int)rank) * MSUB + ms) * BM + rl;
             const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf + ms) * BN);
-            __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
+            __half* crow = (EPI == GEPI_STORE && p.push_rows > 0) ? push_row_ptr(p, row)
+                                                                   : p.C + (long long)b * p.sC + (long long)row * p.ldc;
             // 32 finished accumulator columns of this thread's row -> the fused epilogue
             auto emit = [&](int c, const uint32_t* r) {
                 const int col0 = ntl * BN + c;
@@ -608,6 +636,8 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8 * buf);
+                if (EPI == GEPI_STORE && p.push_rows > 0)
+                    push_signal(p, ((mt * 2 + (int)rank) * MSUB + ms) * BM, ntl, 2 + ms, q == 0 && lane == 0);
                 continue;
             }
             // ---- partial tile: fp32 partial to the workspace, last arriver of the tile half adds them up ----
@@ -813,7 +843,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     GemmArgs a = a_in;
     const long long nt = (long long)n_col_tiles * a.batch;
     const int nkb = (a.K + BK - 1) / BK;
-    const PairPlan pl = pair_plan(a.M, nt, nkb, EPI);
+    PairPlan pl = pair_plan(a.M, nt, nkb, EPI);
+    if (a.push_rows > 0) pl.sk_per = 0;      // pushed tiles are signalled whole
     const long long tiles = (long long)((a.M + 256 * pl.msub - 1) / (256 * pl.msub)) * nt;
     int pair_ctas = (int)std::min<long long>(tiles, sm_count() / 2);
     if (pl.sk_per > 0) {
@@ -962,6 +993,38 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, bn));
     const int tiles = mt * ((N + bn - 1) / bn) * batch;
     return launch_any_bn<GEPI_STORE>(bn, ma, mb, mb, mb, a, tiles, st);
+}
+
+// K-split matmul of the tensor-parallel prefill: C is not stored locally; row m goes to the rank that owns it
+// (m / rows_per_owner) and a flag per (128-row block, column tile) tells the owner when it has arrived.
+int launch_hgemm_push(const __half* A, const __half* B, int M, int N, int K, long long lda, long long ldb, const HgemmPush& push,
+                      int* col_tiles, cudaStream_t st) {
+    TL_REQUIRE(hgemm_supported(A, B, nullptr, M, N, K, lda, ldb, N) && N % 32 == 0, "hgemm push: unsupported shape or alignment");
+    TL_REQUIRE(push.world >= 2 && push.world <= 8 && push.rows_per_owner > 0 && push.rows_per_owner % 128 == 0 &&
+               (long long)push.rows_per_owner * push.world >= M, "hgemm push: rows per owner must be a multiple of 128 covering M");
+    const int mt = (M + BM - 1) / BM;
+    const int bn = pick_bn(mt, N, 1);
+    GemmArgs a{};
+    a.C = nullptr; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = N; a.sC = 0;
+    a.status = device_status_word();
+    a.push_rows = push.rows_per_owner; a.push_epoch = push.epoch;
+    for (int r = 0; r < 8; r++) {
+        a.push_base[r] = r < push.world ? push.base[r] : nullptr;
+        a.push_flags[r] = r < push.world ? push.flags[r] : nullptr;
+        if (r < push.world) TL_REQUIRE(push.base[r] && push.flags[r] && al16(push.base[r]), "hgemm push: bad destination");
+    }
+    CUtensorMap ma, mb;
+    TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
+    if (M > BM && pair_cost(M, (N + 255) / 256, 1, K) < single_cost(mt, N, 1, bn, K)) {
+        TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
+        *col_tiles = (N + 255) / 256;
+        TL_REQUIRE(*col_tiles <= PUSH_MAX_COL_TILES, "hgemm push: too many column tiles");
+        return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, (N + 255) / 256, st);
+    }
+    TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, bn));
+    *col_tiles = (N + bn - 1) / bn;
+    TL_REQUIRE(*col_tiles <= PUSH_MAX_COL_TILES, "hgemm push: too many column tiles");
+    return launch_any_bn<GEPI_STORE>(bn, ma, mb, mb, mb, a, mt * *col_tiles, st);
 }
 
 // The fused forms need full 32-column chunks and 16-byte aligned rows everywhere.

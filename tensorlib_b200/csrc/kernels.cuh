@@ -179,6 +179,39 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
                  long long lda, long long ldb, long long ldc, long long sA, long long sB,
                  long long sC, cudaStream_t st);
 
+// K-split matmul whose result rows are pushed to the ranks that own them (tensor-parallel prefill):
+// row m -> base[m / rows_per_owner] + (m % rows_per_owner) * N in that rank's memory; when a 128-row x
+// tile-width piece has been stored, flags[owner][(m0 % rows_per_owner) / 128 * 64 + column tile] = epoch.
+// *col_tiles returns how many column tiles (flags per row block) the chosen kernel produces.
+struct HgemmPush {
+    int world, rows_per_owner;
+    unsigned int epoch;
+    __half* base[TL_MAX_TP];           // already offset to this rank's slot in the owner's receive buffer
+    unsigned int* flags[TL_MAX_TP];    // likewise
+};
+int launch_hgemm_push(const __half* A, const __half* B, int M, int N, int K, long long lda, long long ldb, const HgemmPush& push,
+                      int* col_tiles, cudaStream_t st);
+// The owner's side: rows [0, rows) of this rank's slice = residual + sum over source ranks (rank order, fp32) of
+// the pushed partial rows, once every (row block, column tile) flag of every source reads `epoch`; the new residual
+// rows are written locally, their RMSNorm (times norm_w) is stored into row (row0 + r) of xn_dst[d] on every rank d,
+// then row flag gather_flags[d][row0 + r] = epoch. Bounded waits (TL_ERR_TIMEOUT in the status word).
+struct TpReduceNorm {
+    int world, rows, row0, dim, col_tiles;
+    unsigned int epoch;
+    const __half* recv;                // [world][rows_per_owner][dim] this rank's receive buffer
+    long long recv_slot_stride;        // elements between two sources' slots
+    const unsigned int* arrive_flags;  // [world][row blocks][64]
+    int flags_slot_stride;             // words between two sources' flag blocks
+    const __half* residual;            // local rows [row0, row0 + rows) x dim
+    __half* residual_out;
+    const __half* norm_w; float eps;
+    __half* xn_dst[TL_MAX_TP];
+    unsigned int* gather_flags[TL_MAX_TP];
+};
+int launch_tp_reduce_norm(const TpReduceNorm& p, cudaStream_t st);
+// wait (bounded) until row flags [0, rows) read `epoch`: every owner's normalised rows have arrived here
+int launch_tp_wait_rows(const unsigned int* flags, int rows, unsigned int epoch, cudaStream_t st);
+
 // ---- skinny_sm100.cu: 2 <= M <= 128, weights streamed once (swap-AB tcgen05, stream-K split) --------
 bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K, size_t lda, size_t ldw);
 struct SkinnyPlan { int nb, tiles, nkb, per, grid, cluster_splits; };

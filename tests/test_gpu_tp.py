@@ -19,6 +19,7 @@ ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
 pytestmark = pytest.mark.gpu
 
 N_PROMPT, N_FORCED, N_FREE = 16, 6, 12
+N_LONG = 512      # a prompt long enough for the tcgen05 prefill path and divisible by 128 x world
 
 
 def _free_port() -> int:
@@ -34,9 +35,9 @@ def _config(name):
         cfg = synth.TINY
         return cfg, synth.llama2c_payload(cfg, 20240229)
     if name == "mid":
-        cfg = synth.LlamaConfig(dim=512, hidden_dim=1408, n_layers=2, n_heads=4, vocab_size=1000, seq_len=384)
+        cfg = synth.LlamaConfig(dim=512, hidden_dim=1408, n_layers=2, n_heads=4, vocab_size=1000, seq_len=640)
         return cfg, synth.llama2c_payload(cfg, 777)
-    cfg = synth.LlamaConfig(dim=4096, hidden_dim=11008, n_layers=1, n_heads=32, vocab_size=2000, seq_len=256)
+    cfg = synth.LlamaConfig(dim=4096, hidden_dim=11008, n_layers=1, n_heads=32, vocab_size=2000, seq_len=640)
     payload = (np.random.default_rng(4096).standard_normal(cfg.payload_elems(), dtype=np.float32) * 0.02).astype(np.float16)
     V, d, L = cfg.vocab_size, cfg.dim, cfg.n_layers
     payload[V * d:V * d + L * d] = 1.0
@@ -49,6 +50,11 @@ def _config(name):
 def _tokens(cfg):
     from tensorlib_b200 import synth
     return synth.token_ids(20240229, 100, N_PROMPT, cfg.vocab_size), synth.token_ids(20240229, 101, N_FORCED, cfg.vocab_size)
+
+
+def _long_prompt(cfg):
+    from tensorlib_b200 import synth
+    return synth.token_ids(20240229, 102, N_LONG, cfg.vocab_size) if cfg.seq_len > N_LONG and cfg.head_dim == 128 else None
 
 
 def _worker(rank: int, world: int, port: int, name: str, q):
@@ -67,6 +73,8 @@ def _worker(rank: int, world: int, port: int, name: str, q):
         tp.attach(m, rank, world, dist)
         m.load_payload(payload, shared_classifier=True)
         lg_prefill = m.forward(prompt, 0, all_logits=True)
+        long_prompt = _long_prompt(cfg)
+        lg_long_nccl = m.forward(long_prompt, 0, all_logits=True)[-4:] if long_prompt is not None else None
         lg_decode = np.concatenate([m.forward(forced[i:i + 1], N_PROMPT + i, all_logits=True) for i in range(N_FORCED)])
         m.forward(prompt, 0, all_logits=False)
         ids = m.decode_device(N_PROMPT, N_FREE)             # CUDA-graph decode with NCCL inside the graph
@@ -74,7 +82,16 @@ def _worker(rank: int, world: int, port: int, name: str, q):
         dist.barrier()
         # the same decode with the exchange fused into the GEMV kernels (peer stores, no NCCL)
         tp.open_fused_exchange(m, rank, world, dist)
-        m.forward(prompt, 0, all_logits=False)               # prefill still reduces over NCCL
+        # long prompts: the K-split matmuls push their partial rows to the owning ranks, no NCCL in the layer loop
+        lg_long_fused = None
+        if long_prompt is not None:
+            dist.barrier()
+            lg_long_fused = m.forward(long_prompt, 0, all_logits=True)[-4:]
+            status |= tl.device_status()
+            dist.barrier()
+            again = m.forward(long_prompt, 0, all_logits=True)[-4:]       # a second exchange round over the same buffers
+            assert np.array_equal(again.view(np.uint16), lg_long_fused.view(np.uint16))
+        m.forward(prompt, 0, all_logits=False)               # a 16-token prompt still reduces over NCCL
         lg_fused = np.concatenate([m.forward(forced[i:i + 1], N_PROMPT + i, all_logits=True) for i in range(N_FORCED)])
         m.forward(prompt, 0, all_logits=False)
         dist.barrier()
@@ -86,10 +103,10 @@ def _worker(rank: int, world: int, port: int, name: str, q):
         m.close()
         tp.destroy()
         dist.destroy_process_group()
-        q.put((rank, "ok", lg_prefill, lg_decode, ids, status, lg_fused, ids_fused, stamps.shape))
+        q.put((rank, "ok", lg_prefill, lg_decode, ids, status, lg_fused, ids_fused, stamps.shape, lg_long_nccl, lg_long_fused))
     except Exception as e:  # pragma: no cover
         import traceback
-        q.put((rank, traceback.format_exc() + str(e), None, None, None, None, None, None, None))
+        q.put((rank, traceback.format_exc() + str(e), None, None, None, None, None, None, None, None, None))
 
 
 def _rel_err(got, want):
@@ -108,6 +125,8 @@ def test_tensor_parallel_matches_single_gpu(tl, name, world):
     single.load_payload(payload, shared_classifier=True)
     want_prefill = single.forward(prompt, 0, all_logits=True)
     want_decode = np.concatenate([single.forward(forced[i:i + 1], N_PROMPT + i, all_logits=True) for i in range(N_FORCED)])
+    long_prompt = _long_prompt(cfg)
+    want_long = single.forward(long_prompt, 0, all_logits=True)[-4:] if long_prompt is not None else None
     single.close()
 
     import multiprocessing as mp
@@ -123,8 +142,11 @@ def test_tensor_parallel_matches_single_gpu(tl, name, world):
     for rank, msg, *_ in results:
         assert msg == "ok", f"rank {rank}: {msg}"
     tol = 2e-2          # relative to max(|logit|, row rms): the K-split changes the fp32 summation grouping only
-    for rank, _, lp, ld, ids, status, lf, ids_f, stamp_shape in results:
+    for rank, _, lp, ld, ids, status, lf, ids_f, stamp_shape, ll_nccl, ll_fused in results:
         assert status == 0
+        if want_long is not None:
+            assert _rel_err(ll_nccl, want_long) <= tol, (name, world, "512-token prefill, NCCL allreduce")
+            assert _rel_err(ll_fused, want_long) <= tol, (name, world, "512-token prefill, fused exchange")
         assert _rel_err(lp, want_prefill) <= tol, (name, world, "prefill")
         assert _rel_err(ld, want_decode) <= tol, (name, world, "decode, NCCL exchange")
         assert _rel_err(lf, want_decode) <= tol, (name, world, "decode, fused exchange")
@@ -136,4 +158,6 @@ def test_tensor_parallel_matches_single_gpu(tl, name, world):
         # fused exchange: every rank adds the same partials in the same (rank) order -> identical bits
         assert np.array_equal(first[6].view(np.uint16), other[6].view(np.uint16)), "ranks disagree (fused)"
         assert np.array_equal(first[7], other[7]), "ranks sampled different ids (fused)"
+        if want_long is not None:
+            assert np.array_equal(first[10].view(np.uint16), other[10].view(np.uint16)), "ranks disagree on the fused prefill"
     print(f"{name} x{world}: fused ids {first[7].tolist()}, NCCL ids {first[4].tolist()}")
