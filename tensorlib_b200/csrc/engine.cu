@@ -486,17 +486,15 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
         // one fused compute + collective: push GEMM, owner-side reduce + norm + gather, wait for every owner's rows
         HgemmPush push{};
         push.world = world; push.rows_per_owner = rpo; push.epoch = ++pf_epoch_;
-        const size_t slot = (size_t)pf_rpo_max_ * dim, fslot = (size_t)(pf_rpo_max_ / 128) * 64;
-        for (int d = 0; d < world; d++) {
-            push.base[d] = reinterpret_cast<__half*>(xch_peer_[d] + pf_off_recv_) + (size_t)cfg_.tp_rank * slot;
+        const size_t fslot = (size_t)(pf_rpo_max_ / 128) * 64;
+        for (int d = 0; d < world; d++)
             push.flags[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + pf_off_aflags_) + (size_t)cfg_.tp_rank * fslot;
-        }
         int col_tiles = 0;
         launches_ += 3;
-        TL_PROPAGATE(launch_hgemm_push(A, Wk, T, dim, K, K, K, push, &col_tiles, st));
+        TL_PROPAGATE(launch_hgemm_push(A, Wk, reinterpret_cast<__half*>(xch_base_ + pf_off_recv_), T, dim, K, K, K, push, &col_tiles, st));
         TpReduceNorm rn{};
         rn.world = world; rn.rows = rpo; rn.row0 = row0; rn.dim = dim; rn.col_tiles = col_tiles; rn.epoch = push.epoch;
-        rn.recv = reinterpret_cast<const __half*>(xch_base_ + pf_off_recv_); rn.recv_slot_stride = (long long)slot;
+        for (int d = 0; d < world; d++) rn.partial[d] = reinterpret_cast<const __half*>(xch_peer_[d] + pf_off_recv_);
         rn.arrive_flags = reinterpret_cast<const unsigned int*>(xch_base_ + pf_off_aflags_); rn.flags_slot_stride = (int)fslot;
         rn.residual = resid + (size_t)row0 * dim; rn.residual_out = resid_out + (size_t)row0 * dim;
         rn.norm_w = norm_w; rn.eps = 1e-5f;
@@ -671,11 +669,11 @@ int Llama2Engine::xch_export(cudaIpcMemHandle_t* out) {
         xch_off_pub_[0] = take(dim / 2 * sizeof(unsigned long long));
         xch_off_pub_[1] = take(dim / 2 * sizeof(unsigned long long));
         xch_off_step_ = take(sizeof(unsigned int));
-        // prefill: receive buffer of the pushed partial rows [source][rows per owner][dim], the gathered normalised
+        // prefill: this rank's partial result of a K-split matmul [max_seq][dim] (fetched by the row owners), the gathered normalised
         // rows [max_seq][dim], arrival flags [source][row block][64 column tiles], gather flags [max_seq]
         const size_t S = cfg_.max_seq_len;
         pf_rpo_max_ = (int)(((S + W - 1) / W + 127) / 128 * 128);
-        pf_off_recv_ = take(W * (size_t)pf_rpo_max_ * dim * sizeof(__half));
+        pf_off_recv_ = take(S * dim * sizeof(__half));
         pf_off_xn_ = take(S * dim * sizeof(__half));
         pf_off_aflags_ = take(W * (size_t)(pf_rpo_max_ / 128) * 64 * sizeof(unsigned int));
         pf_off_gflags_ = take(S * sizeof(unsigned int));

@@ -63,12 +63,12 @@ struct GemmArgs {
     int sk_per;
     float* sk_ws;
     unsigned int* sk_counters;
-    // Tensor-parallel push (STORE epilogue of a K-split matmul): row m of the partial result is owned by rank
-    // m / push_rows and is stored at push_base[owner] + (m % push_rows) * ldc in that rank's memory (plain
-    // peer stores); when the 128 rows x BN columns a CTA finished are stored, flag word
-    // push_flags[owner][(m0 % push_rows) / 128 * PUSH_MAX_COL_TILES + column tile] is set to push_epoch.
-    // push_rows = 0: an ordinary store to C.
-    __half* push_base[8];
+    // Tensor-parallel signalling (STORE epilogue of a K-split matmul): row m of the partial result is owned by
+    // rank m / push_rows, which will fetch it from C (this rank's memory) once it is complete: when the 128 rows x
+    // BN columns a CTA finished are stored, flag word push_flags[owner][(m0 % push_rows) / 128 *
+    // PUSH_MAX_COL_TILES + column tile] in the OWNER's memory is set to push_epoch (one 4-byte peer store; the
+    // tile itself stays local, because a thread's share of a tile is 64 contiguous bytes per row, far too small a
+    // unit to send over NVLink). push_rows = 0: no signalling.
     unsigned int* push_flags[8];
     int push_rows;
     unsigned int push_epoch;
@@ -85,10 +85,7 @@ __device__ __forceinline__ void push_signal(const GemmArgs& p, int row0, int col
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flags[owner] + rb * PUSH_MAX_COL_TILES + col_tile), "r"(p.push_epoch) : "memory");
     }
 }
-__device__ __forceinline__ __half* push_row_ptr(const GemmArgs& p, int row) {
-    const int owner = min(row / p.push_rows, 7);
-    return p.push_base[owner] + (long long)(row - owner * p.push_rows) * p.ldc;
-}
+
 
 // 32 consecutive columns of one output row: fp32 accumulators -> fp16 -> 64 bytes
 __device__ __forceinline__ void store32(__half* dst, const uint32_t* r) {
@@ -286,8 +283,7 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
             tc_fence_after();
             const int row = mt * BM + q * 32 + lane;
             const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-            __half* crow = (EPI == GEPI_STORE && p.push_rows > 0) ? push_row_ptr(p, row)
-                                                                   : p.C + (long long)b * p.sC + (long long)row * p.ldc;
+            __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
             if (EPI == GEPI_SWIGLU) {
 #pragma unroll 1
                 for (int c = 0; c < OUT_COLS; c += 32) {
@@ -557,8 +553,7 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             tc_fence_after();
             const int row = ((mt * 2 + (int)rank) * MSUB + ms) * BM + rl;
             const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf + ms) * BN);
-            __half* crow = (EPI == GEPI_STORE && p.push_rows > 0) ? push_row_ptr(p, row)
-                                                                   : p.C + (long long)b * p.sC + (long long)row * p.ldc;
+            __half* crow = p.C + (long long)b * p.sC + (long long)row * p.ldc;
             // 32 finished accumulator columns of this thread's row -> the fused epilogue
             auto emit = [&](int c, const uint32_t* r) {
                 const int col0 = ntl * BN + c;
@@ -995,23 +990,22 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     return launch_any_bn<GEPI_STORE>(bn, ma, mb, mb, mb, a, tiles, st);
 }
 
-// K-split matmul of the tensor-parallel prefill: C is not stored locally; row m goes to the rank that owns it
-// (m / rows_per_owner) and a flag per (128-row block, column tile) tells the owner when it has arrived.
-int launch_hgemm_push(const __half* A, const __half* B, int M, int N, int K, long long lda, long long ldb, const HgemmPush& push,
-                      int* col_tiles, cudaStream_t st) {
-    TL_REQUIRE(hgemm_supported(A, B, nullptr, M, N, K, lda, ldb, N) && N % 32 == 0, "hgemm push: unsupported shape or alignment");
+// K-split matmul of the tensor-parallel prefill: C is this rank's partial result; the rank that owns a block of
+// rows (m / rows_per_owner) is told through a flag per (128-row block, column tile) when it may fetch it.
+int launch_hgemm_push(const __half* A, const __half* B, __half* C, int M, int N, int K, long long lda, long long ldb,
+                      const HgemmPush& push, int* col_tiles, cudaStream_t st) {
+    TL_REQUIRE(hgemm_supported(A, B, C, M, N, K, lda, ldb, N) && N % 32 == 0 && al16(C), "hgemm push: unsupported shape or alignment");
     TL_REQUIRE(push.world >= 2 && push.world <= 8 && push.rows_per_owner > 0 && push.rows_per_owner % 128 == 0 &&
                (long long)push.rows_per_owner * push.world >= M, "hgemm push: rows per owner must be a multiple of 128 covering M");
     const int mt = (M + BM - 1) / BM;
     const int bn = pick_bn(mt, N, 1);
     GemmArgs a{};
-    a.C = nullptr; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = N; a.sC = 0;
+    a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = N; a.sC = 0;
     a.status = device_status_word();
     a.push_rows = push.rows_per_owner; a.push_epoch = push.epoch;
     for (int r = 0; r < 8; r++) {
-        a.push_base[r] = r < push.world ? push.base[r] : nullptr;
         a.push_flags[r] = r < push.world ? push.flags[r] : nullptr;
-        if (r < push.world) TL_REQUIRE(push.base[r] && push.flags[r] && al16(push.base[r]), "hgemm push: bad destination");
+        if (r < push.world) TL_REQUIRE(push.flags[r] != nullptr, "hgemm push: bad destination");
     }
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));

@@ -179,28 +179,27 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
                  long long lda, long long ldb, long long ldc, long long sA, long long sB,
                  long long sC, cudaStream_t st);
 
-// K-split matmul whose result rows are pushed to the ranks that own them (tensor-parallel prefill):
-// row m -> base[m / rows_per_owner] + (m % rows_per_owner) * N in that rank's memory; when a 128-row x
-// tile-width piece has been stored, flags[owner][(m0 % rows_per_owner) / 128 * 64 + column tile] = epoch.
-// *col_tiles returns how many column tiles (flags per row block) the chosen kernel produces.
+// K-split matmul of the tensor-parallel prefill: C[M, N] is this rank's partial result, stored locally; the rank
+// that owns rows [o * rows_per_owner, (o + 1) * rows_per_owner) is told when it may fetch them: after a 128-row x
+// tile-width piece is stored, flags[owner][(m0 % rows_per_owner) / 128 * 64 + column tile] = epoch (a 4-byte peer
+// store). *col_tiles returns how many column tiles (flags per row block) the chosen kernel produces.
 struct HgemmPush {
     int world, rows_per_owner;
     unsigned int epoch;
-    __half* base[TL_MAX_TP];           // already offset to this rank's slot in the owner's receive buffer
-    unsigned int* flags[TL_MAX_TP];    // likewise
+    unsigned int* flags[TL_MAX_TP];    // this rank's flag block in rank d's memory
 };
-int launch_hgemm_push(const __half* A, const __half* B, int M, int N, int K, long long lda, long long ldb, const HgemmPush& push,
-                      int* col_tiles, cudaStream_t st);
+int launch_hgemm_push(const __half* A, const __half* B, __half* C, int M, int N, int K, long long lda, long long ldb,
+                      const HgemmPush& push, int* col_tiles, cudaStream_t st);
 // The owner's side: rows [0, rows) of this rank's slice = residual + sum over source ranks (rank order, fp32) of
-// the pushed partial rows, once every (row block, column tile) flag of every source reads `epoch`; the new residual
-// rows are written locally, their RMSNorm (times norm_w) is stored into row (row0 + r) of xn_dst[d] on every rank d,
-// then row flag gather_flags[d][row0 + r] = epoch. Bounded waits (TL_ERR_TIMEOUT in the status word).
+// their partial rows, fetched from the sources' memory (plain peer loads, a warp reads 512 contiguous bytes) once
+// every (row block, column tile) flag of every source reads `epoch`; the new residual rows are written locally,
+// their RMSNorm (times norm_w) is stored into row (row0 + r) of xn_dst[d] on every rank d, then row flag
+// gather_flags[d][row0 + r] = epoch. Bounded waits (TL_ERR_TIMEOUT in the status word).
 struct TpReduceNorm {
     int world, rows, row0, dim, col_tiles;
     unsigned int epoch;
-    const __half* recv;                // [world][rows_per_owner][dim] this rank's receive buffer
-    long long recv_slot_stride;        // elements between two sources' slots
-    const unsigned int* arrive_flags;  // [world][row blocks][64]
+    const __half* partial[TL_MAX_TP];  // rank s's partial result [T][dim] (peer pointer; s = this rank: local)
+    const unsigned int* arrive_flags;  // [world][row blocks][64], local
     int flags_slot_stride;             // words between two sources' flag blocks
     const __half* residual;            // local rows [row0, row0 + rows) x dim
     __half* residual_out;

@@ -74,11 +74,11 @@ def _worker(rank: int, world: int, port: int, name: str, q):
         m.load_payload(payload, shared_classifier=True)
         lg_prefill = m.forward(prompt, 0, all_logits=True)
         long_prompt = _long_prompt(cfg)
-        lg_long_nccl = m.forward(long_prompt, 0, all_logits=True)[-4:] if long_prompt is not None else None
         lg_decode = np.concatenate([m.forward(forced[i:i + 1], N_PROMPT + i, all_logits=True) for i in range(N_FORCED)])
         m.forward(prompt, 0, all_logits=False)
         ids = m.decode_device(N_PROMPT, N_FREE)             # CUDA-graph decode with NCCL inside the graph
         status = tl.device_status()
+        lg_long_nccl = m.forward(long_prompt, 0, all_logits=True)[-4:] if long_prompt is not None else None
         dist.barrier()
         # the same decode with the exchange fused into the GEMV kernels (peer stores, no NCCL)
         tp.open_fused_exchange(m, rank, world, dist)
