@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -479,9 +480,19 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
     const int world = cfg_.tp_world;
     static const bool force_nccl = [] { const char* e = getenv("TL_TP_PREFILL"); return e && !strcmp(e, "nccl"); }();
     const bool tp_fused = fused && coll_ != nullptr && xch_ready_ && !force_nccl && T % (128 * world) == 0 && dim <= 8192 &&
+                          (world == 2 || world == 4 || world == 8) &&
                           T / world <= pf_rpo_max_;
     const int rpo = tp_fused ? T / world : 0, row0 = cfg_.tp_rank * rpo;
     __half* xn = tp_fused ? reinterpret_cast<__half*>(xch_base_ + pf_off_xn_) : xn_;
+    // TL_PREFILL_TIMING=<layer>: stage-by-stage device times of that layer on stderr (the event records
+    // serialise the stages, so the sum exceeds the layer's share of an untimed run)
+    static const int timing_layer = [] { const char* e = getenv("TL_PREFILL_TIMING"); return e ? atoi(e) : -1; }();
+    std::vector<std::pair<const char*, cudaEvent_t>> marks;
+    bool timing = false;
+    auto mark = [&](const char* name) {
+        if (!timing) return;
+        cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, st); marks.emplace_back(name, e);
+    };
     auto exchange = [&](const __half* A, const __half* Wk, int K, const __half* resid, __half* resid_out, const __half* norm_w) -> int {
         // one fused compute + collective: push GEMM, owner-side reduce + norm + gather, wait for every owner's rows
         HgemmPush push{};
@@ -493,22 +504,29 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
         launches_ += 3;
         TL_PROPAGATE(launch_hgemm_push(A, Wk, reinterpret_cast<__half*>(xch_base_ + pf_off_recv_), T, dim, K, K, K, push, &col_tiles, st));
         TpReduceNorm rn{};
-        rn.world = world; rn.rows = rpo; rn.row0 = row0; rn.dim = dim; rn.col_tiles = col_tiles; rn.epoch = push.epoch;
+        rn.world = world; rn.rank = cfg_.tp_rank; rn.rows = rpo; rn.row0 = row0; rn.dim = dim; rn.col_tiles = col_tiles; rn.epoch = push.epoch;
         for (int d = 0; d < world; d++) rn.partial[d] = reinterpret_cast<const __half*>(xch_peer_[d] + pf_off_recv_);
         rn.arrive_flags = reinterpret_cast<const unsigned int*>(xch_base_ + pf_off_aflags_); rn.flags_slot_stride = (int)fslot;
         rn.residual = resid + (size_t)row0 * dim; rn.residual_out = resid_out + (size_t)row0 * dim;
         rn.norm_w = norm_w; rn.eps = 1e-5f;
         for (int d = 0; d < world; d++) {
             rn.xn_dst[d] = reinterpret_cast<__half*>(xch_peer_[d] + pf_off_xn_);
-            rn.gather_flags[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + pf_off_gflags_);
+            rn.owner_done[d] = reinterpret_cast<unsigned int*>(xch_peer_[d] + pf_off_gflags_);
         }
+        mark("  k-split matmul");
+        rn.rows_done = reinterpret_cast<unsigned int*>(xch_base_ + pf_off_gflags_) + 64;
         TL_PROPAGATE(launch_tp_reduce_norm(rn, st));
-        return launch_tp_wait_rows(reinterpret_cast<const unsigned int*>(xch_base_ + pf_off_gflags_), T, push.epoch, st);
+        mark("  owner reduce + norm + gather");
+        TL_PROPAGATE(launch_tp_wait_owners(reinterpret_cast<const unsigned int*>(xch_base_ + pf_off_gflags_), world, push.epoch, st));
+        mark("  wait for all owners");
+        return TL_OK;
     };
     launches_++;
     TL_PROPAGATE(launch_embedding(x_, emb_, d_tokens_, T, dim, cfg_.vocab_size, st));
     for (int l = 0; l < cfg_.n_layers; l++) {
         const LayerWeights& w = layers_[l];
+        timing = l == timing_layer && T > 128;
+        mark("start");
         // (under the fused exchange the norm of layers > 0 was applied by the owner of each row at the end of the previous layer)
         if (!tp_fused || l == 0) TL_PROPAGATE(launch_rmsnorm_fast(xn, x_, w.attn_norm, 1e-5f, dim, T, st));
         if (fused) {
@@ -527,6 +545,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             TL_PROPAGATE(launch_copy_rows(w.cache_k + (size_t)pos * dl, k_, T, dl, dl, st));
             TL_PROPAGATE(launch_copy_rows(w.cache_v + (size_t)pos * dl, v_, T, dl, dl, st));
         }
+        mark("norm + qkv + rope");
         // scores[h] = q_h . K_h^T ; softmax (scale + causal mask inside) ; att_h = P_h . V_h
         if (flash_prefill_supported(q_, w.cache_k, w.cache_v, att_, T, S, pos, H, hd_, dl, dl, dl, dl)) {
             // one kernel, scores stay in tensor memory / registers, K and V read in place from the caches
@@ -547,6 +566,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             SeqMatmul pv{scores_, w.cache_v, att_, H, T, hd_, S, S, 1, 1, dl, dl, (long long)T * S, hd_, hd_};
             TL_PROPAGATE(launch_matmul_seq(pv, st));
         }
+        mark("attention");
         if (tp_fused) {
             TL_PROPAGATE(exchange(att_, w.wo, dl, x_, h_, w.ffn_norm));          // h = x + wo(att); xn = norm(h) * ffn_norm
         } else if (fused_residual) {
@@ -558,6 +578,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
             TL_PROPAGATE(launch_binary(h_, x_, ao_, (size_t)T * dim, 0, st));
         }
+        mark("wo + exchange + residual");
         if (!tp_fused) {
             launches_++;
             TL_PROPAGATE(launch_rmsnorm_fast(xn, h_, w.ffn_norm, 1e-5f, dim, T, st));
@@ -571,6 +592,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             TL_PROPAGATE(linear(xn, w.w3, u_, T, hl, dim, st));
             TL_PROPAGATE(launch_swiglu_fast(g_, g_, u_, (size_t)T * hl, st));
         }
+        mark("norm + gate/up");
         if (tp_fused) {
             const __half* next_norm = l + 1 < cfg_.n_layers ? layers_[l + 1].attn_norm : final_norm_;
             TL_PROPAGATE(exchange(g_, w.w2, hl, h_, x_, next_norm));             // x = h + w2(g); xn = norm(x) * next norm
@@ -583,7 +605,19 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             if (coll_) TL_PROPAGATE(coll_->allreduce_sum_f16(ao_, (size_t)T * dim, st));
             TL_PROPAGATE(launch_binary(x_, h_, ao_, (size_t)T * dim, 0, st));
         }
+        mark("w2 + exchange + residual");
+        if (timing && !marks.empty()) {
+            cudaStreamSynchronize(st);
+            for (size_t i = 1; i < marks.size(); i++) {
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
+                fprintf(stderr, "[prefill timing rank %d layer %d T %d] %-34s %8.1f us\n", cfg_.tp_rank, l, T, marks[i].first, ms * 1e3f);
+            }
+            for (auto& m : marks) cudaEventDestroy(m.second);
+            marks.clear();
+        }
     }
+    timing = false;
     launches_ += 1;
     const int t0 = all_logits ? 0 : T - 1, tn = all_logits ? T : 1;
     // (fused exchange: the last layer's owner-side kernel already applied the final norm to every row)
@@ -676,7 +710,7 @@ int Llama2Engine::xch_export(cudaIpcMemHandle_t* out) {
         pf_off_recv_ = take(S * dim * sizeof(__half));
         pf_off_xn_ = take(S * dim * sizeof(__half));
         pf_off_aflags_ = take(W * (size_t)(pf_rpo_max_ / 128) * 64 * sizeof(unsigned int));
-        pf_off_gflags_ = take(S * sizeof(unsigned int));
+        pf_off_gflags_ = take(128 * sizeof(unsigned int));   // [0, world): owner flags; [64]: this rank's finished-row counter
         xch_bytes_ = off;
         void* d = nullptr;
         TL_CUDA(cudaMalloc(&d, xch_bytes_));

@@ -75,12 +75,13 @@ struct GemmArgs {
 };
 constexpr int PUSH_MAX_COL_TILES = 64;
 
-// after the epilogue threads of one 128-row sub-tile have stored their rows to the owner's memory: make the
-// stores visible system-wide, meet, and let one thread raise the flag of (row block, column tile)
+// after the epilogue threads of one 128-row sub-tile have stored their rows: meet, and let one thread raise the
+// flag of (row block, column tile) in the owner's memory. The barrier orders the other threads' stores before the
+// writer's release store, which is cumulative at system scope (one fence per tile instead of one per thread).
 __device__ __forceinline__ void push_signal(const GemmArgs& p, int row0, int col_tile, int bar_id, bool writer) {
-    __threadfence_system();
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
     if (writer && row0 < p.M) {
+        __threadfence_system();
         const int owner = row0 / p.push_rows, rb = (row0 - owner * p.push_rows) >> 7;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flags[owner] + rb * PUSH_MAX_COL_TILES + col_tile), "r"(p.push_epoch) : "memory");
     }
@@ -718,6 +719,8 @@ k_hgemm_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     emit(c, r);
                 }
             }
+            if (EPI == GEPI_STORE && p.push_rows > 0)
+                push_signal(p, ((mt * 2 + (int)rank) * MSUB + ms) * BM, ntl, 2 + ms, q == 0 && lane == 0);
         }
     }
     // ---------------- teardown: nobody frees TMEM or leaves while the pair may still use it -----------
@@ -839,7 +842,6 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     const long long nt = (long long)n_col_tiles * a.batch;
     const int nkb = (a.K + BK - 1) / BK;
     PairPlan pl = pair_plan(a.M, nt, nkb, EPI);
-    if (a.push_rows > 0) pl.sk_per = 0;      // pushed tiles are signalled whole
     const long long tiles = (long long)((a.M + 256 * pl.msub - 1) / (256 * pl.msub)) * nt;
     int pair_ctas = (int)std::min<long long>(tiles, sm_count() / 2);
     if (pl.sk_per > 0) {

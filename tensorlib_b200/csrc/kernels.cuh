@@ -193,10 +193,11 @@ int launch_hgemm_push(const __half* A, const __half* B, __half* C, int M, int N,
 // The owner's side: rows [0, rows) of this rank's slice = residual + sum over source ranks (rank order, fp32) of
 // their partial rows, fetched from the sources' memory (plain peer loads, a warp reads 512 contiguous bytes) once
 // every (row block, column tile) flag of every source reads `epoch`; the new residual rows are written locally,
-// their RMSNorm (times norm_w) is stored into row (row0 + r) of xn_dst[d] on every rank d, then row flag
-// gather_flags[d][row0 + r] = epoch. Bounded waits (TL_ERR_TIMEOUT in the status word).
+// their RMSNorm (times norm_w) is stored into row (row0 + r) of xn_dst[d] on every rank d; when the last row of
+// the slice is done (counted in *rows_done, left at 0) owner_done[d][rank] = epoch on every rank d. Bounded waits
+// (TL_ERR_TIMEOUT in the status word).
 struct TpReduceNorm {
-    int world, rows, row0, dim, col_tiles;
+    int world, rank, rows, row0, dim, col_tiles;
     unsigned int epoch;
     const __half* partial[TL_MAX_TP];  // rank s's partial result [T][dim] (peer pointer; s = this rank: local)
     const unsigned int* arrive_flags;  // [world][row blocks][64], local
@@ -205,11 +206,12 @@ struct TpReduceNorm {
     __half* residual_out;
     const __half* norm_w; float eps;
     __half* xn_dst[TL_MAX_TP];
-    unsigned int* gather_flags[TL_MAX_TP];
+    unsigned int* owner_done[TL_MAX_TP];   // [world] flag words in rank d's memory
+    unsigned int* rows_done;               // local counter, 0 between exchanges
 };
 int launch_tp_reduce_norm(const TpReduceNorm& p, cudaStream_t st);
 // wait (bounded) until row flags [0, rows) read `epoch`: every owner's normalised rows have arrived here
-int launch_tp_wait_rows(const unsigned int* flags, int rows, unsigned int epoch, cudaStream_t st);
+int launch_tp_wait_owners(const unsigned int* flags, int owners, unsigned int epoch, cudaStream_t st);
 
 // ---- skinny_sm100.cu: 2 <= M <= 128, weights streamed once (swap-AB tcgen05, stream-K split) --------
 bool skinny_supported(const void* A, const void* W, size_t M, size_t N, size_t K, size_t lda, size_t ldw);

@@ -5,15 +5,15 @@
 // Token rows are dealt out in contiguous slices, one per rank (the owner of a row). The matmul
 // (hgemm_sm100.cu, push mode) keeps its partial result in its own memory and raises a flag in the
 // OWNER's memory for every finished (128-row block, column tile) while its other tiles are still
-// being computed. k_tp_reduce_norm below runs on the owner, one CTA per row: it waits for the flags
+// being computed. k_tp_reduce_norm below runs on the owner, one warp per row: it waits for the flags
 // of its row block from every source rank, fetches the partial rows from the sources' memory with
 // plain peer loads (a warp reads 512 contiguous bytes: the reduce-scatter), adds them in rank order
 // in fp32, rounds once, adds the residual in fp16 (the arithmetic of the single-GPU path up to the
 // fp32 summation order), writes the new residual row locally, applies the RMSNorm of the operator
 // that follows and stores the normalised row into every rank's activation buffer (the all-gather,
-// 512-byte peer stores), then sets that row's flag on every rank. k_tp_wait_rows holds the stream
-// until all rows of all owners have arrived, after which the next matmul reads them like any local
-// buffer. No collective library call, no multicast, every wait is bounded.
+// 512-byte peer stores); the CTA that finishes the slice's last row sets this owner's flag on every
+// rank. k_tp_wait_owners holds the stream until every owner's flag is up, after which the next
+// matmul reads the rows like any local buffer. No collective library call, no multicast, every wait is bounded.
 // (Pushing the tiles from the matmul's epilogue instead was measured first: a thread owns 64
 // contiguous bytes of a row there, and half a million such stores per matmul cost more NVLink time
 // than the allreduce they replace: 18.9 ms against 15.7 ms for the 2048-token prefill on two GPUs.)
@@ -23,7 +23,10 @@ namespace tlb {
 
 namespace {
 
-constexpr int RN_THREADS = 256;
+#ifndef TL_RN_THREADS
+#define TL_RN_THREADS 256
+#endif
+constexpr int RN_THREADS = TL_RN_THREADS;     // one row per warp
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     unsigned int v;
@@ -31,79 +34,93 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     return v;
 }
 
-__global__ void __launch_bounds__(RN_THREADS) k_tp_reduce_norm(TpReduceNorm p, int* status) {
-    __shared__ float red[RN_THREADS / 32];
-    __shared__ int timed_out;
-    const int r = blockIdx.x;                       // row of this rank's slice
-    const int rb = r >> 7;
-    if (threadIdx.x == 0) timed_out = 0;
+__device__ __forceinline__ uint4 ld_peer16(const uint4* ptr) {
+    uint4 v;     // relaxed system-scope load: straight from the source rank's memory, never a stale local cache line
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+
+// One WARP per row (no CTA barrier anywhere on the chain flag -> loads -> sum -> stores -> fence: with one row
+// per 256-thread CTA the kernel measured 30 us for 1024 rows on local memory alone, all of it barrier, fence and
+// load latency at 23 % of the warp slots). W = number of ranks and GPL = 16-byte groups per lane are compile-time
+// constants, so the loads of every source are in flight together and the row stays in registers for the norm.
+template <int W, int GPL>
+__global__ void __launch_bounds__(RN_THREADS, 512 / RN_THREADS) k_tp_reduce_norm(TpReduceNorm p, int* status) {
+    constexpr int CH = W <= 2 ? 4 : (W <= 4 ? 2 : 1);     // groups per lane whose loads are issued together
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (RN_THREADS / 32) + (threadIdx.x >> 5);    // row of this rank's slice
+    __shared__ int rows_here;
+    if (threadIdx.x == 0) rows_here = 0;
     pdl_launch_dependents();
     pdl_wait();
     __syncthreads();
+    const int rb = min(r, p.rows - 1) >> 7;
     // every (source, column tile) flag of this row block
-    for (int i = threadIdx.x; i < p.world * p.col_tiles; i += RN_THREADS) {
+    bool ok = r < p.rows;
+    for (int i = lane; i < W * p.col_tiles; i += 32) {
         const int src = i / p.col_tiles, ct = i - src * p.col_tiles;
         const unsigned int* f = p.arrive_flags + (size_t)src * p.flags_slot_stride + rb * 64 + ct;
         bool here = false;
         for (unsigned int t = 0; t < TL_EXCHANGE_TRIES && !here; t++) here = ld_acquire_sys(f) == p.epoch;
-        if (!here) timed_out = 1;
+        ok &= here;
     }
-    __syncthreads();
-    if (timed_out) {
-        if (threadIdx.x == 0) atomicExch(status, TL_ERR_TIMEOUT);
-        return;
-    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && r < p.rows && lane == 0) atomicExch(status, TL_ERR_TIMEOUT);   // the row is never counted: the waiting kernels give up as well
+    if (ok) {
     // h = residual + half(sum over ranks), kept in registers for the norm; dim / 8 16-byte groups per row
     const int groups = p.dim >> 3;
+    const size_t grow = (size_t)(p.row0 + r);
     const uint4* res4 = reinterpret_cast<const uint4*>(p.residual + (size_t)r * p.dim);
     uint4* out4 = reinterpret_cast<uint4*>(p.residual_out + (size_t)r * p.dim);
-    constexpr int MAXG = 4;                          // groups per thread: dim <= 8 * 256 * 4 = 8192
-    uint4 hval[MAXG];
+    uint4 hval[GPL];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < MAXG; k++) {
-        const int g = threadIdx.x + k * RN_THREADS;
-        if (g >= groups) break;
-        float s[8];
+    for (int c0 = 0; c0 < GPL; c0 += CH) {
+        if (c0 * 32 >= groups) break;
+        uint4 v[CH][W], rv[CH];
 #pragma unroll
-        for (int j = 0; j < 8; j++) s[j] = 0.f;
-        for (int src = 0; src < p.world; src++) {
-            uint4 v;     // straight from the source rank's memory; volatile: never served from a stale local cache line
-            const uint4* ptr = reinterpret_cast<const uint4*>(p.partial[src] + (size_t)(p.row0 + r) * p.dim) + g;
-            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
-            const __half2* vh = reinterpret_cast<const __half2*>(&v);
+        for (int cc = 0; cc < CH; cc++) {
+            const int g = min(lane + (c0 + cc) * 32, groups - 1);
 #pragma unroll
-            for (int j = 0; j < 4; j++) { const float2 f = __half22float2(vh[j]); s[2 * j] += f.x; s[2 * j + 1] += f.y; }
+            for (int src = 0; src < W; src++) v[cc][src] = ld_peer16(reinterpret_cast<const uint4*>(p.partial[src] + grow * p.dim) + g);
+            rv[cc] = res4[g];
         }
-        const uint4 rv = res4[g];
-        const __half* rh = reinterpret_cast<const __half*>(&rv);
-        uint4 hv;
-        __half* hh = reinterpret_cast<__half*>(&hv);
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            hh[j] = hadd_ref(rh[j], __float2half_rn(s[j]));
-            const float f = __half2float(hh[j]);
-            ss = fmaf(f, f, ss);
+        for (int cc = 0; cc < CH; cc++) {
+            const int g = lane + (c0 + cc) * 32;
+            float s[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[j] = 0.f;
+#pragma unroll
+            for (int src = 0; src < W; src++) {
+                const __half2* vh = reinterpret_cast<const __half2*>(&v[cc][src]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) { const float2 f = __half22float2(vh[j]); s[2 * j] += f.x; s[2 * j + 1] += f.y; }
+            }
+            const __half* rh = reinterpret_cast<const __half*>(&rv[cc]);
+            uint4 hv;
+            __half* hh = reinterpret_cast<__half*>(&hv);
+            float part = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                hh[j] = hadd_ref(rh[j], __float2half_rn(s[j]));
+                const float f = __half2float(hh[j]);
+                part = fmaf(f, f, part);
+            }
+            hval[c0 + cc] = hv;
+            if (g < groups) { out4[g] = hv; ss += part; }
         }
-        hval[k] = hv;
-        out4[g] = hv;
     }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < RN_THREADS / 32; w++) tot += red[w];
-    const float rinv = rsqrtf(tot / (float)p.dim + p.eps);
+    const float rinv = rsqrtf(ss / (float)p.dim + p.eps);
     const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
-    const size_t grow = (size_t)(p.row0 + r);
 #pragma unroll
-    for (int k = 0; k < MAXG; k++) {
-        const int g = threadIdx.x + k * RN_THREADS;
+    for (int c = 0; c < GPL; c++) {
+        const int g = lane + c * 32;
         if (g >= groups) break;
         const uint4 wv = nw4[g];
         const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-        const __half2* hh = reinterpret_cast<const __half2*>(&hval[k]);
+        const __half2* hh = reinterpret_cast<const __half2*>(&hval[c]);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -111,19 +128,35 @@ __global__ void __launch_bounds__(RN_THREADS) k_tp_reduce_norm(TpReduceNorm p, i
             const float2 hf = __half22float2(hh[j]), wf = __half22float2(wh[j]);
             oh[j] = __floats2half2_rn(hf.x * rinv * wf.x, hf.y * rinv * wf.y);
         }
-        for (int d = 0; d < p.world; d++) reinterpret_cast<uint4*>(p.xn_dst[d] + grow * p.dim)[g] = o;
+#pragma unroll
+        for (int d = 0; d < W; d++) reinterpret_cast<uint4*>(p.xn_dst[d] + grow * p.dim)[g] = o;
     }
-    __threadfence_system();
+    if (lane == 0) atomicAdd(&rows_here, 1);
+    }
+    // The CTA barrier orders every warp's stores before thread 0's fence (cumulative at system scope: one fence
+    // per CTA; a fence per row measured 8 us more over 1024 rows, and it is the only system-scope fence on the
+    // chain). The CTA that counts the last row of the slice then tells every rank that this owner's rows are all
+    // in place: every other row's stores were performed system-wide before its count was added, and the flag
+    // stores are issued after the count was read.
     __syncthreads();
-    if (threadIdx.x < p.world)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather_flags[threadIdx.x] + grow), "r"(p.epoch) : "memory");
+    if (threadIdx.x == 0 && rows_here > 0) {
+        __threadfence_system();
+        if (atomicAdd(p.rows_done, (unsigned int)rows_here) + (unsigned int)rows_here == (unsigned int)p.rows) {
+            *p.rows_done = 0;           // the next exchange's kernel starts after this one has finished
+            __threadfence();
+#pragma unroll
+            for (int d = 0; d < W; d++)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.owner_done[d] + p.rank), "r"(p.epoch) : "memory");
+        }
+    }
 }
 
-__global__ void __launch_bounds__(1024) k_tp_wait_rows(const unsigned int* flags, int rows, unsigned int epoch, int* status) {
+// holds the stream until every owner has announced its rows (one flag per owner)
+__global__ void __launch_bounds__(32) k_tp_wait_owners(const unsigned int* flags, int owners, unsigned int epoch, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     bool all = true;
-    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+    for (int i = threadIdx.x; i < owners; i += blockDim.x) {
         bool here = false;
         for (unsigned int t = 0; t < TL_EXCHANGE_TRIES && !here; t++) here = ld_acquire_sys(flags + i) == epoch;
         all &= here;
@@ -133,15 +166,29 @@ __global__ void __launch_bounds__(1024) k_tp_wait_rows(const unsigned int* flags
 
 }  // namespace
 
-int launch_tp_reduce_norm(const TpReduceNorm& p, cudaStream_t st) {
-    TL_REQUIRE(p.world >= 2 && p.world <= TL_MAX_TP && p.rows > 0 && p.dim % 8 == 0 && p.dim <= 8 * RN_THREADS * 4 &&
-               p.col_tiles >= 1 && p.col_tiles <= 64, "tp reduce: bad shape");
-    return launch_pdl(k_tp_reduce_norm, dim3((unsigned)p.rows), dim3(RN_THREADS), 0, st, true, p, device_status_word());
+template <int W>
+int launch_reduce_w(const TpReduceNorm& p, cudaStream_t st) {
+    const dim3 grid((unsigned)((p.rows + RN_THREADS / 32 - 1) / (RN_THREADS / 32))), block(RN_THREADS);
+    const int groups = p.dim / 8;
+    if (groups <= 4 * 32) return launch_pdl(k_tp_reduce_norm<W, 4>, grid, block, 0, st, true, p, device_status_word());
+    if (groups <= 16 * 32) return launch_pdl(k_tp_reduce_norm<W, 16>, grid, block, 0, st, true, p, device_status_word());
+    return launch_pdl(k_tp_reduce_norm<W, 32>, grid, block, 0, st, true, p, device_status_word());
 }
 
-int launch_tp_wait_rows(const unsigned int* flags, int rows, unsigned int epoch, cudaStream_t st) {
-    if (rows <= 0) return TL_OK;
-    return launch_pdl(k_tp_wait_rows, dim3(1), dim3(1024), 0, st, true, flags, rows, epoch, device_status_word());
+int launch_tp_reduce_norm(const TpReduceNorm& p, cudaStream_t st) {
+    TL_REQUIRE(p.rows > 0 && p.dim % 8 == 0 && p.dim <= 8192 && p.col_tiles >= 1 && p.col_tiles <= 64, "tp reduce: bad shape");
+    switch (p.world) {
+        case 2: return launch_reduce_w<2>(p, st);
+        case 4: return launch_reduce_w<4>(p, st);
+        case 8: return launch_reduce_w<8>(p, st);
+    }
+    TL_REQUIRE(false, "tp reduce: 2, 4 or 8 ranks");
+    return TL_ERR_UNSUPPORTED;
+}
+
+int launch_tp_wait_owners(const unsigned int* flags, int owners, unsigned int epoch, cudaStream_t st) {
+    if (owners <= 0) return TL_OK;
+    return launch_pdl(k_tp_wait_owners, dim3(1), dim3(32), 0, st, true, flags, owners, epoch, device_status_word());
 }
 
 }  // namespace tlb
