@@ -545,6 +545,8 @@ def prefill_2048(model, cfg, world, torch, dist, T: int = 2048):
     """Config 3/4 of the benchmark spec: one 2048-token prompt, batch 1, through
     tl_llama2_forward (token ids from the host, last-position logits back to the host)."""
     prompt = synth.prompt_tokens(cfg, SEED + 1, T)
+    if world > 1:
+        dist.barrier()          # rank 0 arrives late from its single-rank roofline measurement
     model.forward(prompt[:T], 0, all_logits=False)                       # warm-up (allocates score buffers)
     times = []
     for _ in range(3):

@@ -514,6 +514,7 @@ int tl_llama2_decode_device(tl_llama2* m, int start_pos, int steps, int* out_tok
     TL_REQUIRE(m && steps >= 0, "bad argument");
     Llama2Engine& e = *m->eng;
     cudaStream_t st = as_stream(stream);
+    TL_PROPAGATE(e.align_ranks(st));
     TL_PROPAGATE(e.decode_steps(start_pos, steps, st));
     if (out_tokens_host && steps > 0) {
         int* stat = status_slot(m);

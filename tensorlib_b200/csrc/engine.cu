@@ -521,6 +521,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
         mark("  wait for all owners");
         return TL_OK;
     };
+    if (tp_fused) TL_PROPAGATE(align_ranks(st));
     launches_++;
     TL_PROPAGATE(launch_embedding(x_, emb_, d_tokens_, T, dim, cfg_.vocab_size, st));
     for (int l = 0; l < cfg_.n_layers; l++) {
@@ -997,6 +998,7 @@ int Llama2Engine::ensure_mega() {
 
 int Llama2Engine::decode_profile(int start_pos, int cta, unsigned long long* out_host, int capacity, int* n_phases) {
     TL_REQUIRE(out_host && n_phases, "null argument");
+    TL_PROPAGATE(align_ranks(nullptr));
     if (!use_mega()) {
         // the step as plain launches (programmatic dependent launch, no graph), CTA 0 of every GEMV phase stamping
         // %globaltimer at its first instruction, when its activation vector is staged and when it is done
@@ -1066,6 +1068,21 @@ int Llama2Engine::decode_step_mega(cudaStream_t st, unsigned long long* prof, in
     }
     launches_ += 1;
     return launch_decode_flow(a, mega_grid_, mega_smem_, st);
+}
+
+// The waits of the fused exchange are bounded (about two seconds), the skew between the ranks' host threads is
+// not: a tiny allreduce through the collective library, which waits as long as it takes, lines the ranks up
+// before a call enters the kernels that wait for one another. Once per call, never inside the layer loop.
+int Llama2Engine::align_ranks(cudaStream_t st) {
+    if (!coll_ || !xch_ready_) return TL_OK;
+    if (!align_buf_) {
+        void* d = nullptr;
+        TL_CUDA(cudaMalloc(&d, 256));
+        TL_CUDA(cudaMemset(d, 0, 256));
+        allocs_.push_back(d);
+        align_buf_ = static_cast<__half*>(d);
+    }
+    return coll_->allreduce_sum_f16(align_buf_, 8, st);
 }
 
 int Llama2Engine::decode_steps(int start_pos, int steps, cudaStream_t st) {

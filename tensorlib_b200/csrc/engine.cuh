@@ -45,6 +45,7 @@ public:
     // One decode step replayed from a CUDA graph: token = *d_next_, position = *d_pos_; writes the
     // sampled id to d_next_ and d_generated_[pos], then increments *d_pos_.
     int decode_steps(int start_pos, int steps, cudaStream_t st);
+    int align_ranks(cudaStream_t st);
     int ensure_decode_graph(cudaStream_t st);
 
     const tl_llama2_config& cfg() const { return cfg_; }
@@ -127,6 +128,7 @@ private:
     size_t pf_off_recv_ = 0, pf_off_xn_ = 0, pf_off_aflags_ = 0, pf_off_gflags_ = 0;
     int pf_rpo_max_ = 0;
     unsigned int pf_epoch_ = 0;
+    __half* align_buf_ = nullptr;       // operand of the rank-aligning allreduce (align_ranks)
     const __half* last_logits_ = nullptr;
 };
 
