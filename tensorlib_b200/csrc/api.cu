@@ -37,6 +37,9 @@ int tl_matmul_batched_f16(const tl_half* A, const tl_half* B, tl_half* C, size_t
     if (numerics == TL_NUMERICS_FAST && K > 0) {
         if (batch == 1 && gemv_ring_rows_supported(A, B, M, N, K, ldb, lda))
             return launch_gemv(H(A), H(B), H(C), (int)M, (int)N, (int)K, ldb, lda, ldc, st);
+        if (batch == 1 && M > 8 && M <= 128 && hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc) && ldc % 8 == 0 &&
+            (reinterpret_cast<uintptr_t>(C) & 15) == 0 && hgemm_splitk_preferred((int)M, (int)N, (int)K))
+            return launch_hgemm(H(A), H(B), H(C), 1, (int)M, (int)N, (int)K, lda, ldb, ldc, 0, 0, 0, st);
         if (batch == 1 && M >= 2 && M <= 128 && skinny_supported(A, B, M, N, K, lda, ldb))
             return launch_skinny(H(A), H(B), H(C), (int)M, (int)N, (int)K, lda, ldb, ldc, st);
         if (M > 8 && strideA % 8 == 0 && strideB % 8 == 0 && hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc))
@@ -77,13 +80,25 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
         *kernel = TL_PLAN_GEMV_RING; *grid = (int)std::min<size_t>((size_t)sm_count, (N / 2 + 7) / 8);
         return TL_OK;
     }
+    auto splitk = [&]() -> bool {      // few 128-row tiles, long K: one tile per cluster, K split over its CTAs
+        if (M <= 8 || K % 8 != 0) return false;
+        int kind = 0, bn = 0, ks = 0;
+        hgemm_plan((int)M, (int)N, (int)K, 1, sm_count, &kind, &bn, &ks);
+        if (kind != 3) return false;
+        *kernel = TL_PLAN_HGEMM_SPLITK; *tile_n = bn; *cluster = ks;
+        *grid = (int)(((M + 127) / 128) * ((N + bn - 1) / bn)) * ks;
+        *k_blocks_per_cta = (int)(((K + 63) / 64 + ks - 1) / ks);
+        return true;
+    };
     if (M >= 2 && M <= 128 && K % 8 == 0) {
+        if (M > 32 && splitk()) return TL_OK;       // up to 32 rows the skinny kernel measured faster
         const SkinnyPlan pl = skinny_plan((int)M, (int)N, (int)K, sm_count);
         *kernel = pl.cluster_splits >= 2 ? TL_PLAN_SKINNY_CLUSTER : TL_PLAN_SKINNY_STREAMK;
         *grid = pl.grid; *tile_n = pl.nb; *k_blocks_per_cta = pl.per; *cluster = pl.cluster_splits;
         return TL_OK;
     }
     if (M > 8 && K % 8 == 0) {
+        if (splitk()) return TL_OK;
         int kind = 0, bn = 0, sk_per = 0;
         hgemm_plan((int)M, (int)N, (int)K, 1, sm_count, &kind, &bn, &sk_per);
         *kernel = kind == 2 ? TL_PLAN_HGEMM_PAIR512 : (kind == 1 ? TL_PLAN_HGEMM_PAIR : TL_PLAN_HGEMM);
@@ -173,8 +188,13 @@ int tl_linear_f16(const tl_half* x, const tl_half* W, tl_half* y, size_t T, size
         return launch_gemv(H(x), H(W), H(y), 1, (int)N, (int)K, K, K, N, st, true);
     if (gemv_ring_rows_supported(x, W, T, N, K, K, K))
         return launch_gemv(H(x), H(W), H(y), (int)T, (int)N, (int)K, K, K, N, st, true);
+    if (T > 8 && T <= 128 && hgemm_supported(x, W, y, T, N, K, K, K, N) && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+        hgemm_splitk_preferred((int)T, (int)N, (int)K))
+        return launch_hgemm(H(x), H(W), H(y), 1, (int)T, (int)N, (int)K, K, K, N, 0, 0, 0, st, true);
     if (T >= 2 && T <= 128 && skinny_supported(x, W, T, N, K, K, K))
         return launch_skinny(H(x), H(W), H(y), (int)T, (int)N, (int)K, K, K, N, st, true);
+    if (T > 8 && hgemm_supported(x, W, y, T, N, K, K, K, N))
+        return launch_hgemm(H(x), H(W), H(y), 1, (int)T, (int)N, (int)K, K, K, N, 0, 0, 0, st, true);
     return tl_matmul2d_f16(x, W, y, T, N, K, TL_NUMERICS_FAST, stream);
 }
 

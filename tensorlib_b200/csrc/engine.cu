@@ -377,13 +377,18 @@ int Llama2Engine::linear(const __half* x, const __half* W, __half* y, int T, int
         launches_++;
         return launch_gemv(x, W, y, T, N, K, K, K, N, st, true);
     }
+    if (T > 8 && T <= 128 && hgemm_supported(x, W, y, T, N, K, K, K, N) && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+        hgemm_splitk_preferred(T, N, K)) {
+        launches_++;
+        return launch_hgemm(x, W, y, 1, T, N, K, K, K, N, 0, 0, 0, st, true);
+    }
     if (T >= 2 && T <= 128 && skinny_supported(x, W, T, N, K, K, K)) {
         launches_++;
         return launch_skinny(x, W, y, T, N, K, K, K, N, st, true);     // model weights are constants
     }
     if (T > 8 && hgemm_supported(x, W, y, T, N, K, K, K, N)) {
         launches_++;
-        return launch_hgemm(x, W, y, 1, T, N, K, K, K, N, 0, 0, 0, st);
+        return launch_hgemm(x, W, y, 1, T, N, K, K, K, N, 0, 0, 0, st, true);
     }
     if (gemv_supported(x, W, T <= 8 ? T : 8, N, K, K)) {
         for (int t0 = 0; t0 < T; t0 += 8) {  // skinny batches: stream the weights once per 8 rows
@@ -572,7 +577,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             TL_PROPAGATE(exchange(att_, w.wo, dl, x_, h_, w.ffn_norm));          // h = x + wo(att); xn = norm(h) * ffn_norm
         } else if (fused_residual) {
             launches_++;
-            TL_PROPAGATE(launch_hgemm_residual(att_, w.wo, x_, h_, T, dim, dl, dl, dl, dim, dim, st));
+            TL_PROPAGATE(launch_hgemm_residual(att_, w.wo, x_, h_, T, dim, dl, dl, dl, dim, dim, st, true));
         } else {
             launches_++;
             TL_PROPAGATE(linear(att_, w.wo, ao_, T, dim, dl, st));
@@ -599,7 +604,7 @@ int Llama2Engine::forward_fast_prefill(int T, int pos, bool all_logits, cudaStre
             TL_PROPAGATE(exchange(g_, w.w2, hl, h_, x_, next_norm));             // x = h + w2(g); xn = norm(x) * next norm
         } else if (fused_residual) {
             launches_++;
-            TL_PROPAGATE(launch_hgemm_residual(g_, w.w2, h_, x_, T, dim, hl, hl, hl, dim, dim, st));
+            TL_PROPAGATE(launch_hgemm_residual(g_, w.w2, h_, x_, T, dim, hl, hl, hl, dim, dim, st, true));
         } else {
             launches_++;
             TL_PROPAGATE(linear(g_, w.w2, ao_, T, dim, hl, st));

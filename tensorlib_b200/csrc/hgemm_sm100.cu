@@ -50,6 +50,7 @@ struct GemmArgs {
     int M, N, K, batch;
     long long ldc, sC;
     int a_batched, b_batched;   // 0: the operand is shared by all batches (batch coordinate 0)
+    int b_const;                // cluster split-K kernel: B is a constant (a weight), its first tiles may be fetched before the dependency wait
     int* status;
     // RESIDUAL
     const __half* R; long long ldr;
@@ -333,6 +334,196 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
+}
+
+// ---- K split inside a cluster: KS CTAs share one 128 x BN output tile ----------------------------------
+// Few output tiles and a long K (M <= 512 against the 7B weights, or any M <= 128): whole tiles leave most
+// SMs idle, and splitting K through global memory costs a round trip of fp32 partial tiles plus a counter.
+// Here the KS CTAs of a cluster each run the TMA -> tcgen05 pipeline over their K / KS share of the SAME
+// tile (accumulator in their own TMEM) and then exchange partial sums over distributed shared memory as a
+// reduce-scatter: CTA r finishes columns [r BN/KS, (r+1) BN/KS) of the tile, every other CTA writes its
+// fp32 partial of those columns into r's receive area (st.shared::cluster, a warp writes 512 contiguous
+// bytes) and arrives on r's mbarrier (release at cluster scope); r adds the parts in rank order, converts
+// and stores. No workspace, no atomics, the order of the additions is fixed, and the epilogue itself is
+// spread over all KS CTAs. One tile per cluster (the launcher uses it only when tiles x KS fits the SMs).
+template <int BN, int KS>
+struct SplitCfg {
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SLICE = BN / KS;                               // output columns one CTA finishes
+    static constexpr int PART_BYTES = BM * SLICE * 4;                   // one sender's partial of my slice
+    static constexpr int RECV_BYTES = (KS - 1) * PART_BYTES;            // received over the pipeline stages, once they are idle
+    static constexpr int NST = (216 * 1024) / STAGE_BYTES > 8 ? 8 : (216 * 1024) / STAGE_BYTES;
+    static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 1024 + 256;
+    static_assert(SLICE % 32 == 0 && NST >= 2 && RECV_BYTES <= NST * STAGE_BYTES, "slice of whole 32-column chunks; the parts fit the stages");
+};
+
+template <int BN, int KS, int EPI>
+__global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
+    using Cfg = SplitCfg<BN, KS>;
+    constexpr int NST = Cfg::NST, STAGE_BYTES = Cfg::STAGE_BYTES, SLICE = Cfg::SLICE;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* recv = smem;                                          // [sender slot][column / 4][row][4 floats], over the idle stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NST * STAGE_BYTES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NST);
+    const uint32_t tfull = smem_u32(bars + 2 * NST), recv_full = smem_u32(bars + 2 * NST + 1), peers_idle = smem_u32(bars + 2 * NST + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NST + 3);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_ctarank();
+    const int tile = blockIdx.x / KS;
+    const int mt_count = (p.M + BM - 1) / BM;
+    const int mt = tile % mt_count, nt = tile / mt_count;
+    const int nkb = (p.K + BK - 1) / BK;
+    const int kb0 = (int)((long long)nkb * rank / KS), kb1 = (int)((long long)nkb * (rank + 1) / KS);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tfull, 1);
+        mbar_init(recv_full, (KS - 1) * 128);        // every epilogue thread of every other CTA arrives once
+        mbar_init(peers_idle, KS - 1);               // one thread of every other CTA, when its stages are idle
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) tmem_alloc<(uint32_t)BN>(tmem_slot);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    cluster_sync_all();                              // nobody arrives on a barrier that is not initialised yet
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ---------------------------------------------------------
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        // B a constant (a model weight): its first tiles are requested while the previous kernel of the
+        // stream is still running; A, which that kernel may have written, only after the dependency wait
+        const int early = p.b_const ? min(NST, kb1 - kb0) : 0;
+        for (int it = 0; it < early; it++) {
+            mbar_arrive_expect_tx(full0 + 8 * it, STAGE_BYTES);
+            tma_load_3d(smem_u32(smem + it * STAGE_BYTES) + A_BYTES, &tmB, (kb0 + it) * BK, nt * BN, 0, full0 + 8 * it);
+        }
+        pdl_wait();
+        bool ok = true;
+        int it = 0;
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+            const int s = it % NST, use = it / NST;
+            if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+            if (it >= early) mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_3d(sa, &tmA, kb * BK, mt * BM, 0, full0 + 8 * s);
+            if (it >= early) tma_load_3d(sb, &tmB, kb * BK, nt * BN, 0, full0 + 8 * s);
+        }
+        if (!ok) {  // let copies already in flight land before the CTA goes away
+            for (int j = max(0, it - NST); j < it; j++)
+                for (uint32_t i = 0; i < (1u << 16); i++)
+                    if (mbar_try_wait(full0 + 8 * (j % NST), (j / NST) & 1)) break;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ------------------------------------------------------------
+        pdl_wait();
+        constexpr uint32_t idesc = make_idesc(BN);
+        bool ok = true;
+        int it = 0;
+        for (int kb = kb0; kb < kb1; kb++, it++) {
+            const int s = it % NST, use_s = it / NST;
+            if (!(ok = mbar_wait(full0 + 8 * s, use_s & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / 16; k++)
+                umma(tmem_base, make_desc(sa + k * 32), make_desc(sb + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            umma_commit(empty0 + 8 * s);
+        }
+        if (ok) umma_commit(tfull);
+    } else if (warp >= 4) {
+        // ---------------- epilogue: send the foreign slices, finish the own one -------------------------
+        pdl_wait();
+        const int q = warp & 3, rl = q * 32 + lane;                       // row of the tile = TMEM lane
+        bool ok = mbar_wait(tfull, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (ok) {
+            // all my MMAs are done, so my stages are idle: the other CTAs may write their parts over them
+            if (warp == 4 && lane == 0) {
+#pragma unroll 1
+                for (int o = 0; o < KS; o++)
+                    if (o != rank) mbar_arrive_cluster(map_to_cta(peers_idle, (uint32_t)o));
+            }
+            ok = mbar_wait_cluster(peers_idle, 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+#pragma unroll 1
+            for (int o = 0; o < KS; o++) {
+                if (o == rank) continue;
+                const int slot = rank < o ? rank : rank - 1;              // senders in rank order, the owner left out
+                const uint32_t dst = map_to_cta(smem_u32(recv), (uint32_t)o) + (uint32_t)(slot * Cfg::PART_BYTES + rl * 16);
+#pragma unroll 1
+                for (int c = 0; c < SLICE; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tbase + (uint32_t)(o * SLICE + c), r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 8; v++)
+                        st_cluster_f4(dst + (uint32_t)((c / 4 + v) * BM * 16), __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                }
+                mbar_arrive_cluster(map_to_cta(recv_full, (uint32_t)o));
+            }
+            ok = mbar_wait_cluster(recv_full, 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            const int row = mt * BM + rl;
+            __half* crow = p.C + (long long)row * p.ldc;
+            const float4* mine = reinterpret_cast<const float4*>(recv) + rl;
+#pragma unroll 1
+            for (int c = 0; c < SLICE; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tbase + (uint32_t)(rank * SLICE + c), r);
+                tmem_ld_wait();
+                float acc[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) acc[i] = 0.f;
+#pragma unroll
+                for (int s = 0; s < KS; s++) {                            // parts in k order = rank order
+                    if (s == rank) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) acc[i] += __uint_as_float(r[i]);
+                    } else {
+                        const float4* src = mine + (size_t)(s < rank ? s : s - 1) * (Cfg::PART_BYTES / 16) + (size_t)(c / 4) * BM;
+#pragma unroll
+                        for (int v = 0; v < 8; v++) {
+                            const float4 f = src[(size_t)v * BM];
+                            acc[4 * v] += f.x; acc[4 * v + 1] += f.y; acc[4 * v + 2] += f.z; acc[4 * v + 3] += f.w;
+                        }
+                    }
+                }
+                const int col0 = nt * BN + rank * SLICE + c;
+                if (row >= p.M || col0 >= p.N) continue;
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = __float_as_uint(acc[i]);
+                if (EPI == GEPI_RESIDUAL) store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
+                else store32(crow + col0, r);
+            }
+        }
+    }
+    // ---------------- teardown: nobody leaves while a CTA of the cluster may still write to it ---------
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc<(uint32_t)BN>(tmem_base);
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
@@ -794,6 +985,23 @@ int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CU
     return launch_k<64, EPI>(ma, mb, mb2, mb3, a, tiles, st);
 }
 
+template <int BN, int KS, int EPI>
+int launch_splitk_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {
+    static PerDeviceOnce once;
+    if (once.needed()) {
+        TL_CUDA(cudaFuncSetAttribute(k_hgemm_splitk<BN, KS, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SplitCfg<BN, KS>::SMEM));
+    }
+    return launch_pdl(k_hgemm_splitk<BN, KS, EPI>, dim3(tiles * KS), dim3(GEMM_THREADS), SplitCfg<BN, KS>::SMEM, st, true, ma, mb, a);
+}
+template <int EPI>
+int launch_splitk(int bn, int ks, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {
+    if (bn == 128 && ks == 4) return launch_splitk_cfg<128, 4, EPI>(ma, mb, a, tiles, st);
+    if (bn == 128 && ks == 2) return launch_splitk_cfg<128, 2, EPI>(ma, mb, a, tiles, st);
+    if (bn == 256 && ks == 2) return launch_splitk_cfg<256, 2, EPI>(ma, mb, a, tiles, st);
+    TL_REQUIRE(false, "hgemm split-K: no kernel for tile width %d split %d", bn, ks);
+    return TL_ERR_UNSUPPORTED;
+}
+
 template <int EPI, int MSUB>
 int launch_pair_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mb3,
                     const GemmArgs& a, int pair_tiles, cudaStream_t st) {
@@ -928,6 +1136,47 @@ long long single_cost(int mt, int N, int batch, int bn, int K) {
     return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64) * ((K + BK - 1) / BK);
 }
 
+// Estimated plan of the cluster split-K kernel (one 128 x bn tile per cluster of ks CTAs): only where every
+// cluster is resident at once; cost = k-blocks per CTA x the single-CTA cost of a k-block + the exchange of the
+// partial slices over distributed shared memory and the two cluster barriers (~3000 cycles).
+// TL_HGEMM_SPLITK=never|always overrides the comparison with the other kernels.
+struct SplitPlan { int bn, ks; long long cost; };
+int splitk_forced() {
+    static const int forced = [] {
+        const char* e = getenv("TL_HGEMM_SPLITK");
+        if (!e) return 0;
+        return !strcmp(e, "never") ? 2 : (!strcmp(e, "always") ? 1 : 0);
+    }();
+    return forced;
+}
+SplitPlan splitk_plan(int M, int N, int K, int batch) {
+    SplitPlan best{0, 0, -1};
+    if (batch != 1 || splitk_forced() == 2 || N % 32 != 0) return best;
+    const int mt = (M + BM - 1) / BM, nkb = (K + BK - 1) / BK;
+    static const int cand[3][2] = {{128, 4}, {128, 2}, {256, 2}};
+    for (const auto& c : cand) {
+        const int bn = c[0], ks = c[1];
+        const long long tiles = (long long)mt * ((N + bn - 1) / bn);
+        if (tiles * ks > plan_sms() || nkb / ks < 4) continue;
+        const long long per_kb = std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
+        const long long cost = (long long)((nkb + ks - 1) / ks) * per_kb + 3000;
+        if (best.cost < 0 || cost < best.cost) best = SplitPlan{bn, ks, cost};
+    }
+    return best;
+}
+
+int pick_bn(int mt, int N, int batch);
+// the cluster split-K kernel where it has a plan and the estimate beats the whole-tile kernels
+bool splitk_wins(int M, int N, int K, int batch, int epi, SplitPlan* out) {
+    const SplitPlan sp = splitk_plan(M, N, K, batch);
+    *out = sp;
+    if (sp.cost < 0) return false;
+    if (splitk_forced() == 1) return true;
+    const int mt = (M + BM - 1) / BM;
+    if (sp.cost >= single_cost(mt, N, batch, pick_bn(mt, N, batch), K)) return false;
+    return M <= BM || sp.cost < pair_cost(M, (N + 255) / 256, batch, K, epi);
+}
+
 // N-tile width with the smallest estimated time: waves of tiles over the SMs times the cost of one
 // k-block of a tile, which is the larger of its MMA time (2 cycles per accumulator column) and
 // the time to bring its operands into shared memory (16 KB of A + BN * 128 B of B at the roughly
@@ -948,11 +1197,26 @@ int pick_bn(int mt, int N, int batch) {
 
 }  // namespace
 
+// Up to 32 rows the skinny kernel (32-row tiles, mma.sync, no tensor-memory set-up) measured 0.6 to 2.5 us faster
+// on the 7B shapes; from 33 rows on the cluster kernel wins (128 rows: 13.6 / 26.1 / 23.0 us against 15.7 / 30.1 / 25.6).
+bool hgemm_splitk_preferred(int M, int N, int K) {
+    SplitPlan sp;
+    return (M > 32 || splitk_forced() == 1) && splitk_wins(M, N, K, 1, GEPI_STORE, &sp);
+}
+
 void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int* sk_per) {
     g_plan_sms = sms;
     const int mt = (M + BM - 1) / BM;
     *bn = pick_bn(mt, N, batch);
     *sk_per = 0;
+    SplitPlan sp;
+    if (N % 32 == 0 && splitk_wins(M, N, K, batch, GEPI_STORE, &sp)) {
+        *kind = 3;                        // 3: cluster split-K, sk_per = CTAs per tile
+        *bn = sp.bn;
+        *sk_per = sp.ks;
+        g_plan_sms = 0;
+        return;
+    }
     *kind = (M > BM && N % 32 == 0 && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, *bn, K)) ? 1 : 0;
     if (*kind == 1) {                     // 1: 256-row pair tiles, 2: 512-row pair tiles
         const PairPlan pl = pair_plan(M, (long long)((N + 255) / 256) * batch, (K + BK - 1) / BK, GEPI_STORE);
@@ -970,7 +1234,7 @@ bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size
 }
 
 int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, int N, int K, long long lda,
-                 long long ldb, long long ldc, long long sA, long long sB, long long sC, cudaStream_t st) {
+                 long long ldb, long long ldc, long long sA, long long sB, long long sC, cudaStream_t st, bool weights_constant) {
     TL_REQUIRE(hgemm_supported(A, B, C, M, N, K, lda, ldb, ldc), "hgemm: unsupported shape or alignment");
     TL_REQUIRE(sA % 8 == 0 && sB % 8 == 0, "hgemm: batch strides must be multiples of 8 elements");
     if (batch <= 0) return TL_OK;
@@ -979,10 +1243,16 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = batch; a.ldc = ldc; a.sC = sC;
     a.a_batched = (sA != 0 && batch > 1) ? 1 : 0; a.b_batched = (sB != 0 && batch > 1) ? 1 : 0;
+    a.b_const = weights_constant ? 1 : 0;
     a.status = device_status_word();
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
     const bool vec_c = ldc % 8 == 0 && sC % 8 == 0 && al16(C) && N % 32 == 0;   // the pair epilogue stores 64-byte chunks
+    SplitPlan sp;
+    if (vec_c && splitk_wins(M, N, K, batch, GEPI_STORE, &sp)) {
+        TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, sp.bn));
+        return launch_splitk<GEPI_STORE>(sp.bn, sp.ks, ma, mb, a, mt * ((N + sp.bn - 1) / sp.bn), st);
+    }
     if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, 128));
         return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, (N + 255) / 256, st);
@@ -1031,7 +1301,7 @@ bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M
 
 // C = half(A B^T) + R
 int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __half* C, int M, int N, int K,
-                          long long lda, long long ldb, long long ldr, long long ldc, cudaStream_t st) {
+                          long long lda, long long ldb, long long ldr, long long ldc, cudaStream_t st, bool weights_constant) {
     TL_REQUIRE(hgemm_fused_supported(A, B, C, M, N, K, lda, ldb, ldc) && R && al16(R) && ldr % 8 == 0,
                "hgemm+residual: unsupported shape or alignment");
     const int mt = (M + BM - 1) / BM;
@@ -1040,7 +1310,12 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
-    a.R = R; a.ldr = ldr;
+    a.R = R; a.ldr = ldr; a.b_const = weights_constant ? 1 : 0;
+    SplitPlan sp;
+    if (splitk_wins(M, N, K, 1, GEPI_RESIDUAL, &sp)) {
+        TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, sp.bn));
+        return launch_splitk<GEPI_RESIDUAL>(sp.bn, sp.ks, ma, mb, a, mt * ((N + sp.bn - 1) / sp.bn), st);
+    }
     if (M > BM && pair_cost(M, (N + 255) / 256, 1, K, GEPI_RESIDUAL) < single_cost(mt, N, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
         return launch_pair<GEPI_RESIDUAL>(ma, mb, mb, mb, a, (N + 255) / 256, st);

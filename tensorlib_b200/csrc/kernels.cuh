@@ -175,9 +175,14 @@ bool tensor_map_encode_available();
 // ---- hgemm_sm100.cu: prefill HGEMM on tcgen05 / TMEM / TMA -----------------------------------------
 bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K,
                      size_t lda, size_t ldb, size_t ldc);
+// true when the cluster split-K HGEMM has a plan for this shape (few tiles, long K): callers prefer it to the
+// skinny kernel for 9..128 rows
+bool hgemm_splitk_preferred(int M, int N, int K);
+// weights_constant: B is never written by another kernel of the stream (a model weight), so a kernel may
+// request its first tiles before the programmatic-dependency wait
 int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, int N, int K,
                  long long lda, long long ldb, long long ldc, long long sA, long long sB,
-                 long long sC, cudaStream_t st);
+                 long long sC, cudaStream_t st, bool weights_constant = false);
 
 // K-split matmul of the tensor-parallel prefill: C[M, N] is this rank's partial result, stored locally; the rank
 // that owns rows [o * rows_per_owner, (o + 1) * rows_per_owner) is told when it may fetch them: after a 128-row x
@@ -227,7 +232,8 @@ void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int
 bool hgemm_fused_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
                            size_t ldb, size_t ldc);
 int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __half* C, int M, int N, int K,
-                          long long lda, long long ldb, long long ldr, long long ldc, cudaStream_t st);
+                          long long lda, long long ldb, long long ldr, long long ldc, cudaStream_t st,
+                          bool weights_constant = false);
 int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __half* C, int M, int N, int K,
                         long long lda, long long ldb, long long ldc, cudaStream_t st);
 int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, const __half* Wv, __half* q_out,

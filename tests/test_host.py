@@ -124,22 +124,30 @@ def test_matmul_plan_picks_the_kernel_each_regime_is_built_for():
                                                   "k_blocks_per_cta": 0, "cluster": 0}, M
     assert tl.matmul_plan(8, 64, 4096)["grid"] == 4                             # 32 units, 8 per CTA at least
     assert tl.matmul_plan(5, 1001, 4096)["kernel"].startswith("skinny")         # odd N: not on the ring
-    for M in (9, 32, 128):                                                      # weights streamed once
+    for M in (9, 32):                                                           # weights streamed once
         assert tl.matmul_plan(M, 11008, 4096)["kernel"].startswith("skinny"), M
+    assert tl.matmul_plan(128, 32000, 4096)["kernel"].startswith("skinny")      # enough tiles for every SM: no K split
     assert tl.matmul_plan(32, 11008, 4096)["grid"] == 145                       # stream-K ranges
-    assert tl.matmul_plan(128, 11008, 4096)["grid"] == 86                       # whole tiles: no partial-tile exchange
     assert tl.matmul_plan(32, 4096, 4096) == {"kernel": "skinny_cluster", "grid": 128, "tile_n": 32,
                                               "k_blocks_per_cta": 16, "cluster": 4}
-    assert tl.matmul_plan(512, 4096, 4096)["kernel"] == "hgemm"
+    # 33..512 rows against few column tiles: one 128-row tile per cluster, K split over its CTAs
+    assert tl.matmul_plan(128, 4096, 4096) == {"kernel": "hgemm_splitk", "grid": 128, "tile_n": 128,
+                                               "k_blocks_per_cta": 16, "cluster": 4}
+    assert tl.matmul_plan(128, 11008, 4096) == {"kernel": "hgemm_splitk", "grid": 86, "tile_n": 256,
+                                                "k_blocks_per_cta": 32, "cluster": 2}
+    assert tl.matmul_plan(512, 4096, 4096) == {"kernel": "hgemm_splitk", "grid": 128, "tile_n": 256,
+                                               "k_blocks_per_cta": 32, "cluster": 2}
+    assert tl.matmul_plan(512, 4096, 11008)["kernel"] == "hgemm_splitk"
+    assert tl.matmul_plan(512, 11008, 4096)["kernel"] == "hgemm_pair512"        # 172 tiles of 128 rows: too many to split
     # prefill shapes: CTA pairs, 512-row tiles where they fill the 74 pairs at least as well as 256-row ones
     for N, K, kernel, grid in ((4096, 4096, "hgemm_pair512", 128), (11008, 4096, "hgemm_pair", 148),
                                (4096, 11008, "hgemm_pair512", 128), (32000, 4096, "hgemm_pair512", 148)):
         p = tl.matmul_plan(2048, N, K)
         assert p["kernel"] == kernel and p["grid"] == grid and p["cluster"] == 2, (N, K, p)
-    # long K with few tiles: stream-K ranges over all CTA pairs instead of 4 whole tiles on 4 pairs
+    # long K with few tiles: 16 tiles of 128 x 128, each split over a cluster of 4
     p = tl.matmul_plan(512, 512, 32768)
-    assert p == {"kernel": "hgemm_pair", "grid": 148, "tile_n": 256, "k_blocks_per_cta": 28, "cluster": 2}, p
-    assert 74 * p["k_blocks_per_cta"] >= 4 * 512 > 73 * p["k_blocks_per_cta"]    # the ranges cover every k-block, none empty
+    assert p == {"kernel": "hgemm_splitk", "grid": 64, "tile_n": 128, "k_blocks_per_cta": 128, "cluster": 4}, p
+    assert p["cluster"] * p["k_blocks_per_cta"] >= 512                           # the CTAs of a cluster cover every k-block
     assert tl.matmul_plan(2048, 4096, 4096)["k_blocks_per_cta"] == 0             # the Llama shapes keep whole tiles
     assert tl.matmul_plan(3, 1000, 300)["kernel"] == "reference_order"          # K % 8 != 0: any-shape kernel
     with pytest.raises(tl.TLError):
@@ -155,6 +163,12 @@ def test_skinny_split_covers_every_k_block_exactly_once(sms):
     for M, N, K in ((2, 127, 64), (9, 4096, 4096), (32, 11008, 4096), (128, 4096, 11008), (100, 32000, 4096),
                     (5, 513, 1032), (64, 127, 8), (17, 9472, 520), (128, 8192, 512)):
         p = tl.matmul_plan(M, N, K, sms)
+        if p["kernel"] == "hgemm_splitk":       # 33..128 rows, few tiles: K split inside a cluster (rank r: k-blocks [nkb r / s, nkb (r + 1) / s))
+            sp, nkb = p["cluster"], -(-K // 64)
+            assert sp in (2, 4) and p["grid"] == -(-M // 128) * -(-N // p["tile_n"]) * sp <= sms
+            cuts = [nkb * r // sp for r in range(sp + 1)]
+            assert cuts[0] == 0 and cuts[-1] == nkb and all(0 < b - a <= p["k_blocks_per_cta"] for a, b in zip(cuts, cuts[1:]))
+            continue
         assert p["kernel"].startswith("skinny")
         tiles, nkb, per = -(-N // 128), -(-K // 64), p["k_blocks_per_cta"]
         assert p["tile_n"] in (32, 64, 128) and p["tile_n"] >= M and per >= 1
