@@ -338,36 +338,41 @@ k_hgemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtenso
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
 
-// ---- K split inside a cluster: KS CTAs share one 128 x BN output tile ----------------------------------
-// Few output tiles and a long K (M <= 512 against the 7B weights, or any M <= 128): whole tiles leave most
-// SMs idle, and splitting K through global memory costs a round trip of fp32 partial tiles plus a counter.
-// Here the KS CTAs of a cluster each run the TMA -> tcgen05 pipeline over their K / KS share of the SAME
-// tile (accumulator in their own TMEM) and then exchange partial sums over distributed shared memory as a
-// reduce-scatter: CTA r finishes columns [r BN/KS, (r+1) BN/KS) of the tile, every other CTA writes its
-// fp32 partial of those columns into r's receive area (st.shared::cluster, a warp writes 512 contiguous
-// bytes) and arrives on r's mbarrier (release at cluster scope); r adds the parts in rank order, converts
-// and stores. No workspace, no atomics, the order of the additions is fixed, and the epilogue itself is
-// spread over all KS CTAs. One tile per cluster (the launcher uses it only when tiles x KS fits the SMs).
-template <int BN, int KS>
+// ---- one tile per cluster, K split over its CTAs ---------------------------------------------------------
+// Few output tiles and a long K (M <= 512 against the 7B weights, or any M <= 128): whole tiles on a persistent
+// grid leave most SMs idle, and splitting K through global memory costs a round trip of fp32 partial tiles plus
+// a counter. Here the KS CTAs of a cluster each run the TMA -> tcgen05 pipeline over their K / KS share of the
+// SAME (128 MSUB) x BN tile (accumulators in their own TMEM) and then exchange partial sums over distributed
+// shared memory as a reduce-scatter: CTA r finishes columns [r BN/KS, (r+1) BN/KS) of the tile, every other CTA
+// writes its fp32 partial of those columns into r's pipeline stages, idle by then (st.shared::cluster, a warp
+// writes 512 contiguous bytes) and arrives on r's mbarrier (release at cluster scope); r adds the parts in rank
+// order, converts and stores. No workspace, no atomics, the order of the additions is fixed, and the epilogue
+// itself is spread over all KS CTAs. MSUB = 2 gives one CTA a 256 x 256 tile (two 128-row A boxes against one
+// B box, all 512 TMEM columns): 64 KB of shared-memory fill per 1024 MMA cycles instead of 48 KB per 512, which
+// takes a single CTA off the fill limit; with KS = 1 that is a plain one-wave kernel for shapes of up to one
+// 256 x 256 tile per SM. The launcher uses the family only when tiles x KS fits the SMs.
+template <int BN, int KS, int MSUB>
 struct SplitCfg {
     static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = MSUB * A_BYTES + B_BYTES;
     static constexpr int SLICE = BN / KS;                               // output columns one CTA finishes
-    static constexpr int PART_BYTES = BM * SLICE * 4;                   // one sender's partial of my slice
+    static constexpr int PART_BYTES = MSUB * BM * SLICE * 4;            // one sender's partial of my slice
     static constexpr int RECV_BYTES = (KS - 1) * PART_BYTES;            // received over the pipeline stages, once they are idle
     static constexpr int NST = (216 * 1024) / STAGE_BYTES > 8 ? 8 : (216 * 1024) / STAGE_BYTES;
     static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 1024 + 256;
+    static constexpr uint32_t TMEM_COLS = MSUB * BN;
     static_assert(SLICE % 32 == 0 && NST >= 2 && RECV_BYTES <= NST * STAGE_BYTES, "slice of whole 32-column chunks; the parts fit the stages");
+    static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "tensor-memory columns: a power of two");
 };
 
-template <int BN, int KS, int EPI>
+template <int BN, int KS, int MSUB, int EPI>
 __global__ void __cluster_dims__(KS, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
-    using Cfg = SplitCfg<BN, KS>;
+    using Cfg = SplitCfg<BN, KS, MSUB>;
     constexpr int NST = Cfg::NST, STAGE_BYTES = Cfg::STAGE_BYTES, SLICE = Cfg::SLICE;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* recv = smem;                                          // [sender slot][column / 4][row][4 floats], over the idle stages
+    unsigned char* recv = smem;                                          // [sender slot][sub-tile][column / 4][row][4 floats], over the idle stages
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NST * STAGE_BYTES);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NST);
     const uint32_t tfull = smem_u32(bars + 2 * NST), recv_full = smem_u32(bars + 2 * NST + 1), peers_idle = smem_u32(bars + 2 * NST + 2);
@@ -375,9 +380,9 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rank = (int)cluster_ctarank();
+    const int rank = KS > 1 ? (int)cluster_ctarank() : 0;
     const int tile = blockIdx.x / KS;
-    const int mt_count = (p.M + BM - 1) / BM;
+    const int mt_count = (p.M + MSUB * BM - 1) / (MSUB * BM);
     const int mt = tile % mt_count, nt = tile / mt_count;
     const int nkb = (p.K + BK - 1) / BK;
     const int kb0 = (int)((long long)nkb * rank / KS), kb1 = (int)((long long)nkb * (rank + 1) / KS);
@@ -385,17 +390,17 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NST; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tfull, 1);
-        mbar_init(recv_full, (KS - 1) * 128);        // every epilogue thread of every other CTA arrives once
-        mbar_init(peers_idle, KS - 1);               // one thread of every other CTA, when its stages are idle
+        mbar_init(recv_full, KS > 1 ? (KS - 1) * 128 : 1);   // every epilogue thread of every other CTA arrives once
+        mbar_init(peers_idle, KS > 1 ? KS - 1 : 1);          // one thread of every other CTA, when its stages are idle
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 2) tmem_alloc<(uint32_t)BN>(tmem_slot);
+    if (warp == 2) tmem_alloc<Cfg::TMEM_COLS>(tmem_slot);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    cluster_sync_all();                              // nobody arrives on a barrier that is not initialised yet
+    if (KS > 1) cluster_sync_all();                  // nobody arrives on a barrier that is not initialised yet
     pdl_launch_dependents();
 
     if (warp == 0 && lane == 0) {
@@ -407,7 +412,7 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int early = p.b_const ? min(NST, kb1 - kb0) : 0;
         for (int it = 0; it < early; it++) {
             mbar_arrive_expect_tx(full0 + 8 * it, STAGE_BYTES);
-            tma_load_3d(smem_u32(smem + it * STAGE_BYTES) + A_BYTES, &tmB, (kb0 + it) * BK, nt * BN, 0, full0 + 8 * it);
+            tma_load_3d(smem_u32(smem + it * STAGE_BYTES) + MSUB * A_BYTES, &tmB, (kb0 + it) * BK, nt * BN, 0, full0 + 8 * it);
         }
         pdl_wait();
         bool ok = true;
@@ -415,9 +420,11 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; kb++, it++) {
             const int s = it % NST, use = it / NST;
             if (use > 0 && !(ok = mbar_wait(empty0 + 8 * s, (use - 1) & 1, abort_flag))) break;
-            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + MSUB * A_BYTES;
             if (it >= early) mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_3d(sa, &tmA, kb * BK, mt * BM, 0, full0 + 8 * s);
+#pragma unroll
+            for (int ms = 0; ms < MSUB; ms++)       // rows beyond M read as zero
+                tma_load_3d(sa + ms * A_BYTES, &tmA, kb * BK, (mt * MSUB + ms) * BM, 0, full0 + 8 * s);
             if (it >= early) tma_load_3d(sb, &tmB, kb * BK, nt * BN, 0, full0 + 8 * s);
         }
         if (!ok) {  // let copies already in flight land before the CTA goes away
@@ -435,22 +442,25 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int s = it % NST, use_s = it / NST;
             if (!(ok = mbar_wait(full0 + 8 * s, use_s & 1, abort_flag))) break;
             tc_fence_after();
-            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + MSUB * A_BYTES;
 #pragma unroll
             for (int k = 0; k < BK / 16; k++)
-                umma(tmem_base, make_desc(sa + k * 32), make_desc(sb + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int ms = 0; ms < MSUB; ms++)
+                    umma(tmem_base + (uint32_t)(ms * BN), make_desc(sa + ms * A_BYTES + k * 32), make_desc(sb + k * 32), idesc,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
             umma_commit(empty0 + 8 * s);
         }
         if (ok) umma_commit(tfull);
     } else if (warp >= 4) {
         // ---------------- epilogue: send the foreign slices, finish the own one -------------------------
         pdl_wait();
-        const int q = warp & 3, rl = q * 32 + lane;                       // row of the tile = TMEM lane
+        const int q = warp & 3, rl = q * 32 + lane;                       // row of a sub-tile = TMEM lane
         bool ok = mbar_wait(tfull, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16);
-        if (ok) {
+        if (KS > 1 && ok) {
             // all my MMAs are done, so my stages are idle: the other CTAs may write their parts over them
             if (warp == 4 && lane == 0) {
 #pragma unroll 1
@@ -460,21 +470,24 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ok = mbar_wait_cluster(peers_idle, 0, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (ok) {
+        if (KS > 1 && ok) {
 #pragma unroll 1
             for (int o = 0; o < KS; o++) {
                 if (o == rank) continue;
                 const int slot = rank < o ? rank : rank - 1;              // senders in rank order, the owner left out
                 const uint32_t dst = map_to_cta(smem_u32(recv), (uint32_t)o) + (uint32_t)(slot * Cfg::PART_BYTES + rl * 16);
 #pragma unroll 1
-                for (int c = 0; c < SLICE; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tbase + (uint32_t)(o * SLICE + c), r);
-                    tmem_ld_wait();
+                for (int ms = 0; ms < MSUB; ms++) {
+#pragma unroll 1
+                    for (int c = 0; c < SLICE; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tbase + (uint32_t)(ms * BN + o * SLICE + c), r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int v = 0; v < 8; v++)
-                        st_cluster_f4(dst + (uint32_t)((c / 4 + v) * BM * 16), __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                        for (int v = 0; v < 8; v++)
+                            st_cluster_f4(dst + (uint32_t)(((ms * SLICE + c) / 4 + v) * BM * 16), __uint_as_float(r[4 * v]),
+                                          __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
                 }
                 mbar_arrive_cluster(map_to_cta(recv_full, (uint32_t)o));
             }
@@ -482,37 +495,42 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
-            const int row = mt * BM + rl;
-            __half* crow = p.C + (long long)row * p.ldc;
             const float4* mine = reinterpret_cast<const float4*>(recv) + rl;
 #pragma unroll 1
-            for (int c = 0; c < SLICE; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tbase + (uint32_t)(rank * SLICE + c), r);
-                tmem_ld_wait();
-                float acc[32];
+            for (int ms = 0; ms < MSUB; ms++) {
+                const int row = (mt * MSUB + ms) * BM + rl;
+                __half* crow = p.C + (long long)row * p.ldc;
+#pragma unroll 1
+                for (int c = 0; c < SLICE; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tbase + (uint32_t)(ms * BN + rank * SLICE + c), r);
+                    tmem_ld_wait();
+                    if (KS > 1) {
+                        float acc[32];
 #pragma unroll
-                for (int i = 0; i < 32; i++) acc[i] = 0.f;
+                        for (int i = 0; i < 32; i++) acc[i] = 0.f;
 #pragma unroll
-                for (int s = 0; s < KS; s++) {                            // parts in k order = rank order
-                    if (s == rank) {
+                        for (int s = 0; s < KS; s++) {                    // parts in k order = rank order
+                            if (s == rank) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) acc[i] += __uint_as_float(r[i]);
-                    } else {
-                        const float4* src = mine + (size_t)(s < rank ? s : s - 1) * (Cfg::PART_BYTES / 16) + (size_t)(c / 4) * BM;
+                                for (int i = 0; i < 32; i++) acc[i] += __uint_as_float(r[i]);
+                            } else {
+                                const float4* src = mine + (size_t)(s < rank ? s : s - 1) * (Cfg::PART_BYTES / 16) + (size_t)((ms * SLICE + c) / 4) * BM;
 #pragma unroll
-                        for (int v = 0; v < 8; v++) {
-                            const float4 f = src[(size_t)v * BM];
-                            acc[4 * v] += f.x; acc[4 * v + 1] += f.y; acc[4 * v + 2] += f.z; acc[4 * v + 3] += f.w;
+                                for (int v = 0; v < 8; v++) {
+                                    const float4 f = src[(size_t)v * BM];
+                                    acc[4 * v] += f.x; acc[4 * v + 1] += f.y; acc[4 * v + 2] += f.z; acc[4 * v + 3] += f.w;
+                                }
+                            }
                         }
-                    }
-                }
-                const int col0 = nt * BN + rank * SLICE + c;
-                if (row >= p.M || col0 >= p.N) continue;
 #pragma unroll
-                for (int i = 0; i < 32; i++) r[i] = __float_as_uint(acc[i]);
-                if (EPI == GEPI_RESIDUAL) store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
-                else store32(crow + col0, r);
+                        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(acc[i]);
+                    }
+                    const int col0 = nt * BN + rank * SLICE + c;
+                    if (row >= p.M || col0 >= p.N) continue;
+                    if (EPI == GEPI_RESIDUAL) store32_residual(crow + col0, p.R + (long long)row * p.ldr + col0, r);
+                    else store32(crow + col0, r);
+                }
             }
         }
     }
@@ -520,10 +538,10 @@ k_hgemm_splitk(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_before();
     __syncthreads();
     __syncwarp();
-    cluster_sync_all();
+    if (KS > 1) cluster_sync_all();
     if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc<(uint32_t)BN>(tmem_base);
+        tmem_dealloc<Cfg::TMEM_COLS>(tmem_base);
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TL_ERR_TIMEOUT);
 }
@@ -985,20 +1003,22 @@ int launch_any_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CU
     return launch_k<64, EPI>(ma, mb, mb2, mb3, a, tiles, st);
 }
 
-template <int BN, int KS, int EPI>
+template <int BN, int KS, int MSUB, int EPI>
 int launch_splitk_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {
     static PerDeviceOnce once;
     if (once.needed()) {
-        TL_CUDA(cudaFuncSetAttribute(k_hgemm_splitk<BN, KS, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SplitCfg<BN, KS>::SMEM));
+        TL_CUDA(cudaFuncSetAttribute(k_hgemm_splitk<BN, KS, MSUB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SplitCfg<BN, KS, MSUB>::SMEM));
     }
-    return launch_pdl(k_hgemm_splitk<BN, KS, EPI>, dim3(tiles * KS), dim3(GEMM_THREADS), SplitCfg<BN, KS>::SMEM, st, true, ma, mb, a);
+    return launch_pdl(k_hgemm_splitk<BN, KS, MSUB, EPI>, dim3(tiles * KS), dim3(GEMM_THREADS), SplitCfg<BN, KS, MSUB>::SMEM, st, true, ma, mb, a);
 }
 template <int EPI>
-int launch_splitk(int bn, int ks, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {
-    if (bn == 128 && ks == 4) return launch_splitk_cfg<128, 4, EPI>(ma, mb, a, tiles, st);
-    if (bn == 128 && ks == 2) return launch_splitk_cfg<128, 2, EPI>(ma, mb, a, tiles, st);
-    if (bn == 256 && ks == 2) return launch_splitk_cfg<256, 2, EPI>(ma, mb, a, tiles, st);
-    TL_REQUIRE(false, "hgemm split-K: no kernel for tile width %d split %d", bn, ks);
+int launch_splitk(int bn, int ks, int msub, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& a, int tiles, cudaStream_t st) {
+    if (msub == 1) {
+        if (bn == 128 && ks == 4) return launch_splitk_cfg<128, 4, 1, EPI>(ma, mb, a, tiles, st);
+        if (bn == 128 && ks == 2) return launch_splitk_cfg<128, 2, 1, EPI>(ma, mb, a, tiles, st);
+        if (bn == 256 && ks == 2) return launch_splitk_cfg<256, 2, 1, EPI>(ma, mb, a, tiles, st);
+    }
+    TL_REQUIRE(false, "hgemm split-K: no kernel for tile %d x %d, split %d", 128 * msub, bn, ks);
     return TL_ERR_UNSUPPORTED;
 }
 
@@ -1136,11 +1156,12 @@ long long single_cost(int mt, int N, int batch, int bn, int K) {
     return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64) * ((K + BK - 1) / BK);
 }
 
-// Estimated plan of the cluster split-K kernel (one 128 x bn tile per cluster of ks CTAs): only where every
-// cluster is resident at once; cost = k-blocks per CTA x the single-CTA cost of a k-block + the exchange of the
-// partial slices over distributed shared memory and the two cluster barriers (~3000 cycles).
+// Estimated plan of the one-tile-per-cluster kernel ((128 msub) x bn tile, K split over ks CTAs): only where
+// every cluster is resident at once; cost = k-blocks per CTA x the cost of a k-block (the larger of MMA time and
+// shared-memory fill, as for the single-CTA kernel; the 256 x 256 tile is MMA-bound at 1024 cycles) + the exchange
+// of the partial slices over distributed shared memory and the cluster barriers + the unhidden epilogue.
 // TL_HGEMM_SPLITK=never|always overrides the comparison with the other kernels.
-struct SplitPlan { int bn, ks; long long cost; };
+struct SplitPlan { int bn, ks, msub; long long cost; };
 int splitk_forced() {
     static const int forced = [] {
         const char* e = getenv("TL_HGEMM_SPLITK");
@@ -1150,17 +1171,20 @@ int splitk_forced() {
     return forced;
 }
 SplitPlan splitk_plan(int M, int N, int K, int batch) {
-    SplitPlan best{0, 0, -1};
+    SplitPlan best{0, 0, 0, -1};
     if (batch != 1 || splitk_forced() == 2 || N % 32 != 0) return best;
-    const int mt = (M + BM - 1) / BM, nkb = (K + BK - 1) / BK;
-    static const int cand[3][2] = {{128, 4}, {128, 2}, {256, 2}};
+    const int nkb = (K + BK - 1) / BK;
+    // (the 256 x 256 tile per CTA, msub = 2, measured slower: 28.3 us against 20.1 us at M = 512, 4096 x 4096 with the
+    // split 4 against 128 x 256 tiles with the split 2 - the exchange moves 192 KB per CTA through four epilogue warps)
+    static const int cand[3][3] = {{128, 4, 1}, {128, 2, 1}, {256, 2, 1}};
     for (const auto& c : cand) {
-        const int bn = c[0], ks = c[1];
-        const long long tiles = (long long)mt * ((N + bn - 1) / bn);
+        const int bn = c[0], ks = c[1], msub = c[2];
+        if (msub == 2 && M <= BM) continue;
+        const long long tiles = (long long)((M + BM * msub - 1) / (BM * msub)) * ((N + bn - 1) / bn);
         if (tiles * ks > plan_sms() || nkb / ks < 4) continue;
-        const long long per_kb = std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
-        const long long cost = (long long)((nkb + ks - 1) / ks) * per_kb + 3000;
-        if (best.cost < 0 || cost < best.cost) best = SplitPlan{bn, ks, cost};
+        const long long per_kb = msub == 2 ? 1040 : std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
+        const long long cost = (long long)((nkb + ks - 1) / ks) * per_kb + (ks > 1 ? 3000 * msub : 0) + 1500 * msub;
+        if (best.cost < 0 || cost < best.cost) best = SplitPlan{bn, ks, msub, cost};
     }
     return best;
 }
@@ -1173,8 +1197,9 @@ bool splitk_wins(int M, int N, int K, int batch, int epi, SplitPlan* out) {
     if (sp.cost < 0) return false;
     if (splitk_forced() == 1) return true;
     const int mt = (M + BM - 1) / BM;
-    if (sp.cost >= single_cost(mt, N, batch, pick_bn(mt, N, batch), K)) return false;
-    return M <= BM || sp.cost < pair_cost(M, (N + 255) / 256, batch, K, epi);
+    // the whole-tile estimates leave out their last tile's epilogue: ask for a clear margin before displacing them
+    if (sp.cost * 10 >= single_cost(mt, N, batch, pick_bn(mt, N, batch), K) * 9) return false;
+    return M <= BM || sp.cost * 10 < pair_cost(M, (N + 255) / 256, batch, K, epi) * 9;
 }
 
 // N-tile width with the smallest estimated time: waves of tiles over the SMs times the cost of one
@@ -1211,7 +1236,7 @@ void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int
     *sk_per = 0;
     SplitPlan sp;
     if (N % 32 == 0 && splitk_wins(M, N, K, batch, GEPI_STORE, &sp)) {
-        *kind = 3;                        // 3: cluster split-K, sk_per = CTAs per tile
+        *kind = sp.msub == 2 ? 4 : 3;     // one tile per cluster, 128 (3) or 256 (4) rows; sk_per = CTAs sharing the tile's K
         *bn = sp.bn;
         *sk_per = sp.ks;
         g_plan_sms = 0;
@@ -1251,7 +1276,7 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     SplitPlan sp;
     if (vec_c && splitk_wins(M, N, K, batch, GEPI_STORE, &sp)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, sp.bn));
-        return launch_splitk<GEPI_STORE>(sp.bn, sp.ks, ma, mb, a, mt * ((N + sp.bn - 1) / sp.bn), st);
+        return launch_splitk<GEPI_STORE>(sp.bn, sp.ks, sp.msub, ma, mb, a, ((M + BM * sp.msub - 1) / (BM * sp.msub)) * ((N + sp.bn - 1) / sp.bn), st);
     }
     if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, 128));
@@ -1314,7 +1339,7 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     SplitPlan sp;
     if (splitk_wins(M, N, K, 1, GEPI_RESIDUAL, &sp)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, sp.bn));
-        return launch_splitk<GEPI_RESIDUAL>(sp.bn, sp.ks, ma, mb, a, mt * ((N + sp.bn - 1) / sp.bn), st);
+        return launch_splitk<GEPI_RESIDUAL>(sp.bn, sp.ks, sp.msub, ma, mb, a, ((M + BM * sp.msub - 1) / (BM * sp.msub)) * ((N + sp.bn - 1) / sp.bn), st);
     }
     if (M > BM && pair_cost(M, (N + 255) / 256, 1, K, GEPI_RESIDUAL) < single_cost(mt, N, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
