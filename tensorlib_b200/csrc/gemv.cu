@@ -298,6 +298,36 @@ __device__ __forceinline__ void exchange_reduce_slice(const RingArgs& p, unsigne
         st_words2(e.local_pub + 4 * c + 2, out.z, out.w, epoch);
     }
 }
+// direct form: this thread sums group c (8 elements) of every rank's slot itself; the CTA whose slice holds c also
+// writes the sum to sum_out
+__device__ __forceinline__ uint4 exchange_reduce_group(const RingArgs& p, unsigned int epoch, int c, int g_begin, int g_end) {
+    const PeerExchange& e = p.xin;
+    float s[8];
+    bool all_here = false;
+    for (uint32_t tries = 0; tries < p.xin_tries && !all_here; tries++) {
+        all_here = true;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s[i] = 0.f;
+        for (int r = 0; r < e.world; r++) {
+            const unsigned long long* src = e.local_slots + (size_t)r * e.n + 8 * c;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const uint4 w = ld_words2(src + 2 * q);
+                s[2 * q] += __uint_as_float(w.x);
+                s[2 * q + 1] += __uint_as_float(w.z);
+                all_here &= (w.y == epoch) & (w.w == epoch);
+            }
+        }
+    }
+    if (!all_here) atomicExch(p.status, TL_ERR_TIMEOUT);
+    uint4 res = __ldcg(reinterpret_cast<const uint4*>(e.residual) + c), out;
+    const __half* rh = reinterpret_cast<const __half*>(&res);
+    __half* oh = reinterpret_cast<__half*>(&out);
+#pragma unroll
+    for (int i = 0; i < 8; i++) oh[i] = hadd_ref(rh[i], __float2half_rn(s[i]));
+    if (e.sum_out && c >= g_begin && c < g_end) reinterpret_cast<uint4*>(e.sum_out)[c] = out;
+    return out;
+}
 __device__ __forceinline__ uint4 exchange_gather_group(const RingArgs& p, unsigned int epoch, int c) {
     const unsigned long long* src = p.xin.local_pub + 4 * c;
     uint4 lo, hi;
@@ -336,9 +366,14 @@ __device__ __forceinline__ bool ring_consume(const RingArgs& p, const RingSmem& 
     float rinv = 1.0f;
     const unsigned int xin_epoch = p.has_xin ? exchange_epoch(p.xin) : 0u;
     const unsigned int xout_epoch = (EPI == EPI_PUSH_F32 || EPI == EPI_PUSH_F16) ? exchange_epoch(p.xout) : 0u;
-    if (p.has_xin) exchange_reduce_slice<CW>(p, xin_epoch, ctid);
+    const bool xin_direct = p.has_xin && p.xin.direct;
+    if (p.has_xin && !xin_direct) exchange_reduce_slice<CW>(p, xin_epoch, ctid);
+    const int xg_begin = (int)((long long)K8 * blockIdx.x / gridDim.x), xg_end = (int)((long long)K8 * (blockIdx.x + 1) / gridDim.x);
     // one 16-byte group of the activation vector (plain, or reduced over the ranks)
-    auto load_x = [&](int c) -> uint4 { return p.has_xin ? exchange_gather_group(p, xin_epoch, c) : x4[c]; };
+    auto load_x = [&](int c) -> uint4 {
+        if (!p.has_xin) return x4[c];
+        return xin_direct ? exchange_reduce_group(p, xin_epoch, c, xg_begin, xg_end) : exchange_gather_group(p, xin_epoch, c);
+    };
     if (NORM) {
         // RMSNorm in one pass: the staged vector is x * w (fp16); the scalar 1/rms multiplies the
         // finished dot products instead (sum_k rinv*x_k*w_k*W_nk = rinv * sum_k (x_k*w_k)*W_nk), so

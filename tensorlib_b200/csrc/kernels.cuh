@@ -106,6 +106,9 @@ struct PeerExchange {
     int phases_per_step, phase_id;               // epoch = *step_ptr * phases_per_step + phase_id + 1
     // consumer extras
     const __half* residual; __half* sum_out;     // x = residual + sum; CTA 0 also writes it to sum_out
+    // 1: every CTA sums the ranks' slots itself (world x n words of L2 reads per CTA, no publish / gather hop);
+    // 0: CTA c sums slice c and publishes it, every CTA gathers the published vector (one more on-chip hop, n / 2 words per CTA)
+    int direct;
 };
 struct FusedGemv {
     // input vector (M = 1) and optional RMSNorm prologue
