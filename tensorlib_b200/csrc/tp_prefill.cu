@@ -5,7 +5,7 @@
 // Token rows are dealt out in contiguous slices, one per rank (the owner of a row). The matmul
 // (hgemm_sm100.cu, push mode) keeps its partial result in its own memory and raises a flag in the
 // OWNER's memory for every finished (128-row block, column tile) while its other tiles are still
-// being computed. k_tp_reduce_norm below runs on the owner, one warp per row: it waits for the flags
+// being computed. k_tp_reduce_norm below runs on the owner, four warps per row: it waits for the flags
 // of its row block from every source rank, fetches the partial rows from the sources' memory with
 // plain peer loads (a warp reads 512 contiguous bytes: the reduce-scatter), adds them in rank order
 // in fp32, rounds once, adds the residual in fp16 (the arithmetic of the single-GPU path up to the
@@ -23,10 +23,9 @@ namespace tlb {
 
 namespace {
 
-#ifndef TL_RN_THREADS
-#define TL_RN_THREADS 256
-#endif
-constexpr int RN_THREADS = TL_RN_THREADS;     // one row per warp
+constexpr int RN_ROW_THREADS = 128;                // four warps share a row
+constexpr int RN_ROWS = 2;                         // rows per CTA
+constexpr int RN_THREADS = RN_ROW_THREADS * RN_ROWS;
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     unsigned int v;
@@ -34,104 +33,126 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     return v;
 }
 
+// barrier among the four warps of row `rsub` of the CTA (named barriers 1, 2; 0 is __syncthreads)
+__device__ __forceinline__ void row_bar_sync(int rsub) {
+    asm volatile("bar.sync %0, %1;" ::"r"(rsub + 1), "n"(RN_ROW_THREADS) : "memory");
+}
 __device__ __forceinline__ uint4 ld_peer16(const uint4* ptr) {
     uint4 v;     // relaxed system-scope load: straight from the source rank's memory, never a stale local cache line
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
     return v;
 }
 
-// One WARP per row (no CTA barrier anywhere on the chain flag -> loads -> sum -> stores -> fence: with one row
-// per 256-thread CTA the kernel measured 30 us for 1024 rows on local memory alone, all of it barrier, fence and
-// load latency at 23 % of the warp slots). W = number of ranks and GPL = 16-byte groups per lane are compile-time
-// constants, so the loads of every source are in flight together and the row stays in registers for the norm.
-template <int W, int GPL>
-__global__ void __launch_bounds__(RN_THREADS, 512 / RN_THREADS) k_tp_reduce_norm(TpReduceNorm p, int* status) {
-    constexpr int CH = W <= 2 ? 4 : (W <= 4 ? 2 : 1);     // groups per lane whose loads are issued together
-    const int lane = threadIdx.x & 31;
-    const int r = blockIdx.x * (RN_THREADS / 32) + (threadIdx.x >> 5);    // row of this rank's slice
+// Four warps per row, two rows per CTA. Everything on a row's chain is a round trip over NVLink or a
+// system-scope fence, so the kernel is built to have few of them in sequence: every lane holds GPT 16-byte groups
+// of the row and issues the loads of all ranks for up to 16 of them before it uses any (one round trip for dim
+// 4096 on up to four ranks; the first form, one warp per row with 16 groups per lane in batches of 4 / world,
+// took 55 us for 512 rows on four GPUs where this one needs one batch), the row's sum of squares meets in shared
+// memory across the four warps, and one thread per CTA fences. W = number of ranks, GPT = groups per thread.
+template <int W, int GPT>
+__global__ void __launch_bounds__(RN_THREADS) k_tp_reduce_norm(TpReduceNorm p, int* status) {
+    constexpr int CH = GPT * W <= 16 ? GPT : (16 / W >= 1 ? 16 / W : 1);      // groups per thread whose loads are issued together
+    __shared__ float red[RN_THREADS / 32];
     __shared__ int rows_here;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rsub = threadIdx.x / RN_ROW_THREADS;                       // which of the CTA's rows
+    const int t = threadIdx.x - rsub * RN_ROW_THREADS;                   // thread within the row
+    const int r = blockIdx.x * RN_ROWS + rsub;                           // row of this rank's slice
     if (threadIdx.x == 0) rows_here = 0;
     pdl_launch_dependents();
     pdl_wait();
     __syncthreads();
     const int rb = min(r, p.rows - 1) >> 7;
-    // every (source, column tile) flag of this row block
+    // every (source, column tile) flag of this row block, polled by the row's first warp
     bool ok = r < p.rows;
-    for (int i = lane; i < W * p.col_tiles; i += 32) {
-        const int src = i / p.col_tiles, ct = i - src * p.col_tiles;
-        const unsigned int* f = p.arrive_flags + (size_t)src * p.flags_slot_stride + rb * 64 + ct;
-        bool here = false;
-        for (unsigned int t = 0; t < TL_EXCHANGE_TRIES && !here; t++) here = ld_acquire_sys(f) == p.epoch;
-        ok &= here;
+    if (ok && t < 32) {
+        for (int i = lane; i < W * p.col_tiles; i += 32) {
+            const int src = i / p.col_tiles, ct = i - src * p.col_tiles;
+            const unsigned int* f = p.arrive_flags + (size_t)src * p.flags_slot_stride + rb * 64 + ct;
+            bool here = false;
+            for (unsigned int tr = 0; tr < TL_EXCHANGE_TRIES && !here; tr++) here = ld_acquire_sys(f) == p.epoch;
+            ok &= here;
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok && lane == 0) atomicExch(status, TL_ERR_TIMEOUT);     // the row is never counted: the waiting kernels give up as well
+        if (lane == 0) red[warp] = ok ? 1.f : 0.f;
     }
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok && r < p.rows && lane == 0) atomicExch(status, TL_ERR_TIMEOUT);   // the row is never counted: the waiting kernels give up as well
-    if (ok) {
+    row_bar_sync(rsub);
+    ok = r < p.rows && red[rsub * (RN_ROW_THREADS / 32)] != 0.f;
+    row_bar_sync(rsub);                                                  // red is reused for the sums below
     // h = residual + half(sum over ranks), kept in registers for the norm; dim / 8 16-byte groups per row
     const int groups = p.dim >> 3;
-    const size_t grow = (size_t)(p.row0 + r);
-    const uint4* res4 = reinterpret_cast<const uint4*>(p.residual + (size_t)r * p.dim);
-    uint4* out4 = reinterpret_cast<uint4*>(p.residual_out + (size_t)r * p.dim);
-    uint4 hval[GPL];
+    const size_t grow = (size_t)(p.row0 + min(r, p.rows - 1));
+    const uint4* res4 = reinterpret_cast<const uint4*>(p.residual + (size_t)min(r, p.rows - 1) * p.dim);
+    uint4* out4 = reinterpret_cast<uint4*>(p.residual_out + (size_t)min(r, p.rows - 1) * p.dim);
+    uint4 hval[GPT];
     float ss = 0.f;
+    if (ok) {
 #pragma unroll
-    for (int c0 = 0; c0 < GPL; c0 += CH) {
-        if (c0 * 32 >= groups) break;
-        uint4 v[CH][W], rv[CH];
+        for (int c0 = 0; c0 < GPT; c0 += CH) {
+            if (c0 * RN_ROW_THREADS >= groups) break;
+            uint4 v[CH][W], rv[CH];
 #pragma unroll
-        for (int cc = 0; cc < CH; cc++) {
-            const int g = min(lane + (c0 + cc) * 32, groups - 1);
+            for (int cc = 0; cc < CH; cc++) {
+                const int g = min(t + (c0 + cc) * RN_ROW_THREADS, groups - 1);
 #pragma unroll
-            for (int src = 0; src < W; src++) v[cc][src] = ld_peer16(reinterpret_cast<const uint4*>(p.partial[src] + grow * p.dim) + g);
-            rv[cc] = res4[g];
-        }
-#pragma unroll
-        for (int cc = 0; cc < CH; cc++) {
-            const int g = lane + (c0 + cc) * 32;
-            float s[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) s[j] = 0.f;
-#pragma unroll
-            for (int src = 0; src < W; src++) {
-                const __half2* vh = reinterpret_cast<const __half2*>(&v[cc][src]);
-#pragma unroll
-                for (int j = 0; j < 4; j++) { const float2 f = __half22float2(vh[j]); s[2 * j] += f.x; s[2 * j + 1] += f.y; }
+                for (int src = 0; src < W; src++) v[cc][src] = ld_peer16(reinterpret_cast<const uint4*>(p.partial[src] + grow * p.dim) + g);
+                rv[cc] = res4[g];
             }
-            const __half* rh = reinterpret_cast<const __half*>(&rv[cc]);
-            uint4 hv;
-            __half* hh = reinterpret_cast<__half*>(&hv);
-            float part = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                hh[j] = hadd_ref(rh[j], __float2half_rn(s[j]));
-                const float f = __half2float(hh[j]);
-                part = fmaf(f, f, part);
+            for (int cc = 0; cc < CH; cc++) {
+                const int g = t + (c0 + cc) * RN_ROW_THREADS;
+                float s[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) s[j] = 0.f;
+#pragma unroll
+                for (int src = 0; src < W; src++) {
+                    const __half2* vh = reinterpret_cast<const __half2*>(&v[cc][src]);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { const float2 f = __half22float2(vh[j]); s[2 * j] += f.x; s[2 * j + 1] += f.y; }
+                }
+                const __half* rh = reinterpret_cast<const __half*>(&rv[cc]);
+                uint4 hv;
+                __half* hh = reinterpret_cast<__half*>(&hv);
+                float part = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    hh[j] = hadd_ref(rh[j], __float2half_rn(s[j]));
+                    const float f = __half2float(hh[j]);
+                    part = fmaf(f, f, part);
+                }
+                hval[c0 + cc] = hv;
+                if (g < groups) { out4[g] = hv; ss += part; }
             }
-            hval[c0 + cc] = hv;
-            if (g < groups) { out4[g] = hv; ss += part; }
         }
     }
     ss = warp_sum(ss);
-    const float rinv = rsqrtf(ss / (float)p.dim + p.eps);
-    const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
+    if (lane == 0) red[warp] = ss;
+    row_bar_sync(rsub);
+    if (ok) {
+        float tot = 0.f;
 #pragma unroll
-    for (int c = 0; c < GPL; c++) {
-        const int g = lane + c * 32;
-        if (g >= groups) break;
-        const uint4 wv = nw4[g];
-        const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-        const __half2* hh = reinterpret_cast<const __half2*>(&hval[c]);
-        uint4 o;
-        __half2* oh = reinterpret_cast<__half2*>(&o);
+        for (int w = 0; w < RN_ROW_THREADS / 32; w++) tot += red[rsub * (RN_ROW_THREADS / 32) + w];
+        const float rinv = rsqrtf(tot / (float)p.dim + p.eps);
+        const uint4* nw4 = reinterpret_cast<const uint4*>(p.norm_w);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 hf = __half22float2(hh[j]), wf = __half22float2(wh[j]);
-            oh[j] = __floats2half2_rn(hf.x * rinv * wf.x, hf.y * rinv * wf.y);
+        for (int c = 0; c < GPT; c++) {
+            const int g = t + c * RN_ROW_THREADS;
+            if (g >= groups) break;
+            const uint4 wv = nw4[g];
+            const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+            const __half2* hh = reinterpret_cast<const __half2*>(&hval[c]);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 hf = __half22float2(hh[j]), wf = __half22float2(wh[j]);
+                oh[j] = __floats2half2_rn(hf.x * rinv * wf.x, hf.y * rinv * wf.y);
+            }
+#pragma unroll
+            for (int d = 0; d < W; d++) reinterpret_cast<uint4*>(p.xn_dst[d] + grow * p.dim)[g] = o;
         }
-#pragma unroll
-        for (int d = 0; d < W; d++) reinterpret_cast<uint4*>(p.xn_dst[d] + grow * p.dim)[g] = o;
-    }
-    if (lane == 0) atomicAdd(&rows_here, 1);
+        if (t == 0) atomicAdd(&rows_here, 1);
     }
     // The CTA barrier orders every warp's stores before thread 0's fence (cumulative at system scope: one fence
     // per CTA; a fence per row measured 8 us more over 1024 rows, and it is the only system-scope fence on the
@@ -168,11 +189,11 @@ __global__ void __launch_bounds__(32) k_tp_wait_owners(const unsigned int* flags
 
 template <int W>
 int launch_reduce_w(const TpReduceNorm& p, cudaStream_t st) {
-    const dim3 grid((unsigned)((p.rows + RN_THREADS / 32 - 1) / (RN_THREADS / 32))), block(RN_THREADS);
+    const dim3 grid((unsigned)((p.rows + RN_ROWS - 1) / RN_ROWS)), block(RN_THREADS);
     const int groups = p.dim / 8;
-    if (groups <= 4 * 32) return launch_pdl(k_tp_reduce_norm<W, 4>, grid, block, 0, st, true, p, device_status_word());
-    if (groups <= 16 * 32) return launch_pdl(k_tp_reduce_norm<W, 16>, grid, block, 0, st, true, p, device_status_word());
-    return launch_pdl(k_tp_reduce_norm<W, 32>, grid, block, 0, st, true, p, device_status_word());
+    if (groups <= RN_ROW_THREADS) return launch_pdl(k_tp_reduce_norm<W, 1>, grid, block, 0, st, true, p, device_status_word());
+    if (groups <= 4 * RN_ROW_THREADS) return launch_pdl(k_tp_reduce_norm<W, 4>, grid, block, 0, st, true, p, device_status_word());
+    return launch_pdl(k_tp_reduce_norm<W, 8>, grid, block, 0, st, true, p, device_status_word());
 }
 
 int launch_tp_reduce_norm(const TpReduceNorm& p, cudaStream_t st) {
