@@ -382,6 +382,18 @@ TL_API int tl_tp_exchange_close(tl_llama2* m);
  * TL_OK, after which tl_device_status() reports TL_ERR_TIMEOUT once and the library stays usable.
  * Nothing faults or traps. Allocates and frees its own few KB. */
 TL_API int tl_selftest_unposted_exchange(int max_polls, tl_stream stream);
+/* Self-test of the tensor-parallel prefill exchange on ONE GPU, the ranks emulated by one stream over all
+ * ranks' data (no kernel waits for another launch): the K-split matmul in signalling mode computes
+ * P = A[M,K] B[dim,K]^T and raises its flags as source rank `owner`... every other source's flags are
+ * pre-set and every source's partial points at the same P, so the owner-side kernel of rank `owner`
+ * (rows [owner M/world, (owner+1) M/world)) must produce residual_out = residual + half(world x P) and
+ * xn = RMSNorm(residual_out) * norm_w in each of the `world` destination copies xn_out[d][M][dim] (rows of
+ * other owners stay untouched). All pointers are device memory; residual / residual_out hold the owner's
+ * M / world rows. M must be a multiple of 128 x world, world 2, 4 or 8. Synchronises `stream`. */
+TL_API int tl_selftest_tp_prefill_exchange(const tl_half* A, const tl_half* B, const tl_half* residual,
+                                           const tl_half* norm_w, tl_half* residual_out, tl_half* xn_out,
+                                           int M, int dim, int K, int world, int owner, float eps,
+                                           tl_stream stream);
 /* Host-only: the block of a [rows, cols] checkpoint tensor that rank `rank` of `world` keeps.
  * kind 0 = replicated, 1 = split by rows, 2 = split by columns. */
 TL_API int tl_tp_shard(int kind, int rows, int cols, int rank, int world, int* row0, int* nrows,

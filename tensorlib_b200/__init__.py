@@ -97,6 +97,7 @@ _SIGS = {
     "tl_tp_exchange_close": [_vp],
     "tl_tp_shard": [_int] * 5 + [C.POINTER(_int)] * 4,
     "tl_selftest_unposted_exchange": [_int, _vp],
+    "tl_selftest_tp_prefill_exchange": [_vp] * 6 + [_int] * 5 + [C.c_float, _vp],
     "tl_contiguous_f16": [_vp, _vp, _vp, _vp, _int, _sz, _sz, _vp],
     "tl_set_item_f16": [_vp, _vp, _vp, _vp, _int, _sz, _sz, _vp],
     "tl_set_item_scalar_f16": [_vp, C.c_uint16, _vp, _vp, _int, _sz, _sz, _vp],
@@ -384,6 +385,19 @@ UNARY_OPS = {"neg": 0, "sin": 1, "cos": 2, "exp": 3, "log": 4, "abs": 5, "tanh":
              "silu_cpu_half": 10}
 BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4}
 REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3}
+
+
+def selftest_tp_prefill_exchange(A, B, residual, norm_w, world: int, owner: int, eps: float = 1e-5):
+    """tl_selftest_tp_prefill_exchange: the tensor-parallel prefill exchange of rank `owner` of `world`, the ranks
+    emulated on one GPU. Returns (residual_out [M / world, dim], xn [world, M, dim]; xn starts as zeros)."""
+    M, K = A.shape
+    dim = B.shape[0]
+    dA, dB, dr, dw = (DeviceBuffer.from_numpy(np.ascontiguousarray(a, dtype=np.float16)) for a in (A, B, residual, norm_w))
+    dout = DeviceBuffer(M // world * dim * 2)
+    dxn = DeviceBuffer.from_numpy(np.zeros((world, M, dim), np.float16))
+    check(load().tl_selftest_tp_prefill_exchange(dA.ptr, dB.ptr, dr.ptr, dw.ptr, dout.ptr, dxn.ptr, M, dim, K, world, owner,
+                                                 eps, None), "tl_selftest_tp_prefill_exchange")
+    return dout.to_numpy(np.float16, (M // world, dim)), dxn.to_numpy(np.float16, (world, M, dim))
 
 
 def _ints(v):

@@ -664,6 +664,67 @@ int tl_selftest_unposted_exchange(int max_polls, tl_stream stream) {
     return rc;
 }
 
+int tl_selftest_tp_prefill_exchange(const tl_half* A, const tl_half* B, const tl_half* residual, const tl_half* norm_w,
+                                    tl_half* residual_out, tl_half* xn_out, int M, int dim, int K, int world, int owner,
+                                    float eps, tl_stream stream) {
+    TL_CHECK_INIT();
+    TL_REQUIRE(A && B && residual && norm_w && residual_out && xn_out, "null pointer");
+    TL_REQUIRE((world == 2 || world == 4 || world == 8) && owner >= 0 && owner < world && M > 0 && M % (128 * world) == 0 &&
+               dim % 32 == 0 && dim <= 8192 && K % 8 == 0, "self-test: M a multiple of 128 x world, world 2, 4 or 8, dim %% 32 == 0");
+    cudaStream_t st = as_stream(stream);
+    const int rpo = M / world;
+    const size_t fslot = (size_t)(rpo / 128) * 64;          // flag words per source rank
+    // [P: M x dim halfs][arrival flags: world x fslot][owner flags + row counter: 128 words]
+    const size_t p_bytes = (size_t)M * dim * sizeof(__half), f_bytes = (size_t)world * fslot * sizeof(unsigned int);
+    unsigned char* base = nullptr;
+    TL_CUDA(cudaMalloc(&base, p_bytes + f_bytes + 512));
+    __half* P = reinterpret_cast<__half*>(base);
+    unsigned int* aflags = reinterpret_cast<unsigned int*>(base + p_bytes);
+    unsigned int* gflags = reinterpret_cast<unsigned int*>(base + p_bytes + f_bytes);
+    const unsigned int epoch = 1;
+    int rc = TL_OK;
+    {   // every source but `owner` has "already signalled"; the matmul below signals as source `owner`
+        std::vector<unsigned int> h((size_t)world * fslot, epoch);
+        for (size_t i = 0; i < fslot; i++) h[(size_t)owner * fslot + i] = 0;
+        cudaError_t e = cudaMemcpyAsync(aflags, h.data(), f_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(gflags, 0, 512, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) rc = set_error(TL_ERR_CUDA, "self-test set-up failed: %s", cudaGetErrorString(e));
+    }
+    if (rc == TL_OK) {
+        HgemmPush push{};
+        push.world = world; push.rows_per_owner = rpo; push.epoch = epoch;
+        // the matmul raises the flags of every owner; only `owner`'s block is read back, the others land in a scratch slot
+        unsigned int* scratch = nullptr;
+        if (cudaMalloc(&scratch, fslot * sizeof(unsigned int)) != cudaSuccess) rc = set_error(TL_ERR_OUT_OF_MEMORY, "self-test scratch");
+        if (rc == TL_OK) {
+            for (int d = 0; d < world; d++) push.flags[d] = d == owner ? aflags + (size_t)owner * fslot : scratch;
+            int col_tiles = 0;
+            rc = launch_hgemm_push(H(A), H(B), P, M, dim, K, K, K, push, &col_tiles, st);
+            if (rc == TL_OK) {
+                TpReduceNorm rn{};
+                rn.world = world; rn.rank = owner; rn.rows = rpo; rn.row0 = owner * rpo; rn.dim = dim; rn.col_tiles = col_tiles; rn.epoch = epoch;
+                for (int d = 0; d < world; d++) {
+                    rn.partial[d] = P;
+                    rn.xn_dst[d] = reinterpret_cast<__half*>(xn_out) + (size_t)d * M * dim;
+                    rn.owner_done[d] = gflags + 8 * d;       // a separate flag block per emulated destination
+                }
+                rn.arrive_flags = aflags; rn.flags_slot_stride = (int)fslot;
+                rn.residual = H(residual); rn.residual_out = reinterpret_cast<__half*>(residual_out);
+                rn.norm_w = H(norm_w); rn.eps = eps;
+                rn.rows_done = gflags + 64;
+                rc = launch_tp_reduce_norm(rn, st);
+                // this rank's view as a destination: the flag of owner `owner` in block 0
+                if (rc == TL_OK) rc = launch_tp_wait_owners(gflags + owner, 1, epoch, st);
+            }
+        }
+        cudaStreamSynchronize(st);
+        if (scratch) cudaFree(scratch);
+    }
+    cudaFree(base);
+    return rc;
+}
+
 int tl_llama2_decode_profile(tl_llama2* m, int start_pos, int cta, unsigned long long* stamps_host, int capacity,
                              int* n_phases) {
     TL_CHECK_INIT();

@@ -296,6 +296,37 @@ def test_bounded_wait_runs_out_and_the_library_stays_usable(tl, oracle):
     assert tl.load().tl_selftest_unposted_exchange(0, None) == 1      # out-of-range limit is refused
 
 
+@pytest.mark.parametrize("world,owner,M,dim,K", [(2, 1, 512, 4096, 256), (4, 2, 512, 4096, 192), (8, 5, 1024, 4096, 128),
+                                                 (8, 0, 2048, 512, 64), (4, 3, 1024, 5120, 64)])
+def test_tp_prefill_exchange_with_the_ranks_emulated_on_one_gpu(tl, world, owner, M, dim, K):
+    """The K-split matmul in signalling mode followed by the owner-side reduce + RMSNorm + gather kernel, for
+    2, 4 and 8 ranks, on one GPU: every rank's partial is the same matrix P, so the owner's rows must come out
+    as residual + half(world x P), normalised, in every destination copy, and nobody else's rows are touched."""
+    A = synth.normal_f16(77, 1, M * K, 1.0).reshape(M, K)
+    B = synth.normal_f16(77, 2, dim * K, 0.05).reshape(dim, K)
+    rpo = M // world
+    resid = synth.normal_f16(77, 3, rpo * dim, 1.0).reshape(rpo, dim)
+    w = (1.0 + synth.normal_f16(77, 4, dim, 0.1).astype(np.float32)).astype(np.float16)
+    h, xn = tl.selftest_tp_prefill_exchange(A, B, resid, w, world, owner)
+    assert tl.device_status() == 0
+    rows = slice(owner * rpo, (owner + 1) * rpo)
+    P = (A[rows].astype(np.float32) @ B.astype(np.float32).T).astype(np.float16)          # the matmul's fp16 result
+    # the kernel adds the `world` fp16 partials in fp32, rounds once, then adds the residual in fp16
+    s16 = (P.astype(np.float32) * world).astype(np.float16)
+    want_h = (resid.astype(np.float32) + s16.astype(np.float32)).astype(np.float16)
+    # P itself carries the matmul's rounding: allow one fp16 ulp of P (times world) in h
+    tol = np.maximum(np.abs(want_h.astype(np.float32)), 1.0) * 2e-3 * world
+    assert np.all(np.abs(h.astype(np.float32) - want_h.astype(np.float32)) <= tol)
+    hf = h.astype(np.float32)
+    want_xn = hf * (1.0 / np.sqrt((hf * hf).mean(axis=1, keepdims=True) + 1e-5)) * w.astype(np.float32)
+    for d in range(world):
+        got = xn[d].astype(np.float32)
+        assert np.max(np.abs(got[rows] - want_xn)) <= 4e-3 * max(1.0, float(np.abs(want_xn).max())), d
+        mask = np.ones(M, bool); mask[rows] = False
+        assert not got[mask].any(), d                               # other owners' rows untouched
+        assert np.array_equal(xn[d][rows], xn[0][rows])             # every destination holds the same bits
+
+
 def test_batched_matmul_with_a_batch_stride_that_is_not_a_multiple_of_8(tl, oracle):
     """Aligned pitches but an odd batch stride: the tensor-core kernels cannot take it, the call
     must fall through to the any-shape kernel instead of failing."""
