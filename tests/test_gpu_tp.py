@@ -4,7 +4,8 @@ box has are skipped).
 One process per GPU, NCCL inside the library (gloo only carries the unique id and the IPC handles).
 Each rank loads its shard; prefill and decode logits must match the single-GPU fast path within the
 model tolerance, every rank must sample the same ids, and the exchange fused into the GEMV kernels
-(peer stores, the sum formed once per GPU, three launches per layer) must agree with the NCCL form.
+(peer stores, three launches per layer; the sum formed by every CTA or, `TL_TP_REDUCE=slice`, once per GPU as
+eight ranks do by default) must agree with the NCCL form.
 Configurations: the tiny model (world 2), a head_dim-128 model (world 2 and 4) and ONE layer of the
 7B shape (dim 4096, hidden 11008, 32 heads; world 2 and 4), where a consumer gathers 4096 words.
 """
@@ -57,10 +58,12 @@ def _long_prompt(cfg):
     return synth.token_ids(20240229, 102, N_LONG, cfg.vocab_size) if cfg.seq_len > N_LONG and cfg.head_dim == 128 else None
 
 
-def _worker(rank: int, world: int, port: int, name: str, q):
+def _worker(rank: int, world: int, port: int, name: str, q, reduce_form: str = ""):
     try:
         sys.path.insert(0, ROOT)
         os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        if reduce_form:      # the form of the decode exchange's sum that eight ranks take by default
+            os.environ["TL_TP_REDUCE"] = reduce_form
         import torch.distributed as dist
 
         import tensorlib_b200 as tl
@@ -115,8 +118,10 @@ def _rel_err(got, want):
     return float((np.abs(g - w) / np.maximum(np.abs(w), scale)).max())
 
 
-@pytest.mark.parametrize("name,world", [("tiny", 2), ("mid", 2), ("mid", 4), ("layer7b", 2), ("layer7b", 4)])
-def test_tensor_parallel_matches_single_gpu(tl, name, world):
+@pytest.mark.parametrize("name,world,reduce_form", [("tiny", 2, ""), ("mid", 2, ""), ("mid", 4, ""), ("layer7b", 2, ""),
+                                                    ("layer7b", 4, ""), ("mid", 2, "slice"), ("layer7b", 2, "slice"),
+                                                    ("layer7b", 4, "slice")])
+def test_tensor_parallel_matches_single_gpu(tl, name, world, reduce_form):
     if tl.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     cfg, payload = _config(name)
@@ -133,7 +138,7 @@ def test_tensor_parallel_matches_single_gpu(tl, name, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, name, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, name, q, reduce_form)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted((q.get(timeout=900) for _ in procs), key=lambda r: r[0])
