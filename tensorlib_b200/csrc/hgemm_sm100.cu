@@ -1035,7 +1035,7 @@ int launch_pair_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensor
 // estimated plan of the CTA-pair kernel: tile height (msub x 256 rows), whole tiles (sk_per = 0) or stream-K
 // ranges of sk_per k-blocks per pair, and the estimated cycles of the launch
 struct PairPlan { int msub, sk_per; long long cost; };
-PairPlan pair_plan(int M, long long n_col_tiles, int nkb, int epi);
+PairPlan pair_plan(int sms, int M, long long n_col_tiles, int nkb, int epi);
 
 // workspace of the stream-K mode per (device, stream): partial tiles of every pair (two per pair, fp32)
 // and the arrival counters (zero between launches: the last arriver of a tile resets its counter)
@@ -1069,7 +1069,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     GemmArgs a = a_in;
     const long long nt = (long long)n_col_tiles * a.batch;
     const int nkb = (a.K + BK - 1) / BK;
-    PairPlan pl = pair_plan(a.M, nt, nkb, EPI);
+    PairPlan pl = pair_plan(sm_count(), a.M, nt, nkb, EPI);
     const long long tiles = (long long)((a.M + 256 * pl.msub - 1) / (256 * pl.msub)) * nt;
     int pair_ctas = (int)std::min<long long>(tiles, sm_count() / 2);
     if (pl.sk_per > 0) {
@@ -1084,10 +1084,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
 
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
-// when non-zero, the planning functions use it instead of the device's SM count; per thread, so a
-// host-only plan query on one thread cannot change what a launch on another thread decides
-thread_local int g_plan_sms = 0;
-int plan_sms() { return g_plan_sms > 0 ? g_plan_sms : sm_count(); }
+// the planning functions below take the SM count they plan for: the device's for a launch, the caller's for a
+// host-only plan query
 
 // Estimated cycles of the CTA-pair kernel. Per k-block a 256 x 256 pair tile measures ~590 cycles (512 of
 // MMA stretched by the shared-memory fill running at its limit beside them), a 512 x 256 tile ~1090
@@ -1114,8 +1112,8 @@ int pair_forced() {
     }();
     return forced;
 }
-PairPlan pair_plan(int M, long long n_col_tiles, int nkb, int epi) {
-    const long long pairs = std::max(1, plan_sms() / 2);
+PairPlan pair_plan(int sms, int M, long long n_col_tiles, int nkb, int epi) {
+    const long long pairs = std::max(1, sms / 2);
     const int forced = pair_forced();
     PairPlan best{1, 0, -1};
     for (int msub = 1; msub <= 2; msub++) {
@@ -1143,16 +1141,16 @@ PairPlan pair_plan(int M, long long n_col_tiles, int nkb, int epi) {
     return best;
 }
 // estimated cycles of the pair kernel for the choice between it and the single-CTA kernel
-long long pair_cost(int M, int n_tiles_256, int batch, int K, int epi = GEPI_STORE) {
+long long pair_cost(int sms, int M, int n_tiles_256, int batch, int K, int epi = GEPI_STORE) {
     const int forced = pair_forced();
     if (forced == 2) return (1ll << 60);
     if (forced != 0) return -1;
-    return pair_plan(M, (long long)n_tiles_256 * batch, (K + BK - 1) / BK, epi).cost;
+    return pair_plan(sms, M, (long long)n_tiles_256 * batch, (K + BK - 1) / BK, epi).cost;
 }
 // estimated cycles of the single-CTA kernel
-long long single_cost(int mt, int N, int batch, int bn, int K) {
+long long single_cost(int sms, int mt, int N, int batch, int bn, int K) {
     const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
-    const long long waves = (tiles + plan_sms() - 1) / plan_sms();
+    const long long waves = (tiles + sms - 1) / sms;
     return waves * std::max<long long>(2 * bn, (16384 + bn * 128) / 64) * ((K + BK - 1) / BK);
 }
 
@@ -1170,7 +1168,7 @@ int splitk_forced() {
     }();
     return forced;
 }
-SplitPlan splitk_plan(int M, int N, int K, int batch) {
+SplitPlan splitk_plan(int sms, int M, int N, int K, int batch) {
     SplitPlan best{0, 0, 0, -1};
     if (batch != 1 || splitk_forced() == 2 || N % 32 != 0) return best;
     const int nkb = (K + BK - 1) / BK;
@@ -1181,7 +1179,7 @@ SplitPlan splitk_plan(int M, int N, int K, int batch) {
         const int bn = c[0], ks = c[1], msub = c[2];
         if (msub == 2 && M <= BM) continue;
         const long long tiles = (long long)((M + BM * msub - 1) / (BM * msub)) * ((N + bn - 1) / bn);
-        if (tiles * ks > plan_sms() || nkb / ks < 4) continue;
+        if (tiles * ks > sms || nkb / ks < 4) continue;
         const long long per_kb = msub == 2 ? 1040 : std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
         const long long cost = (long long)((nkb + ks - 1) / ks) * per_kb + (ks > 1 ? 3000 * msub : 0) + 1500 * msub;
         if (best.cost < 0 || cost < best.cost) best = SplitPlan{bn, ks, msub, cost};
@@ -1189,17 +1187,17 @@ SplitPlan splitk_plan(int M, int N, int K, int batch) {
     return best;
 }
 
-int pick_bn(int mt, int N, int batch);
+int pick_bn(int sms, int mt, int N, int batch);
 // the cluster split-K kernel where it has a plan and the estimate beats the whole-tile kernels
-bool splitk_wins(int M, int N, int K, int batch, int epi, SplitPlan* out) {
-    const SplitPlan sp = splitk_plan(M, N, K, batch);
+bool splitk_wins(int sms, int M, int N, int K, int batch, int epi, SplitPlan* out) {
+    const SplitPlan sp = splitk_plan(sms, M, N, K, batch);
     *out = sp;
     if (sp.cost < 0) return false;
     if (splitk_forced() == 1) return true;
     const int mt = (M + BM - 1) / BM;
     // the whole-tile estimates leave out their last tile's epilogue: ask for a clear margin before displacing them
-    if (sp.cost * 10 >= single_cost(mt, N, batch, pick_bn(mt, N, batch), K) * 9) return false;
-    return M <= BM || sp.cost * 10 < pair_cost(M, (N + 255) / 256, batch, K, epi) * 9;
+    if (sp.cost * 10 >= single_cost(sms, mt, N, batch, pick_bn(sms, mt, N, batch), K) * 9) return false;
+    return M <= BM || sp.cost * 10 < pair_cost(sms, M, (N + 255) / 256, batch, K, epi) * 9;
 }
 
 // N-tile width with the smallest estimated time: waves of tiles over the SMs times the cost of one
@@ -1207,12 +1205,12 @@ bool splitk_wins(int M, int N, int K, int batch, int epi, SplitPlan* out) {
 // the time to bring its operands into shared memory (16 KB of A + BN * 128 B of B at the roughly
 // 64 bytes per cycle one SM sustains from L2; measured: the 128x256 tile runs the tensor pipe
 // at 69 %, i.e. it is fill-bound, 48 KB per 512 MMA cycles).
-int pick_bn(int mt, int N, int batch) {
+int pick_bn(int sms, int mt, int N, int batch) {
     int best = 256;
     long long best_cost = -1;
     for (int bn = 256; bn >= 64; bn >>= 1) {
         const long long tiles = (long long)mt * ((N + bn - 1) / bn) * batch;
-        const long long waves = (tiles + plan_sms() - 1) / plan_sms();
+        const long long waves = (tiles + sms - 1) / sms;
         const long long per_kb = std::max<long long>(2 * bn, (16384 + bn * 128) / 64);
         const long long cost = waves * per_kb;
         if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
@@ -1226,30 +1224,27 @@ int pick_bn(int mt, int N, int batch) {
 // on the 7B shapes; from 33 rows on the cluster kernel wins (128 rows: 13.6 / 26.1 / 23.0 us against 15.7 / 30.1 / 25.6).
 bool hgemm_splitk_preferred(int M, int N, int K) {
     SplitPlan sp;
-    return (M > 32 || splitk_forced() == 1) && splitk_wins(M, N, K, 1, GEPI_STORE, &sp);
+    return (M > 32 || splitk_forced() == 1) && splitk_wins(sm_count(), M, N, K, 1, GEPI_STORE, &sp);
 }
 
 void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int* sk_per) {
-    g_plan_sms = sms;
     const int mt = (M + BM - 1) / BM;
-    *bn = pick_bn(mt, N, batch);
+    *bn = pick_bn(sms, mt, N, batch);
     *sk_per = 0;
     SplitPlan sp;
-    if (N % 32 == 0 && splitk_wins(M, N, K, batch, GEPI_STORE, &sp)) {
+    if (N % 32 == 0 && splitk_wins(sms, M, N, K, batch, GEPI_STORE, &sp)) {
         *kind = sp.msub == 2 ? 4 : 3;     // one tile per cluster, 128 (3) or 256 (4) rows; sk_per = CTAs sharing the tile's K
         *bn = sp.bn;
         *sk_per = sp.ks;
-        g_plan_sms = 0;
         return;
     }
-    *kind = (M > BM && N % 32 == 0 && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, *bn, K)) ? 1 : 0;
+    *kind = (M > BM && N % 32 == 0 && pair_cost(sms, M, (N + 255) / 256, batch, K) < single_cost(sms, mt, N, batch, *bn, K)) ? 1 : 0;
     if (*kind == 1) {                     // 1: 256-row pair tiles, 2: 512-row pair tiles
-        const PairPlan pl = pair_plan(M, (long long)((N + 255) / 256) * batch, (K + BK - 1) / BK, GEPI_STORE);
+        const PairPlan pl = pair_plan(sms, M, (long long)((N + 255) / 256) * batch, (K + BK - 1) / BK, GEPI_STORE);
         *bn = 256;
         *kind = pl.msub;
         *sk_per = pl.sk_per;
     }
-    g_plan_sms = 0;
 }
 
 bool hgemm_supported(const void* A, const void* B, const void* C, size_t M, size_t N, size_t K, size_t lda,
@@ -1264,7 +1259,7 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     TL_REQUIRE(sA % 8 == 0 && sB % 8 == 0, "hgemm: batch strides must be multiples of 8 elements");
     if (batch <= 0) return TL_OK;
     const int mt = (M + BM - 1) / BM;
-    const int bn = pick_bn(mt, N, batch);
+    const int bn = pick_bn(sm_count(), mt, N, batch);
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = batch; a.ldc = ldc; a.sC = sC;
     a.a_batched = (sA != 0 && batch > 1) ? 1 : 0; a.b_batched = (sB != 0 && batch > 1) ? 1 : 0;
@@ -1274,11 +1269,11 @@ int launch_hgemm(const __half* A, const __half* B, __half* C, int batch, int M, 
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, sA, batch, BM));
     const bool vec_c = ldc % 8 == 0 && sC % 8 == 0 && al16(C) && N % 32 == 0;   // the pair epilogue stores 64-byte chunks
     SplitPlan sp;
-    if (vec_c && splitk_wins(M, N, K, batch, GEPI_STORE, &sp)) {
+    if (vec_c && splitk_wins(sm_count(), M, N, K, batch, GEPI_STORE, &sp)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, sp.bn));
         return launch_splitk<GEPI_STORE>(sp.bn, sp.ks, sp.msub, ma, mb, a, ((M + BM * sp.msub - 1) / (BM * sp.msub)) * ((N + sp.bn - 1) / sp.bn), st);
     }
-    if (M > BM && vec_c && pair_cost(M, (N + 255) / 256, batch, K) < single_cost(mt, N, batch, bn, K)) {
+    if (M > BM && vec_c && pair_cost(sm_count(), M, (N + 255) / 256, batch, K) < single_cost(sm_count(), mt, N, batch, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, sB, batch, 128));
         return launch_pair<GEPI_STORE>(ma, mb, mb, mb, a, (N + 255) / 256, st);
     }
@@ -1295,7 +1290,7 @@ int launch_hgemm_push(const __half* A, const __half* B, __half* C, int M, int N,
     TL_REQUIRE(push.world >= 2 && push.world <= 8 && push.rows_per_owner > 0 && push.rows_per_owner % 128 == 0 &&
                (long long)push.rows_per_owner * push.world >= M, "hgemm push: rows per owner must be a multiple of 128 covering M");
     const int mt = (M + BM - 1) / BM;
-    const int bn = pick_bn(mt, N, 1);
+    const int bn = pick_bn(sm_count(), mt, N, 1);
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = N; a.sC = 0;
     a.status = device_status_word();
@@ -1306,7 +1301,7 @@ int launch_hgemm_push(const __half* A, const __half* B, __half* C, int M, int N,
     }
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
-    if (M > BM && pair_cost(M, (N + 255) / 256, 1, K) < single_cost(mt, N, 1, bn, K)) {
+    if (M > BM && pair_cost(sm_count(), M, (N + 255) / 256, 1, K) < single_cost(sm_count(), mt, N, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
         *col_tiles = (N + 255) / 256;
         TL_REQUIRE(*col_tiles <= PUSH_MAX_COL_TILES, "hgemm push: too many column tiles");
@@ -1330,18 +1325,18 @@ int launch_hgemm_residual(const __half* A, const __half* B, const __half* R, __h
     TL_REQUIRE(hgemm_fused_supported(A, B, C, M, N, K, lda, ldb, ldc) && R && al16(R) && ldr % 8 == 0,
                "hgemm+residual: unsupported shape or alignment");
     const int mt = (M + BM - 1) / BM;
-    const int bn = pick_bn(mt, N, 1);
+    const int bn = pick_bn(sm_count(), mt, N, 1);
     CUtensorMap ma, mb;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
     a.R = R; a.ldr = ldr; a.b_const = weights_constant ? 1 : 0;
     SplitPlan sp;
-    if (splitk_wins(M, N, K, 1, GEPI_RESIDUAL, &sp)) {
+    if (splitk_wins(sm_count(), M, N, K, 1, GEPI_RESIDUAL, &sp)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, sp.bn));
         return launch_splitk<GEPI_RESIDUAL>(sp.bn, sp.ks, sp.msub, ma, mb, a, ((M + BM * sp.msub - 1) / (BM * sp.msub)) * ((N + sp.bn - 1) / sp.bn), st);
     }
-    if (M > BM && pair_cost(M, (N + 255) / 256, 1, K, GEPI_RESIDUAL) < single_cost(mt, N, 1, bn, K)) {
+    if (M > BM && pair_cost(sm_count(), M, (N + 255) / 256, 1, K, GEPI_RESIDUAL) < single_cost(sm_count(), mt, N, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mb, B, N, K, ldb, 0, 1, 128));
         return launch_pair<GEPI_RESIDUAL>(ma, mb, mb, mb, a, (N + 255) / 256, st);
     }
@@ -1361,7 +1356,7 @@ int launch_hgemm_swiglu(const __half* A, const __half* W1, const __half* W3, __h
     TL_PROPAGATE(make_tensor_map_f16(&m3, W3, N, K, ldb, 0, 1, 128));
     GemmArgs a{};
     a.C = C; a.M = M; a.N = N; a.K = K; a.batch = 1; a.ldc = ldc; a.status = device_status_word();
-    if (M > BM && pair_cost(M, nt, 1, K, GEPI_SWIGLU) < single_cost(mt, N, 1, 128, K) * 768 / 512)   // single: 128 output columns per 256-wide tile
+    if (M > BM && pair_cost(sm_count(), M, nt, 1, K, GEPI_SWIGLU) < single_cost(sm_count(), mt, N, 1, 128, K) * 768 / 512)   // single: 128 output columns per 256-wide tile
         return launch_pair<GEPI_SWIGLU>(ma, m1, m3, m3, a, nt, st);
     return launch_k<256, GEPI_SWIGLU>(ma, m1, m3, m3, a, mt * nt, st);
 }
@@ -1382,7 +1377,7 @@ int launch_hgemm_qkv_rope(const __half* A, const __half* Wq, const __half* Wk, c
     while (bn > 64 && (n_each % bn != 0 || (long long)mt * 3 * (n_each / bn) < sm_count())) bn >>= 1;
     CUtensorMap ma, mq, mk, mv;
     TL_PROPAGATE(make_tensor_map_f16(&ma, A, M, K, lda, 0, 1, BM));
-    if (M > BM && n_each % 256 == 0 && pair_cost(M, 3 * (n_each / 256), 1, K, GEPI_QKV_ROPE) < single_cost(mt, 3 * n_each, 1, bn, K)) {
+    if (M > BM && n_each % 256 == 0 && pair_cost(sm_count(), M, 3 * (n_each / 256), 1, K, GEPI_QKV_ROPE) < single_cost(sm_count(), mt, 3 * n_each, 1, bn, K)) {
         TL_PROPAGATE(make_tensor_map_f16(&mq, Wq, n_each, K, ldb, 0, 1, 128));
         TL_PROPAGATE(make_tensor_map_f16(&mk, Wk, n_each, K, ldb, 0, 1, 128));
         TL_PROPAGATE(make_tensor_map_f16(&mv, Wv, n_each, K, ldb, 0, 1, 128));
