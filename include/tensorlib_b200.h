@@ -136,8 +136,7 @@ TL_API int tl_matmul_strided_f16(const tl_half* lhs, const tl_half* rhs, tl_half
 enum { TL_PLAN_REFERENCE_ORDER = 0, TL_PLAN_GEMV_RING = 1, TL_PLAN_GEMV_SMALL = 2, TL_PLAN_SKINNY_STREAMK = 3,
        TL_PLAN_SKINNY_CLUSTER = 4, TL_PLAN_HGEMM = 5, TL_PLAN_HGEMM_PAIR = 6 /* 256-row tiles per CTA pair */,
        TL_PLAN_HGEMM_PAIR512 = 7 /* 512-row tiles per CTA pair */,
-       TL_PLAN_HGEMM_SPLITK = 8 /* one 128-row tile per cluster, K split over its CTAs (cluster = CTAs per tile) */,
-       TL_PLAN_HGEMM_SPLITK256 = 9 /* the same with a 256 x 256 tile per CTA (cluster 1: no split) */ };
+       TL_PLAN_HGEMM_SPLITK = 8 /* one 128-row tile per cluster, K split over its CTAs (cluster = CTAs per tile) */ };
 TL_API int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int* grid, int* tile_n,
                    int* k_blocks_per_cta, int* cluster);
 /* Same contract as tl_matmul2d_f16 with HOST buffers: copies A and B in, C out, synchronises. */

@@ -472,7 +472,7 @@ def cast(x: np.ndarray, to) -> np.ndarray:
 
 
 PLAN_NAMES = {0: "reference_order", 1: "gemv_ring", 2: "gemv_small", 3: "skinny_streamk", 4: "skinny_cluster",
-              5: "hgemm", 6: "hgemm_pair", 7: "hgemm_pair512", 8: "hgemm_splitk", 9: "hgemm_splitk256"}
+              5: "hgemm", 6: "hgemm_pair", 7: "hgemm_pair512", 8: "hgemm_splitk"}
 
 
 def matmul_plan(M: int, N: int, K: int, sm_count: int = 148) -> dict:

@@ -84,9 +84,9 @@ int tl_matmul_plan(size_t M, size_t N, size_t K, int sm_count, int* kernel, int*
         if (M <= 8 || K % 8 != 0) return false;
         int kind = 0, bn = 0, ks = 0;
         hgemm_plan((int)M, (int)N, (int)K, 1, sm_count, &kind, &bn, &ks);
-        if (kind != 3 && kind != 4) return false;
-        const size_t tile_m = kind == 4 ? 256 : 128;
-        *kernel = kind == 4 ? TL_PLAN_HGEMM_SPLITK256 : TL_PLAN_HGEMM_SPLITK; *tile_n = bn; *cluster = ks;
+        if (kind != 3) return false;
+        const size_t tile_m = 128;
+        *kernel = TL_PLAN_HGEMM_SPLITK; *tile_n = bn; *cluster = ks;
         *grid = (int)(((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn)) * ks;
         *k_blocks_per_cta = (int)(((K + 63) / 64 + ks - 1) / ks);
         return true;

@@ -1233,7 +1233,7 @@ void hgemm_plan(int M, int N, int K, int batch, int sms, int* kind, int* bn, int
     *sk_per = 0;
     SplitPlan sp;
     if (N % 32 == 0 && splitk_wins(sms, M, N, K, batch, GEPI_STORE, &sp)) {
-        *kind = sp.msub == 2 ? 4 : 3;     // one tile per cluster, 128 (3) or 256 (4) rows; sk_per = CTAs sharing the tile's K
+        *kind = 3;                        // one 128-row tile per cluster; sk_per = CTAs sharing the tile's K
         *bn = sp.bn;
         *sk_per = sp.ks;
         return;
