@@ -485,8 +485,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         # the same eight steps with the plain NCCL exchange: summation order differs (ring order against
         # rank order), so equal ids are reported, not required
         from tensorlib_b200 import tp
+        model.forward(prompt, 0, all_logits=False)      # the same prefill as for the ids above, so only the decode exchange differs
         tp.close_fused_exchange(model, dist)
-        model.forward(prompt, 0, all_logits=False)
         with torch.cuda.stream(stream):
             ids_nccl = model.decode_device(pos0, min(8, K), fetch=True, stream=sp)
         require_clean_status(tl, "the NCCL-exchange decode steps")
