@@ -966,8 +966,9 @@ EncodeTiledFn encode_fn() {
 
 bool tensor_map_encode_available() { return encode_fn() != nullptr; }
 
-int make_tensor_map_f16(CUtensorMap* map, const __half* base, int rows, int K, long long ld, long long stride,
-                        int batch, int box_rows) {
+namespace {
+int encode_tensor_map_f16(CUtensorMap* map, const __half* base, int rows, int K, long long ld, long long stride,
+                          int batch, int box_rows) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return set_error(TL_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
     const bool batched = stride != 0 && batch > 1;
@@ -981,6 +982,46 @@ int make_tensor_map_f16(CUtensorMap* map, const __half* base, int rows, int K, l
     if (r != CUDA_SUCCESS) return set_error(TL_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return TL_OK;
 }
+
+// Encoded maps are kept per (address, shape, pitches, box): a descriptor is a pure function of those, so a hit is
+// always valid, and the model's weights, caches and activation buffers are encoded once instead of on every launch
+// (an encode costs the host about a microsecond, two or three per launch).
+struct MapKey {
+    const void* base; long long ld, stride; int rows, K, batch, box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && ld == o.ld && stride == o.stride && rows == o.rows && K == o.K && batch == o.batch && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        auto mix = [&](unsigned long long v) { h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2); };
+        mix((unsigned long long)k.ld); mix((unsigned long long)k.stride); mix((unsigned long long)k.rows);
+        mix((unsigned long long)k.K); mix((unsigned long long)k.batch); mix((unsigned long long)k.box_rows);
+        return h;
+    }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+constexpr size_t MAP_CACHE_LIMIT = 8192;      // entries; the cache is simply emptied when it gets there
+
+}  // namespace
+
+int make_tensor_map_f16(CUtensorMap* map, const __half* base, int rows, int K, long long ld, long long stride,
+                        int batch, int box_rows) {
+    const MapKey key{base, ld, stride, rows, K, batch, box_rows};
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        auto it = g_map_cache.find(key);
+        if (it != g_map_cache.end()) { *map = it->second; return TL_OK; }
+    }
+    TL_PROPAGATE(encode_tensor_map_f16(map, base, rows, K, ld, stride, batch, box_rows));
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_map_cache.size() >= MAP_CACHE_LIMIT) g_map_cache.clear();
+    g_map_cache.emplace(key, *map);
+    return TL_OK;
+}
+
 
 namespace {
 
