@@ -11,6 +11,7 @@
 //   Llama2<half>::generate(prompt_tokens)     llama2.hpp:19     Llama2::generate(prompt_tokens, max_new)
 //   Tokenizer::encode / decode                Tokenizer.hpp:33  Tokenizer::encode / decode (host only)
 //   Llama2<half>::text_completion(prompt)     llama2.hpp:20     Llama2::text_completion(tokenizer, prompt)
+//   Llama2<half>::chat()                      llama2.hpp:21     Llama2::chat(tokenizer, in, out)
 //
 // Error behaviour follows the reference: argument/shape errors throw std::invalid_argument
 // (matmul.cpp:209-221); CUDA failures, which the reference answers with exit(1) (CUDA.cuh:131-151),
@@ -21,6 +22,8 @@
 #include <cstdint>
 #include <cstdio>
 #include <fstream>
+#include <istream>
+#include <ostream>
 #include <memory>
 #include <optional>
 #include <stdexcept>
@@ -275,7 +278,7 @@ struct GenerateResult {
 };
 
 // Llama2::generate (llama2.cpp:15-101): prefill, then greedy steps; stops early on id 1 or 2 when
-// stop_on_eos is set (llama2.cpp:88-91). The tokenizer and chat loop are outside this path.
+// stop_on_eos is set (llama2.cpp:88-91); text_completion and the chat loop sit on top of it.
 class Llama2 {
 public:
     Llama2(const ModelArgs& args, const std::string& checkpoint_path, int numerics = TL_NUMERICS_FAST)
@@ -304,7 +307,49 @@ public:
         }
         return out;
     }
+    // One turn continuing at position `start_pos` over the KV cache of earlier turns (the reference keeps that
+    // position in the global total_len, llama2.cpp:13, :51-52, :79).
+    GenerateResult generate_at(int start_pos, const std::vector<int>& prompt_tokens, int max_new = 256, bool stop_on_eos = true) {
+        GenerateResult r;
+        r.tokens.resize((size_t)max_new);
+        int n_out = 0;
+        check(tl_llama2_generate_at(model.handle(), start_pos, prompt_tokens.data(), (int)prompt_tokens.size(), max_new,
+                                    stop_on_eos ? 1 : 0, r.tokens.data(), &n_out, &r.prefill_seconds, &r.decode_seconds));
+        r.tokens.resize((size_t)n_out);
+        return r;
+    }
+    // Llama2::chat (llama2.cpp:119-146): every line read from `in` is one user turn (at most 511 characters, the
+    // reference's buffer), rendered as "[INST] %s [/INST]", encoded with BOS and answered by a generation that
+    // continues at the running position, so earlier turns stay in the KV cache; every piece is written to `out` as
+    // decode(-1, token), like the reference prints it. A turn generates at most 1 + 256 tokens (the reference's
+    // first token from the prefill and generate_len = 256 steps) and stops on id 1 or 2. The reference loops for
+    // ever; this loop ends at end of input or when the context cannot hold another turn. Returns the turns answered.
+    int chat(const Tokenizer& tokenizer, std::istream& in, std::ostream& out, int max_new = 257) {
+        int turns = 0;
+        std::string line;
+        while (true) {
+            out << "> " << std::flush;
+            if (!std::getline(in, line)) break;
+            if (line.size() > 511) line.resize(511);
+            const std::vector<int> ids = tokenizer.encode("[INST] " + line + " [/INST]", true, false);
+            const int room = model.args.max_seq_len - total_len_ - (int)ids.size();     // positions left after the prompt
+            if (ids.empty() || room < 0) break;
+            const GenerateResult r = generate_at(total_len_, ids, max_new < room + 1 ? max_new : room + 1, true);
+            total_len_ += (int)ids.size() + (int)r.tokens.size() - 1;                 // one decode step per token after the first
+            for (int t : r.tokens) {
+                if (t == 1 || t == 2) break;
+                out << tokenizer.decode(-1, t) << std::flush;
+            }
+            out << std::endl;
+            turns++;
+        }
+        return turns;
+    }
+    int total_len() const { return total_len_; }
     Transformer model;
+
+private:
+    int total_len_ = 0;     // running position of chat(): prompt and generated tokens of all turns so far
 };
 
 }  // namespace tlb200

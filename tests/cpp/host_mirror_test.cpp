@@ -9,11 +9,15 @@
 //       case.txt: dim hidden layers heads vocab seq | n_prompt ids... | n_expected ids... |
 //                 M N K | M*K A bits | N*K W bits | M*N expected C bits (reference CPU matmul)
 //       prints "OK <what>" lines; exit code 0 only if all checks pass.
+//   host_mirror_test chat <checkpoint.bin> <tokenizer.bin> dim hidden layers heads vocab seq
+//       Llama2::chat over two lines of input against a replay of the same turns through generate_at:
+//       the second turn must continue at the first turn's end position (the reference's total_len).
 #include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
 #include <iostream>
+#include <sstream>
 
 #include "tensorlib_b200.hpp"
 
@@ -138,8 +142,44 @@ static int run_tokenizer(const char* vocab_path, const char* cases_path) {
     return failures;
 }
 
+static int run_chat(int argc, char** argv) {
+    int failures = 0;
+    ModelArgs a;
+    a.dim = std::atoi(argv[4]); a.hidden_dim = std::atoi(argv[5]); a.n_layers = std::atoi(argv[6]); a.n_heads = std::atoi(argv[7]);
+    a.vocab_size = std::atoi(argv[8]); a.max_seq_len = std::atoi(argv[9]); a.n_kv_heads = a.n_heads;
+    init(0);
+    Tokenizer tok(argv[3], a.vocab_size);
+    const int max_new = 12;
+    const std::string turns[2] = {"the cat sat", "and then"};
+    Llama2 llm(a, argv[2], TL_NUMERICS_REFERENCE_ORDER);
+    std::istringstream in(turns[0] + "\n" + turns[1] + "\n");
+    std::ostringstream out;
+    const int answered = llm.chat(tok, in, out, max_new);
+    // the same two turns by hand on a second model: positions carry over from turn to turn
+    Llama2 replay(a, argv[2], TL_NUMERICS_REFERENCE_ORDER);
+    std::string want;
+    int pos = 0;
+    for (int t = 0; t < 2; t++) {
+        const std::vector<int> ids = tok.encode("[INST] " + turns[t] + " [/INST]", true, false);
+        const GenerateResult r = replay.generate_at(pos, ids, max_new, true);
+        pos += (int)ids.size() + (int)r.tokens.size() - 1;
+        want += "> ";
+        for (int id : r.tokens) { if (id == 1 || id == 2) break; want += tok.decode(-1, id); }
+        want += "\n";
+    }
+    want += "> ";
+    if (answered == 2 && out.str() == want) std::puts("OK chat: two turns, output identical to the replay through generate_at");
+    else { std::printf("FAIL chat: answered %d turns, output differs\n", answered); failures++; }
+    if (llm.total_len() == pos) std::printf("OK chat: running position %d = prompts + decode steps of both turns\n", pos);
+    else { std::printf("FAIL chat: running position %d, expected %d\n", llm.total_len(), pos); failures++; }
+    try { llm.generate_at(a.max_seq_len - 2, tok.encode("the", true, false), 8, true); std::puts("FAIL turn beyond the context accepted"); failures++; }
+    catch (const std::invalid_argument&) { std::puts("OK chat: a turn beyond the context is rejected"); }
+    return failures;
+}
+
 int main(int argc, char** argv) {
     try {
+        if (argc >= 10 && !std::strcmp(argv[1], "chat")) return run_chat(argc, argv) ? 1 : 0;
         if (argc >= 4 && !std::strcmp(argv[1], "tokenizer")) return run_tokenizer(argv[2], argv[3]) ? 1 : 0;
         if (argc >= 2 && !std::strcmp(argv[1], "nogpu")) return run_nogpu() ? 1 : 0;
         if (argc >= 4 && !std::strcmp(argv[1], "gpu")) return run_gpu(argv[2], argv[3]) ? 1 : 0;
@@ -147,6 +187,6 @@ int main(int argc, char** argv) {
         std::printf("FAIL unexpected exception: %s\n", e.what());
         return 1;
     }
-    std::puts("usage: host_mirror_test nogpu | gpu <checkpoint> <case> | tokenizer <tokenizer.bin> <cases>");
+    std::puts("usage: host_mirror_test nogpu | gpu <checkpoint> <case> | tokenizer <tokenizer.bin> <cases> | chat <checkpoint> <tokenizer.bin> dim hidden layers heads vocab seq");
     return 2;
 }

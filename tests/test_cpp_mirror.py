@@ -81,3 +81,22 @@ def test_cpp_mirror_matches_reference_on_tiny_config(mirror_binary, oracle, gold
     r = subprocess.run([mirror_binary, "gpu", ckpt, str(case)], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "FAIL" not in r.stdout and r.stdout.count("OK ") >= 7, r.stdout
+
+
+@pytest.mark.gpu
+def test_cpp_mirror_chat_carries_the_position_across_turns(mirror_binary, tmp_path):
+    """Llama2::chat of the mirror (the reference's llama2.cpp:119-146): two user turns read from a stream, each
+    rendered as [INST] .. [/INST]; the second turn must continue at the first turn's end position over the same KV
+    cache. A small random model whose vocabulary is the synthetic tokenizer's."""
+    import json
+    golden = os.path.join(ROOT, "tests", "golden")
+    with open(os.path.join(golden, "tokenizer_cases.json")) as f:
+        vocab = int(json.load(f)["vocab_size"])
+    cfg = synth.LlamaConfig(dim=64, hidden_dim=160, n_layers=2, n_heads=2, vocab_size=vocab, seq_len=128)
+    ckpt = str(tmp_path / "chat.bin")
+    synth.write_llama2c_file(ckpt, cfg, 4242)
+    r = subprocess.run([mirror_binary, "chat", ckpt, os.path.join(golden, "tokenizer.bin"), str(cfg.dim), str(cfg.hidden_dim),
+                        str(cfg.n_layers), str(cfg.n_heads), str(cfg.vocab_size), str(cfg.seq_len)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "FAIL" not in r.stdout and r.stdout.count("OK chat") == 3, r.stdout
