@@ -1164,7 +1164,12 @@ PairPlan pair_plan(int sms, int M, long long n_col_tiles, int nkb, int epi) {
         const long long tiles = (long long)((M + 256 * msub - 1) / (256 * msub)) * n_col_tiles;
         const long long c = msub == 1 ? 590 : 1090;
         if (forced != 4 && forced != 5) {
-            const long long cost = ((tiles + pairs - 1) / pairs) * nkb * c;
+            // epilogues the MMAs cannot hide: the last tile's (~4000 cycles for 256 rows, ~8000 for 512), and for the
+            // 512-row tile, which has no second accumulator buffer, ~3500 more per earlier round. Measured at
+            // M = 2048, N = 4096: 256-row tiles win up to K ~ 2700 (K = 1024: 19.2 against 21.1 us), 512-row above
+            // (K = 5504: 67.3 against 70.8 us).
+            const long long rounds = (tiles + pairs - 1) / pairs;
+            const long long cost = rounds * nkb * c + (msub == 2 ? (rounds - 1) * 3500 + 8000 : 4000);
             if (best.cost < 0 || cost < best.cost) best = PairPlan{msub, 0, cost};
         }
         if (tiles <= SK_MAX_TILES && pairs <= SK_MAX_PAIRS && forced != 1 && forced != 3) {
