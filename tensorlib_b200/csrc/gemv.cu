@@ -2,7 +2,7 @@
 // llama2.c [out,in] fp16 layout the reference keeps (nn::Linear, tensorLib/src/nn/linear.cpp:10-14).
 // Replaces gemv_v6 / gemv_v4 (tensorLib/src/device/cuda/gemv.cu:379-450, :260-306).
 //
-// Two kernels:
+// The kernels:
 //
 //  k_gemv_ring (M = 1, the decode step). One persistent CTA per SM. A producer warp streams the
 //  CTA's weight rows through a 3-stage shared-memory ring with TMA bulk copies
@@ -18,8 +18,18 @@
 //  previous kernel, so the producer does not wait for it), RoPE + KV-cache write / residual add /
 //  SiLU*up in the epilogue.
 //
-//  k_gemv (M = 1..8, tl_matmul2d_f16): activations staged in shared memory, each warp owns two
-//  rows and streams them with 128-bit non-allocating loads, 16 of them in flight per lane.
+//  k_gemv_ring_rows (M = 2..8, tl_matmul2d_f16 / tl_linear_f16): the same ring; the activation rows are
+//  columns 0..M-1 of the B fragment the M = 1 kernel fills with one column, so the weights are
+//  streamed once for all rows.
+//
+//  k_gemv_ring2 (tensor-parallel decode): two ring phases in one launch (wo -> gate/up, w2 -> next
+//  QKV or classifier); the first phase's epilogue pushes its fp32 partial sums to every rank as
+//  (payload, epoch) words, the second phase's prologue sums the ranks' words (every CTA by itself up
+//  to four ranks; one slice per CTA, published once per GPU, at eight) behind a bounded wait.
+//
+//  k_gemv (M = 1..8 for shapes the ring does not take: odd N, K not a multiple of 16): activations
+//  staged in shared memory, each warp owns two rows and streams them with 128-bit non-allocating
+//  loads, 16 of them in flight per lane.
 #include <cstdlib>
 #include <cstring>
 
